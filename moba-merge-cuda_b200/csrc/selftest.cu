@@ -1,0 +1,91 @@
+// Device self-test of the tcgen05 tile primitives in sm100.cuh: one CTA multiplies two bf16
+// matrices through shared-memory operand descriptors in each operand-major combination the
+// attention kernels use, and returns the fp32 accumulator read back from tensor memory.
+//   mode 0:  D[128,N]  = A[128,K] * B[N,K]^T     (both operands K-major;   S = Q K^T, dP = dO V^T)
+//   mode 1:  D[128,N]  = A[128,K] * B[K,N]       (A K-major, B MN-major;   O = P V,  dQ = dS K)
+//   mode 2:  D[128,N]  = A[K,128]^T * B[K,N]     (both operands MN-major;  dV = P^T dO, dK = dS^T Q)
+#include "moba_b200.h"
+#include "sm100.cuh"
+
+namespace moba {
+
+__device__ __forceinline__ void load_tile_sw128(uint8_t* tile, const __nv_bfloat16* g, int rows, int cols, int ld) {
+  const int upr = cols >> 3;
+  for (int i = threadIdx.x; i < rows * upr; i += blockDim.x) {
+    int r = i / upr, u = i - r * upr;
+    cp_async16(smem_u32(tile) + sw128_offset(rows, r, u), g + (size_t)r * ld + u * 8, true);
+  }
+}
+
+__global__ void __launch_bounds__(128) umma_selftest_kernel(int mode, const __nv_bfloat16* A, const __nv_bfloat16* B,
+                                                            float* D, int N, int K, unsigned* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5;
+
+  // Tile geometry per mode (rows x cols of the row-major global matrices).
+  const int a_rows = (mode == 2) ? K : 128, a_cols = (mode == 2) ? 128 : K;
+  const int b_rows = (mode == 0) ? N : K, b_cols = (mode == 0) ? K : N;
+  uint8_t* tA = smem;
+  uint8_t* tB = smem + (size_t)a_rows * a_cols * 2;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)N) ncols <<= 1;
+  if (warp == 0) tmem_alloc(&tmem_slot, ncols);
+  load_tile_sw128(tA, A, a_rows, a_cols, a_cols);
+  load_tile_sw128(tB, B, b_rows, b_cols, b_cols);
+  cp_async_commit();
+  cp_async_wait<0>();
+  fence_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  if (threadIdx.x == 0) {
+    const uint32_t idesc = umma_idesc_bf16(128, N, mode == 2 ? 1u : 0u, mode == 0 ? 0u : 1u);
+    for (int k0 = 0; k0 < K; k0 += 16) {
+      uint64_t ad = (mode == 2) ? umma_desc_mnmajor(smem_u32(tA), a_rows, k0, 0) : umma_desc_kmajor(smem_u32(tA), a_rows, k0);
+      uint64_t bd = (mode == 0) ? umma_desc_kmajor(smem_u32(tB), b_rows, k0) : umma_desc_mnmajor(smem_u32(tB), b_rows, k0, 0);
+      umma_ss(tmem, ad, bd, idesc, k0 > 0);
+    }
+    umma_commit(&bar);
+  }
+  bool ok = mbar_wait(&bar, 0, status);
+  tc_fence_after_sync();
+  if (ok) {
+    const int row = threadIdx.x;
+    for (int c0 = 0; c0 < N; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem + (uint32_t(warp * 32) << 16) + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (c0 + j < N) D[(size_t)row * N + c0 + j] = __uint_as_float(r[j]);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, ncols);
+}
+
+}  // namespace moba
+
+extern "C" int moba_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int k, unsigned* status,
+                                  void* stream) {
+  if (mode < 0 || mode > 2 || n < 16 || n > 256 || (n % 16) || k < 16 || k > 256 || (k % 16)) return MOBA_ERR_INVALID;
+  if (mode != 2 && (k % 64)) return MOBA_ERR_INVALID;
+  if (mode != 0 && (n % 64)) return MOBA_ERR_INVALID;
+  size_t bytes = (size_t)128 * k * 2 + (size_t)n * k * 2 + 1024;
+  cudaError_t e = cudaFuncSetAttribute(moba::umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return MOBA_ERR_CUDA;
+  moba::umma_selftest_kernel<<<1, 128, bytes, (cudaStream_t)stream>>>(
+      mode, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, d, n, k, status);
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
