@@ -1,0 +1,46 @@
+"""Shared test helpers: golden-fixture loading and bf16 <-> numpy conversions."""
+from pathlib import Path
+
+import numpy as np
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+PREFILL_GOLDENS = ["p_gqa_small", "p_mha_tail", "p_mqa_multi", "p_k9", "p_one_chunk", "p_gqa_256"]
+DECODE_GOLDENS = ["d_small", "d_d128", "d_mha"]
+
+
+def load(name):
+    return dict(np.load(GOLDEN / f"{name}.npz"))
+
+
+def bf16_bits_to_f64(bits):
+    """uint16 bf16 bit patterns -> float64 values."""
+    return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def bf16_bits_to_torch(bits, device="cpu"):
+    import torch
+    t = torch.from_numpy(np.asarray(bits, dtype=np.uint16).view(np.int16).copy()).view(torch.bfloat16)
+    return t.to(device)
+
+
+def torch_to_f64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def cu_from_lens(lens):
+    return np.concatenate(([0], np.cumsum(np.asarray(lens, dtype=np.int64))))
+
+
+def rel_rms(a, b):
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return float(np.sqrt(((a - b) ** 2).mean()) / max(np.sqrt((b ** 2).mean()), 1e-30))
+
+
+def config1_inputs():
+    """BASELINE config 1 inputs: seed 0, q, k, v then dO ~ N(0,1), [2048, 8, 64], rounded to bf16."""
+    import torch
+    rng = torch.Generator().manual_seed(0)
+    q, k, v = [torch.randn(2048, 8, 64, generator=rng).bfloat16() for _ in range(3)]
+    g = torch.randn(2048, 8, 64, generator=rng).bfloat16()
+    return q, k, v, g
