@@ -25,6 +25,63 @@ enum {
 /* Human-readable text for a status code (static storage). */
 const char* moba_status_string(int status);
 
+/* ---------------------------------------------------------------------------------------------
+ * Prefill: MoBA attention over a packed (varlen) batch, forward and backward.
+ *
+ * Replaces the device work behind opt_gqa_cuda (src/moba_opt/grouped_attention.py:29-99 of the
+ * reference): routing (:48-71), expert packing (:76-94), the two FlashAttention calls and the LSE
+ * merge of OptMixedAttention.forward (src/moba_opt/mixed_attention.py:43-139, ops/merge.cu:27-288)
+ * and OptMixedAttention.backward (mixed_attention.py:141-225).
+ *
+ * Layout: q [T,Hq,D], k/v [T,Hkv,D] bf16 with element strides given in the descriptor (last
+ * dimension contiguous, strides multiples of 8 elements, base pointers 16-byte aligned);
+ * out [T,Hq,D] bf16 contiguous; lse [T,Hq] fp32 (natural log).
+ * The int32 metadata arrays are device pointers built by the host from cu_seqlens:
+ *   chunk_start[n+1], chunk_seq[n], chunk_local[n]   (chunking of src/moba_opt/diagnostic.py:30-80)
+ *   qtile_chunk/qtile_tok0/qtile_local[num_qtiles]   128-token query tiles that never cross a chunk;
+ *                                                    qtile_local = chunk_local * ceil(C/128) + tile in chunk
+ *   self_order[num_qtiles]                           query tile ids by decreasing causal work
+ * remote_k = min(topk-1, number of routable chunks); remote_k == 0 selects nothing (the caller
+ * expresses the dense fallback of grouped_attention.py:41-46 by passing chunk_size >= max_seqlen).
+ */
+#define MOBA_ROUTE_BF16_MEANS 1
+
+typedef struct moba_prefill_desc {
+  int32_t total_tokens, num_seqs, hq, hkv, dim, chunk_size, remote_k;
+  int32_t num_chunks, num_qtiles, max_tiles_per_seq, max_chunks_per_seq;
+  int32_t flags; /* MOBA_ROUTE_BF16_MEANS: round chunk means to bf16 (route_precision='upstream') */
+  int64_t q_stride_t, q_stride_h, k_stride_t, k_stride_h, v_stride_t, v_stride_h;
+  const int32_t* cu_seqlens;
+  const int32_t* chunk_start;
+  const int32_t* chunk_seq;
+  const int32_t* chunk_local;
+  const int32_t* qtile_chunk;
+  const int32_t* qtile_tok0;
+  const int32_t* qtile_local;
+  const int32_t* self_order;
+} moba_prefill_desc;
+
+/* Bytes of the route state (kept from forward to backward) and of the routing scratch. */
+size_t moba_prefill_route_state_bytes(const moba_prefill_desc* d);
+size_t moba_prefill_route_scratch_bytes(const moba_prefill_desc* d);
+
+/* Routing (grouped_attention.py:48-94, route_precision='fp32', stable_routes=True). The route state
+ * starts with sel[T,Hq,remote_k] int32: global chunk ids per (token, query head), ascending, -1 padded. */
+int moba_prefill_route(const moba_prefill_desc* d, const void* q, const void* k, void* route_state, void* scratch,
+                       size_t scratch_bytes, void* stream);
+
+/* Forward attention + LSE merge (mixed_attention.py:43-139). status: device uint32 error bits (0 = clean). */
+size_t moba_prefill_fwd_scratch_bytes(const moba_prefill_desc* d);
+int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const void* k, const void* v, const void* route_state,
+                     void* scratch, size_t scratch_bytes, void* out, float* lse, unsigned* status, void* stream);
+
+/* Backward (mixed_attention.py:141-225): gradients of out w.r.t. q, k, v with the route held fixed.
+ * dq [T,Hq,D], dk/dv [T,Hkv,D] bf16 contiguous. */
+size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d);
+int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, const void* v, const void* out,
+                     const float* lse, const void* dout, const void* route_state, void* scratch, size_t scratch_bytes,
+                     void* dq, void* dk, void* dv, unsigned* status, void* stream);
+
 /* Device self-test of the tcgen05 tile primitives (see csrc/selftest.cu). No reference counterpart. */
 int moba_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int k, unsigned* status, void* stream);
 

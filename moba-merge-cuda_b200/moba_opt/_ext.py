@@ -1,0 +1,48 @@
+"""ctypes binding of libmoba_b200.so.  There is no fallback: a missing library is an ImportError at
+first use, and a non-zero status from any entry point is raised as RuntimeError."""
+import ctypes
+from pathlib import Path
+
+_LIB_PATH = Path(__file__).resolve().parent / "libmoba_b200.so"
+_lib = None
+
+c_i32, c_i64, c_vp, c_sz = ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
+
+
+class PrefillDesc(ctypes.Structure):
+    """Mirror of moba_prefill_desc in include/moba_b200.h."""
+    _fields_ = ([(n, c_i32) for n in ("total_tokens", "num_seqs", "hq", "hkv", "dim", "chunk_size", "remote_k",
+                                      "num_chunks", "num_qtiles", "max_tiles_per_seq", "max_chunks_per_seq")]
+                + [("flags", c_i32)]
+                + [(n, c_i64) for n in ("q_stride_t", "q_stride_h", "k_stride_t", "k_stride_h", "v_stride_t", "v_stride_h")]
+                + [(n, c_vp) for n in ("cu_seqlens", "chunk_start", "chunk_seq", "chunk_local", "qtile_chunk",
+                                       "qtile_tok0", "qtile_local", "self_order")])
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise ImportError(f"{_LIB_PATH} is missing: build it with `python moba-merge-cuda_b200/build.py` "
+                              "(there is no non-CUDA path)")
+        L = ctypes.CDLL(str(_LIB_PATH))
+        P = ctypes.POINTER(PrefillDesc)
+        L.moba_status_string.restype = ctypes.c_char_p
+        L.moba_status_string.argtypes = [ctypes.c_int]
+        L.moba_selftest_umma.argtypes = [ctypes.c_int, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int, c_vp, c_vp]
+        for name in ("moba_prefill_route_state_bytes", "moba_prefill_route_scratch_bytes",
+                     "moba_prefill_fwd_scratch_bytes", "moba_prefill_bwd_scratch_bytes"):
+            fn = getattr(L, name, None)
+            if fn is not None:
+                fn.restype, fn.argtypes = c_sz, [P]
+        L.moba_prefill_route.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]
+        L.moba_prefill_fwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
+        if hasattr(L, "moba_prefill_bwd"):
+            L.moba_prefill_bwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, c_vp]
+        _lib = L
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        raise RuntimeError(f"{what} failed: {lib().moba_status_string(status).decode()} (status {status})")
