@@ -41,6 +41,8 @@ const char* moba_status_string(int status);
  *   qtile_chunk/qtile_tok0/qtile_local[num_qtiles]   128-token query tiles that never cross a chunk;
  *                                                    qtile_local = chunk_local * ceil(C/128) + tile in chunk
  *   self_order[num_qtiles]                           query tile ids by decreasing causal work
+ *   kv_order[num_qtiles]                             the same tiles seen as key blocks, earliest chunk of a
+ *                                                    sequence first (those are routed to most often)
  * remote_k = min(topk-1, number of routable chunks); remote_k == 0 selects nothing (the caller
  * expresses the dense fallback of grouped_attention.py:41-46 by passing chunk_size >= max_seqlen).
  */
@@ -59,6 +61,7 @@ typedef struct moba_prefill_desc {
   const int32_t* qtile_tok0;
   const int32_t* qtile_local;
   const int32_t* self_order;
+  const int32_t* kv_order;
 } moba_prefill_desc;
 
 /* Bytes of the route state (kept from forward to backward) and of the routing scratch. */

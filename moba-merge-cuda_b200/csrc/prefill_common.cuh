@@ -24,6 +24,7 @@ struct PrefillView {
   const int* qtile_tok0;   // [n_qtiles] first packed token of the tile
   const int* qtile_local;  // [n_qtiles] index of the tile inside its sequence
   const int* self_order;   // [n_qtiles] query tiles ordered by decreasing causal work
+  const int* kv_order;     // [n_qtiles] key blocks ordered by decreasing expected backward work
 };
 
 inline PrefillView make_view(const moba_prefill_desc& d) {
@@ -35,7 +36,7 @@ inline PrefillView make_view(const moba_prefill_desc& d) {
   v.v_st = d.v_stride_t; v.v_sh = d.v_stride_h;
   v.cu_seqlens = d.cu_seqlens; v.chunk_start = d.chunk_start; v.chunk_seq = d.chunk_seq;
   v.chunk_local = d.chunk_local; v.qtile_chunk = d.qtile_chunk; v.qtile_tok0 = d.qtile_tok0;
-  v.qtile_local = d.qtile_local; v.self_order = d.self_order;
+  v.qtile_local = d.qtile_local; v.self_order = d.self_order; v.kv_order = d.kv_order;
   return v;
 }
 

@@ -16,7 +16,7 @@ class PrefillDesc(ctypes.Structure):
                 + [("flags", c_i32)]
                 + [(n, c_i64) for n in ("q_stride_t", "q_stride_h", "k_stride_t", "k_stride_h", "v_stride_t", "v_stride_h")]
                 + [(n, c_vp) for n in ("cu_seqlens", "chunk_start", "chunk_seq", "chunk_local", "qtile_chunk",
-                                       "qtile_tok0", "qtile_local", "self_order")])
+                                       "qtile_tok0", "qtile_local", "self_order", "kv_order")])
 
 
 def lib():

@@ -62,13 +62,14 @@ class PrefillPlan:
         self.max_tiles_per_seq = int(max(qt_local) + 1)
         self.num_routable = len(filtered)
         order = np.argsort(-np.asarray(qt_cost), kind="stable")
-        arrays = [cu, chunk_start, chunk_seq, chunk_local, qt_chunk, qt_tok0, qt_local, order]
+        kv_order = np.lexsort((np.asarray(qt_cost), np.asarray(chunk_local)[np.asarray(qt_chunk)]))
+        arrays = [cu, chunk_start, chunk_seq, chunk_local, qt_chunk, qt_tok0, qt_local, order, kv_order]
         sizes = [len(a) for a in arrays]
         flat = np.concatenate([np.asarray(a, dtype=np.int32) for a in arrays])
         self._flat = torch.from_numpy(flat).to(device)
         views = self._flat.split(sizes)
         (self.cu_seqlens, self.chunk_start, self.chunk_seq, self.chunk_local,
-         self.qtile_chunk, self.qtile_tok0, self.qtile_local, self.self_order) = views
+         self.qtile_chunk, self.qtile_tok0, self.qtile_local, self.self_order, self.kv_order) = views
         self.filtered = np.asarray(filtered, dtype=np.int64)
         self.chunk_to_batch = np.asarray(chunk_seq, dtype=np.int64)
         self.cu_chunk = np.asarray(chunk_start, dtype=np.int64)
@@ -85,7 +86,7 @@ class PrefillPlan:
         d.k_stride_t, d.k_stride_h = k.stride(0), k.stride(1)
         d.v_stride_t, d.v_stride_h = v.stride(0), v.stride(1)
         for name in ("cu_seqlens", "chunk_start", "chunk_seq", "chunk_local", "qtile_chunk", "qtile_tok0",
-                     "qtile_local", "self_order"):
+                     "qtile_local", "self_order", "kv_order"):
             setattr(d, name, getattr(self, name).data_ptr())
         return d
 

@@ -2,7 +2,10 @@
 golden vectors produced by the reference.  Everything goes through the C ABI via moba_opt.
 
 Tolerances (bf16 inputs, FP64 oracle under the kernel's own routes): max-abs <= 2e-2 and
-rel-RMS <= 5e-3 for outputs and gradients; block selection bit-exact.
+rel-RMS <= 5e-3 for outputs and gradients; block selection bit-exact.  The max-abs bound is taken
+relative to max(1, max|reference|): gradients reach magnitudes where one bf16 ulp of the stored
+result already exceeds 2e-2 (ulp(8) = 0.03), while attention outputs are O(1) so for them the bound
+is the plain 2e-2.
 """
 import numpy as np
 import pytest
@@ -40,9 +43,9 @@ def _run(q, k, v, cu, chunk, topk, d_out=None, **flags):
 def _check_close(name, got, ref):
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     assert np.isfinite(got).all(), name
-    err = np.abs(got - ref).max()
+    err = np.abs(got - ref).max() / max(1.0, np.abs(ref).max())
     rr = rel_rms(got, ref)
-    assert err <= MAX_ABS and rr <= REL_RMS, f"{name}: max-abs {err:.3e} rel-rms {rr:.3e}"
+    assert err <= MAX_ABS and rr <= REL_RMS, f"{name}: scaled max-abs {err:.3e} rel-rms {rr:.3e}"
 
 
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
@@ -122,3 +125,70 @@ def test_forward_is_bit_repeatable():
     for _ in range(5):
         again, lse1, _, _ = _run(q, k, v, cu, 128, 4)
         assert torch.equal(first, again) and torch.equal(lse0, lse1)
+
+
+# --------------------------------------------------------------------------- gradients
+@pytest.mark.parametrize("name", PREFILL_GOLDENS)
+def test_gradients_match_reference(name):
+    g = load(name)
+    q, k, v, do = (bf16_bits_to_torch(g[x]) for x in ("q", "k", "v", "g"))
+    cu = cu_from_lens(g["lens"])
+    _, _, _, grads = _run(q, k, v, cu, int(g["chunk"]), int(g["topk"]), d_out=do)
+    for key, got in zip(("dq", "dk", "dv"), grads):
+        _check_close(key, torch_to_f64(got), g[key])
+
+
+def test_config1_gradients():
+    g = load("config1")
+    q, k, v, do = config1_inputs()
+    _, _, _, grads = _run(q, k, v, np.array([0, 2048]), 256, 3, d_out=do)
+    rows = g["rows"]
+    for key, got in zip(("dq", "dk", "dv"), grads):
+        _check_close(key, torch_to_f64(got)[rows], g[f"{key}_rows"])
+        np.testing.assert_allclose(torch_to_f64(got).sum(), g["sums"][2 + ("dq", "dk", "dv").index(key)],
+                                   atol=2e-3 * g["abs_sums"][2 + ("dq", "dk", "dv").index(key)] ** 0.5 + 1.0)
+
+
+@pytest.mark.parametrize("lens,hq,hkv,dim,chunk,topk", [
+    ((700, 1300), 4, 2, 64, 256, 3),
+    ((1024,), 8, 2, 128, 128, 5),
+    ((333,), 2, 1, 96, 48, 4),
+    ((2000,), 6, 1, 64, 500, 2),
+    ((300, 150), 4, 2, 64, 64, 1),       # dense fallback
+])
+def test_gradients_against_oracle_on_seeded_inputs(lens, hq, hkv, dim, chunk, topk):
+    rng = torch.Generator().manual_seed(4321)
+    total = sum(lens)
+    q, k, v = [torch.randn(total, h, dim, generator=rng).bfloat16() for h in (hq, hkv, hkv)]
+    do = torch.randn(total, hq, dim, generator=rng).bfloat16()
+    cu = cu_from_lens(lens)
+    out, lse, captured, grads = _run(q, k, v, cu, chunk, topk, d_out=do)
+    qf, kf, vf, dof = (torch_to_f64(t) for t in (q, k, v, do))
+    if topk == 1:
+        sel = mo.dense_sel(cu, chunk, hq)
+    else:
+        r = mo.route_prefill(qf, kf, cu, chunk, topk)
+        sel = mo.sel_from_selected(captured["selected"].numpy(), r["filtered"], r["sel"].shape[-1])
+    ref = mo.attention_fixed_route(qf, kf, vf, cu, sel, chunk, d_out=dof)
+    _check_close("out", torch_to_f64(out), ref["out"])
+    for key, got in zip(("dq", "dk", "dv"), grads):
+        _check_close(key, torch_to_f64(got), ref[key])
+
+
+def test_non_contiguous_inputs_and_sequence_isolation():
+    """Strided q/k/v views give the same result, and rows of one sequence do not depend on another
+    sequence's tokens (tests/test_attention_opt.py causal & sequence isolation in the reference)."""
+    rng = torch.Generator().manual_seed(5)
+    lens = (200, 184)
+    total = sum(lens)
+    qkv = torch.randn(total, 8, 64, generator=rng).bfloat16()       # fused [T, Hq+2*Hkv, D] projection
+    q, k, v = qkv[:, :4], qkv[:, 4:6], qkv[:, 6:8]
+    cu = cu_from_lens(lens)
+    out_view, _, _, _ = _run(q, k, v, cu, 64, 3)
+    out_cont, _, _, _ = _run(q.contiguous(), k.contiguous(), v.contiguous(), cu, 64, 3)
+    assert torch.equal(out_view, out_cont)
+    k2, v2 = k.clone(), v.clone()
+    k2[200:] = torch.randn(184, 2, 64, generator=rng).bfloat16()
+    v2[200:] = torch.randn(184, 2, 64, generator=rng).bfloat16()
+    out_other, _, _, _ = _run(q.contiguous(), k2, v2, cu, 64, 3)
+    assert torch.equal(out_other[:200], out_cont[:200])
