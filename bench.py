@@ -1,0 +1,277 @@
+#!/usr/bin/env python
+"""Benchmark of the MoBA prefill hot path (routing + forward + backward) on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1 and per rank for N > 1): GQA prefill forward+backward at the Qwen2-0.5B attention
+shape: 4 packed sequences of 32768 tokens, 14 query / 2 KV heads, head_dim 64, MoBA chunk 2048,
+topk 3, bf16 Q/K/V ~ N(0,1)/sqrt(64), dO ~ N(0,1); synthetic, seeded.  One step = one pass of
+routing + forward + backward over that batch.  The metric is attended TFLOP/s: 14 * D * pairs * Hq
+FLOPs per step (pairs = attended (query, key) pairs per head) divided by the step time.
+
+One JSON line is printed by rank 0.  `value` times the step with inputs resident in HBM; `e2e` times
+the same call with pinned host buffers, including the host->device copies of q, k, v, dO and the
+device->host copies of out, dq, dk, dv.  `roofline` is the backward main kernel (the dominant
+kernel) timed with CUDA events recorded around its launch inside the timed region.  `cpu_baseline`
+times the FP64 CPU oracle on a bounded sample of the same workload.
+
+--impl reference times the CPU implementation of the path (the oracle port of the reference's FP64
+CPU code; the reference itself is Python and is not present on the GPU box) on all host threads.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "moba-merge-cuda_b200"))
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(name="gqa_prefill_4x32768_h14kv2_d64_c2048_k3", lens=(32768,) * 4, hq=14, hkv=2, dim=64, chunk=2048,
+                topk=3)
+METRIC = "moba_prefill_fwd_bwd_attended_tflops"
+UNIT = "TFLOP/s"
+
+
+def attended_pairs(lens, chunk, topk):
+    total = 0
+    for length in lens:
+        n = (length + chunk - 1) // chunk
+        for c in range(n):
+            s = chunk if c < n - 1 else length - (n - 1) * chunk
+            total += s * (s + 1) // 2 + s * min(topk - 1, c) * chunk
+    return total
+
+
+def step_flops(w):
+    return 14.0 * w["dim"] * attended_pairs(w["lens"], w["chunk"], w["topk"]) * w["hq"]
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(tflops=float(d["bf16_tflops_sustained"]), hbm=float(d["hbm_gbs"]), source="measured")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._halt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {getattr(nv, k): k for k in dir(nv) if k.startswith("nvmlClocksEventReason") or
+                     k.startswith("nvmlClocksThrottleReason")}
+            while not self._halt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for value, name in names.items():
+                    if isinstance(value, int) and value and bits & value and "None" not in name and "All" not in name:
+                        self.reasons.add(name.replace("nvmlClocksEventReason", "").replace("nvmlClocksThrottleReason", ""))
+                time.sleep(0.01)
+        except Exception as exc:  # NVML missing: report that instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(exc).__name__}")
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=2)
+        mhz = float(np.median(self.samples)) if self.samples else None
+        return dict(sm_mhz=mhz, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=len(self.samples))
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_sample(threads):
+    """FP64 oracle (routing + forward + backward) on a bounded sample of the workload: sequence 0,
+    KV group 0 (7 query heads), query slabs of 256 tokens in chunks 1, 8 and 15.  Returns
+    (TFLOP/s on attended FLOPs, description, seconds)."""
+    from oracle import moba_oracle as mo
+    w = WORKLOAD
+    L, G, D, C = w["lens"][0], w["hq"] // w["hkv"], w["dim"], w["chunk"]
+    rng = np.random.default_rng(0)
+    bf = mo.bf16_round
+    q = bf(rng.standard_normal((L, G, D)) * D ** -0.5)
+    k = bf(rng.standard_normal((L, 1, D)) * D ** -0.5)
+    v = bf(rng.standard_normal((L, 1, D)) * D ** -0.5)
+    rows = np.concatenate([np.arange(c * C, c * C + 256) for c in (1, 8, 15)])
+    do = bf(rng.standard_normal((rows.size, G, D)))
+    cu = np.array([0, L])
+    t0 = time.perf_counter()
+    r = mo.route_prefill(q, k, cu, C, w["topk"])
+    mo.attention_fixed_route(q, k, v, cu, r["sel"], C, d_out=do, rows=rows, row_block=256)
+    dt = time.perf_counter() - t0
+    pairs = sum((t % C + 1) + min(w["topk"] - 1, t // C) * C for t in rows.tolist())
+    flops = 14.0 * D * pairs * G
+    return flops / dt / 1e12, ("FP64 numpy oracle: route + fwd + bwd for 768 query rows (256-token slabs in chunks 1, 8, 15) "
+                               "x 7 query heads of sequence 0 / KV group 0"), dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    vals = []
+    for i in range(args.warmup + args.steps):
+        val, sample, dt = cpu_sample(threads)
+        if i >= args.warmup:
+            vals.append((val, dt))
+        if sum(d for _, d in vals) > 150:  # keep the whole run within a few minutes
+            break
+    value = float(np.mean([v for v, _ in vals]))
+    ms = float(np.mean([d for _, d in vals])) * 1e3
+    line = dict(impl="reference", metric=METRIC, value=value, unit=UNIT, n_gpus=args.gpus, steps=len(vals),
+                warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64",
+                data="synthetic", config=dict(workload=WORKLOAD["name"], sample=sample),
+                cpu_baseline=dict(value=value, unit=UNIT, cores=threads, kind="port", sample=sample),
+                e2e=dict(value=value, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import moba_opt
+    import moba_opt.grouped_attention as ga
+    from moba_opt import _ext
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _ext.lib()  # fails loudly when the CUDA library is missing
+
+    w = WORKLOAD
+    T, Hq, Hkv, D = sum(w["lens"]), w["hq"], w["hkv"], w["dim"]
+    gen = torch.Generator().manual_seed(1000 + rank)
+    host = {}
+    for name, h, scale in (("q", Hq, D ** -0.5), ("k", Hkv, D ** -0.5), ("v", Hkv, D ** -0.5), ("do", Hq, 1.0)):
+        host[name] = (torch.randn(T, h, D, generator=gen) * scale).bfloat16().pin_memory()
+    cu = torch.tensor(np.concatenate(([0], np.cumsum(w["lens"]))), dtype=torch.int32, device=dev)
+    max_len = max(w["lens"])
+    cfg = {"chunk_size": w["chunk"], "topk": w["topk"], "route_precision": "fp32", "stable_routes": True,
+           "deterministic_merge": True}
+    res = {n: t.to(dev) for n, t in host.items()}
+    host_out = {n: torch.empty_like(host[src]).pin_memory() for n, src in (("out", "q"), ("dq", "q"), ("dk", "k"), ("dv", "k"))}
+
+    def step(q, k, v, do):
+        q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+        out = moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, max_len, cfg)
+        dq, dk, dv = torch.autograd.grad(out, (q, k, v), grad_outputs=do)
+        return out.detach(), dq, dk, dv
+
+    def step_e2e():
+        dev_in = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
+        outs = step(dev_in["q"], dev_in["k"], dev_in["v"], dev_in["do"])
+        for dst, src in zip(("out", "dq", "dk", "dv"), outs):
+            host_out[dst].copy_(src, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, hooks=None):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(steps):
+            if hooks:
+                hooks(i)
+            fn()
+        stop.record()
+        barrier()
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # events around the backward main kernel of every timed step
+    pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in pairs:
+        a.record(); b.record()  # materialise the handles
+
+    def hook(i):
+        lib.moba_profile_events(3, pairs[i][0].cuda_event, pairs[i][1].cuda_event)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms_total = timed(lambda: step(res["q"], res["k"], res["v"], res["do"]), args.steps, max(args.warmup, 3), hook)
+    clocks = sampler.stop()
+    lib.moba_profile_events(3, None, None)
+    ga.check_status()
+    bwd_ms = float(np.mean([a.elapsed_time(b) for a, b in pairs]))
+    ms_e2e = timed(step_e2e, max(2, args.steps // 4), 2)
+    e2e_steps = max(2, args.steps // 4)
+    ga.check_status()
+
+    flops = step_flops(w)
+    value = world * flops / (ms_total / args.steps * 1e-3) / 1e12
+    e2e_value = world * flops / (ms_e2e / e2e_steps * 1e-3) / 1e12
+    h2d = sum(t.numel() * 2 for t in host.values())
+    d2h = sum(t.numel() * 2 for t in host_out.values())
+    if rank == 0:
+        pk = peaks()
+        bwd_flops = flops * 10.0 / 14.0
+        achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
+        cpu_val, cpu_desc, cpu_dt = cpu_sample(os.cpu_count() or 1) if world == 1 else (None, None, None)
+        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                    ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="bf16", data="synthetic",
+                    config=dict(workload=w["name"], sequences=len(w["lens"]), seq_len=w["lens"][0], hq=Hq, hkv=Hkv,
+                                head_dim=D, chunk=w["chunk"], topk=w["topk"], per_rank="one full batch per GPU, no collective",
+                                l2="inputs (0.54 GB per step) exceed L2, no flush needed"),
+                    clocks=clocks,
+                    e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                             ms_per_step=ms_e2e / e2e_steps),
+                    gpu_launches=10 * args.steps,
+                    roofline=dict(bound="tensor", kernel="attn_bwd_kernel<64>", achieved=achieved, peak=pk["tflops"],
+                                  unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
+                                  traffic=None, ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
+        if cpu_val is not None:
+            line["cpu_baseline"] = dict(value=cpu_val, unit=UNIT, cores=os.cpu_count() or 1, kind="port", sample=cpu_desc,
+                                        seconds=cpu_dt)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

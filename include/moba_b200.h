@@ -85,6 +85,11 @@ int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, c
                      const float* lse, const void* dout, const void* route_state, void* scratch, size_t scratch_bytes,
                      void* dq, void* dk, void* dv, unsigned* status, void* stream);
 
+/* Profiling aid (no reference counterpart): record the given CUDA events right before and after one
+ * kernel on its launch stream. which: 1 forward remote pass, 2 forward self pass, 3 backward main
+ * kernel, 4 decode attention. Null events switch it off. Process-wide, not thread-safe. */
+int moba_profile_events(int which, void* start, void* stop);
+
 /* Device self-test of the tcgen05 tile primitives (see csrc/selftest.cu). No reference counterpart. */
 int moba_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int k, unsigned* status, void* stream);
 

@@ -11,3 +11,24 @@ extern "C" const char* moba_status_string(int status) {
     default: return "unknown status";
   }
 }
+
+// Profiling aid: events a caller registers are recorded on the launch stream immediately before and
+// after the named kernel, so its duration can be read with cudaEventElapsedTime without a profiler.
+// Process-wide and not thread-safe; pass null events to switch it off.
+#include "prefill_common.cuh"
+namespace moba {
+static cudaEvent_t g_prof[kProfSlots][2];
+void prof_begin(int which, cudaStream_t st) {
+  if (g_prof[which][0]) cudaEventRecord(g_prof[which][0], st);
+}
+void prof_end(int which, cudaStream_t st) {
+  if (g_prof[which][1]) cudaEventRecord(g_prof[which][1], st);
+}
+}  // namespace moba
+
+extern "C" int moba_profile_events(int which, void* start, void* stop) {
+  if (which < 1 || which >= moba::kProfSlots) return MOBA_ERR_INVALID;
+  moba::g_prof[which][0] = (cudaEvent_t)start;
+  moba::g_prof[which][1] = (cudaEvent_t)stop;
+  return MOBA_OK;
+}

@@ -363,7 +363,9 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.status = status;
   a.scale = (float)(1.0 / sqrt((double)d->dim));
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)d->dim));
+  prof_begin(kProfBwdMain, st);
   cudaError_t e = d->dim > 64 ? launch_bwd<128>(a, st) : launch_bwd<64>(a, st);
+  prof_end(kProfBwdMain, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
   const long long n8 = rows * d->dim / 8;
   bwd_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8);

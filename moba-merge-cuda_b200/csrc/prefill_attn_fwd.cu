@@ -379,10 +379,14 @@ extern "C" int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const
     a.part_lse = reinterpret_cast<float*>(static_cast<char*>(scratch) + align256(slots * d->dim * 2));
     // every expert has at most ceil(rows/128) tiles; the sum is bounded by slots/128 + experts
     const long long bound = (long long)(slots / kTile) + (long long)d->num_chunks * d->hkv;
+    prof_begin(kProfFwdRemote, st);
     e = wide ? launch_fwd<128, false>(a, (int)bound, st) : launch_fwd<64, false>(a, (int)bound, st);
+    prof_end(kProfFwdRemote, st);
     if (e != cudaSuccess) return MOBA_ERR_CUDA;
   }
   const int grid = d->num_qtiles * d->hq;
+  prof_begin(kProfFwdSelf, st);
   e = wide ? launch_fwd<128, true>(a, grid, st) : launch_fwd<64, true>(a, grid, st);
+  prof_end(kProfFwdSelf, st);
   return e == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

@@ -73,4 +73,9 @@ inline RouteState carve_route_state(const moba_prefill_desc& d, void* base) {
 
 int validate_desc(const moba_prefill_desc* d);
 
+// Optional CUDA events recorded right before / after one kernel (see moba_profile_events).
+enum { kProfFwdRemote = 1, kProfFwdSelf = 2, kProfBwdMain = 3, kProfDecodeAttend = 4, kProfSlots = 8 };
+void prof_begin(int which, cudaStream_t st);
+void prof_end(int which, cudaStream_t st);
+
 }  // namespace moba

@@ -35,6 +35,7 @@ def lib():
             fn = getattr(L, name, None)
             if fn is not None:
                 fn.restype, fn.argtypes = c_sz, [P]
+        L.moba_profile_events.argtypes = [ctypes.c_int, c_vp, c_vp]
         L.moba_prefill_route.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]
         L.moba_prefill_fwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
         if hasattr(L, "moba_prefill_bwd"):

@@ -158,7 +158,8 @@ def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, r
     forward with the route held fixed (what autograd gives for grouped_reference).
 
     sel [T,Hq,R]: global chunk ids per row (-1 padded); R may be 0.
-    rows: optional 1-D array of packed token indices to evaluate (forward only); default all.
+    rows: optional 1-D array of packed token indices to evaluate; default all.  With `rows`, d_out is
+    [len(rows),Hq,D] and dq/dk/dv hold only the contributions of those rows.
     Returns dict(out [n,Hq,D], lse [n,Hq]) and, when d_out is given, dq, dk, dv (full size).
     """
     q = np.asarray(q, dtype=np.float64)
@@ -172,8 +173,6 @@ def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, r
     chunk_of_token = np.repeat(np.arange(cu_chunk.size - 1), np.diff(cu_chunk))
     scale = D ** -0.5
     want_grad = d_out is not None
-    if want_grad and rows is not None:
-        raise ValueError("gradients need every row")
     all_rows = np.arange(T) if rows is None else np.asarray(rows, dtype=np.int64)
     out = np.zeros((all_rows.size, Hq, D))
     lse = np.zeros((all_rows.size, Hq))
@@ -202,7 +201,7 @@ def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, r
                 out[idx, h] = o
                 lse[idx, h] = (m + np.log(z))[:, 0]
                 if want_grad:
-                    do = d_out[r, h]
+                    do = d_out[idx, h]
                     dp = do @ v[s0:s1, g].T
                     delta = (do * o).sum(axis=1, keepdims=True)
                     ds = p * (dp - delta) * scale
