@@ -73,6 +73,21 @@ size_t moba_prefill_route_scratch_bytes(const moba_prefill_desc* d);
 int moba_prefill_route(const moba_prefill_desc* d, const void* q, const void* k, void* route_state, void* scratch,
                        size_t scratch_bytes, void* stream);
 
+/* Routing without a caller-provided scratch buffer. This entry point has no counterpart in the
+ * reference. It is for callers that cannot allocate device memory themselves (all memory reserved by
+ * one pool at start-up, cudaMalloc forbidden on the request path, or a language binding that only
+ * holds tensors it was given): the routing scratch is a fixed array of
+ * MOBA_ROUTE_STATIC_SCRATCH_BYTES inside the library, held on every GPU that loads the library until
+ * the process exits. Same inputs, outputs and results as moba_prefill_route; it allocates nothing.
+ *   - Returns MOBA_ERR_WORKSPACE when moba_prefill_route_scratch_bytes(d) exceeds the array.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call before starting any stream capture.
+ *   - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
+ *     (different streams, no ordering between them) race. Order them, or use moba_prefill_route. */
+#define MOBA_ROUTE_STATIC_SCRATCH_BYTES (8u << 20)
+size_t moba_prefill_route_static_capacity(void);
+int moba_prefill_route_static(const moba_prefill_desc* d, const void* q, const void* k, void* route_state, void* stream);
+
 /* Forward attention + LSE merge (mixed_attention.py:43-139). status: device uint32 error bits (0 = clean). */
 size_t moba_prefill_fwd_scratch_bytes(const moba_prefill_desc* d);
 int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const void* k, const void* v, const void* route_state,

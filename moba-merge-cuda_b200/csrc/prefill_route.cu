@@ -314,14 +314,9 @@ extern "C" size_t moba_prefill_route_scratch_bytes(const moba_prefill_desc* d) {
          align256((size_t)d->num_chunks * d->hq * d->max_tiles_per_seq * 4) + align256((size_t)d->num_chunks * d->hq * 4);
 }
 
-extern "C" int moba_prefill_route(const moba_prefill_desc* d, const void* q, const void* k, void* route_state,
-                                  void* scratch, size_t scratch_bytes, void* stream) {
-  int rc = validate_desc(d);
-  if (rc != MOBA_OK) return rc;
-  if (!q || !k || !route_state || !scratch) return MOBA_ERR_INVALID;
-  if (scratch_bytes < moba_prefill_route_scratch_bytes(d)) return MOBA_ERR_WORKSPACE;
+static int route_impl(const moba_prefill_desc* d, const void* q, const void* k, void* route_state, void* scratch,
+                      cudaStream_t st) {
   if (d->remote_k == 0) return MOBA_OK;  // dense fallback: nothing to route
-  cudaStream_t st = (cudaStream_t)stream;
   const PrefillView pv = make_view(*d);
   RouteState rs = carve_route_state(*d, route_state);
   char* p = static_cast<char*>(scratch);
@@ -350,4 +345,59 @@ extern "C" int moba_prefill_route(const moba_prefill_desc* d, const void* q, con
   fill_kernel<<<dim3(d->num_qtiles, d->hkv), 128, (size_t)4 * d->max_chunks_per_seq * 4 + 16, st>>>(pv, rs.sel, cnt, rs.seg_base,
                                                                                                  rs.rowlist);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" int moba_prefill_route(const moba_prefill_desc* d, const void* q, const void* k, void* route_state,
+                                  void* scratch, size_t scratch_bytes, void* stream) {
+  int rc = validate_desc(d);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !k || !route_state || !scratch) return MOBA_ERR_INVALID;
+  if (scratch_bytes < moba_prefill_route_scratch_bytes(d)) return MOBA_ERR_WORKSPACE;
+  return route_impl(d, q, k, route_state, scratch, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Routing for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to obtain the routing scratch: a serving loop whose device
+// memory was handed out in full at start-up to one pool, code running under a runtime that forbids
+// cudaMalloc on the request path because it stalls every stream of the device, or a foreign-language
+// binding that only holds the tensors its framework passed in.  For them the scratch lives in the
+// library itself: one fixed array in device memory, reserved on every GPU that loads the library for
+// as long as the process lives.
+constexpr size_t kRouteStaticScratchBytes = MOBA_ROUTE_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_route_scratch[kRouteStaticScratchBytes];
+
+#include <mutex>
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_route_scratch_mutex;
+void* g_route_scratch_addr[kMaxDevices];  // device address of g_route_scratch, per device ordinal
+}  // namespace
+
+extern "C" size_t moba_prefill_route_static_capacity(void) { return kRouteStaticScratchBytes; }
+
+extern "C" int moba_prefill_route_static(const moba_prefill_desc* d, const void* q, const void* k, void* route_state,
+                                         void* stream) {
+  int rc = validate_desc(d);
+  if (rc != MOBA_OK) return rc;
+  if (!q || !k || !route_state) return MOBA_ERR_INVALID;
+  if (moba_prefill_route_scratch_bytes(d) > kRouteStaticScratchBytes) return MOBA_ERR_WORKSPACE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return MOBA_ERR_CUDA;
+  void* scratch = nullptr;
+  {
+    // First call on a device: resolve the array's device address.  In host code the symbol is only
+    // a handle; the kernels need the address cudaGetSymbolAddress returns for the current device.
+    std::lock_guard<std::mutex> lock(g_route_scratch_mutex);
+    if (!g_route_scratch_addr[dev]) {
+      void* addr = nullptr;
+      if (cudaGetSymbolAddress(&addr, g_route_scratch) != cudaSuccess || !addr) return MOBA_ERR_CUDA;
+      g_route_scratch_addr[dev] = addr;
+    }
+    scratch = g_route_scratch_addr[dev];
+  }
+  // Nothing in the scratch has to start at zero: every word the later passes read is written by an
+  // earlier pass of the same call, so the previous call's contents are simply overwritten.
+  return route_impl(d, q, k, route_state, scratch, (cudaStream_t)stream);
 }

@@ -37,6 +37,9 @@ def lib():
                 fn.restype, fn.argtypes = c_sz, [P]
         L.moba_profile_events.argtypes = [ctypes.c_int, c_vp, c_vp]
         L.moba_prefill_route.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]
+        L.moba_prefill_route_static.argtypes = [P, c_vp, c_vp, c_vp, c_vp]
+        L.moba_prefill_route_static_capacity.restype = c_sz
+        L.moba_prefill_route_static_capacity.argtypes = []
         L.moba_prefill_fwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
         if hasattr(L, "moba_prefill_bwd"):
             L.moba_prefill_bwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, c_vp]
