@@ -100,6 +100,63 @@ int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, c
                      const float* lse, const void* dout, const void* route_state, void* scratch, size_t scratch_bytes,
                      void* dq, void* dk, void* dv, unsigned* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Decode: paged KV cache, block routing and attention for single-token queries.
+ *
+ * Replaces the Triton kernels behind PagedKVCache / PreparedDecode of the reference
+ * (src/moba_opt/ops/paged_decode.py:11-144, src/moba_opt/ops/prepared_decode.py:7-94) and the
+ * torch.topk of src/moba_opt/kv_cache.py:208-223. The cache pools stay owned by the caller:
+ *   k_cache, v_cache [num_pages, page_size, hkv, dim] bf16      table   [batch_slots, table_width] int32 (-1 unmapped)
+ *   means [batch_slots, max_chunks, hkv, dim] bf16               lengths [batch_slots] int32
+ * dim must be a multiple of 8 (<= 256). All functions enqueue on `stream` and return.
+ */
+typedef struct moba_cache_desc {
+  int32_t batch_slots, max_seq_len, page_size, num_pages, table_width, chunk_size, max_chunks, hkv, dim;
+  void* k_cache;
+  void* v_cache;
+  int32_t* table;
+  int32_t* lengths;
+  void* means;
+} moba_cache_desc;
+
+/* Per-step metadata (ops/prepared_decode.py:7-20): for row i with sequence ids[i], write
+ * table[ids[i]][delta[i]] = delta[rows+i] when delta[i] >= 0 (idempotent), then
+ * append != 0: positions[i] = lengths[ids[i]]++ ; append == 0: positions[i] = lengths[ids[i]] - 1. */
+int moba_decode_metadata(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
+                         int append, void* stream);
+
+/* Scatter k, v [tokens, hkv, dim] (contiguous) to (table[token_seq[t]][token_pos[t]/page], token_pos[t]%page)
+ * (ops/paged_decode.py:11-23). */
+int moba_decode_append(const moba_cache_desc* c, const void* k, const void* v, const int32_t* token_seq,
+                       const int32_t* token_pos, int tokens, unsigned* status, void* stream);
+
+/* Chunk means, FP32 sum / chunk_size rounded to bf16 (ops/paged_decode.py:27-44). predicated == 0: item i is
+ * (seqs[i], chunk chunk_or_pos[i]). predicated != 0: chunk_or_pos holds the position of the token just
+ * appended to seqs[i]; the mean of its chunk is written only if that token completed the chunk
+ * (ops/prepared_decode.py:24-41). */
+int moba_decode_means(const moba_cache_desc* c, const int32_t* seqs, const int32_t* chunk_or_pos, int items, int predicated,
+                      unsigned* status, void* stream);
+
+/* Routing (ops/paged_decode.py:48-64 scores; ops/prepared_decode.py:45-55,78-94 selection): q [rows,hq,dim];
+ * scores [rows,hq,width] fp32 (may be null), -inf for chunks not completed before the query's chunk;
+ * selected [rows,hq,1+remote] int32 = (pos/chunk_size, picks in descending score order with the lowest chunk
+ * winning exact ties, -1 padding). Also writes the per-(row, kv head) union of attended chunks for
+ * moba_decode_attend: u_chunk/u_mask [rows,hkv,umax], u_count [rows,hkv], umax = moba_decode_union_capacity(). */
+int moba_decode_union_capacity(int hq, int hkv, int remote, int width);
+int moba_decode_route(const moba_cache_desc* c, const void* q, const int32_t* ids, const int32_t* positions, int rows, int hq,
+                      int remote, int width, float* scores, int32_t* selected, int32_t* u_chunk, uint32_t* u_mask,
+                      int32_t* u_count, void* stream);
+
+/* Attention (ops/paged_decode.py:68-112): per (row, query head) softmax over the tokens <= positions[row] of the
+ * listed chunks (selected != null, slots = 1+remote) or of the whole prefix (selected == null, slots =
+ * max_chunks); out [rows,hq,dim] bf16, lse [rows,hq] fp32 natural log. The workspace starts with one int32
+ * counter per (row, kv head) that must be zero before the first call; the kernel leaves it zero. */
+size_t moba_decode_attend_workspace_bytes(const moba_cache_desc* c, int rows, int hq, int slots);
+int moba_decode_attend(const moba_cache_desc* c, const void* q, const int32_t* ids, const int32_t* positions, int rows, int hq,
+                       const int32_t* selected, int slots, const int32_t* u_chunk, const uint32_t* u_mask,
+                       const int32_t* u_count, int umax, void* workspace, size_t workspace_bytes, void* out, float* lse,
+                       unsigned* status, void* stream);
+
 /* Profiling aid (no reference counterpart): record the given CUDA events right before and after one
  * kernel on its launch stream. which: 1 forward remote pass, 2 forward self pass, 3 backward main
  * kernel, 4 decode attention. Null events switch it off. Process-wide, not thread-safe. */

@@ -4,3 +4,5 @@ and the KV caches with prepared decode."""
 from . import api  # noqa: F401
 from . import grouped_attention  # noqa: F401  (registers "opt_gqa_cuda")
 from .api import available_impls, register, run_impl  # noqa: F401
+from .kv_cache import AppendResult, ContiguousKVCache, DecodeResult, PagedKVCache  # noqa: F401,E402
+from .prepared_decode import PreparedDecode  # noqa: F401,E402
