@@ -149,6 +149,90 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+
+# ----------------------------------------------------------------------------- decode leg
+DECODE = dict(name="paged_decode_64req_ctx4k-64k_page48_c2048_k4_h12kv2_d128", requests=64, lo=4096, hi=65536, page=48,
+              chunk=2048, topk=4, hq=12, hkv=2, dim=128, steps=512)
+
+
+def run_decode(dev, rank, world, steps, lib):
+    """BASELINE configs[3]: 64 requests (64/world per rank, request i on rank i mod world), context
+    lengths uniform in [4096, 65536] from seed 0, page 48, chunk 2048, topk 4, 12/2 heads, D=128, K/V ~
+    N(0,1) in randomly permuted physical pages; one new token per request per step under
+    prepare_decode + CUDA graph.  Returns tokens/s, algorithmic HBM bytes per step (union of attended
+    tokens per (request, kv head), K and V, from the actual selected tables) and timings."""
+    import torch
+    from moba_opt import PagedKVCache
+    w = DECODE
+    rng = np.random.default_rng(0)
+    all_lens = rng.integers(w["lo"], w["hi"] + 1, size=w["requests"])
+    lens = [int(x) for i, x in enumerate(all_lens) if i % world == rank]
+    b = len(lens)
+    max_len = w["hi"] + steps + 64
+    pages = sum(-(-(n + steps + 64) // w["page"]) for n in lens)
+    cache = PagedKVCache(b, max_len, w["hkv"], w["dim"], page_size=w["page"], num_pages=pages, chunk_size=w["chunk"])
+    free = list(cache._layout.free_pages)
+    np.random.default_rng(1 + rank).shuffle(free)          # physical pages in random order
+    cache._layout.free_pages = tuple(free)
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    slab = 2048
+    done = [0] * b
+    while any(d < n for d, n in zip(done, lens)):
+        ids, counts = [], []
+        for i in range(b):
+            if done[i] < lens[i]:
+                ids.append(i)
+                counts.append(min(slab, lens[i] - done[i]))
+        total = sum(counts)
+        k = torch.randn(total, w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+        v = torch.randn(total, w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+        cache.append(k, v, sequence_ids=ids, cu_seqlens=[0] + [int(x) for x in np.cumsum(counts)])
+        for i, c in zip(ids, counts):
+            done[i] += c
+    plan = cache.prepare_decode(list(range(b)), w["hq"], topk=w["topk"], check_finite=False, stable_routes=True)
+    plan.capture("step")
+    qs = torch.randn(8, b, w["hq"], w["dim"], device=dev, generator=gen).bfloat16()
+    ks = torch.randn(8, b, w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+    vs = torch.randn(8, b, w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(5):
+        plan.step(qs[0], ks[0], vs[0], use_graph=True)
+    torch.cuda.synchronize()
+    sampled_bytes = []
+    G = w["hq"] // w["hkv"]
+    e0.record()
+    for i in range(steps):
+        r = plan.step(qs[i % 8], ks[i % 8], vs[i % 8], use_graph=True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    # algorithmic bytes from the route tables of a few extra steps (outside the timed region)
+    for i in range(4):
+        r = plan.step(qs[i], ks[i], vs[i], use_graph=True)
+        sel = r.selected_blocks.cpu().numpy()
+        total = 0
+        for row, pos in enumerate(r.positions):
+            for g in range(w["hkv"]):
+                chunks = set(int(c) for c in sel[row, g * G:(g + 1) * G].ravel() if c >= 0)
+                cur = pos // w["chunk"]
+                tokens = sum((pos + 1 - c * w["chunk"]) if c == cur else w["chunk"] for c in chunks)
+                total += tokens * 2 * w["dim"] * 2
+            total += (pos // w["chunk"]) * w["hkv"] * w["dim"] * 2      # chunk means read by routing
+        sampled_bytes.append(total)
+    # attention kernel alone, eager launches with events around the kernel
+    a0.record(); a1.record()
+    lib.moba_profile_events(4, a0.cuda_event, a1.cuda_event)
+    att = []
+    for i in range(8):
+        plan.step(qs[i], ks[i], vs[i], use_graph=False)
+        torch.cuda.synchronize()
+        att.append(a0.elapsed_time(a1))
+    lib.moba_profile_events(4, None, None)
+    plan.close()
+    return dict(ms_per_step=ms, requests=b, bytes_per_step=float(np.mean(sampled_bytes)), attend_ms=float(np.median(att)),
+                context_tokens=int(sum(lens)))
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_ours(args):
     import torch
@@ -234,6 +318,17 @@ def run_ours(args):
     ms_e2e = None if args.kernels_only else timed(step_e2e, e2e_steps, 2)
     ga.check_status()
 
+    dec = None
+    if not args.kernels_only and not args.no_decode:
+        dec = run_decode(dev, rank, world, DECODE["steps"], lib)
+        ga.check_status()
+        if world > 1:
+            t = torch.tensor([dec["ms_per_step"], dec["attend_ms"]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            tot = torch.tensor([dec["bytes_per_step"], float(dec["requests"])], device=dev)
+            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+            dec.update(ms_per_step=float(t[0]), attend_ms=float(t[1]), bytes_per_step=float(tot[0]), requests=int(tot[1]))
+
     flops = step_flops(w)
     value = world * flops / (ms_total / args.steps * 1e-3) / 1e12
     e2e_value = None if ms_e2e is None else world * flops / (ms_e2e / e2e_steps * 1e-3) / 1e12
@@ -258,6 +353,15 @@ def run_ours(args):
                     roofline=dict(bound="tensor", kernel="attn_bwd_kernel<64>", achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
                                   traffic=None, ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
+        if dec is not None:
+            sec = dec["ms_per_step"] * 1e-3
+            line["decode"] = dict(workload=DECODE["name"], requests=dec["requests"], steps=DECODE["steps"],
+                                  tokens_per_s=dec["requests"] / sec, ms_per_step=dec["ms_per_step"],
+                                  algorithmic_bytes_per_step=dec["bytes_per_step"], hbm_gbs=dec["bytes_per_step"] / sec / 1e9,
+                                  frac_of_hbm_peak=dec["bytes_per_step"] / sec / 1e9 / pk["hbm"] / world, hbm_peak=pk["hbm"],
+                                  attend_kernel_ms=dec["attend_ms"],
+                                  attend_kernel_gbs=dec["bytes_per_step"] / (dec["attend_ms"] * 1e-3) / 1e9,
+                                  mode="prepare_decode + CUDA graph, one token per request per step")
         if cpu_val is not None:
             line["cpu_baseline"] = dict(value=cpu_val, unit=UNIT, cores=os.cpu_count() or 1, kind="port", sample=cpu_desc,
                                         seconds=cpu_dt)
@@ -273,6 +377,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode leg")
     ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs (profiler runs)")
     args = ap.parse_args()
     global WORKLOAD
