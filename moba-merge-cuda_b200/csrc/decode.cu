@@ -262,19 +262,88 @@ struct AttendArgs {
   float scale_log2;
 };
 
-constexpr int kHeadBatch = 8;
+constexpr int kHeadBlock = 16;    // query heads of a group processed together (MMA M dimension)
+constexpr int kStageTokens = 64;  // tokens per pipeline stage: 16 per warp
+constexpr int kStages = 3;        // cp.async stages in flight per CTA
 
-template <int LPR>
+// Shared-memory K/V stage: row = one token, DP bf16 values; the 16-byte units of a row are
+// XOR-permuted by (token & 7) so that ldmatrix reads of 8 consecutive tokens are conflict-free.
+template <int DP>
+__device__ __forceinline__ uint32_t kv_unit_offset(int tok, int unit) {
+  constexpr int UPR = DP / 8;
+  const int sw = UPR >= 8 ? (unit ^ (tok & 7)) : unit;
+  return (uint32_t)(tok * DP * 2 + sw * 16);
+}
+
+// Two threads per token copy its K and V rows with cp.async; the page is resolved once per thread,
+// missing tokens and head-dim padding are zero-filled.
+template <int DP>
+__device__ __forceinline__ void attend_load_stage(const CacheView& cv, uint8_t* stage, int sid, int g, int t0, int t_end,
+                                                  unsigned* status) {
+  constexpr int UPR = DP / 8;
+  const int tok = threadIdx.x >> 1, half = threadIdx.x & 1;
+  const int t = t0 + tok;
+  bool ok = t < t_end;
+  long long base = 0;
+  if (ok) {
+    const int physical = cv.table[(long long)sid * cv.width + t / cv.page];
+    if (physical < 0 || physical >= cv.num_pages) {
+      atomicOr(status, kErrBadIndex);
+      ok = false;
+    } else {
+      base = (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * cv.D;
+    }
+  }
+  const uint32_t kdst = smem_u32(stage);
+  const uint32_t vdst = kdst + kStageTokens * DP * 2;
+#pragma unroll
+  for (int x = 0; x < UPR / 2; ++x) {
+    const int u = half * (UPR / 2) + x;
+    const bool uok = ok && u * 8 < cv.D;
+    const uint32_t off = kv_unit_offset<DP>(tok, u);
+    cp_async16(kdst + off, uok ? cv.kc + base + u * 8 : cv.kc, uok);
+    cp_async16(vdst + off, uok ? cv.vc + base + u * 8 : cv.vc, uok);
+  }
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t dec_pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Split-K paged attention for one (query row, kv head, union chunk, part).  The query heads of the
+// GQA group are the 16 rows of m16n8k16 tensor-core tiles (unused rows are zero), so a K/V token read
+// from HBM serves every head at no extra cost and the kernel stays memory bound for any group size.
+// Each warp takes 16 tokens of every 64-token stage and keeps its own running (max, sum, O); the
+// four warps are combined through shared memory at the end.
+template <int DP>
 __global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
-  constexpr int NRG = 128 / LPR;  // token rows in flight per CTA
-  extern __shared__ float s_red[];  // [NRG][kHeadBatch][D + 2]
+  constexpr int UPR = DP / 8;
+  constexpr int KSTEPS = DP / 16;
+  constexpr int DT = DP / 8;  // 8-column output tiles
+  constexpr int STAGE_BYTES = 2 * kStageTokens * DP * 2;
+  extern __shared__ __align__(128) uint8_t s_pipe[];  // kStages stages; reused for the cross-warp reduction
   __shared__ int s_last;
   const CacheView& cv = a.cv;
   const int D = cv.D, G = a.Hq / cv.Hkv;
   const int rowg = blockIdx.z, row = rowg / cv.Hkv, g = rowg - row * cv.Hkv;
   const int k = blockIdx.x, part = blockIdx.y;
-  const int tid = threadIdx.x, lane = tid & 31;
-  const int rg = tid / LPR, li = tid - rg * LPR;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qr = lane >> 2, qc = lane & 3;  // fragment row within 8 and column pair
   const int sid = a.ids[row], pos = a.positions[row];
   const int visible = min(pos + 1, cv.lengths[sid]);  // tokens [0, visible) exist and are not in the future
   const int cur = pos / cv.C;
@@ -289,85 +358,124 @@ __global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
   if (t_begin >= t_end) return;
   const int cur_parts = (visible - cur * cv.C + a.part_tokens - 1) / a.part_tokens;
   const int expected = (ucount - 1) * a.parts + cur_parts;
-  const bool dl = li * 8 < D;  // this lane holds 8 head-dim elements
+  const int ntiles = (t_end - t_begin + kStageTokens - 1) / kStageTokens;
 
-  for (int hb = 0; hb < G; hb += kHeadBatch) {
-    const unsigned active = (mask >> hb) & 0xFFu;
+  for (int hb = 0; hb < G; hb += kHeadBlock) {
+    const unsigned active = (mask >> hb) & 0xFFFFu;
     if (!active) continue;
-    float qv[kHeadBatch][8], acc[kHeadBatch][8], m[kHeadBatch], l[kHeadBatch];
+    // Q fragments (A operand): rows qr and qr+8 of the head block, all k-steps
+    uint32_t qf[KSTEPS][4];
+    {
+      const bool r0 = hb + qr < G && ((active >> qr) & 1u), r1 = hb + qr + 8 < G && ((active >> (qr + 8)) & 1u);
+      const __nv_bfloat16* q0 = a.q + ((long long)row * a.Hq + g * G + hb + qr) * D;
+      const __nv_bfloat16* q1 = q0 + 8 * D;
 #pragma unroll
-    for (int hh = 0; hh < kHeadBatch; ++hh) {
-      m[hh] = -INFINITY; l[hh] = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { acc[hh][j] = 0.f; qv[hh][j] = 0.f; }
-      if (((active >> hh) & 1u) && dl) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(a.q + ((long long)row * a.Hq + g * G + hb + hh) * D + li * 8);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) { qv[hh][2 * j] = bf_lo(w[j]) * a.scale_log2; qv[hh][2 * j + 1] = bf_hi(w[j]) * a.scale_log2; }
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int c0 = ks * 16 + qc * 2, c1 = c0 + 8;
+        qf[ks][0] = (r0 && c0 < D) ? *reinterpret_cast<const uint32_t*>(q0 + c0) : 0u;
+        qf[ks][1] = (r1 && c0 < D) ? *reinterpret_cast<const uint32_t*>(q1 + c0) : 0u;
+        qf[ks][2] = (r0 && c1 < D) ? *reinterpret_cast<const uint32_t*>(q0 + c1) : 0u;
+        qf[ks][3] = (r1 && c1 < D) ? *reinterpret_cast<const uint32_t*>(q1 + c1) : 0u;
       }
     }
-    for (int t0 = t_begin; t0 < t_end; t0 += 2 * NRG) {
-      uint4 kr[2], vr[2];
-      bool ok[2];
+    float o[DT][4];
 #pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        const int t = t0 + x * NRG + rg;
-        ok[x] = t < t_end;
-        kr[x] = make_uint4(0, 0, 0, 0);
-        vr[x] = make_uint4(0, 0, 0, 0);
-        if (ok[x]) {
-          const int physical = cv.table[(long long)sid * cv.width + t / cv.page];
-          if (physical < 0 || physical >= cv.num_pages) {
-            atomicOr(a.status, kErrBadIndex);
-            ok[x] = false;
-          } else if (dl) {
-            const long long off = (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * D + li * 8;
-            kr[x] = __ldg(reinterpret_cast<const uint4*>(cv.kc + off));
-            vr[x] = __ldg(reinterpret_cast<const uint4*>(cv.vc + off));
-          }
+    for (int dt = 0; dt < DT; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows qr and qr+8; l: this thread's columns only
+
+    __syncthreads();  // the previous head block is done with shared memory
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+      if (s < ntiles) attend_load_stage<DP>(cv, s_pipe + s * STAGE_BYTES, sid, g, t_begin + s * kStageTokens, t_end, a.status);
+      cp_async_commit();
+    }
+    for (int i = 0; i < ntiles; ++i) {
+      cp_async_wait<kStages - 2>();
+      __syncthreads();  // tile i has landed; every warp finished tile i-1, whose buffer is refilled next
+      {
+        const int nx = i + kStages - 1;
+        if (nx < ntiles)
+          attend_load_stage<DP>(cv, s_pipe + (nx % kStages) * STAGE_BYTES, sid, g, t_begin + nx * kStageTokens, t_end, a.status);
+        cp_async_commit();
+      }
+      const int tok0 = warp * 16;                                 // this warp's tokens inside the stage
+      const int nvalid = t_end - (t_begin + i * kStageTokens + tok0);  // tokens of the warp tile that exist
+      if (nvalid <= 0) continue;                                  // warp-uniform
+      const uint32_t kbase = smem_u32(s_pipe + (i % kStages) * STAGE_BYTES);
+      const uint32_t vbase = kbase + kStageTokens * DP * 2;
+      // ---- S = Q K^T for 16 tokens: two 8-token column tiles
+      float sc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t b[4];
+        const int mat = lane >> 3, r = lane & 7;
+        ldmatrix_x4(kbase + kv_unit_offset<DP>(tok0 + (mat >> 1) * 8 + r, ks * 2 + (mat & 1)), b);
+        mma_bf16_16816(sc[0], qf[ks], b[0], b[1]);
+        mma_bf16_16816(sc[1], qf[ks], b[2], b[3]);
+      }
+      // ---- online softmax of rows qr / qr+8 (exp2 domain)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = nt * 8 + qc * 2 + (e & 1);
+          sc[nt][e] = col < nvalid ? sc[nt][e] * a.scale_log2 : -INFINITY;
         }
       }
+      float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+      float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);  // finite: column 0 of the warp tile always exists
+      const float al0 = dec_exp2(m0 - n0), al1 = dec_exp2(m1 - n1);
+      m0 = n0; m1 = n1;
+      uint32_t pf[4];
+      {
+        const float p00 = dec_exp2(sc[0][0] - n0), p01 = dec_exp2(sc[0][1] - n0), p02 = dec_exp2(sc[0][2] - n1), p03 = dec_exp2(sc[0][3] - n1);
+        const float p10 = dec_exp2(sc[1][0] - n0), p11 = dec_exp2(sc[1][1] - n0), p12 = dec_exp2(sc[1][2] - n1), p13 = dec_exp2(sc[1][3] - n1);
+        l0 = l0 * al0 + (p00 + p01) + (p10 + p11);
+        l1 = l1 * al1 + (p02 + p03) + (p12 + p13);
+        pf[0] = dec_pack_bf16(p00, p01); pf[1] = dec_pack_bf16(p02, p03);
+        pf[2] = dec_pack_bf16(p10, p11); pf[3] = dec_pack_bf16(p12, p13);
+      }
+      // ---- O = O * alpha + P V
 #pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        const uint32_t kw[4] = {kr[x].x, kr[x].y, kr[x].z, kr[x].w}, vw[4] = {vr[x].x, vr[x].y, vr[x].z, vr[x].w};
-        float kf[8], vf[8];
+      for (int dp = 0; dp < DT / 2; ++dp) {
+        uint32_t b[4];
+        const int mat = lane >> 3, r = lane & 7;
+        ldmatrix_x4_trans(vbase + kv_unit_offset<DP>(tok0 + (mat & 1) * 8 + r, dp * 2 + (mat >> 1)), b);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { kf[2 * j] = bf_lo(kw[j]); kf[2 * j + 1] = bf_hi(kw[j]); vf[2 * j] = bf_lo(vw[j]); vf[2 * j + 1] = bf_hi(vw[j]); }
-#pragma unroll
-        for (int hh = 0; hh < kHeadBatch; ++hh) {
-          if (!((active >> hh) & 1u)) continue;
-          float s = 0.f;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) s = fmaf(qv[hh][j], kf[j], s);
-#pragma unroll
-          for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-          if (ok[x]) {
-            const float mn = fmaxf(m[hh], s);
-            const float alpha = dec_exp2(m[hh] - mn), p = dec_exp2(s - mn);
-            l[hh] = l[hh] * alpha + p;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[hh][j] = fmaf(acc[hh][j], alpha, p * vf[j]);
-            m[hh] = mn;
-          }
+        for (int h2 = 0; h2 < 2; ++h2) {
+          float (&acc)[4] = o[dp * 2 + h2];
+          acc[0] *= al0; acc[1] *= al0; acc[2] *= al1; acc[3] *= al1;
+          mma_bf16_16816(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
         }
       }
     }
-    // combine the NRG row groups of the CTA, then write one partial per head
+    // ---- combine the four warps, then write one partial per active head
+    cp_async_wait<0>();
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
     __syncthreads();
+    float* s_o = reinterpret_cast<float*>(s_pipe);                   // [4 warps][16 rows][DP]
+    float* s_ml = s_o + 4 * 16 * DP;                                  // [4 warps][16 rows][2]
 #pragma unroll
-    for (int hh = 0; hh < kHeadBatch; ++hh) {
-      if (!((active >> hh) & 1u)) continue;
-      float* dst = s_red + ((size_t)rg * kHeadBatch + hh) * (D + 2);
-      if (dl) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dst[li * 8 + j] = acc[hh][j];
-      }
-      if (li == 0) { dst[D] = m[hh]; dst[D + 1] = l[hh]; }
+    for (int dt = 0; dt < DT; ++dt) {
+      float* w0 = s_o + ((size_t)warp * 16 + qr) * DP + dt * 8 + qc * 2;
+      float* w1 = w0 + 8 * DP;
+      w0[0] = o[dt][0]; w0[1] = o[dt][1]; w1[0] = o[dt][2]; w1[1] = o[dt][3];
+    }
+    if (qc == 0) {
+      s_ml[((size_t)warp * 16 + qr) * 2] = m0; s_ml[((size_t)warp * 16 + qr) * 2 + 1] = l0;
+      s_ml[((size_t)warp * 16 + qr + 8) * 2] = m1; s_ml[((size_t)warp * 16 + qr + 8) * 2 + 1] = l1;
     }
     __syncthreads();
-    for (int hh = 0; hh < kHeadBatch; ++hh) {
-      if (!((active >> hh) & 1u)) continue;
+    for (int hh = 0; hh < kHeadBlock; ++hh) {
+      if (!((active >> hh) & 1u) || hb + hh >= G) continue;
       const int h = g * G + hb + hh;
       int slot = dense ? chunk : -1;
       if (!dense) {
@@ -377,18 +485,19 @@ __global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
       if (slot < 0) continue;
       const long long pidx = (((long long)row * a.Hq + h) * a.ns + slot) * a.parts + part;
       float big = -INFINITY;
-      for (int r = 0; r < NRG; ++r) big = fmaxf(big, s_red[((size_t)r * kHeadBatch + hh) * (D + 2) + D]);
-      float lsum = 0.f;
-      for (int r = 0; r < NRG; ++r) {
-        const float* src = s_red + ((size_t)r * kHeadBatch + hh) * (D + 2);
-        lsum += src[D + 1] * dec_exp2(src[D] - big);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) big = fmaxf(big, s_ml[((size_t)w * 16 + hh) * 2]);
+      float wgt[4], lsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = s_ml[((size_t)w * 16 + hh) * 2];
+        wgt[w] = mw == -INFINITY ? 0.f : dec_exp2(mw - big);   // a warp that saw no token contributes nothing
+        lsum += s_ml[((size_t)w * 16 + hh) * 2 + 1] * wgt[w];
       }
       for (int d = tid; d < D; d += 128) {
         float v = 0.f;
-        for (int r = 0; r < NRG; ++r) {
-          const float* src = s_red + ((size_t)r * kHeadBatch + hh) * (D + 2);
-          v += src[d] * dec_exp2(src[D] - big);
-        }
+#pragma unroll
+        for (int w = 0; w < 4; ++w) v += s_o[((size_t)w * 16 + hh) * DP + d] * wgt[w];
         a.pacc[pidx * D + d] = v;
       }
       if (tid == 0) { a.pm[pidx] = big; a.pl[pidx] = lsum; }
@@ -509,8 +618,9 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
+static int attend_part_tokens(const moba_cache_desc* c) { return c->chunk_size >= 512 ? 512 : c->chunk_size; }
 static int attend_parts(const moba_cache_desc* c) {
-  const int part_tokens = c->chunk_size >= 256 ? 256 : c->chunk_size;
+  const int part_tokens = attend_part_tokens(c);
   return (c->chunk_size + part_tokens - 1) / part_tokens;
 }
 
@@ -530,6 +640,7 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
     return MOBA_ERR_INVALID;
   if (selected && (!u_chunk || !u_mask || !u_count || umax < 1)) return MOBA_ERR_INVALID;
   if (hq / c->hkv > 32) return MOBA_ERR_UNSUPPORTED;
+  if (c->chunk_size >= 512 && attend_part_tokens(c) % kStageTokens) return MOBA_ERR_UNSUPPORTED;
   if (workspace_bytes < moba_decode_attend_workspace_bytes(c, rows, hq, slots)) return MOBA_ERR_WORKSPACE;
   AttendArgs a;
   a.cv = make_cache_view(*c);
@@ -538,7 +649,7 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
   a.u_chunk = u_chunk; a.u_mask = u_mask; a.u_count = u_count;
   a.Hq = hq; a.ns = slots; a.umax = selected ? umax : slots;
   a.parts = attend_parts(c);
-  a.part_tokens = c->chunk_size >= 256 ? 256 : c->chunk_size;
+  a.part_tokens = attend_part_tokens(c);
   const size_t n = (size_t)rows * hq * slots * a.parts;
   char* p = static_cast<char*>(workspace);
   a.counters = reinterpret_cast<int*>(p); p += align256((size_t)rows * c->hkv * 4);
@@ -549,23 +660,23 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
   a.lse = lse;
   a.status = status;
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)c->dim));
-  const int lpr = c->dim <= 32 ? 4 : c->dim <= 64 ? 8 : c->dim <= 128 ? 16 : 32;
-  const int nrg = 128 / lpr;
-  const size_t smem = (size_t)nrg * kHeadBatch * (c->dim + 2) * 4;
+  const int dp = c->dim <= 32 ? 32 : c->dim <= 64 ? 64 : c->dim <= 128 ? 128 : 256;
+  const size_t red_bytes = (size_t)4 * 16 * (dp + 2) * 4;
+  const size_t pipe_bytes = (size_t)kStages * 2 * kStageTokens * dp * 2;
+  const size_t smem = red_bytes > pipe_bytes ? red_bytes : pipe_bytes;
   const dim3 grid(a.umax, a.parts, rows * c->hkv);
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
   prof_begin(kProfDecodeAttend, st);
 #define MOBA_LAUNCH_ATTEND(L)                                                                                      \
   do {                                                                                                             \
-    if (smem > 48 * 1024)                                                                                          \
-      e = cudaFuncSetAttribute(decode_attend_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    e = cudaFuncSetAttribute(decode_attend_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     if (e == cudaSuccess) decode_attend_kernel<L><<<grid, 128, smem, st>>>(a);                                     \
   } while (0)
-  if (lpr == 4) MOBA_LAUNCH_ATTEND(4);
-  else if (lpr == 8) MOBA_LAUNCH_ATTEND(8);
-  else if (lpr == 16) MOBA_LAUNCH_ATTEND(16);
-  else MOBA_LAUNCH_ATTEND(32);
+  if (dp == 32) MOBA_LAUNCH_ATTEND(32);
+  else if (dp == 64) MOBA_LAUNCH_ATTEND(64);
+  else if (dp == 128) MOBA_LAUNCH_ATTEND(128);
+  else MOBA_LAUNCH_ATTEND(256);
 #undef MOBA_LAUNCH_ATTEND
   prof_end(kProfDecodeAttend, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
