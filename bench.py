@@ -234,6 +234,19 @@ def run_decode(dev, rank, world, steps, lib):
                 context_tokens=int(sum(lens)))
 
 # ----------------------------------------------------------------------------- GPU arm
+def run_decode_only(args):
+    import torch
+    import moba_opt.grouped_attention as ga
+    from moba_opt import _ext
+    torch.cuda.set_device(0)
+    dec = run_decode(torch.device("cuda", 0), 0, 1, args.decode_steps, _ext.lib())
+    ga.check_status()
+    sec = dec["ms_per_step"] * 1e-3
+    print(json.dumps(dict(decode_only=True, workload=DECODE["name"], ms_per_step=dec["ms_per_step"], tokens_per_s=dec["requests"] / sec,
+                          hbm_gbs=dec["bytes_per_step"] / sec / 1e9, attend_kernel_ms=dec["attend_ms"],
+                          algorithmic_bytes_per_step=dec["bytes_per_step"])))
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -320,7 +333,7 @@ def run_ours(args):
 
     dec = None
     if not args.kernels_only and not args.no_decode:
-        dec = run_decode(dev, rank, world, DECODE["steps"], lib)
+        dec = run_decode(dev, rank, world, args.decode_steps, lib)
         ga.check_status()
         if world > 1:
             t = torch.tensor([dec["ms_per_step"], dec["attend_ms"]], device=dev)
@@ -355,7 +368,7 @@ def run_ours(args):
                                   traffic=None, ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
         if dec is not None:
             sec = dec["ms_per_step"] * 1e-3
-            line["decode"] = dict(workload=DECODE["name"], requests=dec["requests"], steps=DECODE["steps"],
+            line["decode"] = dict(workload=DECODE["name"], requests=dec["requests"], steps=args.decode_steps,
                                   tokens_per_s=dec["requests"] / sec, ms_per_step=dec["ms_per_step"],
                                   algorithmic_bytes_per_step=dec["bytes_per_step"], hbm_gbs=dec["bytes_per_step"] / sec / 1e9,
                                   frac_of_hbm_peak=dec["bytes_per_step"] / sec / 1e9 / pk["hbm"] / world, hbm_peak=pk["hbm"],
@@ -378,12 +391,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode leg")
+    ap.add_argument("--only-decode", action="store_true", help="run only the paged-decode leg (profiler runs)")
+    ap.add_argument("--decode-steps", type=int, default=DECODE["steps"])
     ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs (profiler runs)")
     args = ap.parse_args()
     global WORKLOAD
     WORKLOAD = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args)
+    elif args.only_decode:
+        run_decode_only(args)
     else:
         run_ours(args)
 

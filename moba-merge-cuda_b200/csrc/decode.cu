@@ -275,34 +275,37 @@ __device__ __forceinline__ uint32_t kv_unit_offset(int tok, int unit) {
   return (uint32_t)(tok * DP * 2 + sw * 16);
 }
 
-// Two threads per token copy its K and V rows with cp.async; the page is resolved once per thread,
-// missing tokens and head-dim padding are zero-filled.
-template <int DP>
-__device__ __forceinline__ void attend_load_stage(const CacheView& cv, uint8_t* stage, int sid, int g, int t0, int t_end,
-                                                  unsigned* status) {
-  constexpr int UPR = DP / 8;
-  const int tok = threadIdx.x >> 1, half = threadIdx.x & 1;
-  const int t = t0 + tok;
-  bool ok = t < t_end;
-  long long base = 0;
-  if (ok) {
-    const int physical = cv.table[(long long)sid * cv.width + t / cv.page];
-    if (physical < 0 || physical >= cv.num_pages) {
-      atomicOr(status, kErrBadIndex);
-      ok = false;
-    } else {
-      base = (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * cv.D;
-    }
+// Row base (element offset of the token's K/V row of kv head g, or -1) of one token of a stage.  The
+// lookup goes through the page table; it is issued one stage ahead of the copy that needs it.
+__device__ __forceinline__ long long attend_row_base(const CacheView& cv, int sid, int g, int t, int t_end, unsigned* status) {
+  if (t >= t_end) return -1;
+  const int physical = __ldg(cv.table + (long long)sid * cv.width + t / cv.page);
+  if (physical < 0 || physical >= cv.num_pages) {
+    atomicOr(status, kErrBadIndex);
+    return -1;
   }
+  return (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * cv.D;
+}
+
+// Copies the K and V rows of one stage with cp.async.  Consecutive threads copy consecutive 16-byte
+// units of a row, so every 32-byte sector fetched from L2 is used in full; rows that do not exist
+// and head-dim padding are zero-filled.
+template <int DP>
+__device__ __forceinline__ void attend_load_stage(const CacheView& cv, uint8_t* stage, const long long* row_base) {
+  constexpr int UPR = DP / 8;
+  constexpr int ROWS_PER_PASS = 128 / UPR;
+  const int u = threadIdx.x % UPR, r0 = threadIdx.x / UPR;
   const uint32_t kdst = smem_u32(stage);
   const uint32_t vdst = kdst + kStageTokens * DP * 2;
+  const bool uok = u * 8 < cv.D;
 #pragma unroll
-  for (int x = 0; x < UPR / 2; ++x) {
-    const int u = half * (UPR / 2) + x;
-    const bool uok = ok && u * 8 < cv.D;
+  for (int x = 0; x < kStageTokens / ROWS_PER_PASS; ++x) {
+    const int tok = r0 + x * ROWS_PER_PASS;
+    const long long base = row_base[tok];
+    const bool ok = uok && base >= 0;
     const uint32_t off = kv_unit_offset<DP>(tok, u);
-    cp_async16(kdst + off, uok ? cv.kc + base + u * 8 : cv.kc, uok);
-    cp_async16(vdst + off, uok ? cv.vc + base + u * 8 : cv.vc, uok);
+    cp_async16(kdst + off, ok ? cv.kc + base + u * 8 : cv.kc, ok);
+    cp_async16(vdst + off, ok ? cv.vc + base + u * 8 : cv.vc, ok);
   }
 }
 
@@ -338,6 +341,7 @@ __global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
   constexpr int STAGE_BYTES = 2 * kStageTokens * DP * 2;
   extern __shared__ __align__(128) uint8_t s_pipe[];  // kStages stages; reused for the cross-warp reduction
   __shared__ int s_last;
+  __shared__ long long s_rowbase[kStages][kStageTokens];
   const CacheView& cv = a.cv;
   const int D = cv.D, G = a.Hq / cv.Hkv;
   const int rowg = blockIdx.z, row = rowg / cv.Hkv, g = rowg - row * cv.Hkv;
@@ -384,23 +388,34 @@ __global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows qr and qr+8; l: this thread's columns only
 
     __syncthreads();  // the previous head block is done with shared memory
+    // row bases of the tokens of the stages about to be copied (ring of kStages slots)
+    if (tid < kStageTokens) {
+#pragma unroll
+      for (int s = 0; s < kStages; ++s)
+        s_rowbase[s][tid] = attend_row_base(cv, sid, g, t_begin + s * kStageTokens + tid, t_end, a.status);
+    }
+    __syncthreads();
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s) {
-      if (s < ntiles) attend_load_stage<DP>(cv, s_pipe + s * STAGE_BYTES, sid, g, t_begin + s * kStageTokens, t_end, a.status);
+      if (s < ntiles) attend_load_stage<DP>(cv, s_pipe + s * STAGE_BYTES, s_rowbase[s]);
       cp_async_commit();
     }
     for (int i = 0; i < ntiles; ++i) {
       cp_async_wait<kStages - 2>();
       __syncthreads();  // tile i has landed; every warp finished tile i-1, whose buffer is refilled next
-      {
-        const int nx = i + kStages - 1;
-        if (nx < ntiles)
-          attend_load_stage<DP>(cv, s_pipe + (nx % kStages) * STAGE_BYTES, sid, g, t_begin + nx * kStageTokens, t_end, a.status);
-        cp_async_commit();
-      }
+      const int nx = i + kStages - 1;
+      if (nx < ntiles) attend_load_stage<DP>(cv, s_pipe + (nx % kStages) * STAGE_BYTES, s_rowbase[nx % kStages]);
+      cp_async_commit();
+      // look up the rows of tile nx+1 now, publish them after this tile's math (slot i % kStages is free)
+      long long next_base = -1;
+      if (tid < kStageTokens && nx + 1 < ntiles)
+        next_base = attend_row_base(cv, sid, g, t_begin + (nx + 1) * kStageTokens + tid, t_end, a.status);
       const int tok0 = warp * 16;                                 // this warp's tokens inside the stage
       const int nvalid = t_end - (t_begin + i * kStageTokens + tok0);  // tokens of the warp tile that exist
-      if (nvalid <= 0) continue;                                  // warp-uniform
+      if (nvalid <= 0) {                                          // warp-uniform
+        if (tid < kStageTokens) s_rowbase[i % kStages][tid] = next_base;
+        continue;
+      }
       const uint32_t kbase = smem_u32(s_pipe + (i % kStages) * STAGE_BYTES);
       const uint32_t vbase = kbase + kStageTokens * DP * 2;
       // ---- S = Q K^T for 16 tokens: two 8-token column tiles
@@ -455,6 +470,7 @@ __global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
           mma_bf16_16816(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
         }
       }
+      if (tid < kStageTokens) s_rowbase[i % kStages][tid] = next_base;
     }
     // ---- combine the four warps, then write one partial per active head
     cp_async_wait<0>();
@@ -618,7 +634,9 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
-static int attend_part_tokens(const moba_cache_desc* c) { return c->chunk_size >= 512 ? 512 : c->chunk_size; }
+static int attend_part_tokens(const moba_cache_desc* c) {
+  return c->chunk_size >= 2048 ? 1024 : c->chunk_size >= 512 ? 512 : c->chunk_size;
+}
 static int attend_parts(const moba_cache_desc* c) {
   const int part_tokens = attend_part_tokens(c);
   return (c->chunk_size + part_tokens - 1) / part_tokens;
