@@ -18,7 +18,7 @@ FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "--expt-relaxed-constexpr",
     "-I", str(HERE.parent / "include"), "-I", str(CSRC),
-]
+] + os.environ.get("MOBA_NVCC_EXTRA", "").split()
 
 
 def _digest(sources):

@@ -162,30 +162,31 @@ __global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const _
   const int upr = cv.D >> 3;
 
   for (int i = tid; i <= width; i += 128) s_mask[i] = 0u;
-  // scores: warp w takes (head, chunk) pairs round-robin, lanes split the head dimension
-  for (int pair = warp; pair < G * width; pair += 4) {
+  // stage the group's query rows as FP32, then one thread per (head, chunk) pair: the loads of all
+  // pairs are independent, so their latencies overlap instead of adding up
+  float* s_q = reinterpret_cast<float*>(s_mask + width + 1);  // [G][D]
+  for (int i = tid; i < G * cv.D; i += 128)
+    s_q[i] = __bfloat162float(q[((long long)row * Hq + g * G) * cv.D + i]);
+  __syncthreads();
+  for (int pair = tid; pair < G * width; pair += 128) {
     const int hl = pair / width, c = pair - hl * width;
     float s = -INFINITY;
     if (c < nlegal) {
-      float part = 0.f;
-      if (lane < upr) {
-        const uint4 qa = *reinterpret_cast<const uint4*>(q + ((long long)row * Hq + g * G + hl) * cv.D + lane * 8);
-        const uint4 ma = *reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c) * cv.Hkv + g) * cv.D + lane * 8);
-        const uint32_t qw[4] = {qa.x, qa.y, qa.z, qa.w}, mw[4] = {ma.x, ma.y, ma.z, ma.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          part = fmaf(bf_lo(qw[i]), bf_lo(mw[i]), part);
-          part = fmaf(bf_hi(qw[i]), bf_hi(mw[i]), part);
-        }
+      const uint4* mrow = reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c) * cv.Hkv + g) * cv.D);
+      const float* qrow = s_q + hl * cv.D;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+      for (int u = 0; u < upr; ++u) {
+        const uint4 ma = __ldg(mrow + u);
+        const float* qq = qrow + u * 8;
+        a0 = fmaf(qq[0], bf_lo(ma.x), a0); a1 = fmaf(qq[1], bf_hi(ma.x), a1);
+        a2 = fmaf(qq[2], bf_lo(ma.y), a2); a3 = fmaf(qq[3], bf_hi(ma.y), a3);
+        a0 = fmaf(qq[4], bf_lo(ma.z), a0); a1 = fmaf(qq[5], bf_hi(ma.z), a1);
+        a2 = fmaf(qq[6], bf_lo(ma.w), a2); a3 = fmaf(qq[7], bf_hi(ma.w), a3);
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-      s = part;
+      s = (a0 + a1) + (a2 + a3);
     }
-    if (lane == 0) {
-      s_scores[pair] = s;
-      if (scores) scores[((long long)row * Hq + g * G + hl) * width + c] = s;
-    }
+    s_scores[pair] = s;
+    if (scores) scores[((long long)row * Hq + g * G + hl) * width + c] = s;
   }
   __syncthreads();
   // top-k: one warp per head, `remote` rounds of (max value, lowest index among equals)
@@ -264,7 +265,15 @@ struct AttendArgs {
 
 constexpr int kHeadBlock = 16;    // query heads of a group processed together (MMA M dimension)
 constexpr int kStageTokens = 64;  // tokens per pipeline stage: 16 per warp
-constexpr int kStages = 3;        // cp.async stages in flight per CTA
+// Two 32 KB stages (D <= 128) and 160 registers let three CTAs share an SM; measured faster than three
+// stages with two CTAs.
+#ifndef MOBA_DEC_STAGES
+#define MOBA_DEC_STAGES 2
+#endif
+#ifndef MOBA_DEC_MINBLOCKS
+#define MOBA_DEC_MINBLOCKS 3
+#endif
+constexpr int kStages = MOBA_DEC_STAGES;  // cp.async stages in flight per CTA
 
 // Shared-memory K/V stage: row = one token, DP bf16 values; the 16-byte units of a row are
 // XOR-permuted by (token & 7) so that ldmatrix reads of 8 consecutive tokens are conflict-free.
@@ -334,7 +343,7 @@ __device__ __forceinline__ uint32_t dec_pack_bf16(float lo, float hi) {
 // Each warp takes 16 tokens of every 64-token stage and keeps its own running (max, sum, O); the
 // four warps are combined through shared memory at the end.
 template <int DP>
-__global__ void __launch_bounds__(128) decode_attend_kernel(AttendArgs a) {
+__global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
   constexpr int UPR = DP / 8;
   constexpr int KSTEPS = DP / 16;
   constexpr int DT = DP / 8;  // 8-column output tiles
@@ -622,7 +631,7 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
     return MOBA_ERR_INVALID;
   const int G = hq / c->hkv;
   if (G > 32 || remote > 16) return MOBA_ERR_UNSUPPORTED;
-  const size_t smem = ((size_t)G * width + width + 1) * 4;
+  const size_t smem = ((size_t)G * width + width + 1 + (size_t)G * c->dim) * 4;
   if (smem > 200 * 1024) return MOBA_ERR_UNSUPPORTED;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(decode_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
