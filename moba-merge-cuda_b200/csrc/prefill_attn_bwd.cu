@@ -13,42 +13,9 @@
 // (registers, written as bf16 tiles)  ->  dV += P^T dO, dK += dS^T Q, dQ = dS K.
 // The same swizzled shared-memory image of a tile serves as K-major and as MN-major operand, so
 // no transposes are materialised.
-#include "prefill_common.cuh"
-#include "sm100.cuh"
+#include "prefill_bwd.cuh"
 
 namespace moba {
-
-__device__ __forceinline__ float bwd_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t bwd_pack_bf16(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-struct BwdArgs {
-  PrefillView pv;
-  const __nv_bfloat16* q;
-  const __nv_bfloat16* k;
-  const __nv_bfloat16* v;
-  const __nv_bfloat16* dout;  // [T,Hq,D] contiguous
-  const float* lse;           // [T,Hq] natural log
-  const float* delta;         // [T,Hq] rowsum(dO * O)
-  const int* rowlist;
-  const int* seg_base;
-  const int* kv_order;  // [num_qtiles] key blocks by decreasing expected work
-  float* dq_acc;        // [T,Hq,D] fp32, zero-initialised
-  __nv_bfloat16* dk;    // [T,Hkv,D] contiguous
-  __nv_bfloat16* dv;
-  unsigned* status;
-  float scale_log2, scale;
-};
 
 // delta[row] = sum_d dO[row,d] * O[row,d]; one warp per (token, head) row.
 __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __restrict__ out,
@@ -306,323 +273,6 @@ __global__ void __launch_bounds__(128, 1) attn_bwd_kernel(BwdArgs a) {
   if (warp == 0) tmem_free(tmem, TMEM_COLS);
 }
 
-// ---------------------------------------------------------------------------------------------
-// Warp-specialised variant for head_dim <= 64: the same mathematics and work decomposition as
-// attn_bwd_kernel, organised so that the tensor pipe, the exp/FMA pipes and the memory system work on
-// different query tiles at the same time.
-//   warps 0-7  compute: two threads per query row (64 of the 128 key columns each); read S and dP
-//              from TMEM, release them at once, form P and dS in registers, drain dQ of the previous
-//              tile into the FP32 accumulator, store P and dS as swizzled bf16 tiles
-//   warp 8     one thread issues every tcgen05.mma: S and dP of tile i+1 are issued as soon as the
-//              compute warps have read tile i, i.e. they run under the element-wise math of tile i
-//   warp 9     loader: gathers the Q and dO rows (and LSE, delta, row ids) of tile i+2 with cp.async
-//              into a three-deep ring while tiles i and i+1 are being consumed
-// TMEM columns: S 0-127, dP 128-255, dV 256-319, dK 320-383, dQ 384-447.
-constexpr int kWsThreads = 352;  // 8 compute warps, 1 MMA warp, 2 loader warps
-constexpr int kWsRing = 3;
-
-struct WsSmem {
-  uint64_t sdp_full, sdp_free, pds_ready, kvq_done;
-  uint64_t qdo_full[kWsRing], qdo_free[kWsRing];
-  uint32_t tmem_slot;
-  uint32_t pad;
-  int rowth[kWsRing][kTile];
-  float lse2[kWsRing][kTile];
-  float delta_s[kWsRing][kTile];
-  long long qoff[kWsRing][kTile];  // element offset of the row in q, -1 for padding rows
-};
-static_assert(sizeof(WsSmem) <= 8192, "control block must fit its reservation");
-
-__global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
-  constexpr int DPAD = 64, UPR = 8;
-  constexpr int TILE_BYTES = kTile * DPAD * 2;
-  constexpr int PT_BYTES = kTile * kTile * 2;
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  WsSmem& cb = *reinterpret_cast<WsSmem*>(smem);
-  uint8_t* sK = smem + 8192;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;                 // kWsRing tiles
-  uint8_t* sdO = sQ + kWsRing * TILE_BYTES;      // kWsRing tiles
-  uint8_t* sP = sdO + kWsRing * TILE_BYTES;
-  uint8_t* sdS = sP + PT_BYTES;
-
-  const PrefillView& pv = a.pv;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int D = pv.D;
-  const int kblock = a.kv_order[blockIdx.x];
-  const int g = blockIdx.y;
-  const int c = pv.qtile_chunk[kblock];
-  const int k0 = pv.qtile_tok0[kblock];
-  const int chunk_begin = pv.chunk_start[c], chunk_end = pv.chunk_start[c + 1];
-  const int nkeys = min(kTile, chunk_end - k0);
-  const int kb = (k0 - chunk_begin) / kTile;
-  const int tiles_in_chunk = (chunk_end - chunk_begin + kTile - 1) / kTile;
-  const int n_self = tiles_in_chunk - kb;
-  int remote_begin = 0, remote_rows = 0;
-  if (pv.R > 0) {
-    remote_begin = a.seg_base[c * pv.Hq + g * pv.G];
-    remote_rows = a.seg_base[c * pv.Hq + (g + 1) * pv.G] - remote_begin;
-  }
-  const int n_remote = (remote_rows + kTile - 1) / kTile;
-  const int n_iter = pv.G * n_self + n_remote;
-
-  if ((smem_u32(smem) & 1023u) != 0) {
-    if (tid == 0) atomicOr(a.status, kErrBadIndex);
-    return;
-  }
-  if (tid == 0) {
-    mbar_init(&cb.sdp_full, 1);
-    mbar_init(&cb.sdp_free, 256);
-    mbar_init(&cb.pds_ready, 256);
-    mbar_init(&cb.kvq_done, 1);
-    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 66); mbar_init(&cb.qdo_free[i], 1); }
-    mbar_fence_init();
-  }
-  if (warp == 0) tmem_alloc(&cb.tmem_slot, TMEM_COLS);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = cb.tmem_slot;
-  bool alive = true;
-
-  if (warp >= 9) {
-    // ================================================================== loaders (two warps, 64 rows each)
-    // A ring slot is published by 64 asynchronous arrivals (one per lane, fired by the hardware when
-    // that lane's cp.async copies have landed) plus one ordinary arrival per warp that releases the
-    // row metadata, so a tile becomes visible the moment its data is there.
-    const int lw = warp - 9;
-    if (lw == 0) {  // stationary K and V tiles of the key block ride along with tile 0
-      const __nv_bfloat16* kbase = a.k + (long long)g * pv.k_sh;
-      const __nv_bfloat16* vbase = a.v + (long long)g * pv.v_sh;
-      for (int i = lane; i < kTile * UPR; i += 32) {
-        const int r = i >> 3, u = i & 7;
-        const bool ok = r < nkeys && u * 8 < D;
-        cp_async16(smem_u32(sK) + sw128_offset(kTile, r, u), ok ? kbase + (long long)(k0 + r) * pv.k_st + u * 8 : kbase, ok);
-        cp_async16(smem_u32(sV) + sw128_offset(kTile, r, u), ok ? vbase + (long long)(k0 + r) * pv.v_st + u * 8 : vbase, ok);
-      }
-    }
-    for (int j = 0; j < n_iter; ++j) {
-      const int b = j % kWsRing;
-      if (j >= kWsRing && alive) alive = mbar_wait(&cb.qdo_free[b], ((j / kWsRing) - 1) & 1, a.status);
-      // rows of tile j: each lane resolves two of this warp's 64
-      int th2[2];
-#pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        const int r = lw * 64 + lane + 32 * x;
-        int th = -1;
-        if (j < pv.G * n_self) {
-          const int hl = j / n_self, i = kb + (j - hl * n_self);
-          const int tok = chunk_begin + i * kTile + r;
-          if (tok < chunk_end) th = tok * pv.Hq + g * pv.G + hl;
-        } else {
-          const int idx = (j - pv.G * n_self) * kTile + r;
-          if (idx < remote_rows) {
-            th = __ldg(a.rowlist + remote_begin + idx) / pv.R;
-            if (th < 0 || th >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); th = -1; }
-          }
-        }
-        th2[x] = th;
-      }
-#pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        const int r = lw * 64 + lane + 32 * x;
-        const int th = th2[x];
-        const int t = th / pv.Hq, h = th - t * pv.Hq;
-        cb.rowth[b][r] = th;
-        cb.qoff[b][r] = th >= 0 ? (long long)t * pv.q_st + (long long)h * pv.q_sh : -1;
-        cb.lse2[b][r] = th >= 0 ? __ldg(a.lse + th) * 1.4426950408889634f : INFINITY;
-        cb.delta_s[b][r] = th >= 0 ? __ldg(a.delta + th) * a.scale : 0.f;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&cb.qdo_full[b]);  // releases the metadata stores of this warp
-      const uint32_t qdst = smem_u32(sQ + b * TILE_BYTES), odst = smem_u32(sdO + b * TILE_BYTES);
-#pragma unroll
-      for (int x = 0; x < 16; ++x) {
-        const int r = lw * 64 + x * 4 + (lane >> 3), u = lane & 7;
-        const long long qo = cb.qoff[b][r];
-        const int rth = cb.rowth[b][r];
-        const bool ok = qo >= 0 && u * 8 < D;
-        const uint32_t off = sw128_offset(kTile, r, u);
-        cp_async16(qdst + off, ok ? a.q + qo + u * 8 : a.q, ok);
-        cp_async16(odst + off, ok ? a.dout + (long long)rth * D + u * 8 : a.dout, ok);
-      }
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(smem_u32(&cb.qdo_full[b])) : "memory");
-    }
-    cp_async_wait<0>();
-  } else if (warp == 8) {
-    // ================================================================== MMA issue
-    if (lane == 0) {
-      const uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 1, 1);
-      const uint32_t idesc_dq = umma_idesc_bf16(128, DPAD, 0, 1);
-      auto issue_sdp = [&](int j) {
-        const uint32_t q = smem_u32(sQ + (j % kWsRing) * TILE_BYTES), o = smem_u32(sdO + (j % kWsRing) * TILE_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < DPAD; kk += 16)
-          umma_ss(tmem + COL_S, umma_desc_kmajor(q, kTile, kk), umma_desc_kmajor(smem_u32(sK), kTile, kk), idesc_qk, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < DPAD; kk += 16)
-          umma_ss(tmem + COL_DP, umma_desc_kmajor(o, kTile, kk), umma_desc_kmajor(smem_u32(sV), kTile, kk), idesc_qk, kk > 0);
-        umma_commit(&cb.sdp_full);
-      };
-      auto issue_kvq = [&](int it) {
-        const uint32_t q = smem_u32(sQ + (it % kWsRing) * TILE_BYTES), o = smem_u32(sdO + (it % kWsRing) * TILE_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO
-          umma_ss(tmem + COL_DV, umma_desc_mnmajor(smem_u32(sP), kTile, kk, 0), umma_desc_mnmajor(o, kTile, kk, 0), idesc_kv,
-                  (it > 0) || (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < kTile; kk += 16)  // dK += dS^T Q
-          umma_ss(tmem + COL_DK, umma_desc_mnmajor(smem_u32(sdS), kTile, kk, 0), umma_desc_mnmajor(q, kTile, kk, 0), idesc_kv,
-                  (it > 0) || (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < kTile; kk += 16)  // dQ = dS K
-          umma_ss(tmem + COL_DQ, umma_desc_kmajor(smem_u32(sdS), kTile, kk), umma_desc_mnmajor(smem_u32(sK), kTile, kk, 0),
-                  idesc_dq, kk > 0);
-        umma_commit(&cb.kvq_done);
-        umma_commit(&cb.qdo_free[it % kWsRing]);
-      };
-      // Two streams of work are issued as their inputs become ready, whichever comes first:
-      //   S, dP of tile n   needs the tile's Q/dO in the ring and S/dP of tile n-1 read by every compute thread
-      //   dV, dK, dQ of tile i needs P and dS of tile i in shared memory
-      int next_sdp = 0, next_kvq = 0;
-      const long long t_start = clock64();
-      while (next_kvq < n_iter) {
-        bool progressed = false;
-        if (next_sdp < n_iter && next_sdp <= next_kvq + 1) {
-          const bool loaded = !alive || mbar_test(&cb.qdo_full[next_sdp % kWsRing], (next_sdp / kWsRing) & 1);
-          const bool freed = next_sdp == 0 || !alive || mbar_test(&cb.sdp_free, (next_sdp - 1) & 1);
-          if (loaded && freed) {
-            fence_async_smem();  // cp.async data of the ring -> visible to the tensor pipe
-            tc_fence_after_sync();
-            issue_sdp(next_sdp++);
-            progressed = true;
-          }
-        }
-        if (next_kvq < next_sdp && (!alive || mbar_test(&cb.pds_ready, next_kvq & 1))) {
-          tc_fence_after_sync();
-          issue_kvq(next_kvq++);
-          progressed = true;
-        }
-        if (!progressed && alive && clock64() - t_start > 4000000000ll) {
-          atomicOr(a.status, kErrBarrierTimeout);
-          alive = false;
-        }
-      }
-    }
-  } else {
-    // ================================================================== compute (warps 0-7)
-    const int quad = warp & 3, half = warp >> 2;
-    const int r = quad * 32 + lane;
-    const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
-    int th_prev = -1;
-    auto drain_dq = [&](int th) {  // dQ of the previous tile: this thread's 32 of the 64 columns
-      uint32_t v[32];
-      tmem_ld32(tlane + COL_DQ + half * 32, v);
-      tmem_ld_wait();
-      if (th >= 0 && alive) {
-        float* dst = a.dq_acc + (long long)th * D + half * 32;
-#pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          if (half * 32 + i < D)
-            red_add_v4(dst + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-      }
-    };
-    for (int it = 0; it < n_iter; ++it) {
-      const int b = it % kWsRing;
-      if (alive) alive = mbar_wait(&cb.qdo_full[b], (it / kWsRing) & 1, a.status);
-      const int th = cb.rowth[b][r];
-      const float lse2 = cb.lse2[b][r], delta_s = cb.delta_s[b][r];
-      const bool diag = it < pv.G * n_self && (it % n_self) == 0;
-      int klimit = nkeys;
-      if (diag) klimit = min(klimit, r + 1);
-      klimit -= half * 64;  // relative to this thread's first column
-
-      if (alive) alive = mbar_wait(&cb.sdp_full, it & 1, a.status);
-      tc_fence_after_sync();
-      uint32_t sv[64], dv[64];
-      {
-        uint32_t t0[32], t1[32];
-        tmem_ld32(tlane + COL_S + half * 64, t0);
-        tmem_ld32(tlane + COL_S + half * 64 + 32, t1);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = t0[i]; sv[32 + i] = t1[i]; }
-        tmem_ld32(tlane + COL_DP + half * 64, t0);
-        tmem_ld32(tlane + COL_DP + half * 64 + 32, t1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { dv[i] = t0[i]; dv[32 + i] = t1[i]; }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&cb.sdp_free);  // S and dP may be overwritten by the next tile's products
-
-      uint32_t pp[32], ds[32];
-#pragma unroll
-      for (int i = 0; i < 64; i += 2) {
-        float p0 = bwd_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
-        float p1 = bwd_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
-        if (i >= klimit) p0 = 0.f;
-        if (i + 1 >= klimit) p1 = 0.f;
-        const float d0 = p0 * fmaf(__uint_as_float(dv[i]), a.scale, -delta_s);
-        const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), a.scale, -delta_s);
-        pp[i >> 1] = bwd_pack_bf16(p0, p1);
-        ds[i >> 1] = bwd_pack_bf16(d0, d1);
-      }
-      if (it > 0) {  // previous tile's dV/dK/dQ products are complete: sP/sdS are free, dQ can be drained
-        if (alive) alive = mbar_wait(&cb.kvq_done, (it - 1) & 1, a.status);
-        tc_fence_after_sync();
-        drain_dq(th_prev);
-        tc_fence_before_sync();
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        *reinterpret_cast<uint4*>(sP + sw128_offset(kTile, r, half * 8 + u)) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-        *reinterpret_cast<uint4*>(sdS + sw128_offset(kTile, r, half * 8 + u)) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
-      }
-      fence_async_smem();
-      mbar_arrive(&cb.pds_ready);
-      th_prev = th;
-    }
-    if (n_iter > 0) {
-      if (alive) alive = mbar_wait(&cb.kvq_done, (n_iter - 1) & 1, a.status);
-      tc_fence_after_sync();
-      drain_dq(th_prev);
-      // dK (warps 0-3) and dV (warps 4-7) of the key block: thread = key row
-      const bool ok = r < nkeys && alive;
-      __nv_bfloat16* dst = (half == 0 ? a.dk : a.dv) + ((long long)(k0 + r) * pv.Hkv + g) * D;
-#pragma unroll
-      for (int pc = 0; pc < 2; ++pc) {
-        uint32_t v[32];
-        tmem_ld32(tlane + (half == 0 ? COL_DK : COL_DV) + pc * 32, v);
-        tmem_ld_wait();
-        if (ok) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8)
-            if (pc * 32 + i < D)
-              *reinterpret_cast<uint4*>(dst + pc * 32 + i) =
-                  make_uint4(bwd_pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
-        }
-      }
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_free(tmem, TMEM_COLS);
-}
-
-static cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st) {
-  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 * 2;
-  cudaError_t e = cudaFuncSetAttribute(attn_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  attn_bwd_ws_kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kWsThreads, smem, st>>>(a);
-  return cudaGetLastError();
-}
-
 template <int DPAD>
 static cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t st) {
   const size_t smem = 1024 + (size_t)kTile * DPAD * 2 * 4 + (size_t)kTile * kTile * 2 * 2;
@@ -635,6 +285,7 @@ static cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t st) {
 }  // namespace moba
 
 using namespace moba;
+
 
 extern "C" size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d) {
   if (validate_desc(d) != MOBA_OK) return 0;

@@ -1,0 +1,43 @@
+// Shared by the two backward kernels: argument block and small device helpers.
+#pragma once
+#include "prefill_common.cuh"
+#include "sm100.cuh"
+
+namespace moba {
+
+__device__ __forceinline__ float bwd_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t bwd_pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+struct BwdArgs {
+  PrefillView pv;
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const __nv_bfloat16* dout;  // [T,Hq,D] contiguous
+  const float* lse;           // [T,Hq] natural log
+  const float* delta;         // [T,Hq] rowsum(dO * O)
+  const int* rowlist;
+  const int* seg_base;
+  const int* kv_order;  // [num_qtiles] key blocks by decreasing expected work
+  float* dq_acc;        // [T,Hq,D] fp32, zero-initialised
+  __nv_bfloat16* dk;    // [T,Hkv,D] contiguous
+  __nv_bfloat16* dv;
+  unsigned* status;
+  float scale_log2, scale;
+};
+
+// Warp-specialised backward for head_dim <= 64 (prefill_attn_bwd_ws.cu).
+cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st);
+
+}  // namespace moba
