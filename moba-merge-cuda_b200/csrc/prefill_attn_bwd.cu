@@ -290,7 +290,12 @@ using namespace moba;
 extern "C" size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d) {
   if (validate_desc(d) != MOBA_OK) return 0;
   const size_t rows = (size_t)d->total_tokens * d->hq;
-  return align256(rows * 4) + align256(rows * d->dim * 4);
+  size_t bytes = align256(rows * 4) + align256(rows * d->dim * 4);
+  if (d->dim <= 64 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP)) {
+    const size_t tiles = (size_t)bwd_pack_tiles(*d);
+    bytes += 2 * align256(tiles * kTile * 64 * 2) + 3 * align256(tiles * kTile * 4);
+  }
+  return bytes;
 }
 
 extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, const void* v, const void* out,
@@ -325,14 +330,34 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
     a.seg_base = rs.seg_base;
   }
   a.kv_order = d->kv_order;
+  a.tile_base = nullptr;
+  if (d->remote_k > 0) a.tile_base = carve_route_state(*d, const_cast<void*>(route_state)).tile_base;
+  a.qpack = a.dopack = nullptr;
+  a.rowpack = nullptr;
+  a.lsepack = a.deltapack = nullptr;
   a.dq_acc = dq_acc;
   a.dk = static_cast<__nv_bfloat16*>(dk);
   a.dv = static_cast<__nv_bfloat16*>(dv);
   a.status = status;
   a.scale = (float)(1.0 / sqrt((double)d->dim));
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)d->dim));
+  const bool ws = d->dim <= 64 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP);
+  if (ws) {
+    const size_t tiles = (size_t)bwd_pack_tiles(*d);
+    char* p = reinterpret_cast<char*>(dq_acc) + align256((size_t)rows * d->dim * 4);
+    void* qpack = p; p += align256(tiles * kTile * 64 * 2);
+    void* dopack = p; p += align256(tiles * kTile * 64 * 2);
+    int* rowpack = reinterpret_cast<int*>(p); p += align256(tiles * kTile * 4);
+    float* lsepack = reinterpret_cast<float*>(p); p += align256(tiles * kTile * 4);
+    float* deltapack = reinterpret_cast<float*>(p);
+    a.scale = (float)(1.0 / sqrt((double)d->dim));
+    if (launch_bwd_pack(a, (long long)tiles, qpack, dopack, rowpack, lsepack, deltapack, st) != cudaSuccess) return MOBA_ERR_CUDA;
+    a.qpack = static_cast<const __nv_bfloat16*>(qpack);
+    a.dopack = static_cast<const __nv_bfloat16*>(dopack);
+    a.rowpack = rowpack; a.lsepack = lsepack; a.deltapack = deltapack;
+  }
   prof_begin(kProfBwdMain, st);
-  cudaError_t e = d->dim > 64 ? launch_bwd<128>(a, st) : ((d->flags & MOBA_BWD_SINGLE_WARPGROUP) ? launch_bwd<64>(a, st) : launch_bwd_ws(a, st));
+  cudaError_t e = d->dim > 64 ? launch_bwd<128>(a, st) : (ws ? launch_bwd_ws(a, st) : launch_bwd<64>(a, st));
   prof_end(kProfBwdMain, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
   const long long n8 = rows * d->dim / 8;

@@ -3,15 +3,16 @@
 // query tile that attends them), organised so that the tensor pipe, the exp/FMA pipes and the memory
 // system work on different query tiles at the same time.
 //   warps 0-7  compute: two threads per query row (64 of the 128 key columns each).  Per tile they read
-//              S and dP from TMEM and release them at once, form P and dS in registers, drain dQ of the
-//              previous tile into the FP32 accumulator, issue the cp.async copies of the Q and dO rows
-//              of tile i+2 (256 threads issuing keeps enough copies in flight; two dedicated loader
-//              warps could not), and store P and dS as swizzled bf16 tiles
+//              S and dP from TMEM and release them at once, form P and dS in registers, add dQ of the
+//              previous tile into the FP32 accumulator with vector reductions, and store P and dS as
+//              swizzled bf16 tiles
 //   warp 8     one thread issues every tcgen05.mma, polling two work streams: S/dP of tile n as soon
-//              as its rows have landed and the compute warps have read tile n-1; dV/dK/dQ of tile i
+//              as the tile has landed and the compute warps have read tile n-1; dV/dK/dQ of tile i
 //              as soon as P and dS of tile i are in shared memory
-//   warp 9     resolves row ids (expert list) and gathers LSE and delta of tiles further ahead into a
-//              four-slot metadata ring, with its dependent global loads software-pipelined
+//   warp 9     one thread asks the copy engine for the tiles: a packing pass (bwd_pack_kernel) has
+//              gathered the scattered Q and dO rows, row ids, LSE and delta of every tile into
+//              contiguous, already swizzled 16 KB images, so a tile is five bulk copies into a
+//              three-slot ring and costs the SM no load/store issue slots
 // TMEM columns: S 0-127, dP 128-255, dV 256-319, dK 320-383, dQ 384-447.
 #include "prefill_bwd.cuh"
 
@@ -29,9 +30,96 @@ __device__ long long* g_bwd_trace = nullptr;
 #define WS_TRACE(role, it, slot) do {} while (0)
 #endif
 
-constexpr int kWsThreads = 320;  // 8 compute warps, 1 MMA warp, 1 metadata warp
+// ---------------------------------------------------------------------------------------------
+// Packing pass.  Gathering 128 scattered 128-byte rows per tile with per-thread copies costs the
+// attention kernel more issue time than the math of the tile, so the rows are gathered once, here,
+// into ready-made shared-memory images: tile = 128 rows x 64 bf16 in the swizzled operand format,
+// 16 KB contiguous, which the attention kernel then fetches with one bulk copy.  Tile ids:
+//   (query tile qt, head h)            -> qt * Hq + h                     (causal tiles of the own chunk)
+//   expert e = chunk*Hkv + kv head, i  -> num_qtiles*Hq + tile_base[e] + i  (gathered expert rows)
+// Alongside go the row ids, LSE (log2 domain) and delta / sqrt(D) of the tile's rows.
+struct PackArgs {
+  BwdArgs a;
+  long long tiles;
+  __nv_bfloat16* qpack;
+  __nv_bfloat16* dopack;
+  int* rowpack;
+  float* lsepack;
+  float* deltapack;
+};
+
+__global__ void __launch_bounds__(128) bwd_pack_kernel(PackArgs pa) {
+  __shared__ int s_th[kTile];
+  const BwdArgs& a = pa.a;
+  const PrefillView& pv = a.pv;
+  const int tid = threadIdx.x;
+  const long long tile = blockIdx.x;
+  const long long n_self = (long long)pv.n_qtiles * pv.Hq;
+  int th = -1;
+  if (tile < n_self) {
+    const int qt = (int)(tile / pv.Hq), h = (int)(tile - (long long)qt * pv.Hq);
+    const int c = pv.qtile_chunk[qt];
+    const int tok = pv.qtile_tok0[qt] + tid;
+    if (tok < pv.chunk_start[c + 1]) th = tok * pv.Hq + h;
+  } else {
+    if (pv.R == 0) return;
+    const int E = pv.n_chunks * pv.Hkv;
+    const long long w = tile - n_self;
+    if (w >= a.tile_base[E]) return;
+    int lo = 0, hi = E;  // largest e with tile_base[e] <= w
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (a.tile_base[mid] <= w) lo = mid; else hi = mid;
+    }
+    const int e = lo, i = (int)(w - a.tile_base[e]);
+    const int c = e / pv.Hkv, g = e - c * pv.Hkv;
+    const int start = a.seg_base[c * pv.Hq + g * pv.G] + i * kTile;
+    const int end = a.seg_base[c * pv.Hq + (g + 1) * pv.G];
+    if (start + tid < end) {
+      th = a.rowlist[start + tid] / pv.R;
+      if (th < 0 || th >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); th = -1; }
+    }
+  }
+  s_th[tid] = th;
+  pa.rowpack[tile * kTile + tid] = th;
+  pa.lsepack[tile * kTile + tid] = th >= 0 ? a.lse[th] * 1.4426950408889634f : INFINITY;
+  pa.deltapack[tile * kTile + tid] = th >= 0 ? a.delta[th] * a.scale : 0.f;
+  __syncthreads();
+  uint8_t* qdst = reinterpret_cast<uint8_t*>(pa.qpack) + tile * (kTile * 128);
+  uint8_t* odst = reinterpret_cast<uint8_t*>(pa.dopack) + tile * (kTile * 128);
+  const int u = tid & 7;
+#pragma unroll 4
+  for (int x = 0; x < 8; ++x) {
+    const int row = (tid >> 3) + 16 * x;
+    const int rth = s_th[row];
+    uint4 qv = make_uint4(0, 0, 0, 0), ov = make_uint4(0, 0, 0, 0);
+    if (rth >= 0 && u * 8 < pv.D) {
+      const int t = rth / pv.Hq, h = rth - t * pv.Hq;
+      qv = *reinterpret_cast<const uint4*>(a.q + (long long)t * pv.q_st + (long long)h * pv.q_sh + u * 8);
+      ov = *reinterpret_cast<const uint4*>(a.dout + (long long)rth * pv.D + u * 8);
+    }
+    const uint32_t off = sw128_offset(kTile, row, u);
+    *reinterpret_cast<uint4*>(qdst + off) = qv;
+    *reinterpret_cast<uint4*>(odst + off) = ov;
+  }
+}
+
+cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* qpack, void* dopack, int* rowpack, float* lsepack,
+                            float* deltapack, cudaStream_t st) {
+  PackArgs pa;
+  pa.a = a;
+  pa.tiles = tiles;
+  pa.qpack = static_cast<__nv_bfloat16*>(qpack);
+  pa.dopack = static_cast<__nv_bfloat16*>(dopack);
+  pa.rowpack = rowpack;
+  pa.lsepack = lsepack;
+  pa.deltapack = deltapack;
+  bwd_pack_kernel<<<(unsigned)tiles, 128, 0, st>>>(pa);
+  return cudaGetLastError();
+}
+
+constexpr int kWsThreads = 320;  // 8 compute warps, MMA warp, producer warp
 constexpr int kWsRing = 3;       // Q/dO tiles in shared memory
-constexpr int kWsMeta = 4;       // metadata slots
 
 // One lane polls the barrier for its warp; __syncwarp orders the other lanes' later reads after
 // lane 0's acquire.
@@ -48,14 +136,14 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
 }
 
 struct WsSmem {
-  uint64_t sdp_full, sdp_free, pds_ready, kvq_done;
-  uint64_t qdo_full[kWsRing], qdo_free[kWsRing];
-  uint64_t meta_full[kWsMeta], meta_free[kWsMeta];
+  uint64_t sdp_full, sdp_free, pds_ready, kvq_done, kv_ready;
+  uint64_t qdo_full[kWsRing];      // tile (Q, dO, row metadata) landed in the slot
+  uint64_t qdo_free[kWsRing];      // dV and dK of the tile are done: the slot may take its next tile
   uint32_t tmem_slot;
   uint32_t pad;
-  int rowth[kWsMeta][kTile];      // t*Hq+h of every row of the tile, -1 = padding row
-  float lse2[kWsMeta][kTile];     // LSE in the log2 domain (+inf for padding rows)
-  float delta_s[kWsMeta][kTile];  // rowsum(dO*O) / sqrt(D)
+  __align__(16) int rowth[kWsRing][kTile];      // t*Hq+h of every row of the tile, -1 = padding row
+  __align__(16) float lse2[kWsRing][kTile];     // LSE in the log2 domain (+inf for padding rows)
+  __align__(16) float delta_s[kWsRing][kTile];  // rowsum(dO*O) / sqrt(D)
 };
 static_assert(sizeof(WsSmem) <= 8192, "control block must fit its reservation");
 
@@ -69,9 +157,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   WsSmem& cb = *reinterpret_cast<WsSmem*>(smem);
   uint8_t* sK = smem + 8192;
   uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;             // kWsRing tiles
-  uint8_t* sdO = sQ + kWsRing * TILE_BYTES;  // kWsRing tiles
-  uint8_t* sP = sdO + kWsRing * TILE_BYTES;
+  constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // ring slot: Q tile followed by dO tile (32 KB, later the dQ staging area)
+  uint8_t* sQ = sV + TILE_BYTES;
+  uint8_t* sdO = sQ + TILE_BYTES;
+  uint8_t* sP = sQ + kWsRing * SLOT_BYTES;
   uint8_t* sdS = sP + PT_BYTES;
 
   const PrefillView& pv = a.pv;
@@ -103,8 +192,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     mbar_init(&cb.sdp_free, 8);
     mbar_init(&cb.pds_ready, 8);
     mbar_init(&cb.kvq_done, 1);
-    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 256); mbar_init(&cb.qdo_free[i], 1); }
-    for (int i = 0; i < kWsMeta; ++i) { mbar_init(&cb.meta_full[i], 1); mbar_init(&cb.meta_free[i], 8); }
+    mbar_init(&cb.kv_ready, 8);
+    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 1); }
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(&cb.tmem_slot, TMEM_COLS);
@@ -115,55 +204,32 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   bool alive = true;
 
   if (warp == 9) {
-    // ================================================================== metadata
-    // Row ids come from the expert list and LSE/delta are gathered by row id: two dependent global
-    // loads per row, pipelined (ids two tiles ahead, LSE/delta one tile ahead of their use).
-    auto resolve = [&](int j, int x) -> int {
-      if (j >= n_iter) return -1;
-      const int r = lane + 32 * x;
-      if (j < pv.G * n_self) {
-        const int hl = j / n_self, i = kb + (j - hl * n_self);
-        const int tok = chunk_begin + i * kTile + r;
-        return tok < chunk_end ? tok * pv.Hq + g * pv.G + hl : -1;
-      }
-      const int idx = (j - pv.G * n_self) * kTile + r;
-      if (idx >= remote_rows) return -1;
-      const int th = __ldg(a.rowlist + remote_begin + idx) / pv.R;
-      if (th < 0 || th >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); return -1; }
-      return th;
-    };
-    int th_cur[4], th_nxt[4];
-    float lse_cur[4], del_cur[4];
-#pragma unroll
-    for (int x = 0; x < 4; ++x) { th_cur[x] = resolve(0, x); th_nxt[x] = resolve(1, x); }
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      lse_cur[x] = th_cur[x] >= 0 ? __ldg(a.lse + th_cur[x]) : 0.f;
-      del_cur[x] = th_cur[x] >= 0 ? __ldg(a.delta + th_cur[x]) : 0.f;
-    }
-    for (int j = 0; j < n_iter; ++j) {
-      const int ms = j % kWsMeta;
-      int th_nn[4];
-      float lse_nxt[4], del_nxt[4];
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        th_nn[x] = resolve(j + 2, x);
-        lse_nxt[x] = th_nxt[x] >= 0 ? __ldg(a.lse + th_nxt[x]) : 0.f;
-        del_nxt[x] = th_nxt[x] >= 0 ? __ldg(a.delta + th_nxt[x]) : 0.f;
-      }
-      if (j >= kWsMeta) alive = warp_wait(&cb.meta_free[ms], ((j / kWsMeta) - 1) & 1, a.status, alive);
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int r = lane + 32 * x;
-        cb.rowth[ms][r] = th_cur[x];
-        cb.lse2[ms][r] = th_cur[x] >= 0 ? lse_cur[x] * 1.4426950408889634f : INFINITY;
-        cb.delta_s[ms][r] = th_cur[x] >= 0 ? del_cur[x] * a.scale : 0.f;
-      }
-      warp_arrive(&cb.meta_full[ms]);
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        th_cur[x] = th_nxt[x]; th_nxt[x] = th_nn[x];
-        lse_cur[x] = lse_nxt[x]; del_cur[x] = del_nxt[x];
+    // ================================================================== producer
+    // One thread asks the copy engine for the packed tiles: 16 KB of Q, 16 KB of dO and three 512-byte
+    // metadata rows per tile, all contiguous in global memory, completion counted on the slot's barrier.
+    if (lane == 0) {
+      const long long self_tiles = (long long)pv.n_qtiles * pv.Hq;
+      const long long remote_tile0 = pv.R > 0 ? self_tiles + a.tile_base[c * pv.Hkv + g] : 0;
+      for (int j = 0; j < n_iter; ++j) {
+        const int b = j % kWsRing;
+        long long tile;
+        if (j < pv.G * n_self) {
+          const int hl = j / n_self, i = kb + (j - hl * n_self);
+          tile = (long long)(kblock - kb + i) * pv.Hq + g * pv.G + hl;  // query tiles of a chunk are consecutive
+        } else {
+          // The key blocks of a chunk walk the same expert list; starting each at a different offset
+          // keeps them from adding into the same dQ rows at the same time.
+          int jr = j - pv.G * n_self + (int)(((long long)kb * n_remote) / tiles_in_chunk);
+          if (jr >= n_remote) jr -= n_remote;
+          tile = remote_tile0 + jr;
+        }
+        if (j >= kWsRing && alive) alive = mbar_wait(&cb.qdo_free[b], ((j / kWsRing) - 1) & 1, a.status);
+        mbar_arrive_expect_tx(&cb.qdo_full[b], 2 * TILE_BYTES + 3 * kTile * 4);
+        bulk_load(sQ + b * SLOT_BYTES, reinterpret_cast<const uint8_t*>(a.qpack) + tile * TILE_BYTES, TILE_BYTES, &cb.qdo_full[b]);
+        bulk_load(sdO + b * SLOT_BYTES, reinterpret_cast<const uint8_t*>(a.dopack) + tile * TILE_BYTES, TILE_BYTES, &cb.qdo_full[b]);
+        bulk_load(cb.rowth[b], a.rowpack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
+        bulk_load(cb.lse2[b], a.lsepack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
+        bulk_load(cb.delta_s[b], a.deltapack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
       }
     }
   } else if (warp == 8) {
@@ -181,7 +247,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       const uint64_t p_mn = umma_desc_mnmajor(smem_u32(sP), kTile, 0, 0);
       const uint64_t s_mn = umma_desc_mnmajor(smem_u32(sdS), kTile, 0, 0), s_km = umma_desc_kmajor(smem_u32(sdS), kTile, 0);
       auto issue_sdp = [&](int j) {
-        const uint64_t slot = (uint64_t)((j % kWsRing) * (TILE_BYTES >> 4));
+        const uint64_t slot = (uint64_t)((j % kWsRing) * (SLOT_BYTES >> 4));
 #pragma unroll
         for (int kk = 0; kk < DPAD; kk += 16)  // K-major step: 16 elements = 32 bytes = 2 units
           umma_ss(tmem + COL_S, q_km + slot + (kk >> 3), k_km + (kk >> 3), idesc_qk, kk > 0);
@@ -191,7 +257,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         umma_commit(&cb.sdp_full);
       };
       auto issue_kvq = [&](int it) {
-        const uint64_t slot = (uint64_t)((it % kWsRing) * (TILE_BYTES >> 4));
+        const uint64_t slot = (uint64_t)((it % kWsRing) * (SLOT_BYTES >> 4));
         const uint32_t acc = it > 0;
 #pragma unroll
         for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO; MN-major step: 16 rows = 2048 bytes = 128 units
@@ -213,7 +279,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       while (next_kvq < n_iter) {
         bool progressed = false;
         if (next_sdp < n_iter && next_sdp <= next_kvq + 1) {
-          const bool loaded = !alive || mbar_test(&cb.qdo_full[next_sdp % kWsRing], (next_sdp / kWsRing) & 1);
+          const bool loaded = !alive || (mbar_test(&cb.qdo_full[next_sdp % kWsRing], (next_sdp / kWsRing) & 1) &&
+                                         (next_sdp > 0 || mbar_test(&cb.kv_ready, 0)));
           const bool freed = next_sdp == 0 || !alive || mbar_test(&cb.sdp_free, (next_sdp - 1) & 1);
           if (loaded && freed) {
             fence_async_smem();  // cp.async data of the ring -> visible to the tensor pipe
@@ -243,27 +310,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     const int quad = warp & 3, half = warp >> 2;
     const int r = quad * 32 + lane;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
-    // Copies of the Q and dO rows of tile j into ring slot j % kWsRing: thread = (unit, 4 rows), so
-    // eight consecutive threads fetch one 128-byte row.  The slot's barrier gets one asynchronous
-    // arrival per thread, fired by the hardware when that thread's copies have landed.
-    auto issue_tile_copies = [&](int j) {
-      const int ms = j % kWsMeta, b = j % kWsRing;
-      alive = warp_wait(&cb.meta_full[ms], (j / kWsMeta) & 1, a.status, alive);
-      const uint32_t qdst = smem_u32(sQ + b * TILE_BYTES), odst = smem_u32(sdO + b * TILE_BYTES);
-      const int u = tid & 7;
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int row = (tid >> 3) + 32 * x;
-        const int rth = cb.rowth[ms][row];
-        const bool ok = rth >= 0 && u * 8 < D;
-        const int t = rth / pv.Hq, h = rth - t * pv.Hq;
-        const uint32_t off = sw128_offset(kTile, row, u);
-        cp_async16(qdst + off, ok ? a.q + (long long)t * pv.q_st + (long long)h * pv.q_sh + u * 8 : a.q, ok);
-        cp_async16(odst + off, ok ? a.dout + (long long)rth * D + u * 8 : a.dout, ok);
-      }
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(smem_u32(&cb.qdo_full[b])) : "memory");
-    };
-    {  // stationary K and V tiles of the key block ride along with tile 0
+    {  // stationary K and V tiles of the key block (strided rows: per-thread copies, once per CTA)
       const __nv_bfloat16* kbase = a.k + (long long)g * pv.k_sh;
       const __nv_bfloat16* vbase = a.v + (long long)g * pv.v_sh;
       for (int i = tid; i < kTile * UPR; i += 256) {
@@ -272,34 +319,38 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         cp_async16(smem_u32(sK) + sw128_offset(kTile, row, u), ok ? kbase + (long long)(k0 + row) * pv.k_st + u * 8 : kbase, ok);
         cp_async16(smem_u32(sV) + sw128_offset(kTile, row, u), ok ? vbase + (long long)(k0 + row) * pv.v_st + u * 8 : vbase, ok);
       }
+      cp_async_commit();
+      cp_async_wait<0>();
+      fence_async_smem();
+      warp_arrive(&cb.kv_ready);
     }
-    issue_tile_copies(0);
-    if (n_iter > 1) issue_tile_copies(1);
 
+    // dQ of tile j: this thread's 32 of the row's 64 columns are added into the FP32 accumulator with
+    // vector reductions straight from registers.  (Parking the rows in shared memory for bulk
+    // add-reductions by the copy engine was measured slower: shared-memory bandwidth is the scarce
+    // resource of this kernel.)
     int th_prev = -1;
-    auto drain_dq = [&](int th) {  // dQ of the previous tile: this thread's 32 of the 64 columns
+    auto drain_dq = [&](int th) {  // th: row id kept from the tile's own iteration (its ring slot may be refilled by now)
       uint32_t v[32];
       tmem_ld32(tlane + COL_DQ + half * 32, v);
       tmem_ld_wait();
-#ifdef MOBA_BWD_NODRAIN
-      if (th == -12345) {
-#else
+#ifndef MOBA_BWD_NODRAIN
       if (th >= 0 && alive) {
-#endif
         float* dst = a.dq_acc + (long long)th * D + half * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 4)
           if (half * 32 + i < D)
             red_add_v4(dst + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
       }
+#endif
     };
     for (int it = 0; it < n_iter; ++it) {
-      const int ms = it % kWsMeta;
+      const int ms = it % kWsRing;
       if (tid == 0) WS_TRACE(0, it, 0);
-      // metadata of this tile was acquired when its copies were issued (two tiles ago)
+      alive = warp_wait(&cb.qdo_full[ms], (it / kWsRing) & 1, a.status, alive);  // the tile's metadata is in the slot
+      if (tid == 0) WS_TRACE(0, it, 1);
       const int th = cb.rowth[ms][r];
       const float lse2 = cb.lse2[ms][r], delta_s = cb.delta_s[ms][r];
-      warp_arrive(&cb.meta_free[ms]);
       const bool diag = it < pv.G * n_self && (it % n_self) == 0;
       int klimit = nkeys;
       if (diag) klimit = min(klimit, r + 1);
@@ -326,16 +377,28 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       if (tid == 0) WS_TRACE(0, it, 3);
 
       uint32_t pp[32], ds[32];
+      if (__all_sync(0xFFFFFFFFu, klimit >= 64)) {  // no causal edge and no missing key in this warp's columns
 #pragma unroll
-      for (int i = 0; i < 64; i += 2) {
-        float p0 = bwd_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
-        float p1 = bwd_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
-        if (i >= klimit) p0 = 0.f;
-        if (i + 1 >= klimit) p1 = 0.f;
-        const float d0 = p0 * fmaf(__uint_as_float(dv[i]), a.scale, -delta_s);
-        const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), a.scale, -delta_s);
-        pp[i >> 1] = bwd_pack_bf16(p0, p1);
-        ds[i >> 1] = bwd_pack_bf16(d0, d1);
+        for (int i = 0; i < 64; i += 2) {
+          const float p0 = bwd_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
+          const float p1 = bwd_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
+          const float d0 = p0 * fmaf(__uint_as_float(dv[i]), a.scale, -delta_s);
+          const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), a.scale, -delta_s);
+          pp[i >> 1] = bwd_pack_bf16(p0, p1);
+          ds[i >> 1] = bwd_pack_bf16(d0, d1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 2) {
+          float p0 = bwd_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
+          float p1 = bwd_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
+          if (i >= klimit) p0 = 0.f;
+          if (i + 1 >= klimit) p1 = 0.f;
+          const float d0 = p0 * fmaf(__uint_as_float(dv[i]), a.scale, -delta_s);
+          const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), a.scale, -delta_s);
+          pp[i >> 1] = bwd_pack_bf16(p0, p1);
+          ds[i >> 1] = bwd_pack_bf16(d0, d1);
+        }
       }
       if (tid == 0) WS_TRACE(0, it, 4);
       if (it > 0) {  // previous tile's dV/dK/dQ products are complete: sP/sdS are free, dQ can be drained
@@ -346,8 +409,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         tc_fence_before_sync();
       }
       if (tid == 0) WS_TRACE(3, it, 0);
-      // ring slot (it+2) % 3 held tile it-1, whose last readers (dV, dK) finished before kvq_done(it-1)
-      if (it + 2 < n_iter) issue_tile_copies(it + 2);
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         *reinterpret_cast<uint4*>(sP + sw128_offset(kTile, r, half * 8 + u)) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
@@ -359,7 +420,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       if (tid == 0) WS_TRACE(0, it, 7);
       th_prev = th;
     }
-    cp_async_wait<0>();
     if (n_iter > 0) {
       alive = warp_wait(&cb.kvq_done, (n_iter - 1) & 1, a.status, alive);
       tc_fence_after_sync();
