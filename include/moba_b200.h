@@ -65,7 +65,9 @@ typedef struct moba_prefill_desc {
   const int32_t* kv_order;
 } moba_prefill_desc;
 
-/* Bytes of the route state (kept from forward to backward) and of the routing scratch. */
+/* Bytes of the state kept from forward to backward (route lists written by moba_prefill_route, followed by
+ * packed operand tiles written by moba_prefill_fwd) and of the routing scratch. The state is required for
+ * every call, also when remote_k == 0. */
 size_t moba_prefill_route_state_bytes(const moba_prefill_desc* d);
 size_t moba_prefill_route_scratch_bytes(const moba_prefill_desc* d);
 

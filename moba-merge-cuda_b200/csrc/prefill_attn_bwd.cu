@@ -292,8 +292,8 @@ extern "C" size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d) {
   const size_t rows = (size_t)d->total_tokens * d->hq;
   size_t bytes = align256(rows * 4) + align256(rows * d->dim * 4);
   if (d->dim <= 64 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP)) {
-    const size_t tiles = (size_t)bwd_pack_tiles(*d);
-    bytes += 2 * align256(tiles * kTile * 64 * 2) + 3 * align256(tiles * kTile * 4);
+    const size_t tiles = (size_t)pack_q_tiles(*d);
+    bytes += align256(tiles * kTile * 64 * 2) + 2 * align256(tiles * kTile * 4);
   }
   return bytes;
 }
@@ -304,7 +304,7 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   int rc = validate_desc(d);
   if (rc != MOBA_OK) return rc;
   if (!q || !k || !v || !out || !lse || !dout || !scratch || !dq || !dk || !dv || !status || !d->kv_order ||
-      (d->remote_k > 0 && !route_state))
+      !route_state)
     return MOBA_ERR_INVALID;
   if (d->dim > 128) return MOBA_ERR_UNSUPPORTED;
   if (scratch_bytes < moba_prefill_bwd_scratch_bytes(d)) return MOBA_ERR_WORKSPACE;
@@ -332,7 +332,7 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.kv_order = d->kv_order;
   a.tile_base = nullptr;
   if (d->remote_k > 0) a.tile_base = carve_route_state(*d, const_cast<void*>(route_state)).tile_base;
-  a.qpack = a.dopack = nullptr;
+  a.qpack = a.dopack = a.kpack = a.vpack = nullptr;
   a.rowpack = nullptr;
   a.lsepack = a.deltapack = nullptr;
   a.dq_acc = dq_acc;
@@ -343,18 +343,17 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)d->dim));
   const bool ws = d->dim <= 64 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP);
   if (ws) {
-    const size_t tiles = (size_t)bwd_pack_tiles(*d);
+    const size_t tiles = (size_t)pack_q_tiles(*d);
     char* p = reinterpret_cast<char*>(dq_acc) + align256((size_t)rows * d->dim * 4);
-    void* qpack = p; p += align256(tiles * kTile * 64 * 2);
     void* dopack = p; p += align256(tiles * kTile * 64 * 2);
-    int* rowpack = reinterpret_cast<int*>(p); p += align256(tiles * kTile * 4);
     float* lsepack = reinterpret_cast<float*>(p); p += align256(tiles * kTile * 4);
     float* deltapack = reinterpret_cast<float*>(p);
-    a.scale = (float)(1.0 / sqrt((double)d->dim));
-    if (launch_bwd_pack(a, (long long)tiles, qpack, dopack, rowpack, lsepack, deltapack, st) != cudaSuccess) return MOBA_ERR_CUDA;
-    a.qpack = static_cast<const __nv_bfloat16*>(qpack);
+    const PackState ps = carve_pack_state(*d, const_cast<void*>(route_state));
+    a.qpack = ps.qpack; a.kpack = ps.kpack; a.vpack = ps.vpack; a.rowpack = ps.rowpack;
+    const long long used = d->remote_k > 0 ? (long long)tiles : (long long)d->num_qtiles * d->hq;
+    if (launch_bwd_pack(a, used, dopack, lsepack, deltapack, st) != cudaSuccess) return MOBA_ERR_CUDA;
     a.dopack = static_cast<const __nv_bfloat16*>(dopack);
-    a.rowpack = rowpack; a.lsepack = lsepack; a.deltapack = deltapack;
+    a.lsepack = lsepack; a.deltapack = deltapack;
   }
   prof_begin(kProfBwdMain, st);
   cudaError_t e = d->dim > 64 ? launch_bwd<128>(a, st) : (ws ? launch_bwd_ws(a, st) : launch_bwd<64>(a, st));

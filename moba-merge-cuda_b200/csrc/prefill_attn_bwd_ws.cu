@@ -31,19 +31,11 @@ __device__ long long* g_bwd_trace = nullptr;
 #endif
 
 // ---------------------------------------------------------------------------------------------
-// Packing pass.  Gathering 128 scattered 128-byte rows per tile with per-thread copies costs the
-// attention kernel more issue time than the math of the tile, so the rows are gathered once, here,
-// into ready-made shared-memory images: tile = 128 rows x 64 bf16 in the swizzled operand format,
-// 16 KB contiguous, which the attention kernel then fetches with one bulk copy.  Tile ids:
-//   (query tile qt, head h)            -> qt * Hq + h                     (causal tiles of the own chunk)
-//   expert e = chunk*Hkv + kv head, i  -> num_qtiles*Hq + tile_base[e] + i  (gathered expert rows)
-// Alongside go the row ids, LSE (log2 domain) and delta / sqrt(D) of the tile's rows.
+// Backward packing pass: dO rows, LSE (log2 domain) and delta / sqrt(D) of every query tile, in the
+// tile order of the forward's Q pack (row ids come from its rowpack), as contiguous swizzled images.
 struct PackArgs {
   BwdArgs a;
-  long long tiles;
-  __nv_bfloat16* qpack;
   __nv_bfloat16* dopack;
-  int* rowpack;
   float* lsepack;
   float* deltapack;
 };
@@ -55,63 +47,28 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(PackArgs pa) {
   const int tid = threadIdx.x;
   const long long tile = blockIdx.x;
   const long long n_self = (long long)pv.n_qtiles * pv.Hq;
-  int th = -1;
-  if (tile < n_self) {
-    const int qt = (int)(tile / pv.Hq), h = (int)(tile - (long long)qt * pv.Hq);
-    const int c = pv.qtile_chunk[qt];
-    const int tok = pv.qtile_tok0[qt] + tid;
-    if (tok < pv.chunk_start[c + 1]) th = tok * pv.Hq + h;
-  } else {
-    if (pv.R == 0) return;
-    const int E = pv.n_chunks * pv.Hkv;
-    const long long w = tile - n_self;
-    if (w >= a.tile_base[E]) return;
-    int lo = 0, hi = E;  // largest e with tile_base[e] <= w
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (a.tile_base[mid] <= w) lo = mid; else hi = mid;
-    }
-    const int e = lo, i = (int)(w - a.tile_base[e]);
-    const int c = e / pv.Hkv, g = e - c * pv.Hkv;
-    const int start = a.seg_base[c * pv.Hq + g * pv.G] + i * kTile;
-    const int end = a.seg_base[c * pv.Hq + (g + 1) * pv.G];
-    if (start + tid < end) {
-      th = a.rowlist[start + tid] / pv.R;
-      if (th < 0 || th >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); th = -1; }
-    }
-  }
+  if (tile >= n_self && (pv.R == 0 || tile - n_self >= a.tile_base[pv.n_chunks * pv.Hkv])) return;
+  const int th = a.rowpack[tile * kTile + tid];
   s_th[tid] = th;
-  pa.rowpack[tile * kTile + tid] = th;
   pa.lsepack[tile * kTile + tid] = th >= 0 ? a.lse[th] * 1.4426950408889634f : INFINITY;
   pa.deltapack[tile * kTile + tid] = th >= 0 ? a.delta[th] * a.scale : 0.f;
   __syncthreads();
-  uint8_t* qdst = reinterpret_cast<uint8_t*>(pa.qpack) + tile * (kTile * 128);
   uint8_t* odst = reinterpret_cast<uint8_t*>(pa.dopack) + tile * (kTile * 128);
   const int u = tid & 7;
 #pragma unroll 4
   for (int x = 0; x < 8; ++x) {
     const int row = (tid >> 3) + 16 * x;
     const int rth = s_th[row];
-    uint4 qv = make_uint4(0, 0, 0, 0), ov = make_uint4(0, 0, 0, 0);
-    if (rth >= 0 && u * 8 < pv.D) {
-      const int t = rth / pv.Hq, h = rth - t * pv.Hq;
-      qv = *reinterpret_cast<const uint4*>(a.q + (long long)t * pv.q_st + (long long)h * pv.q_sh + u * 8);
-      ov = *reinterpret_cast<const uint4*>(a.dout + (long long)rth * pv.D + u * 8);
-    }
-    const uint32_t off = sw128_offset(kTile, row, u);
-    *reinterpret_cast<uint4*>(qdst + off) = qv;
-    *reinterpret_cast<uint4*>(odst + off) = ov;
+    uint4 ov = make_uint4(0, 0, 0, 0);
+    if (rth >= 0 && u * 8 < pv.D) ov = *reinterpret_cast<const uint4*>(a.dout + (long long)rth * pv.D + u * 8);
+    *reinterpret_cast<uint4*>(odst + sw128_offset(kTile, row, u)) = ov;
   }
 }
 
-cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* qpack, void* dopack, int* rowpack, float* lsepack,
-                            float* deltapack, cudaStream_t st) {
+cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, float* lsepack, float* deltapack, cudaStream_t st) {
   PackArgs pa;
   pa.a = a;
-  pa.tiles = tiles;
-  pa.qpack = static_cast<__nv_bfloat16*>(qpack);
   pa.dopack = static_cast<__nv_bfloat16*>(dopack);
-  pa.rowpack = rowpack;
   pa.lsepack = lsepack;
   pa.deltapack = deltapack;
   bwd_pack_kernel<<<(unsigned)tiles, 128, 0, st>>>(pa);
@@ -148,7 +105,7 @@ struct WsSmem {
 static_assert(sizeof(WsSmem) <= 8192, "control block must fit its reservation");
 
 __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
-  constexpr int DPAD = 64, UPR = 8;
+  constexpr int DPAD = 64;
   constexpr int TILE_BYTES = kTile * DPAD * 2;
   constexpr int PT_BYTES = kTile * kTile * 2;
   constexpr uint32_t TMEM_COLS = 512;
@@ -192,7 +149,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     mbar_init(&cb.sdp_free, 8);
     mbar_init(&cb.pds_ready, 8);
     mbar_init(&cb.kvq_done, 1);
-    mbar_init(&cb.kv_ready, 8);
+    mbar_init(&cb.kv_ready, 1);
     for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 1); }
     mbar_fence_init();
   }
@@ -208,6 +165,12 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     // One thread asks the copy engine for the packed tiles: 16 KB of Q, 16 KB of dO and three 512-byte
     // metadata rows per tile, all contiguous in global memory, completion counted on the slot's barrier.
     if (lane == 0) {
+      {  // stationary K and V images of the key block
+        const size_t kvoff = ((size_t)kblock * pv.Hkv + g) * TILE_BYTES;
+        mbar_arrive_expect_tx(&cb.kv_ready, 2 * TILE_BYTES);
+        bulk_load(sK, reinterpret_cast<const uint8_t*>(a.kpack) + kvoff, TILE_BYTES, &cb.kv_ready);
+        bulk_load(sV, reinterpret_cast<const uint8_t*>(a.vpack) + kvoff, TILE_BYTES, &cb.kv_ready);
+      }
       const long long self_tiles = (long long)pv.n_qtiles * pv.Hq;
       const long long remote_tile0 = pv.R > 0 ? self_tiles + a.tile_base[c * pv.Hkv + g] : 0;
       for (int j = 0; j < n_iter; ++j) {
@@ -310,25 +273,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     const int quad = warp & 3, half = warp >> 2;
     const int r = quad * 32 + lane;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
-    {  // stationary K and V tiles of the key block (strided rows: per-thread copies, once per CTA)
-      const __nv_bfloat16* kbase = a.k + (long long)g * pv.k_sh;
-      const __nv_bfloat16* vbase = a.v + (long long)g * pv.v_sh;
-      for (int i = tid; i < kTile * UPR; i += 256) {
-        const int row = i >> 3, u = i & 7;
-        const bool ok = row < nkeys && u * 8 < D;
-        cp_async16(smem_u32(sK) + sw128_offset(kTile, row, u), ok ? kbase + (long long)(k0 + row) * pv.k_st + u * 8 : kbase, ok);
-        cp_async16(smem_u32(sV) + sw128_offset(kTile, row, u), ok ? vbase + (long long)(k0 + row) * pv.v_st + u * 8 : vbase, ok);
-      }
-      cp_async_commit();
-      cp_async_wait<0>();
-      fence_async_smem();
-      warp_arrive(&cb.kv_ready);
-    }
-
-    // dQ of tile j: this thread's 32 of the row's 64 columns are added into the FP32 accumulator with
-    // vector reductions straight from registers.  (Parking the rows in shared memory for bulk
-    // add-reductions by the copy engine was measured slower: shared-memory bandwidth is the scarce
-    // resource of this kernel.)
     int th_prev = -1;
     auto drain_dq = [&](int th) {  // th: row id kept from the tile's own iteration (its ring slot may be refilled by now)
       uint32_t v[32];

@@ -38,6 +38,9 @@ struct FwdArgs {
   const int* rowlist;
   const int* seg_base;
   const int* tile_base;
+  const uint8_t* qpack;  // packed operand tiles, see PackState
+  const uint8_t* kpack;
+  const uint8_t* vpack;
   __nv_bfloat16* part_o;  // [T*Hq*R, D]
   float* part_lse;        // [T*Hq*R] log2 domain
   __nv_bfloat16* out;     // [T, Hq, D]
@@ -46,32 +49,18 @@ struct FwdArgs {
   float scale_log2;
 };
 
-// Loads rows [row0, row0+128) x DPAD of a [*, D] matrix into an SW128 tile; rows >= nvalid and
-// columns >= D are zero-filled.
-template <int DPAD>
-__device__ __forceinline__ void load_kv_tile(uint8_t* tile, const __nv_bfloat16* base, long long st, int row0, int nvalid,
-                                             int D) {
-  constexpr int UPR = DPAD / 8;
-  const uint32_t sbase = smem_u32(tile);
-  for (int i = threadIdx.x; i < kTile * UPR; i += 128) {
-    const int r = i / UPR, u = i - r * UPR;
-    const bool ok = r < nvalid && u * 8 < D;
-    cp_async16(sbase + sw128_offset(kTile, r, u), ok ? base + (long long)(row0 + r) * st + u * 8 : base, ok);
-  }
-}
-
 template <int DPAD, bool SELF>
 __global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(FwdArgs a) {
   constexpr int UPR = DPAD / 8;
   constexpr int TILE_BYTES = kTile * DPAD * 2;
   constexpr uint32_t TMEM_COLS = 256;
   // Dynamic shared memory only (no static), so that two CTAs of the D<=64 variant fit one SM:
-  // [0,1024) control block (barriers, TMEM slot, row ids), then the 1024-aligned operand tiles.
+  // [0,1024) control block (barriers, TMEM slot), then the 1024-aligned operand tiles.
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t& bar_s = *reinterpret_cast<uint64_t*>(smem);
   uint64_t& bar_o = *reinterpret_cast<uint64_t*>(smem + 8);
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + 16);
-  int* s_rowth = reinterpret_cast<int*>(smem + 64);  // [128] t*Hq+h of every row, -1 = padding row
+  uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + 32);  // [2] K/V stage (and, for stage 0's first fill, Q) has landed
   uint8_t* sQ = smem + 1024;
   uint8_t* sK = sQ + TILE_BYTES;      // 2 stages
   uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
@@ -84,6 +73,8 @@ __global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(Fwd
   // ---- decode the work item
   int kv_head, key_begin, key_end, nrows, n_kv_tiles;
   int row_id = -1;   // SELF: t*Hq+h of this thread's row; REMOTE: slot id
+  long long q_tile;  // packed query tile of this CTA
+  int kblock0;       // packed key block (= 128-token tile id) holding the chunk's first keys
   int tok = 0;       // SELF: packed token of this thread's row
   if (SELF) {
     const int w = blockIdx.x;
@@ -97,7 +88,8 @@ __global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(Fwd
     kv_head = h / pv.G;
     tok = tok0 + tid;
     if (tid < nrows) row_id = tok * pv.Hq + h;
-    s_rowth[tid] = tid < nrows ? tok * pv.Hq + h : -1;
+    q_tile = (long long)tile * pv.Hq + h;
+    kblock0 = tile - (tok0 - key_begin) / kTile;  // the tiles of a chunk have consecutive ids
   } else {
     const int E = pv.n_chunks * pv.Hkv;
     const int w = blockIdx.x;
@@ -115,13 +107,17 @@ __global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(Fwd
     nrows = min(kTile, end - start);
     key_begin = pv.chunk_start[c];
     key_end = pv.chunk_start[c + 1];
-    int th = -1;
     if (tid < nrows) {
       row_id = a.rowlist[start + tid];
-      th = row_id / pv.R;
-      if (row_id < 0 || th >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); row_id = -1; th = -1; }
+      if (row_id < 0 || row_id / pv.R >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); row_id = -1; }
     }
-    s_rowth[tid] = th;
+    q_tile = (long long)pv.n_qtiles * pv.Hq + w;
+    int qlo = 0, qhi = pv.n_qtiles - 1;  // first 128-token tile of chunk c (tile ids ascend with the chunk id)
+    while (qlo < qhi) {
+      const int mid = (qlo + qhi) >> 1;
+      if (pv.qtile_chunk[mid] < c) qlo = mid + 1; else qhi = mid;
+    }
+    kblock0 = qlo;
   }
   n_kv_tiles = (key_end - key_begin + kTile - 1) / kTile;
 
@@ -132,27 +128,23 @@ __global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(Fwd
   if (tid == 0) {
     mbar_init(&bar_s, 1);
     mbar_init(&bar_o, 1);
+    mbar_init(&bar_kv[0], 1);
+    mbar_init(&bar_kv[1], 1);
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
   __syncthreads();
 
-  // ---- Q tile and first K/V tile
-  {
-    const uint32_t sbase = smem_u32(sQ);
-    for (int i = tid; i < kTile * UPR; i += 128) {
-      const int r = i / UPR, u = i - r * UPR;
-      const int th = s_rowth[r];
-      const bool ok = th >= 0 && u * 8 < D;
-      const int t = th / pv.Hq, h = th - t * pv.Hq;
-      cp_async16(sbase + sw128_offset(kTile, r, u), ok ? a.q + (long long)t * pv.q_st + (long long)h * pv.q_sh + u * 8 : a.q, ok);
-    }
+  // ---- Q tile and first K/V tile: three bulk copies of packed tile images, issued by one thread
+  const uint8_t* kp = a.kpack + ((size_t)kblock0 * pv.Hkv + kv_head) * TILE_BYTES;
+  const uint8_t* vp = a.vpack + ((size_t)kblock0 * pv.Hkv + kv_head) * TILE_BYTES;
+  const size_t kv_step = (size_t)pv.Hkv * TILE_BYTES;  // next key block of the same kv head
+  if (tid == 0) {
+    mbar_arrive_expect_tx(&bar_kv[0], 3 * TILE_BYTES);
+    bulk_load(sQ, a.qpack + q_tile * TILE_BYTES, TILE_BYTES, &bar_kv[0]);
+    bulk_load(sK, kp, TILE_BYTES, &bar_kv[0]);
+    bulk_load(sV, vp, TILE_BYTES, &bar_kv[0]);
   }
-  const __nv_bfloat16* kbase = a.k + (long long)kv_head * pv.k_sh;
-  const __nv_bfloat16* vbase = a.v + (long long)kv_head * pv.v_sh;
-  load_kv_tile<DPAD>(sK, kbase, pv.k_st, key_begin, min(kTile, key_end - key_begin), D);
-  load_kv_tile<DPAD>(sV, vbase, pv.v_st, key_begin, min(kTile, key_end - key_begin), D);
-  cp_async_commit();
 
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
@@ -171,25 +163,20 @@ __global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(Fwd
   for (int j = 0; j < n_kv_tiles; ++j) {
     const int st = j & 1;
     const int k0 = key_begin + j * kTile;
-    // prefetch the next K/V tile into the other stage (its previous readers finished last iteration)
-    if (j + 1 < n_kv_tiles) {
-      const int nk0 = k0 + kTile;
-      load_kv_tile<DPAD>(sK + (st ^ 1) * TILE_BYTES, kbase, pv.k_st, nk0, min(kTile, key_end - nk0), D);
-      load_kv_tile<DPAD>(sV + (st ^ 1) * TILE_BYTES, vbase, pv.v_st, nk0, min(kTile, key_end - nk0), D);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    fence_async_smem();
-    __syncthreads();
     if (tid == 0) {
+      if (alive) alive = mbar_wait(&bar_kv[st], (j >> 1) & 1, a.status);
       tc_fence_after_sync();
 #pragma unroll
       for (int kk = 0; kk < DPAD; kk += 16)
         umma_ss(tmem, umma_desc_kmajor(smem_u32(sQ), kTile, kk), umma_desc_kmajor(smem_u32(sK + st * TILE_BYTES), kTile, kk),
                 idesc_s, kk > 0);
       umma_commit(&bar_s);
+      // prefetch the next K/V tile into the other stage: its readers (S and PV of tile j-1) are done
+      if (j + 1 < n_kv_tiles) {
+        mbar_arrive_expect_tx(&bar_kv[st ^ 1], 2 * TILE_BYTES);
+        bulk_load(sK + (st ^ 1) * TILE_BYTES, kp + (size_t)(j + 1) * kv_step, TILE_BYTES, &bar_kv[st ^ 1]);
+        bulk_load(sV + (st ^ 1) * TILE_BYTES, vp + (size_t)(j + 1) * kv_step, TILE_BYTES, &bar_kv[st ^ 1]);
+      }
     }
     if (alive) alive = mbar_wait(&bar_s, phase, a.status);
     tc_fence_after_sync();
@@ -353,7 +340,7 @@ extern "C" int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const
                                 unsigned* status, void* stream) {
   int rc = validate_desc(d);
   if (rc != MOBA_OK) return rc;
-  if (!q || !k || !v || !out || !lse || !status || (d->remote_k > 0 && (!route_state || !scratch))) return MOBA_ERR_INVALID;
+  if (!q || !k || !v || !out || !lse || !status || !route_state || (d->remote_k > 0 && !scratch)) return MOBA_ERR_INVALID;
   if (d->dim > 128) return MOBA_ERR_UNSUPPORTED;
   if (scratch_bytes < moba_prefill_fwd_scratch_bytes(d)) return MOBA_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
@@ -370,7 +357,14 @@ extern "C" int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const
   a.part_o = nullptr;
   a.part_lse = nullptr;
   const bool wide = d->dim > 64;
-  cudaError_t e = cudaSuccess;
+  cudaError_t e = launch_prefill_pack(*d, q, k, v, const_cast<void*>(route_state), status, st);
+  if (e != cudaSuccess) return MOBA_ERR_CUDA;
+  {
+    const PackState ps = carve_pack_state(*d, const_cast<void*>(route_state));
+    a.qpack = reinterpret_cast<const uint8_t*>(ps.qpack);
+    a.kpack = reinterpret_cast<const uint8_t*>(ps.kpack);
+    a.vpack = reinterpret_cast<const uint8_t*>(ps.vpack);
+  }
   if (d->remote_k > 0) {
     RouteState rs = carve_route_state(*d, const_cast<void*>(route_state));
     a.sel = rs.sel; a.rowlist = rs.rowlist; a.seg_base = rs.seg_base; a.tile_base = rs.tile_base;

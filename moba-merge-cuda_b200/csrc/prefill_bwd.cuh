@@ -32,8 +32,10 @@ struct BwdArgs {
   const int* kv_order;  // [num_qtiles] key blocks by decreasing expected work
   const int* tile_base; // [n_chunks*Hkv + 1] 128-row tiles of all experts before expert e
   // Packed query tiles (warp-specialised kernel only), see bwd_pack_kernel
-  const __nv_bfloat16* qpack;   // [tiles][128 x 64] swizzled shared-memory images of Q rows
-  const __nv_bfloat16* dopack;  // same for dO rows
+  const __nv_bfloat16* qpack;   // [tiles][128 x 64] swizzled shared-memory images of Q rows (from the forward)
+  const __nv_bfloat16* kpack;   // [key blocks * Hkv] images of the K and V key blocks (from the forward)
+  const __nv_bfloat16* vpack;
+  const __nv_bfloat16* dopack;  // images of the dO rows, tile for tile like qpack
   const int* rowpack;           // [tiles][128] t*Hq+h, -1 = padding row
   const float* lsepack;         // [tiles][128] LSE * log2(e), +inf for padding rows
   const float* deltapack;       // [tiles][128] delta / sqrt(D)
@@ -46,13 +48,7 @@ struct BwdArgs {
 
 // Warp-specialised backward for head_dim <= 64 (prefill_attn_bwd_ws.cu).
 cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st);
-// Number of packed tiles the warp-specialised kernel may address: every (query tile, head) pair plus an
-// upper bound of the expert tiles.
-inline long long bwd_pack_tiles(const moba_prefill_desc& d) {
-  const long long slots = (long long)d.total_tokens * d.hq * d.remote_k;
-  return (long long)d.num_qtiles * d.hq + slots / kTile + (long long)d.num_chunks * d.hkv;
-}
-cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* qpack, void* dopack, int* rowpack, float* lsepack,
-                            float* deltapack, cudaStream_t st);
+// Packs dO, LSE and delta of every query tile (rows as listed in a.rowpack).
+cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, float* lsepack, float* deltapack, cudaStream_t st);
 
 }  // namespace moba

@@ -55,7 +55,7 @@ struct RouteState {
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
-inline size_t route_state_bytes(const moba_prefill_desc& d) {
+inline size_t route_lists_bytes(const moba_prefill_desc& d) {
   size_t rows = (size_t)d.total_tokens * d.hq * (d.remote_k > 0 ? d.remote_k : 1);
   return align256(rows * 4) * 2 + align256(((size_t)d.num_chunks * d.hq + 1) * 4) +
          align256(((size_t)d.num_chunks * d.hkv + 1) * 4);
@@ -70,6 +70,46 @@ inline RouteState carve_route_state(const moba_prefill_desc& d, void* base) {
   s.tile_base = reinterpret_cast<int*>(p);
   return s;
 }
+
+// Packed operand tiles (second part of the state kept from forward to backward).  Gathering 128
+// scattered rows per tile with per-thread copies costs an attention kernel more issue time than the
+// math of the tile, so rows are gathered once into ready-made shared-memory images - 128 rows x DPAD
+// bf16 in the swizzled operand format, contiguous - which the kernels fetch with bulk copies.
+//   kpack, vpack [num_qtiles * Hkv]  key block (128 tokens of a chunk) x kv head
+//   qpack        [pack_q_tiles]      query tiles: (query tile qt, head h) -> qt*Hq + h, then the
+//                                    expert tiles: num_qtiles*Hq + tile_base[e] + i
+//   rowpack      [pack_q_tiles][128] t*Hq+h of every row, -1 = padding row
+struct PackState {
+  __nv_bfloat16* kpack;
+  __nv_bfloat16* vpack;
+  __nv_bfloat16* qpack;
+  int* rowpack;
+};
+inline int pack_dpad(const moba_prefill_desc& d) { return d.dim <= 64 ? 64 : 128; }
+inline long long pack_q_tiles(const moba_prefill_desc& d) {
+  const long long slots = (long long)d.total_tokens * d.hq * d.remote_k;
+  return (long long)d.num_qtiles * d.hq + slots / kTile + (d.remote_k > 0 ? (long long)d.num_chunks * d.hkv : 0);
+}
+inline size_t pack_state_bytes(const moba_prefill_desc& d) {
+  if (d.dim > 128) return 0;
+  const size_t tile = (size_t)kTile * pack_dpad(d) * 2;
+  return 2 * align256((size_t)d.num_qtiles * d.hkv * tile) + align256((size_t)pack_q_tiles(d) * tile) +
+         align256((size_t)pack_q_tiles(d) * kTile * 4);
+}
+inline size_t route_state_bytes(const moba_prefill_desc& d) { return route_lists_bytes(d) + pack_state_bytes(d); }
+inline PackState carve_pack_state(const moba_prefill_desc& d, void* base) {
+  const size_t tile = (size_t)kTile * pack_dpad(d) * 2;
+  char* p = static_cast<char*>(base) + route_lists_bytes(d);
+  PackState s;
+  s.kpack = reinterpret_cast<__nv_bfloat16*>(p); p += align256((size_t)d.num_qtiles * d.hkv * tile);
+  s.vpack = reinterpret_cast<__nv_bfloat16*>(p); p += align256((size_t)d.num_qtiles * d.hkv * tile);
+  s.qpack = reinterpret_cast<__nv_bfloat16*>(p); p += align256((size_t)pack_q_tiles(d) * tile);
+  s.rowpack = reinterpret_cast<int*>(p);
+  return s;
+}
+// Fills the pack state (prefill_pack.cu).
+cudaError_t launch_prefill_pack(const moba_prefill_desc& d, const void* q, const void* k, const void* v, void* route_state,
+                                unsigned* status, cudaStream_t st);
 
 int validate_desc(const moba_prefill_desc* d);
 

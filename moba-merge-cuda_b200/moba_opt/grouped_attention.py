@@ -163,7 +163,7 @@ class _MobaPrefill(torch.autograd.Function):
         lib = _ext.lib()
         q, k, v = _aligned(q), _aligned(k), _aligned(v)
         with torch.cuda.device(q.device):
-            state = route(q, k, plan, remote_k, flags) if remote_k > 0 else None
+            state = route(q, k, plan, remote_k, flags)
             if ROUTE_HOOK is not None and remote_k > 0:
                 _fire_hook(plan, state, q.shape[0], q.shape[1], remote_k)
             d = plan.desc(q, k, v, remote_k)
@@ -172,10 +172,10 @@ class _MobaPrefill(torch.autograd.Function):
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
             lse = torch.empty((q.shape[0], q.shape[1]), dtype=torch.float32, device=q.device)
             _ext.check(lib.moba_prefill_fwd(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                            state.data_ptr() if state is not None else None, scratch.data_ptr(), nbytes,
+                                            state.data_ptr(), scratch.data_ptr(), nbytes,
                                             out.data_ptr(), lse.data_ptr(), _status_word(q.device).data_ptr(),
                                             _stream(q.device)), "moba_prefill_fwd")
-        ctx.save_for_backward(q, k, v, out, lse, state if state is not None else torch.empty(0, device=q.device))
+        ctx.save_for_backward(q, k, v, out, lse, state)
         ctx.plan, ctx.remote_k = plan, remote_k
         ctx.mark_non_differentiable(lse)
         return out, lse
@@ -194,7 +194,7 @@ class _MobaPrefill(torch.autograd.Function):
             dk = torch.empty(k.shape, dtype=k.dtype, device=q.device)
             dv = torch.empty(v.shape, dtype=v.dtype, device=q.device)
             _ext.check(lib.moba_prefill_bwd(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                            lse.data_ptr(), d_out.data_ptr(), state.data_ptr() if remote_k > 0 else None,
+                                            lse.data_ptr(), d_out.data_ptr(), state.data_ptr(),
                                             scratch.data_ptr(), nbytes, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                             _status_word(q.device).data_ptr(), _stream(q.device)), "moba_prefill_bwd")
         return dq, dk, dv, None, None, None
