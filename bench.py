@@ -362,8 +362,8 @@ def run_ours(args):
                     clocks=clocks,
                     e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                              ms_per_step=None if ms_e2e is None else ms_e2e / e2e_steps),
-                    gpu_launches=10 * args.steps,
-                    roofline=dict(bound="tensor", kernel="attn_bwd_kernel<64>", achieved=achieved, peak=pk["tflops"],
+                    gpu_launches=13 * args.steps,  # route 5, pack 2, forward 2, backward 4 (memsets not counted)
+                    roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel", achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
                                   traffic=None, ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
         if dec is not None:

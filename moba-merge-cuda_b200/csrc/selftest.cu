@@ -4,6 +4,7 @@
 //   mode 0:  D[128,N]  = A[128,K] * B[N,K]^T     (both operands K-major;   S = Q K^T, dP = dO V^T)
 //   mode 1:  D[128,N]  = A[128,K] * B[K,N]       (A K-major, B MN-major;   O = P V,  dQ = dS K)
 //   mode 2:  D[128,N]  = A[K,128]^T * B[K,N]     (both operands MN-major;  dV = P^T dO, dK = dS^T Q)
+//   mode 3:  D[128,N]  = A[128,K] * B[K,N]       (A in tensor memory as packed bf16 pairs, B MN-major; O = P V)
 #include "moba_b200.h"
 #include "sm100.cuh"
 
@@ -36,9 +37,10 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(int mode, const __nv
     mbar_fence_init();
   }
   uint32_t ncols = 32;
-  while (ncols < (uint32_t)N) ncols <<= 1;
+  while (ncols < (uint32_t)N + (mode == 3 ? 128u : 0u)) ncols <<= 1;
+  const uint32_t a_col0 = (uint32_t)N;  // mode 3: the A operand sits after the accumulator columns
   if (warp == 0) tmem_alloc(&tmem_slot, ncols);
-  load_tile_sw128(tA, A, a_rows, a_cols, a_cols);
+  if (mode != 3) load_tile_sw128(tA, A, a_rows, a_cols, a_cols);
   load_tile_sw128(tB, B, b_rows, b_cols, b_cols);
   cp_async_commit();
   cp_async_wait<0>();
@@ -48,7 +50,26 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(int mode, const __nv
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
 
-  if (threadIdx.x == 0) {
+  if (mode == 3) {  // every thread writes its row of A into tensor memory, 64 elements per store
+    for (int c0 = 0; c0 < K; c0 += 64) {
+      uint32_t r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        r[j] = (c0 + 2 * j < K) ? *reinterpret_cast<const uint32_t*>(A + (size_t)threadIdx.x * K + c0 + 2 * j) : 0u;
+      tmem_st32(tmem + (uint32_t(warp * 32) << 16) + a_col0 + c0 / 2, r);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+  }
+
+  if (threadIdx.x == 0 && mode == 3) {
+    const uint32_t idesc = umma_idesc_bf16(128, N, 0u, 1u);
+    for (int k0 = 0; k0 < K; k0 += 16)
+      umma_ts(tmem, tmem + a_col0 + k0 / 2, umma_desc_mnmajor(smem_u32(tB), b_rows, k0, 0), idesc, k0 > 0);
+    umma_commit(&bar);
+  } else if (threadIdx.x == 0) {
     const uint32_t idesc = umma_idesc_bf16(128, N, mode == 2 ? 1u : 0u, mode == 0 ? 0u : 1u);
     for (int k0 = 0; k0 < K; k0 += 16) {
       uint64_t ad = (mode == 2) ? umma_desc_mnmajor(smem_u32(tA), a_rows, k0, 0) : umma_desc_kmajor(smem_u32(tA), a_rows, k0);
@@ -79,8 +100,9 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(int mode, const __nv
 
 extern "C" int moba_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int k, unsigned* status,
                                   void* stream) {
-  if (mode < 0 || mode > 2 || n < 16 || n > 256 || (n % 16) || k < 16 || k > 256 || (k % 16)) return MOBA_ERR_INVALID;
+  if (mode < 0 || mode > 3 || n < 16 || n > 256 || (n % 16) || k < 16 || k > 256 || (k % 16)) return MOBA_ERR_INVALID;
   if (mode != 2 && (k % 64)) return MOBA_ERR_INVALID;
+  if (mode == 3 && n > 128) return MOBA_ERR_INVALID;
   if (mode != 0 && (n % 64)) return MOBA_ERR_INVALID;
   size_t bytes = (size_t)128 * k * 2 + (size_t)n * k * 2 + 1024;
   cudaError_t e = cudaFuncSetAttribute(moba::umma_selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);

@@ -8,7 +8,7 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("mode,n,k", [(0, 128, 64), (0, 128, 128), (0, 256, 128), (1, 64, 128), (1, 128, 128),
-                                      (2, 64, 128), (2, 128, 128), (2, 128, 16)])
+                                      (2, 64, 128), (2, 128, 128), (2, 128, 16), (3, 64, 128), (3, 128, 128), (3, 64, 64)])
 def test_umma_selftest(mode, n, k):
     from moba_opt import _ext
     lib = _ext.lib()
@@ -17,7 +17,7 @@ def test_umma_selftest(mode, n, k):
     if mode == 0:
         a, b = torch.randn(128, k, device=dev, generator=gen).bfloat16(), torch.randn(n, k, device=dev, generator=gen).bfloat16()
         ref = a.float() @ b.float().T
-    elif mode == 1:
+    elif mode in (1, 3):
         a, b = torch.randn(128, k, device=dev, generator=gen).bfloat16(), torch.randn(k, n, device=dev, generator=gen).bfloat16()
         ref = a.float() @ b.float()
     else:
