@@ -40,7 +40,9 @@ const char* moba_status_string(int status);
  *   chunk_start[n+1], chunk_seq[n], chunk_local[n]   (chunking of src/moba_opt/diagnostic.py:30-80)
  *   qtile_chunk/qtile_tok0/qtile_local[num_qtiles]   128-token query tiles that never cross a chunk;
  *                                                    qtile_local = chunk_local * ceil(C/128) + tile in chunk
- *   self_order[num_qtiles]                           query tile ids by decreasing causal work
+ *   self_pairs[num_self_pairs]                       first tile of every pair of consecutive query tiles of a
+ *                                                    chunk (tiles 2i and 2i+1 of the chunk; the second may be
+ *                                                    missing), by decreasing causal work
  *   kv_order[num_qtiles]                             the same tiles seen as key blocks, earliest chunk of a
  *                                                    sequence first (those are routed to most often)
  * remote_k = min(topk-1, number of routable chunks); remote_k == 0 selects nothing (the caller
@@ -53,6 +55,7 @@ typedef struct moba_prefill_desc {
   int32_t total_tokens, num_seqs, hq, hkv, dim, chunk_size, remote_k;
   int32_t num_chunks, num_qtiles, max_tiles_per_seq, max_chunks_per_seq;
   int32_t flags; /* MOBA_ROUTE_BF16_MEANS: round chunk means to bf16 (route_precision='upstream') */
+  int32_t num_self_pairs, reserved0;
   int64_t q_stride_t, q_stride_h, k_stride_t, k_stride_h, v_stride_t, v_stride_h;
   const int32_t* cu_seqlens;
   const int32_t* chunk_start;
@@ -61,7 +64,7 @@ typedef struct moba_prefill_desc {
   const int32_t* qtile_chunk;
   const int32_t* qtile_tok0;
   const int32_t* qtile_local;
-  const int32_t* self_order;
+  const int32_t* self_pairs;
   const int32_t* kv_order;
 } moba_prefill_desc;
 

@@ -1,18 +1,24 @@
 // Prefill attention forward on tcgen05 tensor cores with the LSE merge fused into the epilogue.
 //
 // Work decomposition (KV-stationary experts as in the reference, src/moba_opt/grouped_attention.py:76-90):
-//   remote pass  one CTA per 128 gathered query rows of an expert (chunk, kv head): the rows of any
-//                query head of the group that selected the chunk attend the whole chunk; the
+//   remote pass  a work item is a pair of 128-row tiles of one expert (chunk, kv head): the gathered rows
+//                of any query head of the group that selected the chunk attend the whole chunk; the
 //                normalised partial output (bf16) and its log2-sum-exp go to the fixed slot of the
 //                (row, chunk) pair, so no atomics or tickets are needed and the merge order is fixed
-//   self pass    one CTA per (128-token query tile, query head): causal attention inside the own
-//                chunk, then the epilogue merges the row's remote partials with the global-softmax
-//                rule of src/moba_opt/ops/merge.cu:113-151 and writes O (bf16) and LSE (fp32) once
+//   self pass    a work item is a pair of consecutive 128-token query tiles of a chunk for one query
+//                head: causal attention inside the own chunk, then the epilogue merges the row's remote
+//                partials with the global-softmax rule of src/moba_opt/ops/merge.cu:113-151 and writes
+//                O (bf16) and LSE (fp32) once
 //
-// Per key tile (128 keys): S = Q K^T (tcgen05.mma, accumulator in TMEM) -> each thread owns one
-// query row, reads it with tcgen05.ld, applies masks and the online softmax in the exp2 domain,
-// writes P (bf16) into a swizzled shared-memory tile -> O' = P V (tcgen05.mma) -> O = O*alpha + O'.
-// K/V tiles are double-buffered with cp.async so the next tile's loads overlap this tile's math.
+// One persistent CTA per SM walks its share of the items.  Inside a CTA the two tiles of an item are
+// two "lanes" that share one stream of K/V tiles and are served by specialised warps:
+//   warps 0-3   softmax of lane 0 (a thread owns a query row)      warp 8   issues every tcgen05.mma
+//   warps 4-7   softmax of lane 1                                   warp 9   issues the bulk copies
+// Per key tile and lane: S = Q K^T (accumulator in TMEM) -> the row is read with tcgen05.ld, masked,
+// exponentiated in the exp2 domain against a running maximum that is only raised when it grew by more
+// than 2^8 (the rescale of O in TMEM is then done by the row's own thread), P is written back into
+// tensor memory over S as packed bf16 -> O += P V with P read from TMEM.  While one lane does its
+// softmax the tensor pipe works for the other, and the copy engine runs K/V tiles ahead of both.
 #include "prefill_common.cuh"
 #include "sm100.cuh"
 
@@ -31,9 +37,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct FwdArgs {
   PrefillView pv;
-  const __nv_bfloat16* q;
-  const __nv_bfloat16* k;
-  const __nv_bfloat16* v;
   const int* sel;
   const int* rowlist;
   const int* seg_base;
@@ -49,279 +52,463 @@ struct FwdArgs {
   float scale_log2;
 };
 
-template <int DPAD, bool SELF>
-__global__ void __launch_bounds__(128, (DPAD <= 64 ? 2 : 1)) attn_fwd_kernel(FwdArgs a) {
-  constexpr int UPR = DPAD / 8;
-  constexpr int TILE_BYTES = kTile * DPAD * 2;
-  constexpr uint32_t TMEM_COLS = 256;
-  // Dynamic shared memory only (no static), so that two CTAs of the D<=64 variant fit one SM:
-  // [0,1024) control block (barriers, TMEM slot), then the 1024-aligned operand tiles.
-  extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t& bar_s = *reinterpret_cast<uint64_t*>(smem);
-  uint64_t& bar_o = *reinterpret_cast<uint64_t*>(smem + 8);
-  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + 16);
-  uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + 32);  // [2] K/V stage (and, for stage 0's first fill, Q) has landed
-  uint8_t* sQ = smem + 1024;
-  uint8_t* sK = sQ + TILE_BYTES;      // 2 stages
-  uint8_t* sV = sK + 2 * TILE_BYTES;  // 2 stages
-  uint8_t* sP = sV + 2 * TILE_BYTES;  // 128 x 128 bf16
+// One work item as every role sees it.
+struct FwdItem {
+  long long q_tile[2];  // packed query tile of each lane
+  int n[2];             // key tiles the lane walks (0 = lane idle)
+  int rows[2];          // valid rows of the lane's tile
+  int first[2];         // SELF: first packed token of the tile; REMOTE: first rowlist entry of the tile
+  int kblock0;          // packed key block holding the chunk's first keys
+  int key_begin, key_end;
+  int g, h;             // kv head; SELF: query head
+};
 
+template <bool SELF>
+__device__ __forceinline__ bool fwd_decode_item(const FwdArgs& a, long long idx, FwdItem& it) {
   const PrefillView& pv = a.pv;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int D = pv.D;
-
-  // ---- decode the work item
-  int kv_head, key_begin, key_end, nrows, n_kv_tiles;
-  int row_id = -1;   // SELF: t*Hq+h of this thread's row; REMOTE: slot id
-  long long q_tile;  // packed query tile of this CTA
-  int kblock0;       // packed key block (= 128-token tile id) holding the chunk's first keys
-  int tok = 0;       // SELF: packed token of this thread's row
   if (SELF) {
-    const int w = blockIdx.x;
-    const int tile = pv.self_order[w / pv.Hq];
-    const int h = w - (w / pv.Hq) * pv.Hq;
-    const int c = pv.qtile_chunk[tile];
-    const int tok0 = pv.qtile_tok0[tile];
-    key_begin = pv.chunk_start[c];
-    nrows = min(kTile, pv.chunk_start[c + 1] - tok0);
-    key_end = tok0 + nrows;  // causal: no row of the tile sees keys past the tile's last token
-    kv_head = h / pv.G;
-    tok = tok0 + tid;
-    if (tid < nrows) row_id = tok * pv.Hq + h;
-    q_tile = (long long)tile * pv.Hq + h;
-    kblock0 = tile - (tok0 - key_begin) / kTile;  // the tiles of a chunk have consecutive ids
+    if (idx >= (long long)pv.n_self_pairs * pv.Hq) return false;
+    const int pair = (int)(idx / pv.Hq);
+    it.h = (int)(idx - (long long)pair * pv.Hq);
+    it.g = it.h / pv.G;
+    const int t0 = pv.self_pairs[pair];
+    const int c = pv.qtile_chunk[t0];
+    const int tok0 = pv.qtile_tok0[t0];
+    it.key_begin = pv.chunk_start[c];
+    it.key_end = pv.chunk_start[c + 1];
+    const int i0 = (tok0 - it.key_begin) / kTile;
+    it.kblock0 = t0 - i0;  // the tiles of a chunk have consecutive ids
+    it.first[0] = tok0;
+    it.first[1] = tok0 + kTile;
+    it.rows[0] = min(kTile, it.key_end - tok0);
+    it.rows[1] = max(0, min(kTile, it.key_end - tok0 - kTile));
+    it.n[0] = i0 + 1;
+    it.n[1] = it.rows[1] > 0 ? i0 + 2 : 0;
+    it.q_tile[0] = (long long)t0 * pv.Hq + it.h;
+    it.q_tile[1] = (long long)(t0 + 1) * pv.Hq + it.h;
+    return true;
   } else {
     const int E = pv.n_chunks * pv.Hkv;
-    const int w = blockIdx.x;
-    if (w >= a.tile_base[E]) return;
+    const long long w = idx * 2;
+    if (w >= a.tile_base[E]) return false;
     int lo = 0, hi = E;  // largest e with tile_base[e] <= w
     while (hi - lo > 1) {
       const int mid = (lo + hi) >> 1;
       if (a.tile_base[mid] <= w) lo = mid; else hi = mid;
     }
-    const int e = lo, i = w - a.tile_base[e];
+    const int e = lo, i = (int)(w - a.tile_base[e]);
     const int c = e / pv.Hkv;
-    kv_head = e - c * pv.Hkv;
-    const int start = a.seg_base[c * pv.Hq + kv_head * pv.G] + i * kTile;
-    const int end = a.seg_base[c * pv.Hq + (kv_head + 1) * pv.G];
-    nrows = min(kTile, end - start);
-    key_begin = pv.chunk_start[c];
-    key_end = pv.chunk_start[c + 1];
-    if (tid < nrows) {
-      row_id = a.rowlist[start + tid];
-      if (row_id < 0 || row_id / pv.R >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); row_id = -1; }
-    }
-    q_tile = (long long)pv.n_qtiles * pv.Hq + w;
+    it.g = e - c * pv.Hkv;
+    it.h = 0;
+    const int start = a.seg_base[c * pv.Hq + it.g * pv.G] + i * kTile;
+    const int end = a.seg_base[c * pv.Hq + (it.g + 1) * pv.G];
+    it.key_begin = pv.chunk_start[c];
+    it.key_end = pv.chunk_start[c + 1];
+    const int nt = (it.key_end - it.key_begin + kTile - 1) / kTile;
+    it.first[0] = start;
+    it.first[1] = start + kTile;
+    it.rows[0] = max(0, min(kTile, end - start));
+    it.rows[1] = max(0, min(kTile, end - start - kTile));
+    it.n[0] = it.rows[0] > 0 ? nt : 0;
+    it.n[1] = it.rows[1] > 0 ? nt : 0;
+    it.q_tile[0] = (long long)pv.n_qtiles * pv.Hq + w;
+    it.q_tile[1] = it.q_tile[0] + 1;
     int qlo = 0, qhi = pv.n_qtiles - 1;  // first 128-token tile of chunk c (tile ids ascend with the chunk id)
     while (qlo < qhi) {
       const int mid = (qlo + qhi) >> 1;
       if (pv.qtile_chunk[mid] < c) qlo = mid + 1; else qhi = mid;
     }
-    kblock0 = qlo;
+    it.kblock0 = qlo;
+    return true;
   }
-  n_kv_tiles = (key_end - key_begin + kTile - 1) / kTile;
+}
+
+// k-th item of this CTA: rounds alternate direction so that the sorted (heaviest first) item list is
+// dealt out evenly.
+__device__ __forceinline__ long long fwd_item_index(int k) {
+  const long long G = gridDim.x;
+  return (long long)k * G + ((k & 1) ? (G - 1 - blockIdx.x) : blockIdx.x);
+}
+
+constexpr int kFwdThreads = 384;  // warps 10 and 11 only complete the third warpgroup (register hand-over works per warpgroup)
+
+template <int DPAD>
+struct FwdCfg {
+  static constexpr int TILE_BYTES = kTile * DPAD * 2;
+  static constexpr int QBUFS = DPAD <= 64 ? 2 : 1;   // query tile buffers per lane
+  static constexpr int STAGES = DPAD <= 64 ? 4 : 2;  // K/V ring depth (a stage = K tile + V tile)
+  static constexpr int SMEM = 1024 + 2 * QBUFS * TILE_BYTES + STAGES * 2 * TILE_BYTES;
+  static constexpr uint32_t TMEM_COLS = 512;
+  static constexpr uint32_t COL_S = 0;    // + lane * 128; P overlays the first 64 columns
+  static constexpr uint32_t COL_O = 256;  // + lane * DPAD
+};
+
+struct FwdSmem {
+  uint64_t q_full[2][2], q_free[2][2];  // [lane][buffer]
+  uint64_t s_full[2], p_ready[2], o_full[2], o_free[2];
+  uint64_t kv_full[4], kv_free[4];
+  uint32_t tmem_slot;
+};
+static_assert(sizeof(FwdSmem) <= 1024, "control block must fit its reservation");
+
+template <int DPAD, bool SELF>
+__global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
+  using Cfg = FwdCfg<DPAD>;
+  constexpr int TILE_BYTES = Cfg::TILE_BYTES, QBUFS = Cfg::QBUFS, STAGES = Cfg::STAGES;
+  constexpr int UPR = DPAD / 8;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  FwdSmem& cb = *reinterpret_cast<FwdSmem*>(smem);
+  uint8_t* sQ = smem + 1024;                      // [lane][buffer]
+  uint8_t* sKV = sQ + 2 * QBUFS * TILE_BYTES;     // [stage]{K, V}
+
+  const PrefillView& pv = a.pv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane_id = tid & 31;
+  const int D = pv.D;
 
   if ((smem_u32(smem) & 1023u) != 0) {  // operand tiles need 1024-byte alignment for the swizzle
     if (tid == 0) atomicOr(a.status, kErrBadIndex);
     return;
   }
   if (tid == 0) {
-    mbar_init(&bar_s, 1);
-    mbar_init(&bar_o, 1);
-    mbar_init(&bar_kv[0], 1);
-    mbar_init(&bar_kv[1], 1);
+    for (int l = 0; l < 2; ++l) {
+      for (int b = 0; b < 2; ++b) { mbar_init(&cb.q_full[l][b], 1); mbar_init(&cb.q_free[l][b], 1); }
+      mbar_init(&cb.s_full[l], 1);
+      mbar_init(&cb.p_ready[l], 4);
+      mbar_init(&cb.o_full[l], 1);
+      mbar_init(&cb.o_free[l], 4);
+    }
+    for (int s = 0; s < 4; ++s) { mbar_init(&cb.kv_full[s], 1); mbar_init(&cb.kv_free[s], 1); }
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
+  if (warp == 0) tmem_alloc(&cb.tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before_sync();
   __syncthreads();
-
-  // ---- Q tile and first K/V tile: three bulk copies of packed tile images, issued by one thread
-  const uint8_t* kp = a.kpack + ((size_t)kblock0 * pv.Hkv + kv_head) * TILE_BYTES;
-  const uint8_t* vp = a.vpack + ((size_t)kblock0 * pv.Hkv + kv_head) * TILE_BYTES;
-  const size_t kv_step = (size_t)pv.Hkv * TILE_BYTES;  // next key block of the same kv head
-  if (tid == 0) {
-    mbar_arrive_expect_tx(&bar_kv[0], 3 * TILE_BYTES);
-    bulk_load(sQ, a.qpack + q_tile * TILE_BYTES, TILE_BYTES, &bar_kv[0]);
-    bulk_load(sK, kp, TILE_BYTES, &bar_kv[0]);
-    bulk_load(sV, vp, TILE_BYTES, &bar_kv[0]);
-  }
-
   tc_fence_after_sync();
-  const uint32_t tmem = tmem_slot;
-  const uint32_t tS = tmem + (uint32_t(warp * 32) << 16);
-  const uint32_t tO = tS + 128;
-  const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-  const uint32_t idesc_o = umma_idesc_bf16(128, DPAD, 0, 1);
-
-  float o_acc[DPAD];
-#pragma unroll
-  for (int d = 0; d < DPAD; ++d) o_acc[d] = 0.f;
-  float m_run = -INFINITY, l_run = 0.f;
-  uint32_t phase = 0;
+  const uint32_t tmem = cb.tmem_slot;
   bool alive = true;
 
-  for (int j = 0; j < n_kv_tiles; ++j) {
-    const int st = j & 1;
-    const int k0 = key_begin + j * kTile;
-    if (tid == 0) {
-      if (alive) alive = mbar_wait(&bar_kv[st], (j >> 1) & 1, a.status);
-      tc_fence_after_sync();
+  // The softmax warpgroups keep a whole row of S in registers; the third warpgroup gives them its share.
+  if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  if (warp == 9) {
+    // ================================================================== producer (one thread)
+    if (lane_id == 0) {
+      int use[2] = {0, 0};  // items each lane took part in so far
+      int kvt = 0;          // K/V tiles fetched so far
+      FwdItem it;
+      for (int k = 0; fwd_decode_item<SELF>(a, fwd_item_index(k), it); ++k) {
 #pragma unroll
-      for (int kk = 0; kk < DPAD; kk += 16)
-        umma_ss(tmem, umma_desc_kmajor(smem_u32(sQ), kTile, kk), umma_desc_kmajor(smem_u32(sK + st * TILE_BYTES), kTile, kk),
-                idesc_s, kk > 0);
-      umma_commit(&bar_s);
-      // prefetch the next K/V tile into the other stage: its readers (S and PV of tile j-1) are done
-      if (j + 1 < n_kv_tiles) {
-        mbar_arrive_expect_tx(&bar_kv[st ^ 1], 2 * TILE_BYTES);
-        bulk_load(sK + (st ^ 1) * TILE_BYTES, kp + (size_t)(j + 1) * kv_step, TILE_BYTES, &bar_kv[st ^ 1]);
-        bulk_load(sV + (st ^ 1) * TILE_BYTES, vp + (size_t)(j + 1) * kv_step, TILE_BYTES, &bar_kv[st ^ 1]);
-      }
-    }
-    if (alive) alive = mbar_wait(&bar_s, phase, a.status);
-    tc_fence_after_sync();
-
-    // ---- online softmax of this thread's row
-    int klimit = key_end - k0;                       // keys of the tile that exist
-    if (SELF) klimit = min(klimit, tok - k0 + 1);    // causal inside the own chunk
-    const bool need_mask = klimit < kTile;
-    float mx = -INFINITY;
-#pragma unroll
-    for (int pc = 0; pc < 4; ++pc) {
-      uint32_t r[32];
-      tmem_ld32(tS + pc * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float s = __uint_as_float(r[i]);
-        if (need_mask && pc * 32 + i >= klimit) s = -INFINITY;
-        mx = fmaxf(mx, s);
-      }
-    }
-    float m_new = fmaxf(m_run, mx * a.scale_log2);
-    if (m_new == -INFINITY) m_new = 0.f;  // row with no visible key in this tile (padding rows only)
-    const float alpha = fast_exp2(m_run - m_new);
-    float l_tile = 0.f;
-#pragma unroll
-    for (int pc = 0; pc < 4; ++pc) {
-      uint32_t r[32];
-      tmem_ld32(tS + pc * 32, r);
-      tmem_ld_wait();
-      uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), a.scale_log2, -m_new));
-        float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), a.scale_log2, -m_new));
-        if (need_mask) {
-          if (pc * 32 + i >= klimit) p0 = 0.f;
-          if (pc * 32 + i + 1 >= klimit) p1 = 0.f;
+        for (int l = 0; l < 2; ++l) {
+          if (it.n[l] == 0) continue;
+          const int u = use[l]++, b = u % QBUFS;
+          if (u >= QBUFS && alive) alive = mbar_wait(&cb.q_free[l][b], ((u / QBUFS) - 1) & 1, a.status);
+          mbar_arrive_expect_tx(&cb.q_full[l][b], TILE_BYTES);
+          bulk_load(sQ + (l * QBUFS + b) * TILE_BYTES, a.qpack + it.q_tile[l] * TILE_BYTES, TILE_BYTES, &cb.q_full[l][b]);
         }
-        l_tile += p0 + p1;
-        pk[i >> 1] = pack_bf16(p0, p1);
+        const int n = max(it.n[0], it.n[1]);
+        const size_t kv_step = (size_t)pv.Hkv * TILE_BYTES;  // next key block of the same kv head
+        const size_t kv0 = ((size_t)it.kblock0 * pv.Hkv + it.g) * TILE_BYTES;
+        for (int j = 0; j < n; ++j, ++kvt) {
+          const int s = kvt % STAGES;
+          if (kvt >= STAGES && alive) alive = mbar_wait(&cb.kv_free[s], ((kvt / STAGES) - 1) & 1, a.status);
+          mbar_arrive_expect_tx(&cb.kv_full[s], 2 * TILE_BYTES);
+          bulk_load(sKV + s * 2 * TILE_BYTES, a.kpack + kv0 + j * kv_step, TILE_BYTES, &cb.kv_full[s]);
+          bulk_load(sKV + s * 2 * TILE_BYTES + TILE_BYTES, a.vpack + kv0 + j * kv_step, TILE_BYTES, &cb.kv_full[s]);
+        }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        *reinterpret_cast<uint4*>(sP + sw128_offset(kTile, tid, pc * 4 + u)) =
-            make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+      // no copy may be in flight when the CTA exits: the last stages are consumed by the MMA warp in
+      // normal operation; after a timeout wait for them here
+      if (!alive)
+        for (int s = 0; s < STAGES && s < kvt; ++s) mbar_wait(&cb.kv_full[(kvt - 1 - s) % STAGES], (((kvt - 1 - s) / STAGES)) & 1, nullptr);
     }
-    l_run = l_run * alpha + l_tile;
-    m_run = m_new;
-
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
+  } else if (warp == 8) {
+    // ================================================================== MMA issue (one thread)
+    if (lane_id == 0) {
+      const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_o = umma_idesc_bf16(128, DPAD, 0, 1);
+      int use[2] = {0, 0};
+      int tc[2] = {0, 0};  // tiles each lane has been issued so far (phase of s_full / p_ready)
+      int kvt0 = 0;        // K/V tiles of all earlier items
+      FwdItem it;
+      for (int k = 0; fwd_decode_item<SELF>(a, fwd_item_index(k), it); ++k) {
+        const int n = max(it.n[0], it.n[1]);
+        int js[2] = {0, 0}, jp[2] = {0, 0}, rel = 0;
+        int qb[2], qph[2];
 #pragma unroll
-      for (int kk = 0; kk < kTile; kk += 16)
-        umma_ss(tmem + 128, umma_desc_kmajor(smem_u32(sP), kTile, kk),
-                umma_desc_mnmajor(smem_u32(sV + st * TILE_BYTES), kTile, kk, 0), idesc_o, kk > 0);
-      umma_commit(&bar_o);
-    }
-    if (alive) alive = mbar_wait(&bar_o, phase, a.status);
-    tc_fence_after_sync();
-    phase ^= 1;
+        for (int l = 0; l < 2; ++l) { qb[l] = use[l] % QBUFS; qph[l] = (use[l] / QBUFS) & 1; }
+        const long long t_start = clock64();
+        while (rel < n) {
+          bool progressed = false;
 #pragma unroll
-    for (int pc = 0; pc < DPAD / 32; ++pc) {
-      uint32_t r[32];
-      tmem_ld32(tO + pc * 32, r);
-      tmem_ld_wait();
+          for (int l = 0; l < 2; ++l) {
+            const uint32_t tS = tmem + Cfg::COL_S + l * 128, tO = tmem + Cfg::COL_O + l * DPAD;
+            // O += P V of tile jp: P of the tile is in tensor memory, V in its ring stage
+            if (jp[l] < js[l] && (!alive || (mbar_test(&cb.p_ready[l], (tc[l] + jp[l]) & 1) &&
+                                              (jp[l] > 0 || use[l] == 0 || mbar_test(&cb.o_free[l], (use[l] - 1) & 1))))) {
+              tc_fence_after_sync();
+              const int s = (kvt0 + jp[l]) % STAGES;
+              const uint32_t v_addr = smem_u32(sKV + s * 2 * TILE_BYTES + TILE_BYTES);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) o_acc[pc * 32 + i] = fmaf(o_acc[pc * 32 + i], alpha, __uint_as_float(r[i]));
-    }
-    tc_fence_before_sync();
-  }
-
-  // ---- epilogue
-  if (row_id >= 0 && alive) {
-    if (!SELF) {
-      const float inv = 1.f / l_run;
-      __nv_bfloat16* dst = a.part_o + (long long)row_id * D;
+              for (int kk = 0; kk < kTile; kk += 16)
+                umma_ts(tO, tS + kk / 2, umma_desc_mnmajor(v_addr, kTile, kk, 0), idesc_o, (jp[l] > 0) | (kk > 0));
+              umma_commit(&cb.o_full[l]);
+              ++jp[l];
+              progressed = true;
+            }
+            // S = Q K^T of tile js: only after P V of the previous tile was issued (P lives in S's columns)
+            if (js[l] < it.n[l] && js[l] == jp[l] &&
+                (!alive || (mbar_test(&cb.kv_full[(kvt0 + js[l]) % STAGES], ((kvt0 + js[l]) / STAGES) & 1) &&
+                            (js[l] > 0 || mbar_test(&cb.q_full[l][qb[l]], qph[l]))))) {
+              tc_fence_after_sync();
+              const int s = (kvt0 + js[l]) % STAGES;
+              const uint32_t q_addr = smem_u32(sQ + (l * QBUFS + qb[l]) * TILE_BYTES);
+              const uint32_t k_addr = smem_u32(sKV + s * 2 * TILE_BYTES);
 #pragma unroll
-      for (int u = 0; u < UPR; ++u) {
-        if (u * 8 < D)
-          *reinterpret_cast<uint4*>(dst + u * 8) =
-              make_uint4(pack_bf16(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack_bf16(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
-                         pack_bf16(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack_bf16(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
-      }
-      a.part_lse[row_id] = m_run + log2f(l_run);
-    } else {
-      // global-softmax merge of the self branch with the row's remote partials (fixed slot order)
-      const int R = pv.R;
-      const float l2_self = m_run + log2f(l_run);
-      float big = l2_self;
-      const int* mysel = a.sel + (long long)row_id * R;
-      int nsel = 0;
-      for (int s = 0; s < R; ++s) {
-        if (mysel[s] < 0) break;
-        big = fmaxf(big, a.part_lse[(long long)row_id * R + s]);
-        ++nsel;
-      }
-      const float w_self = fast_exp2(l2_self - big);
-      float z = w_self;
-      const float f_self = w_self / l_run;
-#pragma unroll
-      for (int d = 0; d < DPAD; ++d) o_acc[d] *= f_self;
-      for (int s = 0; s < nsel; ++s) {
-        const long long slot = (long long)row_id * R + s;
-        const float w = fast_exp2(a.part_lse[slot] - big);
-        z += w;
-        const __nv_bfloat16* src = a.part_o + slot * D;
-#pragma unroll
-        for (int u = 0; u < UPR; ++u) {
-          if (u * 8 < D) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + u * 8);
-            const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              o_acc[u * 8 + 2 * i] = fmaf(w, __uint_as_float(wv[i] << 16), o_acc[u * 8 + 2 * i]);
-              o_acc[u * 8 + 2 * i + 1] = fmaf(w, __uint_as_float(wv[i] & 0xFFFF0000u), o_acc[u * 8 + 2 * i + 1]);
+              for (int kk = 0; kk < DPAD; kk += 16)
+                umma_ss(tS, umma_desc_kmajor(q_addr, kTile, kk), umma_desc_kmajor(k_addr, kTile, kk), idesc_s, kk > 0);
+              umma_commit(&cb.s_full[l]);
+              if (js[l] == it.n[l] - 1) umma_commit(&cb.q_free[l][qb[l]]);
+              ++js[l];
+              progressed = true;
+            }
+          }
+          // a ring stage is free once every lane that walks it has issued its P V
+          while (rel < n && (it.n[0] <= rel || jp[0] > rel) && (it.n[1] <= rel || jp[1] > rel)) {
+            umma_commit(&cb.kv_free[(kvt0 + rel) % STAGES]);
+            ++rel;
+            progressed = true;
+          }
+          if (!progressed) {
+            __nanosleep(20);
+            if (alive && clock64() - t_start > 4000000000ll) {
+              atomicOr(a.status, kErrBarrierTimeout);
+              alive = false;
             }
           }
         }
-      }
-      const float inv = 1.f / z;
-      __nv_bfloat16* dst = a.out + (long long)row_id * D;
 #pragma unroll
-      for (int u = 0; u < UPR; ++u) {
-        if (u * 8 < D)
-          *reinterpret_cast<uint4*>(dst + u * 8) =
-              make_uint4(pack_bf16(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack_bf16(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
-                         pack_bf16(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack_bf16(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
+        for (int l = 0; l < 2; ++l)
+          if (it.n[l] > 0) { ++use[l]; tc[l] += it.n[l]; }
+        kvt0 += n;
       }
-      a.lse[row_id] = (big + log2f(z)) * 0.6931471805599453f;
     }
   }
+  } else {
+    // ================================================================== softmax + epilogue, one lane per warpgroup
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    const int l = warp >> 2;
+    const int row = tid & 127;
+    const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_off + Cfg::COL_S + l * 128;
+    const uint32_t tO = tmem + lane_off + Cfg::COL_O + l * DPAD;
+    int tc = 0;  // tiles this lane has processed
+    FwdItem it;
+    for (int k = 0; fwd_decode_item<SELF>(a, fwd_item_index(k), it); ++k) {
+      const int n = it.n[l];
+      if (n == 0) continue;
+      int row_id = -1;  // SELF: t*Hq+h of this thread's row; REMOTE: slot id
+      const int tok = it.first[l] + row;
+      if (row < it.rows[l]) {
+        if (SELF) {
+          row_id = tok * pv.Hq + it.h;
+        } else {
+          row_id = a.rowlist[it.first[l] + row];
+          if (row_id < 0 || row_id / pv.R >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); row_id = -1; }
+        }
+      }
+      const int key_end = SELF ? it.first[l] + it.rows[l] : it.key_end;  // causal: nothing past the tile's last token
+      float m_used = 0.f, l_run = 0.f;
+      for (int j = 0; j < n; ++j, ++tc) {
+        const int k0 = it.key_begin + j * kTile;
+        int klimit = key_end - k0;                     // keys of the tile that exist
+        if (SELF) klimit = min(klimit, tok - k0 + 1);  // causal inside the own chunk
+        const bool need_mask = __any_sync(0xFFFFFFFFu, klimit < kTile);
+        if (alive) alive = mbar_wait(&cb.s_full[l], tc & 1, a.status);
+        tc_fence_after_sync();
+        uint32_t s0[32], s1[32], s2[32], s3[32];
+        tmem_ld32(tS, s0);
+        tmem_ld32(tS + 32, s1);
+        tmem_ld32(tS + 64, s2);
+        tmem_ld32(tS + 96, s3);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (i >= klimit) s0[i] = 0xFF800000u;
+            if (32 + i >= klimit) s1[i] = 0xFF800000u;
+            if (64 + i >= klimit) s2[i] = 0xFF800000u;
+            if (96 + i >= klimit) s3[i] = 0xFF800000u;
+          }
+        }
+        float mx0 = __uint_as_float(s0[0]), mx1 = __uint_as_float(s1[0]), mx2 = __uint_as_float(s2[0]), mx3 = __uint_as_float(s3[0]);
+#pragma unroll
+        for (int i = 1; i < 32; ++i) {
+          mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
+          mx2 = fmaxf(mx2, __uint_as_float(s2[i]));
+          mx3 = fmaxf(mx3, __uint_as_float(s3[i]));
+        }
+        const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;
+        // The maximum in use is raised only when the row's maximum outgrew it by 2^8; P stays below 2^8.
+        float alpha = 1.f;
+        bool raise = false;
+        if (j == 0) {
+          m_used = m_tile;
+        } else if (m_tile > m_used + 8.f) {
+          alpha = fast_exp2(m_used - m_tile);
+          m_used = m_tile;
+          raise = true;
+        }
+        if (j > 0 && __any_sync(0xFFFFFFFFu, raise)) {
+          // rescale the row's O in tensor memory; P V of the previous tile must have landed
+          if (alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
+          tc_fence_after_sync();
+#pragma unroll
+          for (int pc = 0; pc < DPAD / 32; ++pc) {
+            uint32_t o[32];
+            tmem_ld32(tO + pc * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + pc * 32, o);
+          }
+          l_run *= alpha;
+        }
+        float sum0 = 0.f, sum1 = 0.f;
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s0[i]), a.scale_log2, -m_used));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s0[i + 1]), a.scale_log2, -m_used));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(s1[i]), a.scale_log2, -m_used));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(s1[i + 1]), a.scale_log2, -m_used));
+          sum0 += p0 + p1;
+          sum1 += p2 + p3;
+          pk[i >> 1] = pack_bf16(p0, p1);
+          pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+        }
+        tmem_st32(tS, pk);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s2[i]), a.scale_log2, -m_used));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s2[i + 1]), a.scale_log2, -m_used));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(s3[i]), a.scale_log2, -m_used));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(s3[i + 1]), a.scale_log2, -m_used));
+          sum0 += p0 + p1;
+          sum1 += p2 + p3;
+          pk[i >> 1] = pack_bf16(p0, p1);
+          pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+        }
+        tmem_st32(tS + 32, pk);
+        l_run += sum0 + sum1;
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane_id == 0) mbar_arrive(&cb.p_ready[l]);
+      }
+
+      // ---- epilogue: O of the row leaves tensor memory, then the lane's accumulator is free again
+      if (alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
+      tc_fence_after_sync();
+      float o_acc[DPAD];
+#pragma unroll
+      for (int pc = 0; pc < DPAD / 32; ++pc) {
+        uint32_t o[32];
+        tmem_ld32(tO + pc * 32, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[pc * 32 + i] = __uint_as_float(o[i]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane_id == 0) mbar_arrive(&cb.o_free[l]);
+      if (row_id < 0 || !alive) continue;
+      if (!SELF) {
+        const float inv = 1.f / l_run;
+        __nv_bfloat16* dst = a.part_o + (long long)row_id * D;
+#pragma unroll
+        for (int u = 0; u < UPR; ++u) {
+          if (u * 8 < D)
+            *reinterpret_cast<uint4*>(dst + u * 8) =
+                make_uint4(pack_bf16(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack_bf16(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
+                           pack_bf16(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack_bf16(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
+        }
+        a.part_lse[row_id] = m_used + log2f(l_run);
+      } else {
+        // global-softmax merge of the self branch with the row's remote partials (fixed slot order)
+        const int R = pv.R;
+        const float l2_self = m_used + log2f(l_run);
+        float big = l2_self;
+        const int* mysel = a.sel + (long long)row_id * R;
+        int nsel = 0;
+        for (int s = 0; s < R; ++s) {
+          if (mysel[s] < 0) break;
+          big = fmaxf(big, a.part_lse[(long long)row_id * R + s]);
+          ++nsel;
+        }
+        const float w_self = fast_exp2(l2_self - big);
+        float z = w_self;
+        const float f_self = w_self / l_run;
+#pragma unroll
+        for (int d = 0; d < DPAD; ++d) o_acc[d] *= f_self;
+        for (int s = 0; s < nsel; ++s) {
+          const long long slot = (long long)row_id * R + s;
+          const float w = fast_exp2(a.part_lse[slot] - big);
+          z += w;
+          const __nv_bfloat16* src = a.part_o + slot * D;
+#pragma unroll
+          for (int u = 0; u < UPR; ++u) {
+            if (u * 8 < D) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(src + u * 8);
+              const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                o_acc[u * 8 + 2 * i] = fmaf(w, __uint_as_float(wv[i] << 16), o_acc[u * 8 + 2 * i]);
+                o_acc[u * 8 + 2 * i + 1] = fmaf(w, __uint_as_float(wv[i] & 0xFFFF0000u), o_acc[u * 8 + 2 * i + 1]);
+              }
+            }
+          }
+        }
+        const float inv = 1.f / z;
+        __nv_bfloat16* dst = a.out + (long long)row_id * D;
+#pragma unroll
+        for (int u = 0; u < UPR; ++u) {
+          if (u * 8 < D)
+            *reinterpret_cast<uint4*>(dst + u * 8) =
+                make_uint4(pack_bf16(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack_bf16(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
+                           pack_bf16(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack_bf16(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
+        }
+        a.lse[row_id] = (big + log2f(z)) * 0.6931471805599453f;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_free(tmem, TMEM_COLS);
+  if (warp == 0) tmem_free(tmem, Cfg::TMEM_COLS);
+}
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
 
 template <int DPAD, bool SELF>
-static cudaError_t launch_fwd(const FwdArgs& a, int grid, cudaStream_t st) {
-  const size_t smem = 1024 + (size_t)kTile * DPAD * 2 * 5 + (size_t)kTile * kTile * 2;
-  cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<DPAD, SELF>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static cudaError_t launch_fwd(const FwdArgs& a, long long items, cudaStream_t st) {
+  const int smem = FwdCfg<DPAD>::SMEM;
+  cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<DPAD, SELF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
-  attn_fwd_kernel<DPAD, SELF><<<grid, 128, smem, st>>>(a);
+  const int sms = sm_count();
+  if (sms <= 0) return cudaErrorUnknown;
+  const int grid = (int)(items < sms ? (items < 1 ? 1 : items) : sms);
+  attn_fwd_kernel<DPAD, SELF><<<grid, kFwdThreads, smem, st>>>(a);
   return cudaGetLastError();
 }
 
@@ -346,9 +533,6 @@ extern "C" int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const
   cudaStream_t st = (cudaStream_t)stream;
   FwdArgs a;
   a.pv = make_view(*d);
-  a.q = static_cast<const __nv_bfloat16*>(q);
-  a.k = static_cast<const __nv_bfloat16*>(k);
-  a.v = static_cast<const __nv_bfloat16*>(v);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.lse = lse;
   a.status = status;
@@ -371,16 +555,16 @@ extern "C" int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const
     const size_t slots = (size_t)d->total_tokens * d->hq * d->remote_k;
     a.part_o = static_cast<__nv_bfloat16*>(scratch);
     a.part_lse = reinterpret_cast<float*>(static_cast<char*>(scratch) + align256(slots * d->dim * 2));
-    // every expert has at most ceil(rows/128) tiles; the sum is bounded by slots/128 + experts
-    const long long bound = (long long)(slots / kTile) + (long long)d->num_chunks * d->hkv;
+    // every expert has at most ceil(rows/128) + 1 tiles; half of the bound is the number of tile pairs
+    const long long bound = ((long long)(slots / kTile) + 2ll * d->num_chunks * d->hkv + 1) / 2;
     prof_begin(kProfFwdRemote, st);
-    e = wide ? launch_fwd<128, false>(a, (int)bound, st) : launch_fwd<64, false>(a, (int)bound, st);
+    e = wide ? launch_fwd<128, false>(a, bound, st) : launch_fwd<64, false>(a, bound, st);
     prof_end(kProfFwdRemote, st);
     if (e != cudaSuccess) return MOBA_ERR_CUDA;
   }
-  const int grid = d->num_qtiles * d->hq;
+  const long long items = (long long)d->num_self_pairs * d->hq;
   prof_begin(kProfFwdSelf, st);
-  e = wide ? launch_fwd<128, true>(a, grid, st) : launch_fwd<64, true>(a, grid, st);
+  e = wide ? launch_fwd<128, true>(a, items, st) : launch_fwd<64, true>(a, items, st);
   prof_end(kProfFwdSelf, st);
   return e == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

@@ -14,7 +14,7 @@ constexpr int kTile = 128;  // query rows per tile and keys per tile
 // Plain-value copy of moba_prefill_desc with typed pointers, passed to kernels by value.
 struct PrefillView {
   int T, B, Hq, Hkv, G, D, C, R;
-  int n_chunks, n_qtiles, max_tiles_per_seq;
+  int n_chunks, n_qtiles, max_tiles_per_seq, n_self_pairs;
   long long q_st, q_sh, k_st, k_sh, v_st, v_sh;  // element strides of token and head
   const int* cu_seqlens;   // [B+1]
   const int* chunk_start;  // [n_chunks+1] first packed token of every chunk
@@ -23,7 +23,7 @@ struct PrefillView {
   const int* qtile_chunk;  // [n_qtiles] chunk a 128-token query tile lies in
   const int* qtile_tok0;   // [n_qtiles] first packed token of the tile
   const int* qtile_local;  // [n_qtiles] index of the tile inside its sequence
-  const int* self_order;   // [n_qtiles] query tiles ordered by decreasing causal work
+  const int* self_pairs;   // [n_self_pairs] first tile of each pair of query tiles of a chunk, by decreasing causal work
   const int* kv_order;     // [n_qtiles] key blocks ordered by decreasing expected backward work
 };
 
@@ -31,12 +31,12 @@ inline PrefillView make_view(const moba_prefill_desc& d) {
   PrefillView v;
   v.T = d.total_tokens; v.B = d.num_seqs; v.Hq = d.hq; v.Hkv = d.hkv; v.G = d.hq / d.hkv; v.D = d.dim;
   v.C = d.chunk_size; v.R = d.remote_k; v.n_chunks = d.num_chunks; v.n_qtiles = d.num_qtiles;
-  v.max_tiles_per_seq = d.max_tiles_per_seq;
+  v.max_tiles_per_seq = d.max_tiles_per_seq; v.n_self_pairs = d.num_self_pairs;
   v.q_st = d.q_stride_t; v.q_sh = d.q_stride_h; v.k_st = d.k_stride_t; v.k_sh = d.k_stride_h;
   v.v_st = d.v_stride_t; v.v_sh = d.v_stride_h;
   v.cu_seqlens = d.cu_seqlens; v.chunk_start = d.chunk_start; v.chunk_seq = d.chunk_seq;
   v.chunk_local = d.chunk_local; v.qtile_chunk = d.qtile_chunk; v.qtile_tok0 = d.qtile_tok0;
-  v.qtile_local = d.qtile_local; v.self_order = d.self_order; v.kv_order = d.kv_order;
+  v.qtile_local = d.qtile_local; v.self_pairs = d.self_pairs; v.kv_order = d.kv_order;
   return v;
 }
 
@@ -45,7 +45,9 @@ inline PrefillView make_view(const moba_prefill_desc& d) {
 //   rowlist    [T*Hq*R]   int32   for every expert (chunk, kv head) the slot ids (t*Hq+h)*R+s of
 //                                 the rows that chose it, ordered by (head in group, token)
 //   seg_base   [n_chunks*Hq + 1]  start of the (chunk, query head) segment inside rowlist
-//   tile_base  [n_chunks*Hkv + 1] number of 128-row tiles of all experts before expert e
+//   tile_base  [n_chunks*Hkv + 1] number of 128-row tiles of all experts before expert e; every expert's
+//                                 count is rounded up to even (the forward works on pairs of tiles), the
+//                                 padding tile has no rows
 struct RouteState {
   int* sel;
   int* rowlist;
@@ -88,7 +90,7 @@ struct PackState {
 inline int pack_dpad(const moba_prefill_desc& d) { return d.dim <= 64 ? 64 : 128; }
 inline long long pack_q_tiles(const moba_prefill_desc& d) {
   const long long slots = (long long)d.total_tokens * d.hq * d.remote_k;
-  return (long long)d.num_qtiles * d.hq + slots / kTile + (d.remote_k > 0 ? (long long)d.num_chunks * d.hkv : 0);
+  return (long long)d.num_qtiles * d.hq + slots / kTile + (d.remote_k > 0 ? 2ll * d.num_chunks * d.hkv : 0);
 }
 inline size_t pack_state_bytes(const moba_prefill_desc& d) {
   if (d.dim > 128) return 0;

@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(128) segment_scan_kernel(PrefillView pv, int* 
 
 // --------------------------------------------------------------------------- 4. bases
 // Single block.  seg_base[i] = sum of seg_count[<i]; tile_base[e] = sum over experts < e of
-// ceil(rows(e) / 128), with expert e = chunk * Hkv + kv head.
+// ceil(rows(e) / 128) rounded up to even, with expert e = chunk * Hkv + kv head.
 __global__ void __launch_bounds__(1024) plan_kernel(PrefillView pv, const int* __restrict__ seg_count,
                                                     int* __restrict__ seg_base, int* __restrict__ tile_base) {
   __shared__ int s_part[1024];
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(PrefillView pv, const int* _
       if (pass == 0) return seg_count[i];
       const int cidx = i / pv.Hkv, g = i - cidx * pv.Hkv;
       const int rows = seg_base[cidx * pv.Hq + (g + 1) * pv.G] - seg_base[cidx * pv.Hq + g * pv.G];
-      return (rows + kTile - 1) / kTile;
+      return ((rows + kTile - 1) / kTile + 1) & ~1;  // even: the forward pairs tiles
     };
     int sum = 0;
     for (int i = lo; i < hi; ++i) sum += value(i);
@@ -284,7 +284,7 @@ int validate_desc(const moba_prefill_desc* d) {
   if ((long long)d->total_tokens * d->hq * (d->remote_k > 0 ? d->remote_k : 1) >= (1ll << 31)) return MOBA_ERR_UNSUPPORTED;
   if (d->max_chunks_per_seq > 4096) return MOBA_ERR_UNSUPPORTED;
   if (!d->cu_seqlens || !d->chunk_start || !d->chunk_seq || !d->chunk_local || !d->qtile_chunk || !d->qtile_tok0 ||
-      !d->qtile_local || !d->self_order)
+      !d->qtile_local || !d->self_pairs || d->num_self_pairs < 1 || d->num_self_pairs > d->num_qtiles)
     return MOBA_ERR_INVALID;
   return MOBA_OK;
 }

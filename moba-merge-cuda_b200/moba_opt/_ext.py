@@ -13,10 +13,10 @@ class PrefillDesc(ctypes.Structure):
     """Mirror of moba_prefill_desc in include/moba_b200.h."""
     _fields_ = ([(n, c_i32) for n in ("total_tokens", "num_seqs", "hq", "hkv", "dim", "chunk_size", "remote_k",
                                       "num_chunks", "num_qtiles", "max_tiles_per_seq", "max_chunks_per_seq")]
-                + [("flags", c_i32)]
+                + [("flags", c_i32), ("num_self_pairs", c_i32), ("reserved0", c_i32)]
                 + [(n, c_i64) for n in ("q_stride_t", "q_stride_h", "k_stride_t", "k_stride_h", "v_stride_t", "v_stride_h")]
                 + [(n, c_vp) for n in ("cu_seqlens", "chunk_start", "chunk_seq", "chunk_local", "qtile_chunk",
-                                       "qtile_tok0", "qtile_local", "self_order", "kv_order")])
+                                       "qtile_tok0", "qtile_local", "self_pairs", "kv_order")])
 
 
 def lib():

@@ -61,7 +61,14 @@ class PrefillPlan:
         self.max_chunks_per_seq = int(nchunk.max())
         self.max_tiles_per_seq = int(max(qt_local) + 1)
         self.num_routable = len(filtered)
-        order = np.argsort(-np.asarray(qt_cost), kind="stable")
+        cost = np.asarray(qt_cost)
+        leaders = np.flatnonzero(cost % 2 == 0)  # tiles 2i, 2i+1 of a chunk form a pair; 2i+1 may be missing
+        has_partner = np.zeros(len(leaders), dtype=bool)
+        nxt = leaders + 1
+        ok = nxt < len(cost)
+        has_partner[ok] = (np.asarray(qt_chunk)[nxt[ok]] == np.asarray(qt_chunk)[leaders[ok]])
+        order = leaders[np.argsort(-(cost[leaders] + has_partner), kind="stable")]
+        self.num_self_pairs = len(order)
         kv_order = np.lexsort((np.asarray(qt_cost), np.asarray(chunk_local)[np.asarray(qt_chunk)]))
         arrays = [cu, chunk_start, chunk_seq, chunk_local, qt_chunk, qt_tok0, qt_local, order, kv_order]
         sizes = [len(a) for a in arrays]
@@ -69,7 +76,7 @@ class PrefillPlan:
         self._flat = torch.from_numpy(flat).to(device)
         views = self._flat.split(sizes)
         (self.cu_seqlens, self.chunk_start, self.chunk_seq, self.chunk_local,
-         self.qtile_chunk, self.qtile_tok0, self.qtile_local, self.self_order, self.kv_order) = views
+         self.qtile_chunk, self.qtile_tok0, self.qtile_local, self.self_pairs, self.kv_order) = views
         self.filtered = np.asarray(filtered, dtype=np.int64)
         self.chunk_to_batch = np.asarray(chunk_seq, dtype=np.int64)
         self.cu_chunk = np.asarray(chunk_start, dtype=np.int64)
@@ -81,12 +88,13 @@ class PrefillPlan:
         d.hq, d.hkv, d.dim = q.shape[1], k.shape[1], q.shape[2]
         d.chunk_size, d.remote_k = self.chunk_size, remote_k
         d.num_chunks, d.num_qtiles = self.num_chunks, self.num_qtiles
+        d.num_self_pairs = self.num_self_pairs
         d.max_tiles_per_seq, d.max_chunks_per_seq = self.max_tiles_per_seq, self.max_chunks_per_seq
         d.q_stride_t, d.q_stride_h = q.stride(0), q.stride(1)
         d.k_stride_t, d.k_stride_h = k.stride(0), k.stride(1)
         d.v_stride_t, d.v_stride_h = v.stride(0), v.stride(1)
         for name in ("cu_seqlens", "chunk_start", "chunk_seq", "chunk_local", "qtile_chunk", "qtile_tok0",
-                     "qtile_local", "self_order", "kv_order"):
+                     "qtile_local", "self_pairs", "kv_order"):
             setattr(d, name, getattr(self, name).data_ptr())
         return d
 
