@@ -24,6 +24,19 @@
 
 namespace moba {
 
+#ifdef MOBA_FWD_TRACE
+// Debug build only: per-tile clock stamps of one CTA, for finding where a tile's time goes.
+__device__ long long* g_fwd_trace = nullptr;
+#define FWD_TRACE_INIT long long* const trace_buf = blockIdx.x == 40 ? g_fwd_trace : nullptr
+#define FWD_TRACE(role, it, slot)                                                     \
+  do {                                                                                \
+    if (trace_buf && (it) < 256) trace_buf[((it) * 4 + (role)) * 8 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define FWD_TRACE_INIT do {} while (0)
+#define FWD_TRACE(role, it, slot) do {} while (0)
+#endif
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -33,6 +46,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 
 struct FwdArgs {
@@ -139,13 +158,19 @@ struct FwdCfg {
   static constexpr int STAGES = DPAD <= 64 ? 4 : 2;  // K/V ring depth (a stage = K tile + V tile)
   static constexpr int SMEM = 1024 + 2 * QBUFS * TILE_BYTES + STAGES * 2 * TILE_BYTES;
   static constexpr uint32_t TMEM_COLS = 512;
-  static constexpr uint32_t COL_S = 0;    // + lane * 128; P overlays the first 64 columns
+  // Tensor memory: S0 0-127, S1 128-255, O0/O1 from 256.  With D <= 64 P has columns of its own (384-511),
+  // so the next S of a lane can be computed while its softmax still runs; with D = 128 all 512 columns are
+  // taken and P overlays the first 64 columns of S.
+  static constexpr bool OVERLAY = DPAD > 64;
+  static constexpr uint32_t COL_S = 0;    // + lane * 128
   static constexpr uint32_t COL_O = 256;  // + lane * DPAD
+  static constexpr uint32_t COL_P = OVERLAY ? 0 : 384;
+  static constexpr uint32_t P_STRIDE = OVERLAY ? 128 : 64;
 };
 
 struct FwdSmem {
   uint64_t q_full[2][2], q_free[2][2];  // [lane][buffer]
-  uint64_t s_full[2], p_ready[2], o_full[2], o_free[2];
+  uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], o_free[2];
   uint64_t kv_full[4], kv_free[4];
   uint32_t tmem_slot;
 };
@@ -173,6 +198,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
     for (int l = 0; l < 2; ++l) {
       for (int b = 0; b < 2; ++b) { mbar_init(&cb.q_full[l][b], 1); mbar_init(&cb.q_free[l][b], 1); }
       mbar_init(&cb.s_full[l], 1);
+      mbar_init(&cb.s_free[l], 4);
       mbar_init(&cb.p_ready[l], 4);
       mbar_init(&cb.o_full[l], 1);
       mbar_init(&cb.o_free[l], 4);
@@ -186,6 +212,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
   tc_fence_after_sync();
   const uint32_t tmem = cb.tmem_slot;
   bool alive = true;
+  FWD_TRACE_INIT;
 
   // The softmax warpgroups keep a whole row of S in registers; the third warpgroup gives them its share.
   if (warp >= 8) {
@@ -222,75 +249,109 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         for (int s = 0; s < STAGES && s < kvt; ++s) mbar_wait(&cb.kv_full[(kvt - 1 - s) % STAGES], (((kvt - 1 - s) / STAGES)) & 1, nullptr);
     }
   } else if (warp == 8) {
-    // ================================================================== MMA issue (one thread)
-    if (lane_id == 0) {
-      const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_o = umma_idesc_bf16(128, DPAD, 0, 1);
-      int use[2] = {0, 0};
-      int tc[2] = {0, 0};  // tiles each lane has been issued so far (phase of s_full / p_ready)
-      int kvt0 = 0;        // K/V tiles of all earlier items
-      FwdItem it;
-      for (int k = 0; fwd_decode_item<SELF>(a, fwd_item_index(k), it); ++k) {
-        const int n = max(it.n[0], it.n[1]);
-        int js[2] = {0, 0}, jp[2] = {0, 0}, rel = 0;
-        int qb[2], qph[2];
+    // ================================================================== MMA issue
+    // The whole warp walks the schedule (warp-uniform control flow and operands); one elected lane
+    // issues.  The order is fixed: per key tile, lane 0 then lane 1, each "next S" and "P V".  Every
+    // awaited event depends only on instructions issued earlier in this order, and each has about a
+    // tile of slack, so waiting in a fixed order costs nothing.
+    const bool leader = elect_one_sync();
+    const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+    const uint32_t idesc_o = umma_idesc_bf16(128, DPAD, 0, 1);
+    // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
+    // field counts 16-byte units).
+    const uint64_t qd0 = umma_desc_kmajor(smem_u32(sQ), kTile, 0);
+    const uint64_t kd0 = umma_desc_kmajor(smem_u32(sKV), kTile, 0);
+    const uint64_t vd0 = umma_desc_mnmajor(smem_u32(sKV + TILE_BYTES), kTile, 0, 0);
+    constexpr uint32_t STAGE_U = (2 * TILE_BYTES) >> 4, QBUF_U = TILE_BYTES >> 4;
+    int use_s[2] = {0, 0};  // items whose first S was issued, per lane (query buffer and its phase)
+    int use_p[2] = {0, 0};  // items whose P V products are all issued
+    int ts[2] = {0, 0};     // S products issued per lane (phase of s_free)
+    int tp[2] = {0, 0};     // P V products issued per lane (phase of p_ready)
+    int kvt0 = 0;           // K/V tiles of all earlier items
+    bool pre[2] = {false, false};  // first S of the current item was issued while the previous item ran
+
+    // S of a lane's next tile: Q buffer qb, K/V ring index kv; last = the item's last S for the lane
+    auto issue_s = [&](int l, int qb, int kv, bool last) {
+      if (!Cfg::OVERLAY && ts[l] > 0 && alive) alive = mbar_wait(&cb.s_free[l], (ts[l] - 1) & 1, a.status);
+      if (alive) alive = mbar_wait(&cb.kv_full[kv % STAGES], (kv / STAGES) & 1, a.status);
+      tc_fence_after_sync();
+      if (leader) {
+        const uint32_t tS = tmem + Cfg::COL_S + l * 128;
+        const uint64_t kd = kd0 + (uint64_t)((kv % STAGES) * STAGE_U);
+        const uint64_t qd = qd0 + (uint64_t)((l * QBUFS + qb) * QBUF_U);
 #pragma unroll
-        for (int l = 0; l < 2; ++l) { qb[l] = use[l] % QBUFS; qph[l] = (use[l] / QBUFS) & 1; }
-        const long long t_start = clock64();
-        while (rel < n) {
-          bool progressed = false;
-#pragma unroll
-          for (int l = 0; l < 2; ++l) {
-            const uint32_t tS = tmem + Cfg::COL_S + l * 128, tO = tmem + Cfg::COL_O + l * DPAD;
-            // O += P V of tile jp: P of the tile is in tensor memory, V in its ring stage
-            if (jp[l] < js[l] && (!alive || (mbar_test(&cb.p_ready[l], (tc[l] + jp[l]) & 1) &&
-                                              (jp[l] > 0 || use[l] == 0 || mbar_test(&cb.o_free[l], (use[l] - 1) & 1))))) {
-              tc_fence_after_sync();
-              const int s = (kvt0 + jp[l]) % STAGES;
-              const uint32_t v_addr = smem_u32(sKV + s * 2 * TILE_BYTES + TILE_BYTES);
-#pragma unroll
-              for (int kk = 0; kk < kTile; kk += 16)
-                umma_ts(tO, tS + kk / 2, umma_desc_mnmajor(v_addr, kTile, kk, 0), idesc_o, (jp[l] > 0) | (kk > 0));
-              umma_commit(&cb.o_full[l]);
-              ++jp[l];
-              progressed = true;
-            }
-            // S = Q K^T of tile js: only after P V of the previous tile was issued (P lives in S's columns)
-            if (js[l] < it.n[l] && js[l] == jp[l] &&
-                (!alive || (mbar_test(&cb.kv_full[(kvt0 + js[l]) % STAGES], ((kvt0 + js[l]) / STAGES) & 1) &&
-                            (js[l] > 0 || mbar_test(&cb.q_full[l][qb[l]], qph[l]))))) {
-              tc_fence_after_sync();
-              const int s = (kvt0 + js[l]) % STAGES;
-              const uint32_t q_addr = smem_u32(sQ + (l * QBUFS + qb[l]) * TILE_BYTES);
-              const uint32_t k_addr = smem_u32(sKV + s * 2 * TILE_BYTES);
-#pragma unroll
-              for (int kk = 0; kk < DPAD; kk += 16)
-                umma_ss(tS, umma_desc_kmajor(q_addr, kTile, kk), umma_desc_kmajor(k_addr, kTile, kk), idesc_s, kk > 0);
-              umma_commit(&cb.s_full[l]);
-              if (js[l] == it.n[l] - 1) umma_commit(&cb.q_free[l][qb[l]]);
-              ++js[l];
-              progressed = true;
-            }
-          }
-          // a ring stage is free once every lane that walks it has issued its P V
-          while (rel < n && (it.n[0] <= rel || jp[0] > rel) && (it.n[1] <= rel || jp[1] > rel)) {
-            umma_commit(&cb.kv_free[(kvt0 + rel) % STAGES]);
-            ++rel;
-            progressed = true;
-          }
-          if (!progressed) {
-            __nanosleep(20);
-            if (alive && clock64() - t_start > 4000000000ll) {
-              atomicOr(a.status, kErrBarrierTimeout);
-              alive = false;
-            }
-          }
+        for (int kk = 0; kk < DPAD; kk += 16) {  // K-major step: 16 elements = 32 bytes = 2 units; 64 elements per panel
+          constexpr uint32_t PANEL_U = (kTile * 128) >> 4;
+          const uint32_t off = (kk >> 6) * PANEL_U + ((kk & 63) >> 3);
+          umma_ss(tS, qd + off, kd + off, idesc_s, kk > 0);
         }
-#pragma unroll
-        for (int l = 0; l < 2; ++l)
-          if (it.n[l] > 0) { ++use[l]; tc[l] += it.n[l]; }
-        kvt0 += n;
+        umma_commit(&cb.s_full[l]);
+        if (last) umma_commit(&cb.q_free[l][qb]);
       }
+      __syncwarp();
+      ++ts[l];
+    };
+
+    FwdItem cur, nxt;
+    bool has = fwd_decode_item<SELF>(a, fwd_item_index(0), cur);
+    for (int k = 0; has; ++k) {
+      const bool has_next = fwd_decode_item<SELF>(a, fwd_item_index(k + 1), nxt);
+      const int n = max(cur.n[0], cur.n[1]);
+      bool pre_next[2] = {false, false};
+#pragma unroll
+      for (int l = 0; l < 2; ++l) {
+        if (cur.n[l] > 0 && !pre[l]) {
+          const int qb = use_s[l] % QBUFS;
+          if (alive) alive = mbar_wait(&cb.q_full[l][qb], (use_s[l] / QBUFS) & 1, a.status);
+          issue_s(l, qb, kvt0, cur.n[l] == 1);
+          ++use_s[l];
+        }
+      }
+      for (int j = 0; j < n; ++j) {
+#pragma unroll
+        for (int l = 0; l < 2; ++l) {
+          if (j >= cur.n[l]) continue;
+          auto next_s = [&]() {
+            if (j + 1 < cur.n[l]) {
+              issue_s(l, (use_s[l] - 1) % QBUFS, kvt0 + j + 1, j + 2 == cur.n[l]);
+            } else if (has_next && nxt.n[l] > 0 && j > n - STAGES) {
+              // first S of the lane's next item; its K tile can only be in the ring once the tile that
+              // used the stage before was released, which happened in an earlier iteration if j > n - STAGES
+              const int qb = use_s[l] % QBUFS;
+              if (alive) alive = mbar_wait(&cb.q_full[l][qb], (use_s[l] / QBUFS) & 1, a.status);
+              issue_s(l, qb, kvt0 + n, nxt.n[l] == 1);
+              ++use_s[l];
+              pre_next[l] = true;
+            }
+          };
+          if (!Cfg::OVERLAY) next_s();
+          // O += P V: P of the tile is in tensor memory, V in its ring stage
+          if (alive) alive = mbar_wait(&cb.p_ready[l], tp[l] & 1, a.status);
+          if (j == 0 && use_p[l] > 0 && alive) alive = mbar_wait(&cb.o_free[l], (use_p[l] - 1) & 1, a.status);
+          tc_fence_after_sync();
+          if (leader) {
+            const uint32_t tP = tmem + Cfg::COL_P + l * Cfg::P_STRIDE, tO = tmem + Cfg::COL_O + l * DPAD;
+            const uint64_t vd = vd0 + (uint64_t)(((kvt0 + j) % STAGES) * STAGE_U);
+#pragma unroll
+            for (int kk = 0; kk < kTile; kk += 16)  // MN-major step: 16 rows = 2048 bytes = 128 units
+              umma_ts(tO, tP + kk / 2, vd + kk * 8, idesc_o, (j > 0) | (kk > 0));
+            umma_commit(&cb.o_full[l]);
+          }
+          __syncwarp();
+          ++tp[l];
+          if (Cfg::OVERLAY) next_s();  // P lives in S's columns: the next S may only follow this P V
+        }
+        if (leader) umma_commit(&cb.kv_free[(kvt0 + j) % STAGES]);  // every lane that walks the stage has issued its P V
+        __syncwarp();
+      }
+#pragma unroll
+      for (int l = 0; l < 2; ++l) {
+        if (cur.n[l] > 0) ++use_p[l];
+        pre[l] = pre_next[l];
+      }
+      kvt0 += n;
+      cur = nxt;
+      has = has_next;
     }
   }
   } else {
@@ -301,6 +362,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
     const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_off + Cfg::COL_S + l * 128;
     const uint32_t tO = tmem + lane_off + Cfg::COL_O + l * DPAD;
+    const uint32_t tP = tmem + lane_off + Cfg::COL_P + l * Cfg::P_STRIDE;
     int tc = 0;  // tiles this lane has processed
     FwdItem it;
     for (int k = 0; fwd_decode_item<SELF>(a, fwd_item_index(k), it); ++k) {
@@ -323,14 +385,22 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         int klimit = key_end - k0;                     // keys of the tile that exist
         if (SELF) klimit = min(klimit, tok - k0 + 1);  // causal inside the own chunk
         const bool need_mask = __any_sync(0xFFFFFFFFu, klimit < kTile);
+        if (row == 0) FWD_TRACE(l, tc, 0);
         if (alive) alive = mbar_wait(&cb.s_full[l], tc & 1, a.status);
         tc_fence_after_sync();
+        if (row == 0) FWD_TRACE(l, tc, 1);
         uint32_t s0[32], s1[32], s2[32], s3[32];
         tmem_ld32(tS, s0);
         tmem_ld32(tS + 32, s1);
         tmem_ld32(tS + 64, s2);
         tmem_ld32(tS + 96, s3);
         tmem_ld_wait();
+        if (!Cfg::OVERLAY) {  // S is in registers: the tensor pipe may compute the lane's next S
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane_id == 0) mbar_arrive(&cb.s_free[l]);
+        }
+        if (row == 0) FWD_TRACE(l, tc, 2);
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -359,9 +429,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           m_used = m_tile;
           raise = true;
         }
+        // P V of the previous tile must have landed before its P is overwritten or O is rescaled
+        if (j > 0 && alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
         if (j > 0 && __any_sync(0xFFFFFFFFu, raise)) {
-          // rescale the row's O in tensor memory; P V of the previous tile must have landed
-          if (alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
+          // rescale the row's O in tensor memory
           tc_fence_after_sync();
 #pragma unroll
           for (int pc = 0; pc < DPAD / 32; ++pc) {
@@ -374,6 +445,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           }
           l_run *= alpha;
         }
+        if (row == 0) FWD_TRACE(l, tc, 3);
         float sum0 = 0.f, sum1 = 0.f;
         uint32_t pk[32];
 #pragma unroll
@@ -387,7 +459,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           pk[i >> 1] = pack_bf16(p0, p1);
           pk[16 + (i >> 1)] = pack_bf16(p2, p3);
         }
-        tmem_st32(tS, pk);
+        tmem_st32(tP, pk);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(s2[i]), a.scale_log2, -m_used));
@@ -399,12 +471,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           pk[i >> 1] = pack_bf16(p0, p1);
           pk[16 + (i >> 1)] = pack_bf16(p2, p3);
         }
-        tmem_st32(tS + 32, pk);
+        tmem_st32(tP + 32, pk);
         l_run += sum0 + sum1;
+        if (row == 0) FWD_TRACE(l, tc, 4);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane_id == 0) mbar_arrive(&cb.p_ready[l]);
+        if (row == 0) FWD_TRACE(l, tc, 5);
       }
 
       // ---- epilogue: O of the row leaves tensor memory, then the lane's accumulator is free again
@@ -513,6 +587,12 @@ static cudaError_t launch_fwd(const FwdArgs& a, long long items, cudaStream_t st
 }
 
 }  // namespace moba
+
+#ifdef MOBA_FWD_TRACE
+extern "C" int moba_debug_set_fwd_trace(long long* buf) {
+  return cudaMemcpyToSymbol(moba::g_fwd_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 using namespace moba;
 
