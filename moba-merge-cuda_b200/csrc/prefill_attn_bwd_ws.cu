@@ -21,12 +21,13 @@ namespace moba {
 #ifdef MOBA_BWD_TRACE
 // Debug build only: per-tile clock stamps of one CTA, for finding where a tile's time goes.
 __device__ long long* g_bwd_trace = nullptr;
+#define WS_TRACE_INIT long long* const trace_buf = (blockIdx.x == 40 && blockIdx.y == 0) ? g_bwd_trace : nullptr
 #define WS_TRACE(role, it, slot)                                                                           \
   do {                                                                                                     \
-    if (g_bwd_trace && blockIdx.x == 40 && blockIdx.y == 0 && (it) < 256)                                  \
-      g_bwd_trace[((it) * 4 + (role)) * 8 + (slot)] = clock64();                                           \
+    if (trace_buf && (it) < 256) trace_buf[((it) * 4 + (role)) * 8 + (slot)] = clock64();                  \
   } while (0)
 #else
+#define WS_TRACE_INIT do {} while (0)
 #define WS_TRACE(role, it, slot) do {} while (0)
 #endif
 
@@ -95,7 +96,7 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
 struct WsSmem {
   uint64_t sdp_full, sdp_free, pds_ready, kvq_done, kv_ready;
   uint64_t qdo_full[kWsRing];      // tile (Q, dO, row metadata) landed in the slot
-  uint64_t qdo_free[kWsRing];      // dV and dK of the tile are done: the slot may take its next tile
+  uint64_t qdo_free[kWsRing];      // dQ of the tile has left through the slot (8 warps): it may take its next tile
   uint32_t tmem_slot;
   uint32_t pad;
   __align__(16) int rowth[kWsRing][kTile];      // t*Hq+h of every row of the tile, -1 = padding row
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     mbar_init(&cb.pds_ready, 8);
     mbar_init(&cb.kvq_done, 1);
     mbar_init(&cb.kv_ready, 1);
-    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 1); }
+    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 8); }
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(&cb.tmem_slot, TMEM_COLS);
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   tc_fence_after_sync();
   const uint32_t tmem = cb.tmem_slot;
   bool alive = true;
+  WS_TRACE_INIT;
 
   if (warp == 9) {
     // ================================================================== producer
@@ -228,7 +230,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 #pragma unroll
         for (int kk = 0; kk < kTile; kk += 16)  // dK += dS^T Q
           umma_ss(tmem + COL_DK, s_mn + kk * 8, q_mn + slot + kk * 8, idesc_kv, acc | (kk > 0));
-        umma_commit(&cb.qdo_free[it % kWsRing]);  // the tile's Q and dO rows are no longer needed
 #pragma unroll
         for (int kk = 0; kk < kTile; kk += 16)  // dQ = dS K; dS K-major over two 64-key panels of 16 KB
           umma_ss(tmem + COL_DQ, s_km + (kk >> 6) * (kTile * 128 >> 4) + ((kk & 63) >> 3), k_mn + kk * 8, idesc_dq, kk > 0);
@@ -274,19 +275,34 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     const int r = quad * 32 + lane;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
     int th_prev = -1;
-    auto drain_dq = [&](int th) {  // th: row id kept from the tile's own iteration (its ring slot may be refilled by now)
+    // dQ of a finished tile leaves tensor memory through the tile's own ring slot (its Q and dO rows are
+    // dead by then): every warp parks its 32 rows x 32 columns there and reads them back with eight lanes
+    // per row, so that one red instruction covers four whole 128-byte lines instead of 32 different ones
+    // (a scattered warp-wide red costs the load/store unit one cycle per line).
+    auto drain_dq = [&](int th, int slot) {  // th: row id kept from the tile's own iteration
       uint32_t v[32];
       tmem_ld32(tlane + COL_DQ + half * 32, v);
       tmem_ld_wait();
-#ifndef MOBA_BWD_NODRAIN
-      if (th >= 0 && alive) {
-        float* dst = a.dq_acc + (long long)th * D + half * 32;
+      uint8_t* stage = sQ + slot * SLOT_BYTES + warp * 4096;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          if (half * 32 + i < D)
-            red_add_v4(dst + i, __uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      for (int u = 0; u < 8; ++u)
+        *reinterpret_cast<uint4*>(stage + lane * 128 + ((u ^ (lane & 7)) << 4)) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
+      __syncwarp();
+#ifndef MOBA_BWD_NODRAIN
+      const int c = lane & 7;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const int rl = (lane >> 3) + 4 * x;
+        const int rth = __shfl_sync(0xFFFFFFFFu, th, rl);
+        const uint4 w = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((c ^ (rl & 7)) << 4));
+        if (rth >= 0 && alive && half * 32 + c * 4 < D)
+          red_add_v4(a.dq_acc + (long long)rth * D + half * 32 + c * 4, __uint_as_float(w.x), __uint_as_float(w.y),
+                     __uint_as_float(w.z), __uint_as_float(w.w));
       }
 #endif
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&cb.qdo_free[slot]);  // the slot may take its next tile
     };
     for (int it = 0; it < n_iter; ++it) {
       const int ms = it % kWsRing;
@@ -349,7 +365,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         alive = warp_wait(&cb.kvq_done, (it - 1) & 1, a.status, alive);
         if (tid == 0) WS_TRACE(0, it, 5);
         tc_fence_after_sync();
-        drain_dq(th_prev);
+        drain_dq(th_prev, (it - 1) % kWsRing);
         tc_fence_before_sync();
       }
       if (tid == 0) WS_TRACE(3, it, 0);
@@ -367,7 +383,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     if (n_iter > 0) {
       alive = warp_wait(&cb.kvq_done, (n_iter - 1) & 1, a.status, alive);
       tc_fence_after_sync();
-      drain_dq(th_prev);
+      drain_dq(th_prev, (n_iter - 1) % kWsRing);
       // dK (warps 0-3) and dV (warps 4-7) of the key block: thread = key row
       const bool ok = r < nkeys && alive;
       __nv_bfloat16* dst = (half == 0 ? a.dk : a.dv) + ((long long)(k0 + r) * pv.Hkv + g) * D;
