@@ -76,7 +76,7 @@ cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, flo
   return cudaGetLastError();
 }
 
-constexpr int kWsThreads = 320;  // 8 compute warps, MMA warp, producer warp
+constexpr int kWsThreads = 512;  // 8 compute warps, MMA warp, producer warp (+2 idle), 4 dQ drain warps
 constexpr int kWsRing = 3;       // Q/dO tiles in shared memory
 
 // One lane polls the barrier for its warp; __syncwarp orders the other lanes' later reads after
@@ -95,8 +95,9 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
 
 struct WsSmem {
   uint64_t sdp_full, sdp_free, pds_ready, kvq_done, kv_ready;
+  uint64_t dq_free;                // the drain warps hold the tile's dQ in registers: the accumulator may be overwritten
   uint64_t qdo_full[kWsRing];      // tile (Q, dO, row metadata) landed in the slot
-  uint64_t qdo_free[kWsRing];      // dQ of the tile has left through the slot (8 warps): it may take its next tile
+  uint64_t qdo_free[kWsRing];      // dV and dK of the tile are done and the drain warps have its row ids: the slot may take its next tile
   uint32_t tmem_slot;
   uint32_t pad;
   __align__(16) int rowth[kWsRing][kTile];      // t*Hq+h of every row of the tile, -1 = padding row
@@ -120,6 +121,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   uint8_t* sdO = sQ + TILE_BYTES;
   uint8_t* sP = sQ + kWsRing * SLOT_BYTES;
   uint8_t* sdS = sP + PT_BYTES;
+  uint8_t* sStage = sdS + PT_BYTES;  // 4 x 4 KB: transposition buffers of the drain warps
 
   const PrefillView& pv = a.pv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -151,7 +153,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     mbar_init(&cb.pds_ready, 8);
     mbar_init(&cb.kvq_done, 1);
     mbar_init(&cb.kv_ready, 1);
-    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 8); }
+    mbar_init(&cb.dq_free, 4);
+    for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 5); }
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(&cb.tmem_slot, TMEM_COLS);
@@ -162,6 +165,57 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   bool alive = true;
   WS_TRACE_INIT;
 
+  if (warp >= 12) {
+    // ================================================================== dQ drain (warps 12-15)
+    // A warp takes the 32 rows of its tensor-memory lanes: dQ of the finished tile goes to registers at
+    // once (the accumulator is then free for the next tile) and from there, 32 columns at a time, through
+    // a 4 KB transposition buffer into dq_acc with eight lanes per row, so that one red instruction
+    // covers four whole 128-byte lines.  The atomics run at the pace the memory system takes them,
+    // in the background of the next tile's math.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    const int quad = warp & 3;
+    const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
+    uint8_t* stage = sStage + quad * 4096;
+    for (int it = 0; it < n_iter; ++it) {
+      const int slot = it % kWsRing;
+      alive = warp_wait(&cb.qdo_full[slot], (it / kWsRing) & 1, a.status, alive);
+      const int th = cb.rowth[slot][quad * 32 + lane];
+      warp_arrive(&cb.qdo_free[slot]);
+      alive = warp_wait(&cb.kvq_done, it & 1, a.status, alive);
+      tc_fence_after_sync();
+      uint32_t v0[32], v1[32];
+      tmem_ld32(tlane + COL_DQ, v0);
+      tmem_ld32(tlane + COL_DQ + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      warp_arrive(&cb.dq_free);
+#ifndef MOBA_BWD_NODRAIN
+      const int c4 = lane & 7;
+#pragma unroll
+      for (int p = 0; p < 2; ++p) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 val = p == 0 ? make_uint4(v0[4 * u], v0[4 * u + 1], v0[4 * u + 2], v0[4 * u + 3])
+                                   : make_uint4(v1[4 * u], v1[4 * u + 1], v1[4 * u + 2], v1[4 * u + 3]);
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((u ^ (lane & 7)) << 4)) = val;
+        }
+        __syncwarp();
+        const int col = p * 32 + c4 * 4;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const int rl = (lane >> 3) + 4 * x;
+          const int rth = __shfl_sync(0xFFFFFFFFu, th, rl);
+          const uint4 w = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((c4 ^ (rl & 7)) << 4));
+          if (rth >= 0 && alive && col < D)
+            red_add_v4(a.dq_acc + (long long)rth * D + col, __uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z),
+                       __uint_as_float(w.w));
+        }
+        __syncwarp();
+      }
+#endif
+    }
+  } else if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 9) {
     // ================================================================== producer
     // One thread asks the copy engine for the packed tiles: 16 KB of Q, 16 KB of dO and three 512-byte
@@ -178,15 +232,17 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       for (int j = 0; j < n_iter; ++j) {
         const int b = j % kWsRing;
         long long tile;
-        if (j < pv.G * n_self) {
-          const int hl = j / n_self, i = kb + (j - hl * n_self);
-          tile = (long long)(kblock - kb + i) * pv.Hq + g * pv.G + hl;  // query tiles of a chunk are consecutive
-        } else {
-          // The key blocks of a chunk walk the same expert list; starting each at a different offset
-          // keeps them from adding into the same dQ rows at the same time.
-          int jr = j - pv.G * n_self + (int)(((long long)kb * n_remote) / tiles_in_chunk);
+        if (j < n_remote) {
+          // The key blocks of a chunk walk the same expert list at the same time, each a couple of tiles
+          // apart: a tile fetched by one of them is still in the L2 cache for the others, the dQ rows
+          // they all add into stay there too, and no two of them add into the same rows at once.
+          int jr = j + (kb * 2) % n_remote;
           if (jr >= n_remote) jr -= n_remote;
           tile = remote_tile0 + jr;
+        } else {
+          const int s = j - n_remote;
+          const int hl = s / n_self, i = kb + (s - hl * n_self);
+          tile = (long long)(kblock - kb + i) * pv.Hq + g * pv.G + hl;  // query tiles of a chunk are consecutive
         }
         if (j >= kWsRing && alive) alive = mbar_wait(&cb.qdo_free[b], ((j / kWsRing) - 1) & 1, a.status);
         mbar_arrive_expect_tx(&cb.qdo_full[b], 2 * TILE_BYTES + 3 * kTile * 4);
@@ -230,6 +286,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 #pragma unroll
         for (int kk = 0; kk < kTile; kk += 16)  // dK += dS^T Q
           umma_ss(tmem + COL_DK, s_mn + kk * 8, q_mn + slot + kk * 8, idesc_kv, acc | (kk > 0));
+        umma_commit(&cb.qdo_free[it % kWsRing]);  // the tile's Q and dO rows are no longer needed
 #pragma unroll
         for (int kk = 0; kk < kTile; kk += 16)  // dQ = dS K; dS K-major over two 64-key panels of 16 KB
           umma_ss(tmem + COL_DQ, s_km + (kk >> 6) * (kTile * 128 >> 4) + ((kk & 63) >> 3), k_mn + kk * 8, idesc_dq, kk > 0);
@@ -237,7 +294,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       };
       // Two streams of work are issued as their inputs become ready, whichever comes first:
       //   S, dP of tile n    needs the tile's Q/dO in the ring and S/dP of tile n-1 read by the compute warps
-      //   dV, dK, dQ of tile i needs P and dS of tile i in shared memory
+      //   dV, dK, dQ of tile i needs P and dS of tile i in shared memory and dQ of tile i-1 taken by the drain warps
       int next_sdp = 0, next_kvq = 0;
       const long long t_start = clock64();
       while (next_kvq < n_iter) {
@@ -254,7 +311,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
             progressed = true;
           }
         }
-        if (next_kvq < next_sdp && (!alive || mbar_test(&cb.pds_ready, next_kvq & 1))) {
+        if (next_kvq < next_sdp && (!alive || (mbar_test(&cb.pds_ready, next_kvq & 1) &&
+                                               (next_kvq == 0 || mbar_test(&cb.dq_free, (next_kvq - 1) & 1))))) {
           tc_fence_after_sync();
           WS_TRACE(1, next_kvq, 1);
           issue_kvq(next_kvq++);
@@ -269,49 +327,20 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         }
       }
     }
+  }
   } else {
     // ================================================================== compute (warps 0-7)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
     const int quad = warp & 3, half = warp >> 2;
     const int r = quad * 32 + lane;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
-    int th_prev = -1;
-    // dQ of a finished tile leaves tensor memory through the tile's own ring slot (its Q and dO rows are
-    // dead by then): every warp parks its 32 rows x 32 columns there and reads them back with eight lanes
-    // per row, so that one red instruction covers four whole 128-byte lines instead of 32 different ones
-    // (a scattered warp-wide red costs the load/store unit one cycle per line).
-    auto drain_dq = [&](int th, int slot) {  // th: row id kept from the tile's own iteration
-      uint32_t v[32];
-      tmem_ld32(tlane + COL_DQ + half * 32, v);
-      tmem_ld_wait();
-      uint8_t* stage = sQ + slot * SLOT_BYTES + warp * 4096;
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        *reinterpret_cast<uint4*>(stage + lane * 128 + ((u ^ (lane & 7)) << 4)) = make_uint4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
-      __syncwarp();
-#ifndef MOBA_BWD_NODRAIN
-      const int c = lane & 7;
-#pragma unroll
-      for (int x = 0; x < 8; ++x) {
-        const int rl = (lane >> 3) + 4 * x;
-        const int rth = __shfl_sync(0xFFFFFFFFu, th, rl);
-        const uint4 w = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((c ^ (rl & 7)) << 4));
-        if (rth >= 0 && alive && half * 32 + c * 4 < D)
-          red_add_v4(a.dq_acc + (long long)rth * D + half * 32 + c * 4, __uint_as_float(w.x), __uint_as_float(w.y),
-                     __uint_as_float(w.z), __uint_as_float(w.w));
-      }
-#endif
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&cb.qdo_free[slot]);  // the slot may take its next tile
-    };
     for (int it = 0; it < n_iter; ++it) {
       const int ms = it % kWsRing;
       if (tid == 0) WS_TRACE(0, it, 0);
       alive = warp_wait(&cb.qdo_full[ms], (it / kWsRing) & 1, a.status, alive);  // the tile's metadata is in the slot
       if (tid == 0) WS_TRACE(0, it, 1);
-      const int th = cb.rowth[ms][r];
       const float lse2 = cb.lse2[ms][r], delta_s = cb.delta_s[ms][r];
-      const bool diag = it < pv.G * n_self && (it % n_self) == 0;
+      const bool diag = it >= n_remote && ((it - n_remote) % n_self) == 0;
       int klimit = nkeys;
       if (diag) klimit = min(klimit, r + 1);
       klimit -= half * 64;  // relative to this thread's first column
@@ -361,12 +390,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         }
       }
       if (tid == 0) WS_TRACE(0, it, 4);
-      if (it > 0) {  // previous tile's dV/dK/dQ products are complete: sP/sdS are free, dQ can be drained
+      if (it > 0) {  // previous tile's dV/dK/dQ products are complete: sP/sdS are free
         alive = warp_wait(&cb.kvq_done, (it - 1) & 1, a.status, alive);
         if (tid == 0) WS_TRACE(0, it, 5);
-        tc_fence_after_sync();
-        drain_dq(th_prev, (it - 1) % kWsRing);
-        tc_fence_before_sync();
       }
       if (tid == 0) WS_TRACE(3, it, 0);
 #pragma unroll
@@ -378,12 +404,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       fence_async_smem();
       warp_arrive(&cb.pds_ready);
       if (tid == 0) WS_TRACE(0, it, 7);
-      th_prev = th;
     }
     if (n_iter > 0) {
       alive = warp_wait(&cb.kvq_done, (n_iter - 1) & 1, a.status, alive);
       tc_fence_after_sync();
-      drain_dq(th_prev, (n_iter - 1) % kWsRing);
       // dK (warps 0-3) and dV (warps 4-7) of the key block: thread = key row
       const bool ok = r < nkeys && alive;
       __nv_bfloat16* dst = (half == 0 ? a.dk : a.dv) + ((long long)(k0 + r) * pv.Hkv + g) * D;
@@ -411,7 +435,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 }
 
 cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st) {
-  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 * 2;
+  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 * 2 + 4 * 4096;
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   attn_bwd_ws_kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kWsThreads, smem, st>>>(a);

@@ -69,7 +69,7 @@ class PrefillPlan:
         has_partner[ok] = (np.asarray(qt_chunk)[nxt[ok]] == np.asarray(qt_chunk)[leaders[ok]])
         order = leaders[np.argsort(-(cost[leaders] + has_partner), kind="stable")]
         self.num_self_pairs = len(order)
-        kv_order = np.lexsort((np.asarray(qt_cost), np.asarray(chunk_local)[np.asarray(qt_chunk)]))
+        kv_order = np.lexsort((cost, np.asarray(chunk_local)[np.asarray(qt_chunk)]))
         arrays = [cu, chunk_start, chunk_seq, chunk_local, qt_chunk, qt_tok0, qt_local, order, kv_order]
         sizes = [len(a) for a in arrays]
         flat = np.concatenate([np.asarray(a, dtype=np.int32) for a in arrays])
