@@ -279,7 +279,7 @@ constexpr int kStages = MOBA_DEC_STAGES;  // cp.async stages in flight per CTA
 // XOR-permuted by (token & 7) so that ldmatrix reads of 8 consecutive tokens are conflict-free.
 template <int DP>
 __device__ __forceinline__ uint32_t kv_unit_offset(int tok, int unit) {
-
+  constexpr int UPR = DP / 8;
   const int sw = UPR >= 8 ? (unit ^ (tok & 7)) : unit;
   return (uint32_t)(tok * DP * 2 + sw * 16);
 }
@@ -301,7 +301,7 @@ __device__ __forceinline__ long long attend_row_base(const CacheView& cv, int si
 // and head-dim padding are zero-filled.
 template <int DP>
 __device__ __forceinline__ void attend_load_stage(const CacheView& cv, uint8_t* stage, const long long* row_base) {
-
+  constexpr int UPR = DP / 8;
   constexpr int ROWS_PER_PASS = 128 / UPR;
   const int u = threadIdx.x % UPR, r0 = threadIdx.x / UPR;
   const uint32_t kdst = smem_u32(stage);
@@ -344,7 +344,6 @@ __device__ __forceinline__ uint32_t dec_pack_bf16(float lo, float hi) {
 // four warps are combined through shared memory at the end.
 template <int DP>
 __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
-
   constexpr int KSTEPS = DP / 16;
   constexpr int DT = DP / 8;  // 8-column output tiles
   constexpr int STAGE_BYTES = 2 * kStageTokens * DP * 2;
