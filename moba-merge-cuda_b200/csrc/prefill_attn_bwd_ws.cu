@@ -1,19 +1,21 @@
-// Warp-specialised prefill backward for head_dim <= 64: the same mathematics and work decomposition
-// as attn_bwd_kernel (one CTA owns 128 keys of one (chunk, kv head) and walks over every 128-row
-// query tile that attends them), organised so that the tensor pipe, the exp/FMA pipes and the memory
-// system work on different query tiles at the same time.
-//   warps 0-7  compute: two threads per query row (64 of the 128 key columns each).  Per tile they read
-//              S and dP from TMEM and release them at once, form P and dS in registers, add dQ of the
-//              previous tile into the FP32 accumulator with vector reductions, and store P and dS as
-//              swizzled bf16 tiles
-//   warp 8     one thread issues every tcgen05.mma, polling two work streams: S/dP of tile n as soon
-//              as the tile has landed and the compute warps have read tile n-1; dV/dK/dQ of tile i
-//              as soon as P and dS of tile i are in shared memory
-//   warp 9     one thread asks the copy engine for the tiles: a packing pass (bwd_pack_kernel) has
-//              gathered the scattered Q and dO rows, row ids, LSE and delta of every tile into
-//              contiguous, already swizzled 16 KB images, so a tile is five bulk copies into a
-//              three-slot ring and costs the SM no load/store issue slots
-// TMEM columns: S 0-127, dP 128-255, dV 256-319, dK 320-383, dQ 384-447.
+// Warp-specialised prefill backward for head_dim <= 64.  One CTA owns 128 keys of one (chunk, kv head),
+// keeps K and V in shared memory and dK, dV in tensor memory for its whole life, and walks over every
+// 128-row query tile that attends them.  Scores are formed transposed, keys on the tensor-memory lanes
+// and queries along the columns:
+//     S^T = K Q^T, dP^T = V dO^T     ->  P^T = exp2(S^T c - LSE[q]),  dS^T = P^T (dP^T - delta[q]) / sqrt(D)
+//     dV += P^T dO,  dK += dS^T Q    with P^T and dS^T read by the tensor cores straight from tensor memory
+//     dQ  = dS K                     with dS^T also stored once as a shared-memory tile
+// so per tile only dS crosses shared memory (the five products of a tile otherwise read every operand
+// from shared memory, which is what bounded the kernel).
+//   warps 0-7    compute: two threads per key row (64 of the 128 query columns each)
+//   warp 8       issues every tcgen05.mma in a fixed order (whole warp walks the schedule, one lane issues)
+//   warp 9       one thread asks the copy engine for the tiles: a packing pass has gathered the scattered
+//                Q and dO rows, row ids, LSE and delta of every tile into contiguous, already swizzled
+//                16 KB images, so a tile is five bulk copies into a four-slot ring
+//   warps 12-15  dQ drain: tensor memory -> registers -> 4 KB transposition buffer -> vector reductions
+//                into the FP32 accumulator, behind the next tile's math
+// Tensor memory: S^T 0-127, dP^T 128-255 (dS^T as packed bf16 over its first columns), dV 256-319,
+// dK 320-383, dQ 384-447, P^T 448-511.
 #include "prefill_bwd.cuh"
 
 namespace moba {
@@ -77,27 +79,37 @@ cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, flo
 }
 
 constexpr int kWsThreads = 512;  // 8 compute warps, MMA warp, producer warp (+2 idle), 4 dQ drain warps
-constexpr int kWsRing = 3;       // Q/dO tiles in shared memory
+constexpr int kWsRing = 4;       // Q/dO tiles in shared memory
 
-// One lane polls the barrier for its warp; __syncwarp orders the other lanes' later reads after
-// lane 0's acquire.
+// One arrival per warp: every lane's earlier writes are ordered before it by __syncwarp.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, unsigned* status, bool alive) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0 && alive) ok = mbar_wait(bar, parity, status);
   __syncwarp();
   return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
 }
-// One arrival per warp: every lane's earlier writes are ordered before it by __syncwarp.
 __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
   __syncwarp();
   if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
 }
+__device__ __forceinline__ bool bwd_elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 
 struct WsSmem {
-  uint64_t sdp_full, sdp_free, pds_ready, kvq_done, kv_ready;
-  uint64_t dq_free;                // the drain warps hold the tile's dQ in registers: the accumulator may be overwritten
-  uint64_t qdo_full[kWsRing];      // tile (Q, dO, row metadata) landed in the slot
-  uint64_t qdo_free[kWsRing];      // dV and dK of the tile are done and the drain warps have its row ids: the slot may take its next tile
+  uint64_t st_full;    // S^T of the tile is in tensor memory (tcgen05.commit)
+  uint64_t st_free;    // the 8 compute warps have read it: S^T of the next tile may be formed
+  uint64_t p_ready;    // P^T of the tile is in tensor memory (8 warps)
+  uint64_t pt_free;    // dV of the tile is done: P^T may be overwritten
+  uint64_t dpt_full;   // dP^T of the tile is in tensor memory
+  uint64_t ds_ready;   // dS^T of the tile is in tensor memory and in shared memory (8 warps)
+  uint64_t dq_done;    // dQ (and everything issued before it) of the tile is done
+  uint64_t dq_free;    // the drain warps hold the tile's dQ in registers (4 warps)
+  uint64_t kv_ready;
+  uint64_t qdo_full[kWsRing];  // tile (Q, dO, row metadata) landed in the slot
+  uint64_t qdo_free[kWsRing];  // dK of the tile is done and the drain warps have its row ids (1 + 4)
   uint32_t tmem_slot;
   uint32_t pad;
   __align__(16) int rowth[kWsRing][kTile];      // t*Hq+h of every row of the tile, -1 = padding row
@@ -111,17 +123,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   constexpr int TILE_BYTES = kTile * DPAD * 2;
   constexpr int PT_BYTES = kTile * kTile * 2;
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384;
+  constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_PT = 448;
   extern __shared__ __align__(1024) uint8_t smem[];
   WsSmem& cb = *reinterpret_cast<WsSmem*>(smem);
   uint8_t* sK = smem + 8192;
   uint8_t* sV = sK + TILE_BYTES;
-  constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // ring slot: Q tile followed by dO tile (32 KB, later the dQ staging area)
+  constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // ring slot: Q tile followed by dO tile
   uint8_t* sQ = sV + TILE_BYTES;
   uint8_t* sdO = sQ + TILE_BYTES;
-  uint8_t* sP = sQ + kWsRing * SLOT_BYTES;
-  uint8_t* sdS = sP + PT_BYTES;
-  uint8_t* sStage = sdS + PT_BYTES;  // 4 x 4 KB: transposition buffers of the drain warps
+  uint8_t* sdS = sQ + kWsRing * SLOT_BYTES;  // dS^T: 128 key rows x 128 query columns, bf16, two 64-column panels
+  uint8_t* sStage = sdS + PT_BYTES;          // 4 x 4 KB: transposition buffers of the drain warps
 
   const PrefillView& pv = a.pv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -148,12 +159,15 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     return;
   }
   if (tid == 0) {
-    mbar_init(&cb.sdp_full, 1);
-    mbar_init(&cb.sdp_free, 8);
-    mbar_init(&cb.pds_ready, 8);
-    mbar_init(&cb.kvq_done, 1);
-    mbar_init(&cb.kv_ready, 1);
+    mbar_init(&cb.st_full, 1);
+    mbar_init(&cb.st_free, 8);
+    mbar_init(&cb.p_ready, 8);
+    mbar_init(&cb.pt_free, 1);
+    mbar_init(&cb.dpt_full, 1);
+    mbar_init(&cb.ds_ready, 8);
+    mbar_init(&cb.dq_done, 1);
     mbar_init(&cb.dq_free, 4);
+    mbar_init(&cb.kv_ready, 1);
     for (int i = 0; i < kWsRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 5); }
     mbar_fence_init();
   }
@@ -181,7 +195,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       alive = warp_wait(&cb.qdo_full[slot], (it / kWsRing) & 1, a.status, alive);
       const int th = cb.rowth[slot][quad * 32 + lane];
       warp_arrive(&cb.qdo_free[slot]);
-      alive = warp_wait(&cb.kvq_done, it & 1, a.status, alive);
+      alive = warp_wait(&cb.dq_done, it & 1, a.status, alive);
       tc_fence_after_sync();
       uint32_t v0[32], v1[32];
       tmem_ld32(tlane + COL_DQ, v0);
@@ -216,197 +230,216 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     }
   } else if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-  if (warp == 9) {
-    // ================================================================== producer
-    // One thread asks the copy engine for the packed tiles: 16 KB of Q, 16 KB of dO and three 512-byte
-    // metadata rows per tile, all contiguous in global memory, completion counted on the slot's barrier.
-    if (lane == 0) {
-      {  // stationary K and V images of the key block
-        const size_t kvoff = ((size_t)kblock * pv.Hkv + g) * TILE_BYTES;
-        mbar_arrive_expect_tx(&cb.kv_ready, 2 * TILE_BYTES);
-        bulk_load(sK, reinterpret_cast<const uint8_t*>(a.kpack) + kvoff, TILE_BYTES, &cb.kv_ready);
-        bulk_load(sV, reinterpret_cast<const uint8_t*>(a.vpack) + kvoff, TILE_BYTES, &cb.kv_ready);
-      }
-      const long long self_tiles = (long long)pv.n_qtiles * pv.Hq;
-      const long long remote_tile0 = pv.R > 0 ? self_tiles + a.tile_base[c * pv.Hkv + g] : 0;
-      for (int j = 0; j < n_iter; ++j) {
-        const int b = j % kWsRing;
-        long long tile;
-        if (j < n_remote) {
-          // The key blocks of a chunk walk the same expert list at the same time, each a couple of tiles
-          // apart: a tile fetched by one of them is still in the L2 cache for the others, the dQ rows
-          // they all add into stay there too, and no two of them add into the same rows at once.
-          int jr = j + (kb * 2) % n_remote;
-          if (jr >= n_remote) jr -= n_remote;
-          tile = remote_tile0 + jr;
-        } else {
-          const int s = j - n_remote;
-          const int hl = s / n_self, i = kb + (s - hl * n_self);
-          tile = (long long)(kblock - kb + i) * pv.Hq + g * pv.G + hl;  // query tiles of a chunk are consecutive
+    if (warp == 9) {
+      // ================================================================== producer
+      // One thread asks the copy engine for the packed tiles: 16 KB of Q, 16 KB of dO and three 512-byte
+      // metadata rows per tile, all contiguous in global memory, completion counted on the slot's barrier.
+      if (lane == 0) {
+        {  // stationary K and V images of the key block
+          const size_t kvoff = ((size_t)kblock * pv.Hkv + g) * TILE_BYTES;
+          mbar_arrive_expect_tx(&cb.kv_ready, 2 * TILE_BYTES);
+          bulk_load(sK, reinterpret_cast<const uint8_t*>(a.kpack) + kvoff, TILE_BYTES, &cb.kv_ready);
+          bulk_load(sV, reinterpret_cast<const uint8_t*>(a.vpack) + kvoff, TILE_BYTES, &cb.kv_ready);
         }
-        if (j >= kWsRing && alive) alive = mbar_wait(&cb.qdo_free[b], ((j / kWsRing) - 1) & 1, a.status);
-        mbar_arrive_expect_tx(&cb.qdo_full[b], 2 * TILE_BYTES + 3 * kTile * 4);
-        bulk_load(sQ + b * SLOT_BYTES, reinterpret_cast<const uint8_t*>(a.qpack) + tile * TILE_BYTES, TILE_BYTES, &cb.qdo_full[b]);
-        bulk_load(sdO + b * SLOT_BYTES, reinterpret_cast<const uint8_t*>(a.dopack) + tile * TILE_BYTES, TILE_BYTES, &cb.qdo_full[b]);
-        bulk_load(cb.rowth[b], a.rowpack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
-        bulk_load(cb.lse2[b], a.lsepack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
-        bulk_load(cb.delta_s[b], a.deltapack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
+        const long long self_tiles = (long long)pv.n_qtiles * pv.Hq;
+        const long long remote_tile0 = pv.R > 0 ? self_tiles + a.tile_base[c * pv.Hkv + g] : 0;
+        for (int j = 0; j < n_iter; ++j) {
+          const int b = j % kWsRing;
+          long long tile;
+          if (j < n_remote) {
+            // The key blocks of a chunk walk the same expert list at the same time, each a couple of tiles
+            // apart: a tile fetched by one of them is still in the L2 cache for the others, the dQ rows
+            // they all add into stay there too, and no two of them add into the same rows at once.
+            int jr = j + (kb * 2) % n_remote;
+            if (jr >= n_remote) jr -= n_remote;
+            tile = remote_tile0 + jr;
+          } else {
+            const int s = j - n_remote;
+            const int hl = s / n_self, i = kb + (s - hl * n_self);
+            tile = (long long)(kblock - kb + i) * pv.Hq + g * pv.G + hl;  // query tiles of a chunk are consecutive
+          }
+          if (j >= kWsRing && alive) alive = mbar_wait(&cb.qdo_free[b], ((j / kWsRing) - 1) & 1, a.status);
+          mbar_arrive_expect_tx(&cb.qdo_full[b], 2 * TILE_BYTES + 3 * kTile * 4);
+          bulk_load(sQ + b * SLOT_BYTES, reinterpret_cast<const uint8_t*>(a.qpack) + tile * TILE_BYTES, TILE_BYTES, &cb.qdo_full[b]);
+          bulk_load(sdO + b * SLOT_BYTES, reinterpret_cast<const uint8_t*>(a.dopack) + tile * TILE_BYTES, TILE_BYTES, &cb.qdo_full[b]);
+          bulk_load(cb.rowth[b], a.rowpack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
+          bulk_load(cb.lse2[b], a.lsepack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
+          bulk_load(cb.delta_s[b], a.deltapack + tile * kTile, kTile * 4, &cb.qdo_full[b]);
+        }
       }
-    }
-  } else if (warp == 8) {
-    // ================================================================== MMA issue
-    if (lane == 0) {
-      const uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 1, 1);
-      const uint32_t idesc_dq = umma_idesc_bf16(128, DPAD, 0, 1);
-      // Operand descriptors are built once; inside the loop a descriptor is its base plus a constant
-      // (the start-address field counts 16-byte units).
+    } else if (warp == 8) {
+      // ================================================================== MMA issue
+      // Fixed order per tile n:  S^T(n+1) | dV(n) | dK(n) | dP^T(n+1) | dQ(n).  dS^T lives in the columns of
+      // dP^T, so dP^T of the next tile follows dK of this one in the (in-order) tensor pipe; every other
+      // awaited event depends only on instructions issued earlier and has most of a tile of slack.
+      const bool leader = bwd_elect_one();
+      const uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 0, 1);   // A from tensor memory, B MN-major
+      const uint32_t idesc_dq = umma_idesc_bf16(128, DPAD, 1, 1);   // A = dS^T tile (MN-major), B = K (MN-major)
+      // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
+      // field counts 16-byte units).
       const uint64_t k_km = umma_desc_kmajor(smem_u32(sK), kTile, 0), k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
       const uint64_t v_km = umma_desc_kmajor(smem_u32(sV), kTile, 0);
       const uint64_t q_km = umma_desc_kmajor(smem_u32(sQ), kTile, 0), q_mn = umma_desc_mnmajor(smem_u32(sQ), kTile, 0, 0);
       const uint64_t o_km = umma_desc_kmajor(smem_u32(sdO), kTile, 0), o_mn = umma_desc_mnmajor(smem_u32(sdO), kTile, 0, 0);
-      const uint64_t p_mn = umma_desc_mnmajor(smem_u32(sP), kTile, 0, 0);
-      const uint64_t s_mn = umma_desc_mnmajor(smem_u32(sdS), kTile, 0, 0), s_km = umma_desc_kmajor(smem_u32(sdS), kTile, 0);
-      auto issue_sdp = [&](int j) {
-        const uint64_t slot = (uint64_t)((j % kWsRing) * (SLOT_BYTES >> 4));
+      const uint64_t s_mn = umma_desc_mnmajor(smem_u32(sdS), kTile, 0, 0);
+      auto slot_u = [&](int n) { return (uint64_t)((n % kWsRing) * (SLOT_BYTES >> 4)); };
+      auto issue_st = [&](int n) {
+        if (alive) alive = mbar_wait(&cb.qdo_full[n % kWsRing], (n / kWsRing) & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+          const uint64_t su = slot_u(n);
 #pragma unroll
-        for (int kk = 0; kk < DPAD; kk += 16)  // K-major step: 16 elements = 32 bytes = 2 units
-          umma_ss(tmem + COL_S, q_km + slot + (kk >> 3), k_km + (kk >> 3), idesc_qk, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < DPAD; kk += 16)
-          umma_ss(tmem + COL_DP, o_km + slot + (kk >> 3), v_km + (kk >> 3), idesc_qk, kk > 0);
-        umma_commit(&cb.sdp_full);
+          for (int kk = 0; kk < DPAD; kk += 16)  // K-major step: 16 elements = 32 bytes = 2 units
+            umma_ss(tmem + COL_ST, k_km + (kk >> 3), q_km + su + (kk >> 3), idesc_st, kk > 0);
+          umma_commit(&cb.st_full);
+        }
+        __syncwarp();
       };
-      auto issue_kvq = [&](int it) {
-        const uint64_t slot = (uint64_t)((it % kWsRing) * (SLOT_BYTES >> 4));
-        const uint32_t acc = it > 0;
+      auto issue_dpt = [&](int n) {
+        if (leader) {
+          const uint64_t su = slot_u(n);
 #pragma unroll
-        for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO; MN-major step: 16 rows = 2048 bytes = 128 units
-          umma_ss(tmem + COL_DV, p_mn + kk * 8, o_mn + slot + kk * 8, idesc_kv, acc | (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < kTile; kk += 16)  // dK += dS^T Q
-          umma_ss(tmem + COL_DK, s_mn + kk * 8, q_mn + slot + kk * 8, idesc_kv, acc | (kk > 0));
-        umma_commit(&cb.qdo_free[it % kWsRing]);  // the tile's Q and dO rows are no longer needed
-#pragma unroll
-        for (int kk = 0; kk < kTile; kk += 16)  // dQ = dS K; dS K-major over two 64-key panels of 16 KB
-          umma_ss(tmem + COL_DQ, s_km + (kk >> 6) * (kTile * 128 >> 4) + ((kk & 63) >> 3), k_mn + kk * 8, idesc_dq, kk > 0);
-        umma_commit(&cb.kvq_done);
+          for (int kk = 0; kk < DPAD; kk += 16)
+            umma_ss(tmem + COL_DPT, v_km + (kk >> 3), o_km + su + (kk >> 3), idesc_st, kk > 0);
+          umma_commit(&cb.dpt_full);
+        }
+        __syncwarp();
       };
-      // Two streams of work are issued as their inputs become ready, whichever comes first:
-      //   S, dP of tile n    needs the tile's Q/dO in the ring and S/dP of tile n-1 read by the compute warps
-      //   dV, dK, dQ of tile i needs P and dS of tile i in shared memory and dQ of tile i-1 taken by the drain warps
-      int next_sdp = 0, next_kvq = 0;
-      const long long t_start = clock64();
-      while (next_kvq < n_iter) {
-        bool progressed = false;
-        if (next_sdp < n_iter && next_sdp <= next_kvq + 1) {
-          const bool loaded = !alive || (mbar_test(&cb.qdo_full[next_sdp % kWsRing], (next_sdp / kWsRing) & 1) &&
-                                         (next_sdp > 0 || mbar_test(&cb.kv_ready, 0)));
-          const bool freed = next_sdp == 0 || !alive || mbar_test(&cb.sdp_free, (next_sdp - 1) & 1);
-          if (loaded && freed) {
-            fence_async_smem();  // cp.async data of the ring -> visible to the tensor pipe
-            tc_fence_after_sync();
-            WS_TRACE(1, next_sdp, 0);
-            issue_sdp(next_sdp++);
-            progressed = true;
-          }
+      if (n_iter > 0) {
+        if (alive) alive = mbar_wait(&cb.kv_ready, 0, a.status);
+        issue_st(0);
+        issue_dpt(0);
+      }
+      for (int n = 0; n < n_iter; ++n) {
+        const uint64_t su = slot_u(n);
+        const uint32_t acc = n > 0;
+        if (n + 1 < n_iter) {
+          if (alive) alive = mbar_wait(&cb.st_free, n & 1, a.status);
+          issue_st(n + 1);
         }
-        if (next_kvq < next_sdp && (!alive || (mbar_test(&cb.pds_ready, next_kvq & 1) &&
-                                               (next_kvq == 0 || mbar_test(&cb.dq_free, (next_kvq - 1) & 1))))) {
-          tc_fence_after_sync();
-          WS_TRACE(1, next_kvq, 1);
-          issue_kvq(next_kvq++);
-          progressed = true;
+        if (alive) alive = mbar_wait(&cb.p_ready, n & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO; B MN-major step: 16 rows = 2048 bytes = 128 units
+            umma_ts(tmem + COL_DV, tmem + COL_PT + (kk >> 1), o_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
+          umma_commit(&cb.pt_free);
         }
-        if (!progressed) {
-          __nanosleep(32);
-          if (alive && clock64() - t_start > 4000000000ll) {
-            atomicOr(a.status, kErrBarrierTimeout);
-            alive = false;
-          }
+        __syncwarp();
+        if (alive) alive = mbar_wait(&cb.ds_ready, n & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kTile; kk += 16)  // dK += dS^T Q; queries 0-63 at columns 128.., 64-127 at columns 192..
+            umma_ts(tmem + COL_DK, tmem + COL_DPT + (kk >> 6) * 64 + ((kk & 63) >> 1), q_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
+          umma_commit(&cb.qdo_free[n % kWsRing]);  // the tile's Q and dO rows are no longer needed
         }
+        __syncwarp();
+        if (n + 1 < n_iter) issue_dpt(n + 1);
+        if (n > 0 && alive) alive = mbar_wait(&cb.dq_free, (n - 1) & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kTile; kk += 16)  // dQ = dS K; both MN-major: 16 key rows = 2048 bytes = 128 units
+            umma_ss(tmem + COL_DQ, s_mn + kk * 8, k_mn + kk * 8, idesc_dq, kk > 0);
+          umma_commit(&cb.dq_done);
+        }
+        __syncwarp();
       }
     }
-  }
   } else {
     // ================================================================== compute (warps 0-7)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
     const int quad = warp & 3, half = warp >> 2;
-    const int r = quad * 32 + lane;
+    const int r = quad * 32 + lane;  // key row of this thread
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
     for (int it = 0; it < n_iter; ++it) {
       const int ms = it % kWsRing;
+      // queries below qmin are masked for this key: all of them for a key that does not exist, the
+      // earlier ones on the causal diagonal (tile of the key block itself)
+      const bool diag = it >= n_remote && ((it - n_remote) % n_self) == 0;
+      const int qmin = r >= nkeys ? kTile : (diag ? r : 0);
+      const bool unmasked = __all_sync(0xFFFFFFFFu, qmin <= half * 64);
       if (tid == 0) WS_TRACE(0, it, 0);
       alive = warp_wait(&cb.qdo_full[ms], (it / kWsRing) & 1, a.status, alive);  // the tile's metadata is in the slot
+      alive = warp_wait(&cb.st_full, it & 1, a.status, alive);
       if (tid == 0) WS_TRACE(0, it, 1);
-      const float lse2 = cb.lse2[ms][r], delta_s = cb.delta_s[ms][r];
-      const bool diag = it >= n_remote && ((it - n_remote) % n_self) == 0;
-      int klimit = nkeys;
-      if (diag) klimit = min(klimit, r + 1);
-      klimit -= half * 64;  // relative to this thread's first column
-
-      alive = warp_wait(&cb.sdp_full, it & 1, a.status, alive);
-      if (tid == 0) WS_TRACE(0, it, 2);
       tc_fence_after_sync();
-      uint32_t sv[64], dv[64];
+      float p[64];
       {
         uint32_t t0[32], t1[32];
-        tmem_ld32(tlane + COL_S + half * 64, t0);
-        tmem_ld32(tlane + COL_S + half * 64 + 32, t1);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { sv[i] = t0[i]; sv[32 + i] = t1[i]; }
-        tmem_ld32(tlane + COL_DP + half * 64, t0);
-        tmem_ld32(tlane + COL_DP + half * 64 + 32, t1);
+        tmem_ld32(tlane + COL_ST + half * 64, t0);
+        tmem_ld32(tlane + COL_ST + half * 64 + 32, t1);
         tmem_ld_wait();
+        tc_fence_before_sync();
+        warp_arrive(&cb.st_free);  // S^T of the next tile may be formed
+        if (tid == 0) WS_TRACE(0, it, 2);
+        const float4* lse4 = reinterpret_cast<const float4*>(&cb.lse2[ms][half * 64]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { dv[i] = t0[i]; dv[32 + i] = t1[i]; }
+        for (int i = 0; i < 32; i += 4) {
+          const float4 la = lse4[i >> 2], lb = lse4[8 + (i >> 2)];
+          p[i] = bwd_exp2(fmaf(__uint_as_float(t0[i]), a.scale_log2, -la.x));
+          p[i + 1] = bwd_exp2(fmaf(__uint_as_float(t0[i + 1]), a.scale_log2, -la.y));
+          p[i + 2] = bwd_exp2(fmaf(__uint_as_float(t0[i + 2]), a.scale_log2, -la.z));
+          p[i + 3] = bwd_exp2(fmaf(__uint_as_float(t0[i + 3]), a.scale_log2, -la.w));
+          p[32 + i] = bwd_exp2(fmaf(__uint_as_float(t1[i]), a.scale_log2, -lb.x));
+          p[32 + i + 1] = bwd_exp2(fmaf(__uint_as_float(t1[i + 1]), a.scale_log2, -lb.y));
+          p[32 + i + 2] = bwd_exp2(fmaf(__uint_as_float(t1[i + 2]), a.scale_log2, -lb.z));
+          p[32 + i + 3] = bwd_exp2(fmaf(__uint_as_float(t1[i + 3]), a.scale_log2, -lb.w));
+        }
       }
+      if (!unmasked) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (half * 64 + i < qmin) p[i] = 0.f;
+      }
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) pk[i] = bwd_pack_bf16(p[2 * i], p[2 * i + 1]);
+      if (it > 0) alive = warp_wait(&cb.pt_free, (it - 1) & 1, a.status, alive);  // dV of the previous tile has read P^T
+      tmem_st32(tlane + COL_PT + half * 32, pk);
+      tmem_st_wait();
       tc_fence_before_sync();
-      warp_arrive(&cb.sdp_free);  // S and dP may be overwritten by the next tile's products
+      warp_arrive(&cb.p_ready);
       if (tid == 0) WS_TRACE(0, it, 3);
 
-      uint32_t pp[32], ds[32];
-      if (__all_sync(0xFFFFFFFFu, klimit >= 64)) {  // no causal edge and no missing key in this warp's columns
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float p0 = bwd_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
-          const float p1 = bwd_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
-          const float d0 = p0 * fmaf(__uint_as_float(dv[i]), a.scale, -delta_s);
-          const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), a.scale, -delta_s);
-          pp[i >> 1] = bwd_pack_bf16(p0, p1);
-          ds[i >> 1] = bwd_pack_bf16(d0, d1);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          float p0 = bwd_exp2(fmaf(__uint_as_float(sv[i]), a.scale_log2, -lse2));
-          float p1 = bwd_exp2(fmaf(__uint_as_float(sv[i + 1]), a.scale_log2, -lse2));
-          if (i >= klimit) p0 = 0.f;
-          if (i + 1 >= klimit) p1 = 0.f;
-          const float d0 = p0 * fmaf(__uint_as_float(dv[i]), a.scale, -delta_s);
-          const float d1 = p1 * fmaf(__uint_as_float(dv[i + 1]), a.scale, -delta_s);
-          pp[i >> 1] = bwd_pack_bf16(p0, p1);
-          ds[i >> 1] = bwd_pack_bf16(d0, d1);
-        }
-      }
+      alive = warp_wait(&cb.dpt_full, it & 1, a.status, alive);
       if (tid == 0) WS_TRACE(0, it, 4);
-      if (it > 0) {  // previous tile's dV/dK/dQ products are complete: sP/sdS are free
-        alive = warp_wait(&cb.kvq_done, (it - 1) & 1, a.status, alive);
-        if (tid == 0) WS_TRACE(0, it, 5);
-      }
-      if (tid == 0) WS_TRACE(3, it, 0);
+      tc_fence_after_sync();
+      const float4* del4 = reinterpret_cast<const float4*>(&cb.delta_s[ms][half * 64]);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        *reinterpret_cast<uint4*>(sP + sw128_offset(kTile, r, half * 8 + u)) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-        *reinterpret_cast<uint4*>(sdS + sw128_offset(kTile, r, half * 8 + u)) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
+      for (int pc = 0; pc < 2; ++pc) {
+        uint32_t t[32];
+        tmem_ld32(tlane + COL_DPT + half * 64 + pc * 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 dl = del4[pc * 8 + (i >> 2)];
+          const float d0 = p[pc * 32 + i] * fmaf(__uint_as_float(t[i]), a.scale, -dl.x);
+          const float d1 = p[pc * 32 + i + 1] * fmaf(__uint_as_float(t[i + 1]), a.scale, -dl.y);
+          const float d2 = p[pc * 32 + i + 2] * fmaf(__uint_as_float(t[i + 2]), a.scale, -dl.z);
+          const float d3 = p[pc * 32 + i + 3] * fmaf(__uint_as_float(t[i + 3]), a.scale, -dl.w);
+          pk[pc * 16 + (i >> 1)] = bwd_pack_bf16(d0, d1);
+          pk[pc * 16 + (i >> 1) + 1] = bwd_pack_bf16(d2, d3);
+        }
       }
-      if (tid == 0) WS_TRACE(0, it, 6);
+      if (tid == 0) WS_TRACE(0, it, 5);
+      // dS^T: over the first 32 of this thread's own dP^T columns for the dK product, and as a tile row
+      // in shared memory for the dQ product (whose previous run must be over)
+      tmem_st32(tlane + COL_DPT + half * 64, pk);
+      if (it > 0) alive = warp_wait(&cb.dq_done, (it - 1) & 1, a.status, alive);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        *reinterpret_cast<uint4*>(sdS + sw128_offset(kTile, r, half * 8 + u)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+      tmem_st_wait();
       fence_async_smem();
-      warp_arrive(&cb.pds_ready);
-      if (tid == 0) WS_TRACE(0, it, 7);
+      tc_fence_before_sync();
+      warp_arrive(&cb.ds_ready);
+      if (tid == 0) WS_TRACE(0, it, 6);
     }
     if (n_iter > 0) {
-      alive = warp_wait(&cb.kvq_done, (n_iter - 1) & 1, a.status, alive);
+      alive = warp_wait(&cb.dq_done, (n_iter - 1) & 1, a.status, alive);
       tc_fence_after_sync();
       // dK (warps 0-3) and dV (warps 4-7) of the key block: thread = key row
       const bool ok = r < nkeys && alive;
@@ -435,7 +468,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 }
 
 cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st) {
-  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 * 2 + 4 * 4096;
+  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 + 4 * 4096;
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   attn_bwd_ws_kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kWsThreads, smem, st>>>(a);
