@@ -83,10 +83,9 @@ constexpr int kWsRing = 4;       // Q/dO tiles in shared memory
 
 // One arrival per warp: every lane's earlier writes are ordered before it by __syncwarp.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, unsigned* status, bool alive) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0 && alive) ok = mbar_wait(bar, parity, status);
-  __syncwarp();
-  return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+  // every lane polls for itself: a barrier that has already completed costs one shared-memory round trip
+  // instead of a poll, a warp barrier and a shuffle
+  return alive ? mbar_wait(bar, parity, status) : true;
 }
 __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
   __syncwarp();
