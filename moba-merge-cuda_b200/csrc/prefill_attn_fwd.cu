@@ -42,6 +42,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -412,11 +417,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         }
         float mx0 = __uint_as_float(s0[0]), mx1 = __uint_as_float(s1[0]), mx2 = __uint_as_float(s2[0]), mx3 = __uint_as_float(s3[0]);
 #pragma unroll
-        for (int i = 1; i < 32; ++i) {
-          mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
-          mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
-          mx2 = fmaxf(mx2, __uint_as_float(s2[i]));
-          mx3 = fmaxf(mx3, __uint_as_float(s3[i]));
+        for (int i = 0; i < 32; i += 2) {
+          mx0 = max3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+          mx1 = max3(mx1, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+          mx2 = max3(mx2, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+          mx3 = max3(mx3, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
         }
         const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2;
         // The maximum in use is raised only when the row's maximum outgrew it by 2^8; P stays below 2^8.
@@ -446,33 +451,35 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           l_run *= alpha;
         }
         if (row == 0) FWD_TRACE(l, tc, 3);
-        float sum0 = 0.f, sum1 = 0.f;
+        // two elements per instruction where the hardware has a packed form (scale-and-shift, row sum)
+        float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
+        const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), neg2 = make_float2(-m_used, -m_used);
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s0[i]), a.scale_log2, -m_used));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s0[i + 1]), a.scale_log2, -m_used));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(s1[i]), a.scale_log2, -m_used));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(s1[i + 1]), a.scale_log2, -m_used));
-          sum0 += p0 + p1;
-          sum1 += p2 + p3;
-          pk[i >> 1] = pack_bf16(p0, p1);
-          pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+          const float2 xa = __ffma2_rn(make_float2(__uint_as_float(s0[i]), __uint_as_float(s0[i + 1])), sc2, neg2);
+          const float2 xb = __ffma2_rn(make_float2(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1])), sc2, neg2);
+          const float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
+          const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
+          sum0 = __fadd2_rn(sum0, pa);
+          sum1 = __fadd2_rn(sum1, pb);
+          pk[i >> 1] = pack_bf16(pa.x, pa.y);
+          pk[16 + (i >> 1)] = pack_bf16(pb.x, pb.y);
         }
         tmem_st32(tP, pk);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s2[i]), a.scale_log2, -m_used));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s2[i + 1]), a.scale_log2, -m_used));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(s3[i]), a.scale_log2, -m_used));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(s3[i + 1]), a.scale_log2, -m_used));
-          sum0 += p0 + p1;
-          sum1 += p2 + p3;
-          pk[i >> 1] = pack_bf16(p0, p1);
-          pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+          const float2 xa = __ffma2_rn(make_float2(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1])), sc2, neg2);
+          const float2 xb = __ffma2_rn(make_float2(__uint_as_float(s3[i]), __uint_as_float(s3[i + 1])), sc2, neg2);
+          const float2 pa = make_float2(fast_exp2(xa.x), fast_exp2(xa.y));
+          const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
+          sum0 = __fadd2_rn(sum0, pa);
+          sum1 = __fadd2_rn(sum1, pb);
+          pk[i >> 1] = pack_bf16(pa.x, pa.y);
+          pk[16 + (i >> 1)] = pack_bf16(pb.x, pb.y);
         }
         tmem_st32(tP + 32, pk);
-        l_run += sum0 + sum1;
+        l_run += (sum0.x + sum0.y) + (sum1.x + sum1.y);
         if (row == 0) FWD_TRACE(l, tc, 4);
         tmem_st_wait();
         tc_fence_before_sync();
