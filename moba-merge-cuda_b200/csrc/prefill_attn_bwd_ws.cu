@@ -53,8 +53,8 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(PackArgs pa) {
   if (tile >= n_self && (pv.R == 0 || tile - n_self >= a.tile_base[pv.n_chunks * pv.Hkv])) return;
   const int th = a.rowpack[tile * kTile + tid];
   s_th[tid] = th;
-  pa.lsepack[tile * kTile + tid] = th >= 0 ? a.lse[th] * 1.4426950408889634f : INFINITY;
-  pa.deltapack[tile * kTile + tid] = th >= 0 ? a.delta[th] * a.scale : 0.f;
+  pa.lsepack[tile * kTile + tid] = th >= 0 ? -a.lse[th] * 1.4426950408889634f : -INFINITY;
+  pa.deltapack[tile * kTile + tid] = th >= 0 ? -a.delta[th] * a.scale : 0.f;
   __syncthreads();
   uint8_t* odst = reinterpret_cast<uint8_t*>(pa.dopack) + tile * (kTile * 128);
   const int u = tid & 7;
@@ -112,8 +112,8 @@ struct WsSmem {
   uint32_t tmem_slot;
   uint32_t pad;
   __align__(16) int rowth[kWsRing][kTile];      // t*Hq+h of every row of the tile, -1 = padding row
-  __align__(16) float lse2[kWsRing][kTile];     // LSE in the log2 domain (+inf for padding rows)
-  __align__(16) float delta_s[kWsRing][kTile];  // rowsum(dO*O) / sqrt(D)
+  __align__(16) float lse2[kWsRing][kTile];     // -LSE in the log2 domain (-inf for padding rows)
+  __align__(16) float delta_s[kWsRing][kTile];  // -rowsum(dO*O) / sqrt(D)
 };
 static_assert(sizeof(WsSmem) <= 8192, "control block must fit its reservation");
 
@@ -375,17 +375,16 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         warp_arrive(&cb.st_free);  // S^T of the next tile may be formed
         if (tid == 0) WS_TRACE(0, it, 2);
         const float4* lse4 = reinterpret_cast<const float4*>(&cb.lse2[ms][half * 64]);
+        const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
+        for (int i = 0; i < 32; i += 4) {  // two elements per instruction for the scale-and-shift
           const float4 la = lse4[i >> 2], lb = lse4[8 + (i >> 2)];
-          p[i] = bwd_exp2(fmaf(__uint_as_float(t0[i]), a.scale_log2, -la.x));
-          p[i + 1] = bwd_exp2(fmaf(__uint_as_float(t0[i + 1]), a.scale_log2, -la.y));
-          p[i + 2] = bwd_exp2(fmaf(__uint_as_float(t0[i + 2]), a.scale_log2, -la.z));
-          p[i + 3] = bwd_exp2(fmaf(__uint_as_float(t0[i + 3]), a.scale_log2, -la.w));
-          p[32 + i] = bwd_exp2(fmaf(__uint_as_float(t1[i]), a.scale_log2, -lb.x));
-          p[32 + i + 1] = bwd_exp2(fmaf(__uint_as_float(t1[i + 1]), a.scale_log2, -lb.y));
-          p[32 + i + 2] = bwd_exp2(fmaf(__uint_as_float(t1[i + 2]), a.scale_log2, -lb.z));
-          p[32 + i + 3] = bwd_exp2(fmaf(__uint_as_float(t1[i + 3]), a.scale_log2, -lb.w));
+          const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(t0[i]), __uint_as_float(t0[i + 1])), sc2, make_float2(la.x, la.y));
+          const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(t0[i + 2]), __uint_as_float(t0[i + 3])), sc2, make_float2(la.z, la.w));
+          const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(t1[i]), __uint_as_float(t1[i + 1])), sc2, make_float2(lb.x, lb.y));
+          const float2 x3 = __ffma2_rn(make_float2(__uint_as_float(t1[i + 2]), __uint_as_float(t1[i + 3])), sc2, make_float2(lb.z, lb.w));
+          p[i] = bwd_exp2(x0.x); p[i + 1] = bwd_exp2(x0.y); p[i + 2] = bwd_exp2(x1.x); p[i + 3] = bwd_exp2(x1.y);
+          p[32 + i] = bwd_exp2(x2.x); p[32 + i + 1] = bwd_exp2(x2.y); p[32 + i + 2] = bwd_exp2(x3.x); p[32 + i + 3] = bwd_exp2(x3.y);
         }
       }
       if (!unmasked) {
@@ -415,12 +414,13 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 dl = del4[pc * 8 + (i >> 2)];
-          const float d0 = p[pc * 32 + i] * fmaf(__uint_as_float(t[i]), a.scale, -dl.x);
-          const float d1 = p[pc * 32 + i + 1] * fmaf(__uint_as_float(t[i + 1]), a.scale, -dl.y);
-          const float d2 = p[pc * 32 + i + 2] * fmaf(__uint_as_float(t[i + 2]), a.scale, -dl.z);
-          const float d3 = p[pc * 32 + i + 3] * fmaf(__uint_as_float(t[i + 3]), a.scale, -dl.w);
-          pk[pc * 16 + (i >> 1)] = bwd_pack_bf16(d0, d1);
-          pk[pc * 16 + (i >> 1) + 1] = bwd_pack_bf16(d2, d3);
+          const float2 sc = make_float2(a.scale, a.scale);
+          const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(t[i]), __uint_as_float(t[i + 1])), sc, make_float2(dl.x, dl.y));
+          const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3])), sc, make_float2(dl.z, dl.w));
+          const float2 d0 = __fmul2_rn(make_float2(p[pc * 32 + i], p[pc * 32 + i + 1]), e0);
+          const float2 d1 = __fmul2_rn(make_float2(p[pc * 32 + i + 2], p[pc * 32 + i + 3]), e1);
+          pk[pc * 16 + (i >> 1)] = bwd_pack_bf16(d0.x, d0.y);
+          pk[pc * 16 + (i >> 1) + 1] = bwd_pack_bf16(d1.x, d1.y);
         }
       }
       if (tid == 0) WS_TRACE(0, it, 5);
