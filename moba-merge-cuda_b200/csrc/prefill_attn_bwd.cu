@@ -17,17 +17,19 @@
 
 namespace moba {
 
-// delta[row] = sum_d dO[row,d] * O[row,d]; one warp per (token, head) row.
+// delta[row] = sum_d dO[row,d] * O[row,d].  LPR lanes share a (token, head) row, 16 bytes of it each, so
+// every lane of a warp has work at any head dimension (LPR = 4, 8, 16 or 32: smallest power of two >= D/8).
+template <int LPR>
 __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __restrict__ out,
                                                         const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
                                                         long long rows, int D) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  constexpr int RPW = 32 / LPR;  // rows per warp
+  const int lane = threadIdx.x & 31, sub = lane % LPR;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
   float s = 0.f;
-  if (lane * 8 < D) {
-    const uint4 a = *reinterpret_cast<const uint4*>(out + row * D + lane * 8);
-    const uint4 b = *reinterpret_cast<const uint4*>(dout + row * D + lane * 8);
+  if (row < rows && sub * 8 < D) {
+    const uint4 a = *reinterpret_cast<const uint4*>(out + row * D + sub * 8);
+    const uint4 b = *reinterpret_cast<const uint4*>(dout + row * D + sub * 8);
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -36,8 +38,8 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __r
     }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-  if (lane == 0) delta[row] = s;
+  for (int o = LPR / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+  if (sub == 0 && row < rows) delta[row] = s;
 }
 
 __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
@@ -313,8 +315,15 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   float* delta = static_cast<float*>(scratch);
   float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(scratch) + align256((size_t)rows * 4));
   if (cudaMemsetAsync(dq_acc, 0, (size_t)rows * d->dim * 4, st) != cudaSuccess) return MOBA_ERR_CUDA;
-  bwd_delta_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(out),
-                                                               static_cast<const __nv_bfloat16*>(dout), delta, rows, d->dim);
+  {
+    const __nv_bfloat16* o16 = static_cast<const __nv_bfloat16*>(out);
+    const __nv_bfloat16* do16 = static_cast<const __nv_bfloat16*>(dout);
+    const int units = d->dim / 8;
+    if (units <= 4) bwd_delta_kernel<4><<<(unsigned)((rows + 63) / 64), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
+    else if (units <= 8) bwd_delta_kernel<8><<<(unsigned)((rows + 31) / 32), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
+    else if (units <= 16) bwd_delta_kernel<16><<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
+    else bwd_delta_kernel<32><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
+  }
   BwdArgs a;
   a.pv = make_view(*d);
   a.q = static_cast<const __nv_bfloat16*>(q);
