@@ -39,6 +39,8 @@ WORKLOADS = {
     "small": dict(name="gqa_prefill_1x32768_h14kv2_d64_c2048_k3", lens=(32768,), hq=14, hkv=2, dim=64, chunk=2048, topk=3),
 }
 WORKLOAD = WORKLOADS["cfg2"]
+# DRAM bytes of one backward launch on one 32768-token sequence, from the committed ncu summary
+BWD_DRAM_BYTES_PER_SEQUENCE = 581.2e6 + 183.5e6
 METRIC = "moba_prefill_fwd_bwd_attended_tflops"
 UNIT = "TFLOP/s"
 
@@ -401,7 +403,10 @@ def run_ours(args):
                     gpu_launches=13 * args.steps,  # route 5, pack 2, forward 2, backward 4 (memsets not counted)
                     roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel", achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
-                                  traffic=None, ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
+                                  traffic=BWD_DRAM_BYTES_PER_SEQUENCE * len(w["lens"]) if w["name"].startswith("gqa_prefill_") and w["lens"][0] == 32768 else None,
+                                  traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on one 32768-token "
+                                                 "sequence (profiles/attn_bwd_ws_kernel_d64_1x32768.md), times the number of sequences",
+                                  ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
         if dec is not None:
             sec = dec["ms_per_step"] * 1e-3
             line["decode"] = dict(workload=DECODE["name"], requests=dec["requests"], steps=args.decode_steps,

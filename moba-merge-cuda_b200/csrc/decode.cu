@@ -465,7 +465,8 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
         pf[0] = dec_pack_bf16(p00, p01); pf[1] = dec_pack_bf16(p02, p03);
         pf[2] = dec_pack_bf16(p10, p11); pf[3] = dec_pack_bf16(p12, p13);
       }
-      // ---- O = O * alpha + P V
+      // ---- O = O * alpha + P V; the running maxima rarely move after the first tiles, and alpha == 1 needs no pass over O
+      const bool rescale = __any_sync(0xFFFFFFFFu, al0 != 1.f || al1 != 1.f);
 #pragma unroll
       for (int dp = 0; dp < DT / 2; ++dp) {
         uint32_t b[4];
@@ -474,7 +475,7 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
 #pragma unroll
         for (int h2 = 0; h2 < 2; ++h2) {
           float (&acc)[4] = o[dp * 2 + h2];
-          acc[0] *= al0; acc[1] *= al0; acc[2] *= al1; acc[3] *= al1;
+          if (rescale) { acc[0] *= al0; acc[1] *= al0; acc[2] *= al1; acc[3] *= al1; }
           mma_bf16_16816(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
         }
       }
