@@ -293,9 +293,9 @@ extern "C" size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d) {
   if (validate_desc(d) != MOBA_OK) return 0;
   const size_t rows = (size_t)d->total_tokens * d->hq;
   size_t bytes = align256(rows * 4) + align256(rows * d->dim * 4);
-  if (d->dim <= 64 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP)) {
+  if (d->dim <= 128 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP)) {
     const size_t tiles = (size_t)pack_q_tiles(*d);
-    bytes += align256(tiles * kTile * 64 * 2) + 2 * align256(tiles * kTile * 4);
+    bytes += align256(tiles * kTile * pack_dpad(*d) * 2) + 2 * align256(tiles * kTile * 4);
   }
   return bytes;
 }
@@ -350,11 +350,11 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.status = status;
   a.scale = (float)(1.0 / sqrt((double)d->dim));
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)d->dim));
-  const bool ws = d->dim <= 64 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP);
+  const bool ws = d->dim <= 128 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP);
   if (ws) {
     const size_t tiles = (size_t)pack_q_tiles(*d);
     char* p = reinterpret_cast<char*>(dq_acc) + align256((size_t)rows * d->dim * 4);
-    void* dopack = p; p += align256(tiles * kTile * 64 * 2);
+    void* dopack = p; p += align256(tiles * kTile * pack_dpad(*d) * 2);
     float* lsepack = reinterpret_cast<float*>(p); p += align256(tiles * kTile * 4);
     float* deltapack = reinterpret_cast<float*>(p);
     const PackState ps = carve_pack_state(*d, const_cast<void*>(route_state));
@@ -365,7 +365,8 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
     a.lsepack = lsepack; a.deltapack = deltapack;
   }
   prof_begin(kProfBwdMain, st);
-  cudaError_t e = d->dim > 64 ? launch_bwd<128>(a, st) : (ws ? launch_bwd_ws(a, st) : launch_bwd<64>(a, st));
+  cudaError_t e = ws ? (d->dim > 64 ? launch_bwd_ws128(a, st) : launch_bwd_ws(a, st))
+                     : (d->dim > 64 ? launch_bwd<128>(a, st) : launch_bwd<64>(a, st));
   prof_end(kProfBwdMain, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
   const long long n8 = rows * d->dim / 8;

@@ -41,6 +41,7 @@ struct PackArgs {
   __nv_bfloat16* dopack;
   float* lsepack;
   float* deltapack;
+  int dpad;  // 64 or 128 columns per packed row
 };
 
 __global__ void __launch_bounds__(128) bwd_pack_kernel(PackArgs pa) {
@@ -56,11 +57,10 @@ __global__ void __launch_bounds__(128) bwd_pack_kernel(PackArgs pa) {
   pa.lsepack[tile * kTile + tid] = th >= 0 ? -a.lse[th] * 1.4426950408889634f : -INFINITY;
   pa.deltapack[tile * kTile + tid] = th >= 0 ? -a.delta[th] * a.scale : 0.f;
   __syncthreads();
-  uint8_t* odst = reinterpret_cast<uint8_t*>(pa.dopack) + tile * (kTile * 128);
-  const int u = tid & 7;
-#pragma unroll 4
-  for (int x = 0; x < 8; ++x) {
-    const int row = (tid >> 3) + 16 * x;
+  const int upr = pa.dpad >> 3;
+  uint8_t* odst = reinterpret_cast<uint8_t*>(pa.dopack) + tile * ((size_t)kTile * pa.dpad * 2);
+  for (int i = tid; i < kTile * upr; i += 128) {
+    const int row = i / upr, u = i - row * upr;
     const int rth = s_th[row];
     uint4 ov = make_uint4(0, 0, 0, 0);
     if (rth >= 0 && u * 8 < pv.D) ov = *reinterpret_cast<const uint4*>(a.dout + (long long)rth * pv.D + u * 8);
@@ -74,28 +74,13 @@ cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, flo
   pa.dopack = static_cast<__nv_bfloat16*>(dopack);
   pa.lsepack = lsepack;
   pa.deltapack = deltapack;
+  pa.dpad = a.pv.D <= 64 ? 64 : 128;
   bwd_pack_kernel<<<(unsigned)tiles, 128, 0, st>>>(pa);
   return cudaGetLastError();
 }
 
 constexpr int kWsThreads = 512;  // 8 compute warps, MMA warp, producer warp (+2 idle), 4 dQ drain warps
 constexpr int kWsRing = 4;       // Q/dO tiles in shared memory
-
-// One arrival per warp: every lane's earlier writes are ordered before it by __syncwarp.
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, unsigned* status, bool alive) {
-  // every lane polls for itself: a barrier that has already completed costs one shared-memory round trip
-  // instead of a poll, a warp barrier and a shuffle
-  return alive ? mbar_wait(bar, parity, status) : true;
-}
-__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
-  __syncwarp();
-  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
-}
-__device__ __forceinline__ bool bwd_elect_one() {
-  uint32_t pred;
-  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-  return pred != 0;
-}
 
 struct WsSmem {
   uint64_t st_full;    // S^T of the tile is in tensor memory (tcgen05.commit)

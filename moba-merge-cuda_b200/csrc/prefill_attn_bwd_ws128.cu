@@ -1,0 +1,379 @@
+// Warp-specialised prefill backward for 64 < head_dim <= 128.  Same scheme as prefill_attn_bwd_ws.cu
+// (one CTA owns 128 keys of one (chunk, kv head); scores transposed, keys on the tensor-memory lanes;
+// P^T and dS^T are tensor-memory operands of the dV and dK products), with the geometry that fits the
+// 512 tensor-memory columns at this head dimension: query tiles are taken 64 rows at a time, and dQ is
+// formed transposed,
+//     S^T[128 keys, 64 q] = K Q^T,  dP^T = V dO^T,  dV[128, D] += P^T dO,  dK[128, D] += dS^T Q,
+//     dQ^T[D, 64 q] = K^T dS^T,
+// with the head dimension on the tensor-memory lanes; the drain warps turn it 16 query rows at a time
+// through a 2 KB buffer so that vector reductions cover whole 128-byte lines of the FP32 accumulator.
+// Tensor memory: S^T 0-63, dP^T 64-127 (dS^T as packed bf16 over the first columns of each thread's own
+// range), dV 128-255, dK 256-383, dQ^T 384-447, P^T 448-479.
+// Shared memory: K and V images (32 KB each), a 4-slot ring of (Q, dO) half tiles (64 rows x 128 columns
+// each, 16 KB), the dS^T tile (128 key rows x 64 query columns, 16 KB).
+#include "prefill_bwd.cuh"
+
+namespace moba {
+
+namespace {
+
+constexpr int kThreads = 512;  // 8 compute warps, MMA warp, producer warp (+2 idle), 4 dQ drain warps
+constexpr int kRing = 4;
+constexpr int kQRows = 64;     // query rows per step
+
+struct Smem128 {
+  uint64_t st_full, st_free, p_ready, pt_free, dpt_full, ds_ready, dq_done, dq_free, kv_ready;
+  uint64_t qdo_full[kRing], qdo_free[kRing];
+  uint32_t tmem_slot;
+  uint32_t pad;
+  __align__(16) int rowth[kRing][kQRows];      // t*Hq+h of every query row of the step, -1 = padding row
+  __align__(16) float lse2[kRing][kQRows];     // -LSE in the log2 domain (-inf for padding rows)
+  __align__(16) float delta_s[kRing][kQRows];  // -rowsum(dO*O) / sqrt(D)
+};
+static_assert(sizeof(Smem128) <= 4096, "control block must fit its reservation");
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) {
+  constexpr int DPAD = 128;
+  constexpr int KV_BYTES = kTile * DPAD * 2;      // 32 KB: two 64-column panels of 128 rows
+  constexpr int HALF_BYTES = kQRows * DPAD * 2;   // 16 KB: two 64-column panels of 64 rows
+  constexpr int PANEL_BYTES = kQRows * 128;       // 8 KB
+  constexpr int SLOT_BYTES = 2 * HALF_BYTES;      // Q half tile followed by dO half tile
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256, COL_DQT = 384, COL_PT = 448;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Smem128& cb = *reinterpret_cast<Smem128*>(smem);
+  uint8_t* sK = smem + 4096;
+  uint8_t* sV = sK + KV_BYTES;
+  uint8_t* sQ = sV + KV_BYTES;
+  uint8_t* sdO = sQ + HALF_BYTES;
+  uint8_t* sdS = sQ + kRing * SLOT_BYTES;  // dS^T: 128 key rows x 64 query columns bf16 (one panel)
+  uint8_t* sStage = sdS + kTile * kQRows * 2;  // 4 x 2 KB: transposition buffers of the drain warps
+
+  const PrefillView& pv = a.pv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int D = pv.D;
+  const int kblock = a.kv_order[blockIdx.x];
+  const int g = blockIdx.y;
+  const int c = pv.qtile_chunk[kblock];
+  const int k0 = pv.qtile_tok0[kblock];
+  const int chunk_begin = pv.chunk_start[c], chunk_end = pv.chunk_start[c + 1];
+  const int nkeys = min(kTile, chunk_end - k0);
+  const int kb = (k0 - chunk_begin) / kTile;
+  const int tiles_in_chunk = (chunk_end - chunk_begin + kTile - 1) / kTile;
+  const int n_self = tiles_in_chunk - kb;
+  int remote_rows = 0;
+  if (pv.R > 0) remote_rows = a.seg_base[c * pv.Hq + (g + 1) * pv.G] - a.seg_base[c * pv.Hq + g * pv.G];
+  const int n_remote = (remote_rows + kTile - 1) / kTile;
+  const int n_tiles = pv.G * n_self + n_remote;
+  const int n_iter = 2 * n_tiles;  // two 64-row steps per query tile
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (tid == 0) atomicOr(a.status, kErrBadIndex);
+    return;
+  }
+  if (tid == 0) {
+    mbar_init(&cb.st_full, 1);
+    mbar_init(&cb.st_free, 8);
+    mbar_init(&cb.p_ready, 8);
+    mbar_init(&cb.pt_free, 1);
+    mbar_init(&cb.dpt_full, 1);
+    mbar_init(&cb.ds_ready, 8);
+    mbar_init(&cb.dq_done, 1);
+    mbar_init(&cb.dq_free, 4);
+    mbar_init(&cb.kv_ready, 1);
+    for (int i = 0; i < kRing; ++i) { mbar_init(&cb.qdo_full[i], 1); mbar_init(&cb.qdo_free[i], 5); }
+    mbar_fence_init();
+  }
+  if (warp == 0) tmem_alloc(&cb.tmem_slot, TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = cb.tmem_slot;
+  bool alive = true;
+
+  if (warp >= 12) {
+    // ================================================================== dQ drain (warps 12-15)
+    // dQ^T has the head dimension on the lanes: a warp owns 32 consecutive dimensions, every thread the
+    // 64 query rows of its dimension.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    const int quad = warp & 3;
+    float* stage = reinterpret_cast<float*>(sStage + quad * 2048);
+    const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
+    for (int it = 0; it < n_iter; ++it) {
+      const int slot = it % kRing;
+      alive = warp_wait(&cb.qdo_full[slot], (it / kRing) & 1, a.status, alive);
+      const int th0 = cb.rowth[slot][lane], th1 = cb.rowth[slot][32 + lane];
+      warp_arrive(&cb.qdo_free[slot]);
+      alive = warp_wait(&cb.dq_done, it & 1, a.status, alive);
+      tc_fence_after_sync();
+      uint32_t v0[32], v1[32];
+      tmem_ld32(tlane + COL_DQT, v0);
+      tmem_ld32(tlane + COL_DQT + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      warp_arrive(&cb.dq_free);
+      // 16 query rows at a time through a 2 KB buffer: written one dimension per lane, read back four
+      // dimensions per lane, so that one vector reduction covers four whole 128-byte lines (scalar
+      // reductions run at a quarter of the rate)
+#pragma unroll
+      for (int piece = 0; piece < 4; ++piece) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          stage[i * 32 + lane] = piece < 2 ? __uint_as_float(v0[(piece & 1) * 16 + i]) : __uint_as_float(v1[(piece & 1) * 16 + i]);
+        __syncwarp();
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int ql = (lane >> 3) + 4 * x;                 // query row inside the piece
+          const int qi = (piece & 1) * 16 + ql;               // inside its group of 32
+          const int rth = __shfl_sync(0xFFFFFFFFu, piece < 2 ? th0 : th1, qi);
+          const float4 w = *reinterpret_cast<const float4*>(stage + ql * 32 + (lane & 7) * 4);
+          const int col = quad * 32 + (lane & 7) * 4;
+          if (rth >= 0 && alive && col < D) red_add_v4(a.dq_acc + (long long)rth * D + col, w.x, w.y, w.z, w.w);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 9) {
+      // ================================================================== producer
+      if (lane == 0) {
+        {  // stationary K and V images of the key block
+          const size_t kvoff = ((size_t)kblock * pv.Hkv + g) * KV_BYTES;
+          mbar_arrive_expect_tx(&cb.kv_ready, 2 * KV_BYTES);
+          bulk_load(sK, reinterpret_cast<const uint8_t*>(a.kpack) + kvoff, KV_BYTES, &cb.kv_ready);
+          bulk_load(sV, reinterpret_cast<const uint8_t*>(a.vpack) + kvoff, KV_BYTES, &cb.kv_ready);
+        }
+        const long long self_tiles = (long long)pv.n_qtiles * pv.Hq;
+        const long long remote_tile0 = pv.R > 0 ? self_tiles + a.tile_base[c * pv.Hkv + g] : 0;
+        for (int j = 0; j < n_iter; ++j) {
+          const int b = j % kRing, jt = j >> 1, sub = j & 1;
+          long long tile;
+          if (jt < n_remote) {
+            // the key blocks of a chunk walk the same expert list at the same time, a couple of tiles apart
+            int jr = jt + (kb * 2) % n_remote;
+            if (jr >= n_remote) jr -= n_remote;
+            tile = remote_tile0 + jr;
+          } else {
+            const int s = jt - n_remote;
+            const int hl = s / n_self, i = kb + (s - hl * n_self);
+            tile = (long long)(kblock - kb + i) * pv.Hq + g * pv.G + hl;  // query tiles of a chunk are consecutive
+          }
+          if (j >= kRing && alive) alive = mbar_wait(&cb.qdo_free[b], ((j / kRing) - 1) & 1, a.status);
+          mbar_arrive_expect_tx(&cb.qdo_full[b], 2 * HALF_BYTES + 3 * kQRows * 4);
+          // rows [64 sub, 64 sub + 64) of both 64-column panels of the packed 128-row images
+          const uint8_t* qsrc = reinterpret_cast<const uint8_t*>(a.qpack) + tile * KV_BYTES + sub * PANEL_BYTES;
+          const uint8_t* osrc = reinterpret_cast<const uint8_t*>(a.dopack) + tile * KV_BYTES + sub * PANEL_BYTES;
+          uint8_t* qdst = sQ + b * SLOT_BYTES;
+          uint8_t* odst = sdO + b * SLOT_BYTES;
+          bulk_load(qdst, qsrc, PANEL_BYTES, &cb.qdo_full[b]);
+          bulk_load(qdst + PANEL_BYTES, qsrc + kTile * 128, PANEL_BYTES, &cb.qdo_full[b]);
+          bulk_load(odst, osrc, PANEL_BYTES, &cb.qdo_full[b]);
+          bulk_load(odst + PANEL_BYTES, osrc + kTile * 128, PANEL_BYTES, &cb.qdo_full[b]);
+          const long long moff = tile * kTile + sub * kQRows;
+          bulk_load(cb.rowth[b], a.rowpack + moff, kQRows * 4, &cb.qdo_full[b]);
+          bulk_load(cb.lse2[b], a.lsepack + moff, kQRows * 4, &cb.qdo_full[b]);
+          bulk_load(cb.delta_s[b], a.deltapack + moff, kQRows * 4, &cb.qdo_full[b]);
+        }
+      }
+    } else if (warp == 8) {
+      // ================================================================== MMA issue
+      // Fixed order per step n:  S^T(n+1) | dV(n) | dK(n) | dP^T(n+1) | dQ^T(n).
+      const bool leader = bwd_elect_one();
+      const uint32_t idesc_st = umma_idesc_bf16(128, kQRows, 0, 0);   // K-major x K-major, N = 64 queries
+      const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 0, 1);     // A from tensor memory, B MN-major, N = 128
+      const uint32_t idesc_dq = umma_idesc_bf16(128, kQRows, 1, 1);   // A = K (MN-major), B = dS^T tile (MN-major)
+      // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
+      // field counts 16-byte units): a K-major step of 16 elements is 2 units inside a 64-column panel,
+      // an MN-major step of 16 rows is 128 units.
+      const uint64_t k_km = umma_desc_kmajor(smem_u32(sK), kTile, 0), k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
+      const uint64_t v_km = umma_desc_kmajor(smem_u32(sV), kTile, 0);
+      const uint64_t q_km = umma_desc_kmajor(smem_u32(sQ), kQRows, 0), q_mn = umma_desc_mnmajor(smem_u32(sQ), kQRows, 0, 0);
+      const uint64_t o_km = umma_desc_kmajor(smem_u32(sdO), kQRows, 0), o_mn = umma_desc_mnmajor(smem_u32(sdO), kQRows, 0, 0);
+      const uint64_t s_mn = umma_desc_mnmajor(smem_u32(sdS), kTile, 0, 0);
+      constexpr uint32_t KV_PANEL_U = (kTile * 128) >> 4, Q_PANEL_U = (kQRows * 128) >> 4;
+      auto slot_u = [&](int n) { return (uint64_t)((n % kRing) * (SLOT_BYTES >> 4)); };
+      auto issue_st = [&](int n) {
+        if (alive) alive = mbar_wait(&cb.qdo_full[n % kRing], (n / kRing) & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+          const uint64_t su = slot_u(n);
+#pragma unroll
+          for (int kk = 0; kk < DPAD; kk += 16)
+            umma_ss(tmem + COL_ST, k_km + (kk >> 6) * KV_PANEL_U + ((kk & 63) >> 3), q_km + su + (kk >> 6) * Q_PANEL_U + ((kk & 63) >> 3),
+                    idesc_st, kk > 0);
+          umma_commit(&cb.st_full);
+        }
+        __syncwarp();
+      };
+      auto issue_dpt = [&](int n) {
+        if (leader) {
+          const uint64_t su = slot_u(n);
+#pragma unroll
+          for (int kk = 0; kk < DPAD; kk += 16)
+            umma_ss(tmem + COL_DPT, v_km + (kk >> 6) * KV_PANEL_U + ((kk & 63) >> 3), o_km + su + (kk >> 6) * Q_PANEL_U + ((kk & 63) >> 3),
+                    idesc_st, kk > 0);
+          umma_commit(&cb.dpt_full);
+        }
+        __syncwarp();
+      };
+      if (n_iter > 0) {
+        if (alive) alive = mbar_wait(&cb.kv_ready, 0, a.status);
+        issue_st(0);
+        issue_dpt(0);
+      }
+      for (int n = 0; n < n_iter; ++n) {
+        const uint32_t acc = n > 0;
+        const uint64_t su = slot_u(n);
+        if (n + 1 < n_iter) {
+          if (alive) alive = mbar_wait(&cb.st_free, n & 1, a.status);
+          issue_st(n + 1);
+        }
+        if (alive) alive = mbar_wait(&cb.p_ready, n & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kQRows; kk += 16)  // dV += P^T dO over the 64 query rows of the step
+            umma_ts(tmem + COL_DV, tmem + COL_PT + (kk >> 1), o_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
+          umma_commit(&cb.pt_free);
+        }
+        __syncwarp();
+        if (alive) alive = mbar_wait(&cb.ds_ready, n & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kQRows; kk += 16)  // dK += dS^T Q; queries 0-31 at columns 64.., 32-63 at columns 96..
+            umma_ts(tmem + COL_DK, tmem + COL_DPT + (kk >> 5) * 32 + ((kk & 31) >> 1), q_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
+          umma_commit(&cb.qdo_free[n % kRing]);  // the step's Q and dO rows are no longer needed
+        }
+        __syncwarp();
+        if (n + 1 < n_iter) issue_dpt(n + 1);
+        if (n > 0 && alive) alive = mbar_wait(&cb.dq_free, (n - 1) & 1, a.status);
+        tc_fence_after_sync();
+        if (leader) {
+#pragma unroll
+          for (int kk = 0; kk < kTile; kk += 16)  // dQ^T = K^T dS^T, contraction over the 128 keys
+            umma_ss(tmem + COL_DQT, k_mn + kk * 8, s_mn + kk * 8, idesc_dq, kk > 0);
+          umma_commit(&cb.dq_done);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ================================================================== compute (warps 0-7)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane;  // key row of this thread; its query columns are [32 half, 32 half + 32)
+    const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
+    for (int it = 0; it < n_iter; ++it) {
+      const int ms = it % kRing, jt = it >> 1, sub = it & 1;
+      // queries below qmin (index inside the 128-row tile) are masked for this key
+      const bool diag = jt >= n_remote && ((jt - n_remote) % n_self) == 0;
+      const int qmin = r >= nkeys ? kTile : (diag ? r : 0);
+      const int q0 = sub * kQRows + half * 32;  // first query of this thread's columns
+      const bool unmasked = __all_sync(0xFFFFFFFFu, qmin <= q0);
+      alive = warp_wait(&cb.qdo_full[ms], (it / kRing) & 1, a.status, alive);
+      alive = warp_wait(&cb.st_full, it & 1, a.status, alive);
+      tc_fence_after_sync();
+      float p[32];
+      {
+        uint32_t t[32];
+        tmem_ld32(tlane + COL_ST + half * 32, t);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        warp_arrive(&cb.st_free);
+        const float4* lse4 = reinterpret_cast<const float4*>(&cb.lse2[ms][half * 32]);
+        const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 la = lse4[i >> 2];
+          const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(t[i]), __uint_as_float(t[i + 1])), sc2, make_float2(la.x, la.y));
+          const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3])), sc2, make_float2(la.z, la.w));
+          p[i] = bwd_exp2(x0.x); p[i + 1] = bwd_exp2(x0.y); p[i + 2] = bwd_exp2(x1.x); p[i + 3] = bwd_exp2(x1.y);
+        }
+      }
+      if (!unmasked) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (q0 + i < qmin) p[i] = 0.f;
+      }
+      uint32_t pk[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = bwd_pack_bf16(p[2 * i], p[2 * i + 1]);
+      if (it > 0) alive = warp_wait(&cb.pt_free, (it - 1) & 1, a.status, alive);  // dV of the previous step has read P^T
+      tmem_st16(tlane + COL_PT + half * 16, pk);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      warp_arrive(&cb.p_ready);
+
+      alive = warp_wait(&cb.dpt_full, it & 1, a.status, alive);
+      tc_fence_after_sync();
+      {
+        uint32_t t[32];
+        tmem_ld32(tlane + COL_DPT + half * 32, t);
+        tmem_ld_wait();
+        const float4* del4 = reinterpret_cast<const float4*>(&cb.delta_s[ms][half * 32]);
+        const float2 sc = make_float2(a.scale, a.scale);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 dl = del4[i >> 2];
+          const float2 e0 = __ffma2_rn(make_float2(__uint_as_float(t[i]), __uint_as_float(t[i + 1])), sc, make_float2(dl.x, dl.y));
+          const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3])), sc, make_float2(dl.z, dl.w));
+          const float2 d0 = __fmul2_rn(make_float2(p[i], p[i + 1]), e0);
+          const float2 d1 = __fmul2_rn(make_float2(p[i + 2], p[i + 3]), e1);
+          pk[i >> 1] = bwd_pack_bf16(d0.x, d0.y);
+          pk[(i >> 1) + 1] = bwd_pack_bf16(d1.x, d1.y);
+        }
+      }
+      // dS^T: over the first 16 of this thread's own dP^T columns for the dK product, and as a tile row in
+      // shared memory for the dQ^T product (whose previous run must be over)
+      tmem_st16(tlane + COL_DPT + half * 32, pk);
+      if (it > 0) alive = warp_wait(&cb.dq_done, (it - 1) & 1, a.status, alive);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        *reinterpret_cast<uint4*>(sdS + sw128_offset(kTile, r, half * 4 + u)) = make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
+      tmem_st_wait();
+      fence_async_smem();
+      tc_fence_before_sync();
+      warp_arrive(&cb.ds_ready);
+    }
+    if (n_iter > 0) {
+      alive = warp_wait(&cb.dq_done, (n_iter - 1) & 1, a.status, alive);
+      tc_fence_after_sync();
+      // dK (warps 0-3) and dV (warps 4-7) of the key block: thread = key row
+      const bool ok = r < nkeys && alive;
+      __nv_bfloat16* dst = (half == 0 ? a.dk : a.dv) + ((long long)(k0 + r) * pv.Hkv + g) * D;
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) {
+        uint32_t v[32];
+        tmem_ld32(tlane + (half == 0 ? COL_DK : COL_DV) + pc * 32, v);
+        tmem_ld_wait();
+        if (ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            if (pc * 32 + i < D)
+              *reinterpret_cast<uint4*>(dst + pc * 32 + i) =
+                  make_uint4(bwd_pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                             bwd_pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                             bwd_pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                             bwd_pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_free(tmem, TMEM_COLS);
+}
+
+cudaError_t launch_bwd_ws128(const BwdArgs& a, cudaStream_t st) {
+  const size_t smem = 4096 + 2 * (size_t)kTile * 128 * 2 + (size_t)kRing * 2 * kQRows * 128 * 2 + (size_t)kTile * kQRows * 2 + 4 * 2048;
+  cudaError_t e = cudaFuncSetAttribute(attn_bwd_ws128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  attn_bwd_ws128_kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kThreads, smem, st>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace moba

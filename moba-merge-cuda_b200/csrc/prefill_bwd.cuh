@@ -47,6 +47,24 @@ struct BwdArgs {
 };
 
 // Warp-specialised backward for head_dim <= 64 (prefill_attn_bwd_ws.cu).
+// ---- small helpers shared by the warp-specialised kernels
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, unsigned* status, bool alive) {
+  // every lane polls for itself: a barrier that has already completed costs one shared-memory round trip
+  // instead of a poll, a warp barrier and a shuffle
+  return alive ? mbar_wait(bar, parity, status) : true;
+}
+// One arrival per warp: every lane's earlier writes are ordered before it by __syncwarp.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+__device__ __forceinline__ bool bwd_elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
+cudaError_t launch_bwd_ws128(const BwdArgs& a, cudaStream_t st);  // 64 < head_dim <= 128
 cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st);
 // Packs dO, LSE and delta of every query tile (rows as listed in a.rowpack).
 cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, float* lsepack, float* deltapack, cudaStream_t st);
