@@ -249,6 +249,29 @@ def run_decode_only(args):
                           algorithmic_bytes_per_step=dec["bytes_per_step"])))
 
 
+def bind_to_gpu_numa(local):
+    """Best effort: run this rank (and so first-touch its pinned host buffers) on the CPUs of the NUMA node
+    the GPU hangs off, so that with several ranks the host copies do not all cross one socket's memory."""
+    try:
+        import torch
+        pr = torch.cuda.get_device_properties(local)
+        dev = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/%s/numa_node" % dev).read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            return node
+    except Exception:
+        pass
+    return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -264,6 +287,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _ext.lib()  # fails loudly when the CUDA library is missing
+    numa_node = bind_to_gpu_numa(local) if world > 1 else None
 
     w = WORKLOAD
     T, Hq, Hkv, D = sum(w["lens"]), w["hq"], w["hkv"], w["dim"]
@@ -399,7 +423,7 @@ def run_ours(args):
                     clocks=clocks,
                     e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                              ms_per_step=None if ms_e2e is None else ms_e2e / e2e_steps, steps=e2e_steps,
-                             mode="host copies on their own streams, double-buffered across steps"),
+                             mode="host copies on their own streams, double-buffered across steps", numa_node=numa_node),
                     gpu_launches=13 * args.steps,  # route 5, pack 2, forward 2, backward 4 (memsets not counted)
                     roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel", achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
