@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz by running the reference's own Python code on CPU.
 
-Run in a container that has the reference checkout (default /root/reference):
-    python tests/golden/make_golden.py [--reference /path/to/reference]
+Run where a checkout of the reference project is available:
+    python tests/golden/make_golden.py --reference /path/to/reference
 
 What is executed from the reference (never copied):
   * routing: src/moba_opt/grouped_attention.py::opt_gqa_cuda on CPU tensors with its CUDA-only
@@ -212,7 +212,7 @@ def merge_case(ref, out_dir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     torch.set_num_threads(8)
     ref = load_reference(Path(args.reference))
