@@ -434,10 +434,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           m_used = m_tile;
           raise = true;
         }
-        // P V of the previous tile must have landed before its P is overwritten or O is rescaled
-        if (j > 0 && alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
-        if (j > 0 && __any_sync(0xFFFFFFFFu, raise)) {
-          // rescale the row's O in tensor memory
+        // P V of the previous tile must have landed before O is rescaled or its P is overwritten; on the usual
+        // path (no rescale) the wait sits right before the first P store, under the first half of the exponentials
+        const bool rescale = j > 0 && __any_sync(0xFFFFFFFFu, raise);
+        if (rescale) {
+          if (alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
           tc_fence_after_sync();
 #pragma unroll
           for (int pc = 0; pc < DPAD / 32; ++pc) {
@@ -466,6 +467,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           pk[i >> 1] = pack_bf16(pa.x, pa.y);
           pk[16 + (i >> 1)] = pack_bf16(pb.x, pb.y);
         }
+        if (j > 0 && !rescale && alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
         tmem_st32(tP, pk);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
