@@ -163,6 +163,20 @@ int moba_decode_attend(const moba_cache_desc* c, const void* q, const int32_t* i
                        const int32_t* u_count, int umax, void* workspace, size_t workspace_bytes, void* out, float* lse,
                        unsigned* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Standalone merge operator: replaces merge_forward of the reference (src/moba_opt/ops/bindings.cpp:6-22,
+ * wrapper src/moba_opt/ops/merge_cuda.py:32-60, kernels ops/merge.cu:27-288) for callers that hold the self
+ * branch and the scattered remote contributions themselves; the prefill path merges in its own epilogue.
+ *   self_out [rows, dim], self_lse [rows]; remote_out [remote_rows, dim], remote_lse [remote_rows];
+ *   mapping [remote_rows] int64: the row each contribution belongs to; at most kmax (<= 32) per row.
+ *   dtype: 0 = bf16, 1 = fp32 (of self_out, remote_out and out); LSE is fp32 natural log.
+ * Contributions are reduced in ascending index order, so the result is bit-repeatable. status bits: 2 = a
+ * mapping entry was out of range (skipped), 4 = a row had more than kmax contributions (the excess is skipped). */
+size_t moba_merge_scratch_bytes(long long rows, int kmax);
+int moba_merge_forward(const void* self_out, const float* self_lse, const void* remote_out, const float* remote_lse,
+                       const int64_t* mapping, long long rows, long long remote_rows, int dim, int kmax, int dtype,
+                       void* scratch, size_t scratch_bytes, void* out, float* lse, unsigned* status, void* stream);
+
 /* Profiling aid (no reference counterpart): record the given CUDA events right before and after one
  * kernel on its launch stream. which: 1 forward remote pass, 2 forward self pass, 3 backward main
  * kernel, 4 decode attention. Null events switch it off. Process-wide, not thread-safe. */

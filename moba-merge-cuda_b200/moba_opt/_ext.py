@@ -43,6 +43,10 @@ def lib():
         L.moba_prefill_fwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
         if hasattr(L, "moba_prefill_bwd"):
             L.moba_prefill_bwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, c_vp]
+        L.moba_merge_scratch_bytes.restype = c_sz
+        L.moba_merge_scratch_bytes.argtypes = [ctypes.c_longlong, ctypes.c_int]
+        L.moba_merge_forward.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int,
+                                         ctypes.c_int, ctypes.c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
         _lib = L
     return _lib
 

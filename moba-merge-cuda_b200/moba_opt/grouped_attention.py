@@ -252,4 +252,23 @@ def opt_gqa_cuda(q, k, v, cu_seqlens, max_seqlen, config):
     return moba_prefill(q, k, v, cu_seqlens, max_seqlen, config)
 
 
+def _opt_mha(q, k, v, cu_seqlens, max_seqlen, config):
+    """The reference's earlier entry points for equal head counts (src/moba_opt/mixed_attention.py:411-420:
+    `opt_merge_atomic`, `opt_merge_cuda`, which differ only in the merge backend).  Same engine; grouped
+    heads are rejected as they are there."""
+    if q.dim() == 3 and k.dim() == 3 and q.shape[1] != k.shape[1]:
+        raise ValueError("q and k/v must have the same number of heads for this implementation")
+    return moba_prefill(q, k, v, cu_seqlens, max_seqlen, config)
+
+
+def opt_merge_atomic(q, k, v, cu_seqlens, max_seqlen, config):
+    return _opt_mha(q, k, v, cu_seqlens, max_seqlen, config)
+
+
+def opt_merge_cuda(q, k, v, cu_seqlens, max_seqlen, config):
+    return _opt_mha(q, k, v, cu_seqlens, max_seqlen, config)
+
+
 register("opt_gqa_cuda", opt_gqa_cuda)
+register("opt_merge_atomic", opt_merge_atomic)
+register("opt_merge_cuda", opt_merge_cuda)
