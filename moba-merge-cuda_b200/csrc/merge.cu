@@ -4,9 +4,9 @@
 // kernel); it exists for callers that hold the two branches themselves.
 //   row p of the self branch (P = T*H rows) and every remote row m with mapping[m] == p are combined as
 //   mx = max l, w = exp(l - mx), z = sum w, O = sum w o / z, L = mx + log z      (natural-log LSE, FP32 math)
-// Two kernels: contributions are ticketed into per-row slot lists (atomic counters), then one warp per row
-// sorts its at most 32 contribution indices and reduces them in ascending order, so the result does not
-// depend on the ticket order.  HBM-bound: every input byte is read once, every output byte written once.
+// Two kernels: contributions are ticketed into per-row slot lists (atomic counters), then every row sorts
+// its at most 32 contribution indices and reduces them in ascending order, so the result does not depend
+// on the ticket order.  HBM-bound: every input byte is read once, every output byte written once.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -29,53 +29,133 @@ __global__ void __launch_bounds__(256) merge_ticket_kernel(const int64_t* __rest
   else atomicOr(status, kErrCapacity);
 }
 
-template <typename T> __device__ __forceinline__ float load_f(const T* p);
-template <> __device__ __forceinline__ float load_f<float>(const float* p) { return *p; }
-template <> __device__ __forceinline__ float load_f<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <typename T> __device__ __forceinline__ void store_f(T* p, float v);
-template <> __device__ __forceinline__ void store_f<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void store_f<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+// 16 bytes of a row as eight (bf16) or four (fp32) FP32 values.
+template <typename T> struct Chunk;
+template <> struct Chunk<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Chunk<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
 
-// One warp per row.
-template <typename T>
+// LPR lanes share a row (16 bytes of it each per pass), 32 / LPR rows per warp.  Every lane of a row's group
+// sorts the row's few contribution indices itself and forms the weights, then accumulates its own columns
+// in ascending index order: no cross-lane traffic, all loads 16 bytes wide.
+template <typename T, int LPR>
 __global__ void __launch_bounds__(256) merge_rows_kernel(const T* __restrict__ self_out, const float* __restrict__ self_lse,
                                                          const T* __restrict__ remote_out, const float* __restrict__ remote_lse,
                                                          const int* __restrict__ counts, const int* __restrict__ slots, long long P,
                                                          int D, int kmax, T* __restrict__ out, float* __restrict__ lse) {
+  constexpr int N = Chunk<T>::N;
+  const int lane = threadIdx.x & 31, sub = lane % LPR;
+  const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * (32 / LPR) + lane / LPR;
+  if (row >= P) return;
+  const int cnt = min(counts[row], kmax);
+  int idx[32];
+  float w[32];
+  for (int i = 0; i < cnt; ++i) {  // insertion sort of the contribution indices (ascending)
+    const int v = slots[row * kmax + i];
+    int j = i;
+    while (j > 0 && idx[j - 1] > v) { idx[j] = idx[j - 1]; --j; }
+    idx[j] = v;
+  }
+  const float l_self = self_lse[row];
+  float mx = l_self;
+  for (int i = 0; i < cnt; ++i) { w[i] = remote_lse[idx[i]]; mx = fmaxf(mx, w[i]); }
+  const bool empty = mx == -INFINITY;  // no branch saw a key: zero output, LSE stays -inf
+  const float w_self = empty ? 0.f : expf(l_self - mx);
+  float z = w_self;
+  for (int i = 0; i < cnt; ++i) { w[i] = empty ? 0.f : expf(w[i] - mx); z += w[i]; }
+  const float inv = z > 0.f ? 1.f / z : 0.f;
+  for (int d = sub * N; d < D; d += LPR * N) {
+    float acc[N], v[N];
+    Chunk<T>::load(self_out + row * D + d, v);
+#pragma unroll
+    for (int e = 0; e < N; ++e) acc[e] = w_self * v[e];
+    for (int i = 0; i < cnt; ++i) {
+      Chunk<T>::load(remote_out + (long long)idx[i] * D + d, v);
+#pragma unroll
+      for (int e = 0; e < N; ++e) acc[e] = fmaf(w[i], v[e], acc[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < N; ++e) acc[e] *= inv;
+    Chunk<T>::store(out + row * D + d, acc);
+  }
+  if (sub == 0) lse[row] = empty ? -INFINITY : mx + logf(z);
+}
+
+// Fallback for head dimensions whose rows are not multiples of 16 bytes: one warp per row, scalar accesses.
+template <typename T>
+__global__ void __launch_bounds__(256) merge_rows_scalar_kernel(const T* __restrict__ self_out, const float* __restrict__ self_lse,
+                                                                const T* __restrict__ remote_out, const float* __restrict__ remote_lse,
+                                                                const int* __restrict__ counts, const int* __restrict__ slots,
+                                                                long long P, int D, int kmax, T* __restrict__ out,
+                                                                float* __restrict__ lse) {
   const int lane = threadIdx.x & 31;
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= P) return;
   const int cnt = min(counts[row], kmax);
-  // contribution indices in ascending order: rank by counting smaller ones, then hand each rank its value
-  const int mine = lane < cnt ? slots[row * kmax + lane] : 0x7FFFFFFF;
-  int rank = 0;
-  for (int i = 0; i < cnt; ++i) rank += __shfl_sync(0xFFFFFFFFu, mine, i) < mine;
-  int idx = 0x7FFFFFFF;
+  int idx[32];
+  float w[32];
   for (int i = 0; i < cnt; ++i) {
-    const int v = __shfl_sync(0xFFFFFFFFu, mine, i), r = __shfl_sync(0xFFFFFFFFu, rank, i);
-    if (r == lane) idx = v;
+    const int v = slots[row * kmax + i];
+    int j = i;
+    while (j > 0 && idx[j - 1] > v) { idx[j] = idx[j - 1]; --j; }
+    idx[j] = v;
   }
   const float l_self = self_lse[row];
-  const float l_mine = lane < cnt ? remote_lse[idx] : -INFINITY;
-  float mx = fmaxf(l_self, l_mine);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-  const bool empty = mx == -INFINITY;  // no branch saw a key: zero output, LSE stays -inf
+  float mx = l_self;
+  for (int i = 0; i < cnt; ++i) { w[i] = remote_lse[idx[i]]; mx = fmaxf(mx, w[i]); }
+  const bool empty = mx == -INFINITY;
   const float w_self = empty ? 0.f : expf(l_self - mx);
-  const float w_mine = (empty || lane >= cnt) ? 0.f : expf(l_mine - mx);
   float z = w_self;
-  for (int i = 0; i < cnt; ++i) z += __shfl_sync(0xFFFFFFFFu, w_mine, i);  // fixed order
+  for (int i = 0; i < cnt; ++i) { w[i] = empty ? 0.f : expf(w[i] - mx); z += w[i]; }
   const float inv = z > 0.f ? 1.f / z : 0.f;
   for (int d = lane; d < D; d += 32) {
-    float acc = w_self * load_f(self_out + row * D + d);
-    for (int i = 0; i < cnt; ++i) {
-      const float w = __shfl_sync(0xFFFFFFFFu, w_mine, i);
-      const int m = __shfl_sync(0xFFFFFFFFu, idx, i);
-      acc = fmaf(w, load_f(remote_out + (long long)m * D + d), acc);
-    }
-    store_f(out + row * D + d, acc * inv);
+    float acc = w_self * (float)self_out[row * D + d];
+    for (int i = 0; i < cnt; ++i) acc = fmaf(w[i], (float)remote_out[(long long)idx[i] * D + d], acc);
+    out[row * D + d] = (T)(acc * inv);
   }
   if (lane == 0) lse[row] = empty ? -INFINITY : mx + logf(z);
+}
+
+template <typename T>
+void launch_rows(const void* self_out, const float* self_lse, const void* remote_out, const float* remote_lse, const int* counts,
+                 const int* slots, long long rows, int dim, int kmax, void* out, float* lse, cudaStream_t st) {
+  const T* so = static_cast<const T*>(self_out);
+  const T* ro = static_cast<const T*>(remote_out);
+  T* o = static_cast<T*>(out);
+  constexpr int N = Chunk<T>::N;
+  const bool vec = dim % N == 0 && (reinterpret_cast<uintptr_t>(so) | reinterpret_cast<uintptr_t>(ro) | reinterpret_cast<uintptr_t>(o)) % 16 == 0;
+  if (!vec) {
+    merge_rows_scalar_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(so, self_lse, ro, remote_lse, counts, slots, rows, dim, kmax, o, lse);
+    return;
+  }
+  const int chunks = dim / N;
+  if (chunks <= 4) merge_rows_kernel<T, 4><<<(unsigned)((rows + 63) / 64), 256, 0, st>>>(so, self_lse, ro, remote_lse, counts, slots, rows, dim, kmax, o, lse);
+  else if (chunks <= 8) merge_rows_kernel<T, 8><<<(unsigned)((rows + 31) / 32), 256, 0, st>>>(so, self_lse, ro, remote_lse, counts, slots, rows, dim, kmax, o, lse);
+  else if (chunks <= 16) merge_rows_kernel<T, 16><<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(so, self_lse, ro, remote_lse, counts, slots, rows, dim, kmax, o, lse);
+  else merge_rows_kernel<T, 32><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(so, self_lse, ro, remote_lse, counts, slots, rows, dim, kmax, o, lse);
 }
 
 inline size_t align256m(size_t x) { return (x + 255) & ~size_t(255); }
@@ -103,13 +183,9 @@ extern "C" int moba_merge_forward(const void* self_out, const float* self_lse, c
   if (cudaMemsetAsync(counts, 0, (size_t)rows * 4, st) != cudaSuccess) return MOBA_ERR_CUDA;
   if (remote_rows > 0)
     merge_ticket_kernel<<<(unsigned)((remote_rows + 255) / 256), 256, 0, st>>>(mapping, remote_rows, rows, kmax, counts, slots, status);
-  const unsigned grid = (unsigned)((rows + 7) / 8);
   if (dtype == 0)
-    merge_rows_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(self_out), self_lse,
-                                                           static_cast<const __nv_bfloat16*>(remote_out), remote_lse, counts, slots,
-                                                           rows, dim, kmax, static_cast<__nv_bfloat16*>(out), lse);
+    launch_rows<__nv_bfloat16>(self_out, self_lse, remote_out, remote_lse, counts, slots, rows, dim, kmax, out, lse, st);
   else
-    merge_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(self_out), self_lse, static_cast<const float*>(remote_out),
-                                                   remote_lse, counts, slots, rows, dim, kmax, static_cast<float*>(out), lse);
+    launch_rows<float>(self_out, self_lse, remote_out, remote_lse, counts, slots, rows, dim, kmax, out, lse, st);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
