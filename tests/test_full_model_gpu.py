@@ -1,0 +1,128 @@
+"""Full-model session (examples/full_qwen2.py of this package) on a small random Qwen2-architecture model: the dense
+session against the Hugging Face forward of the same weights, graph backends against eager (bit for bit), the
+in-graph greedy loop against a host-driven one, decode against a fresh prefill of the extended prompt, life-cycle
+errors.  Logit tolerances (bf16 model): relative L2 <= 2e-2 against an independent implementation."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1] / "moba-merge-cuda_b200" / "examples"))
+
+
+@pytest.fixture(scope="module")
+def model():
+    from full_qwen2 import random_qwen2
+    return random_qwen2(hidden=128, layers=3, heads=4, kv_heads=2, ffn=256, vocab=300, max_positions=512, seed=3)
+
+
+def _rel_l2(a, b):
+    a, b = a.double(), b.double()
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def _ids(n, seed=0, vocab=300):
+    return torch.randint(0, vocab, (1, n), generator=torch.Generator().manual_seed(seed)).cuda()
+
+
+def test_dense_session_matches_hf_forward(model):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(70)
+    with torch.no_grad():
+        want = model(ids).logits[0].float()
+    with FullQwen2Session(model, 128, mode="dense", chunk=16, page=8) as s:
+        got = s.prefill(ids[:, :50])
+        assert _rel_l2(got[0].float(), want[49]) <= 2e-2
+        s.prepare()
+        for i in range(50, 70):
+            got = s.step(int(ids[0, i]))
+            assert _rel_l2(got[0].float(), want[i]) <= 2e-2, i
+
+
+@pytest.mark.parametrize("backend", ["attention_graph", "model_graph"])
+def test_graph_backends_equal_eager_bit_for_bit(model, backend):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(100, seed=1)
+    kw = dict(mode="moba", chunk=16, topk=3, page=8, dense_layers=(1,), stable_routes=True)
+    logits = {}
+    for name in ("eager", backend):
+        with FullQwen2Session(model, 160, backend=name, **kw) as s:
+            s.prefill(ids[:, :90])
+            s.prepare()
+            logits[name] = [s.step(int(ids[0, i])).clone() for i in range(90, 100)]
+    for a, b in zip(logits["eager"], logits[backend]):
+        assert torch.equal(a, b)
+
+
+def test_in_graph_greedy_loop_matches_host_driven_greedy(model):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(64, seed=2)
+    kw = dict(mode="moba", chunk=16, topk=3, page=8, stable_routes=True)
+    with FullQwen2Session(model, 128, backend="model_graph", **kw) as s:
+        s.prefill(ids)
+        s.prepare()
+        fast = s.generate(24)
+    with FullQwen2Session(model, 128, backend="eager", **kw) as s:
+        token = int(s.prefill(ids).argmax(-1))
+        s.prepare()
+        slow = []
+        for _ in range(24):
+            slow.append(token)
+            token = int(s.step(token).argmax(-1))
+    assert fast.tolist() == slow
+
+
+def test_decode_step_agrees_with_prefill_of_the_extended_prompt(model):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(97, seed=4)
+    kw = dict(mode="moba", chunk=16, topk=3, page=8, stable_routes=True)
+    with FullQwen2Session(model, 160, **kw) as s:
+        s.prefill(ids[:, :96])
+        s.prepare()
+        stepped = s.step(int(ids[0, 96]))[0].float()
+    with FullQwen2Session(model, 160, **kw) as s:
+        fresh = s.prefill(ids)[0].float()
+    assert _rel_l2(stepped, fresh) <= 3e-2
+
+
+def test_every_chunk_selected_is_the_dense_model(model):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(60, seed=5)
+    out = []
+    for kw in (dict(mode="dense"), dict(mode="moba", topk=8)):      # 128 / 16 = 8 chunks <= topk
+        with FullQwen2Session(model, 128, chunk=16, page=8, **kw) as s:
+            out.append(s.prefill(ids).clone())
+    assert torch.equal(out[0], out[1])
+
+
+def test_life_cycle_errors(model):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(20, seed=6)
+    with pytest.raises(ValueError):
+        FullQwen2Session(model, 64, mode="sparse")
+    with pytest.raises(ValueError):
+        FullQwen2Session(model, 64, backend="graph")
+    with pytest.raises(ValueError):
+        FullQwen2Session(model, 64, dense_layers=(7,))
+    s = FullQwen2Session(model, 24, mode="moba", chunk=8, topk=2, page=4)
+    with pytest.raises(ValueError):
+        s.prepare()                       # nothing prefilled yet
+    with pytest.raises(ValueError):
+        s.prefill(_ids(24))               # prompt must stay below the capacity
+    s.prefill(ids)
+    with pytest.raises(ValueError):
+        s.step(1)                         # prepare first
+    s.prepare()
+    with pytest.raises(ValueError):
+        s.step(300)                       # not a token of the vocabulary
+    for i in range(4):
+        s.step(i)
+    with pytest.raises(ValueError):
+        s.step(5)                         # capacity 24 reached: rejected before anything is modified
+    s.close()
+    with pytest.raises(ValueError):
+        s.step(1)
