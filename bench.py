@@ -235,6 +235,53 @@ def run_decode(dev, rank, world, steps, lib):
     return dict(ms_per_step=ms, requests=b, bytes_per_step=float(np.mean(sampled_bytes)), attend_ms=float(np.median(att)),
                 context_tokens=int(sum(lens)))
 
+# ----------------------------------------------------------------------------- full-model leg
+FULL_MODEL = dict(name="qwen2_0.5b_random_prompt16384_greedy256_moba12of24_c512_k4", prompt=16384, steps=256, chunk=512, topk=4,
+                  page=16, dense_layers=tuple(range(0, 24, 2)))
+
+
+def run_full_model(dev):
+    """BASELINE configs[4]: random-init Qwen2-0.5B architecture (24 layers, hidden 896, 14/2 heads, D=64, FFN 4864,
+    vocab 151936, N(0, 0.02) bf16), 12 of the 24 layers MoBA (the odd ones; chunk 512, topk 4), batch 1, a prompt of
+    16384 uniform-random token ids, then 256 greedy steps under one whole-model CUDA graph, beside the all-dense
+    session on the same weights and prompt.  Returns prefill and per-step times (CUDA events)."""
+    import torch
+    sys.path.insert(0, str(ROOT / "moba-merge-cuda_b200" / "examples"))
+    from full_qwen2 import FullQwen2Session, random_qwen2
+    w = FULL_MODEL
+    model = random_qwen2(device=dev)
+    ids = torch.randint(0, model.config.vocab_size, (1, w["prompt"]), generator=torch.Generator().manual_seed(0)).to(dev)
+    with FullQwen2Session(model, 2048, chunk=w["chunk"], topk=w["topk"], page=w["page"], mode="moba") as s:   # warm-up
+        s.prefill(ids[:, :1536])
+        s.prepare()
+        s.greedy_step()
+    res = {}
+    for label, kw in (("moba", dict(mode="moba", dense_layers=w["dense_layers"])), ("dense", dict(mode="dense"))):
+        with FullQwen2Session(model, w["prompt"] + w["steps"] + 64, chunk=w["chunk"], topk=w["topk"], page=w["page"],
+                              backend="model_graph", stable_routes=True, **kw) as s:
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            e[0].record()
+            s.prefill(ids)
+            e[1].record()
+            s.prepare()
+            for _ in range(8):
+                s.greedy_step()
+            e[2].record()
+            tokens = s.generate(w["steps"] - 8)
+            e[3].record()
+            torch.cuda.synchronize()
+            res[label] = dict(prefill_ms=e[0].elapsed_time(e[1]), ms_per_step=e[2].elapsed_time(e[3]) / (w["steps"] - 8),
+                              last_token=int(tokens[-1]))
+    del model
+    torch.cuda.empty_cache()
+    return dict(workload=w["name"], moba_layers=12, prompt_tokens=w["prompt"], greedy_steps=w["steps"],
+                decode_tokens_per_s=1e3 / res["moba"]["ms_per_step"], decode_ms_per_step=res["moba"]["ms_per_step"],
+                prefill_ms=res["moba"]["prefill_ms"], dense_decode_ms_per_step=res["dense"]["ms_per_step"],
+                dense_prefill_ms=res["dense"]["prefill_ms"],
+                decode_speedup_vs_dense=res["dense"]["ms_per_step"] / res["moba"]["ms_per_step"],
+                mode="whole-model CUDA graph, greedy token kept on the device")
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_decode_only(args):
     import torch
@@ -440,6 +487,11 @@ def run_ours(args):
                                   attend_kernel_ms=dec["attend_ms"],
                                   attend_kernel_gbs=dec["bytes_per_step"] / (dec["attend_ms"] * 1e-3) / 1e9,
                                   mode="prepare_decode + CUDA graph, one token per request per step")
+        if world == 1 and not args.kernels_only and not args.no_full_model:
+            try:
+                line["full_model"] = run_full_model(dev)
+            except Exception as exc:  # the optional leg must not take the line with it
+                line["full_model"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
         if cpu_val is not None:
             line["cpu_baseline"] = dict(value=cpu_val, unit=UNIT, cores=os.cpu_count() or 1, kind="port", sample=cpu_desc,
                                         seconds=cpu_dt)
@@ -456,6 +508,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode leg")
+    ap.add_argument("--no-full-model", action="store_true", help="skip the full-model decode leg")
     ap.add_argument("--only-decode", action="store_true", help="run only the paged-decode leg (profiler runs)")
     ap.add_argument("--decode-steps", type=int, default=DECODE["steps"])
     ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs (profiler runs)")
