@@ -177,6 +177,19 @@ int moba_merge_forward(const void* self_out, const float* self_lse, const void* 
                        const int64_t* mapping, long long rows, long long remote_rows, int dim, int kmax, int dtype,
                        void* scratch, size_t scratch_bytes, void* out, float* lse, unsigned* status, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Layer glue of the full-model decode step (no reference counterpart: examples/full_qwen2.py of the reference
+ * leaves these operations to the Hugging Face modules).  bf16 tensors, rows contiguous; arithmetic rounds to
+ * bf16 wherever those modules do, so the fused step reproduces their bits.
+ *   moba_add_rmsnorm  h_out = h_in + delta (delta and h_out may be null), y = weight * rmsnorm(h_out)
+ *   moba_rope_split   qkv [rows, (hq + 2 hk) * dim] -> q, k with rotate-half rotary embedding (cos, sin [rows, dim]), v
+ *   moba_silu_mul     gate_up [rows, 2 ffn] (gate then up) -> out [rows, ffn] = silu(gate) * up */
+int moba_add_rmsnorm(const void* h_in, const void* delta, const void* weight, float eps, long long rows, int hidden, void* h_out,
+                     void* y, void* stream);
+int moba_rope_split(const void* qkv, const void* cosv, const void* sinv, long long rows, int hq, int hk, int dim, void* q, void* k,
+                    void* v, void* stream);
+int moba_silu_mul(const void* gate_up, long long rows, int ffn, void* out, void* stream);
+
 /* Profiling aid (no reference counterpart): record the given CUDA events right before and after one
  * kernel on its launch stream. which: 1 forward remote pass, 2 forward self pass, 3 backward main
  * kernel, 4 decode attention. Null events switch it off. Process-wide, not thread-safe. */

@@ -7,8 +7,10 @@ constructor vocabulary (mode, chunk, topk, backend, page, dense_layers, prefill_
 (`prefill_hidden` -> `prepare` -> `step` ... -> `close`).  Differences: every attention, dense layers included, runs
 on this package's kernels (dense prefill is the K=1 fallback of `opt_gqa_cuda`, dense decode is
 `prepare_decode(mode="dense")`), so no FlashAttention is needed; and `greedy_step()` keeps the chosen token on the
-device, so a greedy loop replays the graph without a host round trip.  The weights, norms, MLPs and rotary tables stay
-in the unchanged Hugging Face module (plain library GEMMs and elementwise torch ops).
+device, so a greedy loop replays the graph without a host round trip.  The weights and the rotary tables stay in the
+unchanged Hugging Face module and the projections are plain library GEMMs; in the decode step the elementwise glue of
+a layer (residual add + RMSNorm, rotary embedding + q/k/v split, SiLU * up) runs as three single-launch kernels of this
+package unless `fused_glue=False` asks for the Hugging Face modules.
 """
 import torch
 import torch.nn.functional as F
@@ -33,7 +35,7 @@ class FullQwen2Session:
 
     def __init__(self, model, capacity, *, mode="dense", chunk=128, topk=4, backend="eager", page=16,
                  deterministic_merge=False, stable_routes=False, route_precision="upstream", dense_layers=(),
-                 prefill_mode="match"):
+                 prefill_mode="match", fused_glue=True):
         if mode not in ("dense", "moba"):
             raise ValueError("mode")
         if backend not in self.BACKENDS:
@@ -84,6 +86,19 @@ class FullQwen2Session:
             a = layer.self_attn
             bias = None if a.q_proj.bias is None else torch.cat([a.q_proj.bias, a.k_proj.bias, a.v_proj.bias], 0)
             self.packed.append((torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], 0), bias))
+        # Decode-step glue as single launches (moba_add_rmsnorm, moba_rope_split, moba_silu_mul) instead of the
+        # Hugging Face modules' many small ones; needs bf16 and bias-free MLP projections.
+        if not isinstance(fused_glue, bool):
+            raise ValueError("fused_glue must be bool")
+        self.fused_glue = fused_glue and self.dtype == torch.bfloat16 and all(
+            l.mlp.gate_proj.bias is None and l.mlp.up_proj.bias is None for l in layers)
+        if self.fused_glue:
+            from moba_opt import _ext
+            self._lib = _ext.lib()
+            self.gate_up = [torch.cat([l.mlp.gate_proj.weight, l.mlp.up_proj.weight], 0) for l in layers]
+            hidden, ffn = cfg.hidden_size, cfg.intermediate_size
+            new = lambda n: torch.empty((1, n), dtype=self.dtype, device=self.device)
+            self._h, self._y, self._act = [new(hidden), new(hidden)], new(hidden), new(ffn)
 
     # ------------------------------------------------------------------ helpers
     def _check(self):
@@ -160,6 +175,8 @@ class FullQwen2Session:
 
     def _compute_step(self):
         """Device work of one decode step, embedding to logits and greedy token; no host synchronisation."""
+        if self.fused_glue:
+            return self._compute_step_fused()
         body = self.model.model
         h = body.embed_tokens(self.input)[0]                                   # [1, hidden]
         position = self.caches[0]._lengths[:1].to(torch.long)                  # the new token's position
@@ -169,13 +186,59 @@ class FullQwen2Session:
             p.q.copy_(q)
             p.k.copy_(k)
             p.v.copy_(v)
-            if self.backend == "attention_graph":
-                p._run("step", True)
-            else:
-                p._compute(True)
+            self._attend(p)
             h = h + layer.self_attn.o_proj(p.output.reshape(1, -1))
             h = h + layer.mlp(layer.post_attention_layernorm(h))
         self.logits = self.model.lm_head(body.norm(h))
+        self.next_token.copy_(self.logits.argmax(-1, keepdim=True))
+        return self.logits
+
+    def _attend(self, p):
+        if self.backend == "attention_graph":
+            p._run("step", True)
+        else:
+            p._compute(True)
+
+    def _compute_step_fused(self):
+        """The same step with the layer glue as single launches: residual add + RMSNorm, rotary embedding + split
+        of the fused q/k/v projection straight into the attention's input buffers, SiLU * up."""
+        import ctypes
+        lib, body, cfg = self._lib, self.model.model, self.model.config
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        hidden, ffn = cfg.hidden_size, cfg.intermediate_size
+
+        def check(rc):
+            if rc:
+                raise RuntimeError("glue kernel launch failed (status %d)" % rc)
+
+        def add_norm(h_in, delta, norm, h_out):
+            check(lib.moba_add_rmsnorm(h_in.data_ptr(), None if delta is None else delta.data_ptr(), norm.weight.data_ptr(),
+                                       float(norm.variance_epsilon), 1, hidden, None if h_out is None else h_out.data_ptr(),
+                                       self._y.data_ptr(), st))
+
+        h = body.embed_tokens(self.input)[0]
+        position = self.caches[0]._lengths[:1].to(torch.long)
+        cos, sin = self._rope(h, position)
+        cos, sin = cos.contiguous(), sin.contiguous()
+        delta, flip = None, 0
+        for i, (layer, p) in enumerate(zip(body.layers, self.plans)):
+            if delta is None:
+                add_norm(h, None, layer.input_layernorm, None)
+            else:                                   # h <- h + (MLP output of the previous layer), then normalise
+                add_norm(h, delta, layer.input_layernorm, self._h[flip])
+                h, flip = self._h[flip], flip ^ 1
+            qkv = F.linear(self._y, *self.packed[i])
+            check(lib.moba_rope_split(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, self.hq, self.hk, self.dim,
+                                      p.q.data_ptr(), p.k.data_ptr(), p.v.data_ptr(), st))
+            self._attend(p)
+            att = layer.self_attn.o_proj(p.output.reshape(1, -1))
+            add_norm(h, att, layer.post_attention_layernorm, self._h[flip])
+            h, flip = self._h[flip], flip ^ 1
+            gu = F.linear(self._y, self.gate_up[i])
+            check(lib.moba_silu_mul(gu.data_ptr(), 1, ffn, self._act.data_ptr(), st))
+            delta = layer.mlp.down_proj(self._act)
+        add_norm(h, delta, body.norm, None)
+        self.logits = self.model.lm_head(self._y)
         self.next_token.copy_(self.logits.argmax(-1, keepdim=True))
         return self.logits
 

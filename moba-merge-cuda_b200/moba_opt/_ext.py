@@ -47,6 +47,10 @@ def lib():
         L.moba_merge_scratch_bytes.argtypes = [ctypes.c_longlong, ctypes.c_int]
         L.moba_merge_forward.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int,
                                          ctypes.c_int, ctypes.c_int, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
+        L.moba_add_rmsnorm.argtypes = [c_vp, c_vp, c_vp, ctypes.c_float, ctypes.c_longlong, ctypes.c_int, c_vp, c_vp, c_vp]
+        L.moba_rope_split.argtypes = [c_vp, c_vp, c_vp, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, c_vp, c_vp,
+                                      c_vp, c_vp]
+        L.moba_silu_mul.argtypes = [c_vp, ctypes.c_longlong, ctypes.c_int, c_vp, c_vp]
         _lib = L
     return _lib
 

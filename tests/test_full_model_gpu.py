@@ -126,3 +126,18 @@ def test_life_cycle_errors(model):
     s.close()
     with pytest.raises(ValueError):
         s.step(1)
+
+
+def test_fused_glue_step_agrees_with_the_module_by_module_step(model):
+    from full_qwen2 import FullQwen2Session
+    ids = _ids(80, seed=7)
+    kw = dict(mode="moba", chunk=16, topk=3, page=8, stable_routes=True)
+    logits = {}
+    for fused in (False, True):
+        with FullQwen2Session(model, 128, fused_glue=fused, **kw) as s:
+            assert s.fused_glue == fused
+            s.prefill(ids[:, :70])
+            s.prepare()
+            logits[fused] = [s.step(int(ids[0, i])).float().clone() for i in range(70, 80)]
+    for a, b in zip(logits[False], logits[True]):
+        assert _rel_l2(b, a) <= 5e-3
