@@ -37,6 +37,12 @@ WORKLOADS = {
     "cfg2": dict(name="gqa_prefill_4x32768_h14kv2_d64_c2048_k3", lens=(32768,) * 4, hq=14, hkv=2, dim=64, chunk=2048, topk=3),
     # one of the four sequences: the small case used for multi-pass profiler captures
     "small": dict(name="gqa_prefill_1x32768_h14kv2_d64_c2048_k3", lens=(32768,), hq=14, hkv=2, dim=64, chunk=2048, topk=3),
+    # BASELINE configs[2], the shard one GPU gets at 8 GPUs (one KV head and its 4 query heads), and half of it for
+    # multi-pass profiler captures; unit-variance inputs as that config states
+    "cfg3_shard": dict(name="gqa_prefill_1x131072_h4kv1_d128_c4096_k12", lens=(131072,), hq=4, hkv=1, dim=128, chunk=4096, topk=12,
+                       unit_variance=True),
+    "cfg3_small": dict(name="gqa_prefill_1x65536_h4kv1_d128_c4096_k12", lens=(65536,), hq=4, hkv=1, dim=128, chunk=4096, topk=12,
+                       unit_variance=True),
 }
 WORKLOAD = WORKLOADS["cfg2"]
 # DRAM bytes of one backward launch on one 32768-token sequence, from the committed ncu summary
@@ -340,7 +346,8 @@ def run_ours(args):
     T, Hq, Hkv, D = sum(w["lens"]), w["hq"], w["hkv"], w["dim"]
     gen = torch.Generator().manual_seed(1000 + rank)
     host = {}
-    for name, h, scale in (("q", Hq, D ** -0.5), ("k", Hkv, D ** -0.5), ("v", Hkv, D ** -0.5), ("do", Hq, 1.0)):
+    qkv_scale = 1.0 if w.get("unit_variance") else D ** -0.5
+    for name, h, scale in (("q", Hq, qkv_scale), ("k", Hkv, qkv_scale), ("v", Hkv, qkv_scale), ("do", Hq, 1.0)):
         host[name] = (torch.randn(T, h, D, generator=gen) * scale).bfloat16().pin_memory()
     cu = torch.tensor(np.concatenate(([0], np.cumsum(w["lens"]))), dtype=torch.int32, device=dev)
     max_len = max(w["lens"])
@@ -472,7 +479,7 @@ def run_ours(args):
                              ms_per_step=None if ms_e2e is None else ms_e2e / e2e_steps, steps=e2e_steps,
                              mode="host copies on their own streams, double-buffered across steps", numa_node=numa_node),
                     gpu_launches=13 * args.steps,  # route 5, pack 2, forward 2, backward 4 (memsets not counted)
-                    roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel", achieved=achieved, peak=pk["tflops"],
+                    roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel" if D <= 64 else "attn_bwd_ws128_kernel", achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
                                   traffic=BWD_DRAM_BYTES_PER_SEQUENCE * len(w["lens"]) if w["name"].startswith("gqa_prefill_") and w["lens"][0] == 32768 else None,
                                   traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on one 32768-token "
