@@ -49,7 +49,6 @@ const char* moba_status_string(int status);
  * expresses the dense fallback of grouped_attention.py:41-46 by passing chunk_size >= max_seqlen).
  */
 #define MOBA_ROUTE_BF16_MEANS 1
-#define MOBA_BWD_SINGLE_WARPGROUP 2 /* debugging aid: run the backward without warp specialisation */
 
 typedef struct moba_prefill_desc {
   int32_t total_tokens, num_seqs, hq, hkv, dim, chunk_size, remote_k;

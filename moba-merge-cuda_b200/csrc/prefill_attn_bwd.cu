@@ -1,18 +1,11 @@
-// Prefill attention backward on tcgen05 tensor cores: exact gradients of the merged (global
-// softmax) output with the route held fixed, as OptMixedAttention.backward of the reference
-// (src/moba_opt/mixed_attention.py:141-225) obtains from two FlashAttention backward calls on the
-// global O and LSE.
+// Prefill attention backward, host entry: exact gradients of the merged (global softmax) output with the route
+// held fixed, as OptMixedAttention.backward of the reference (src/moba_opt/mixed_attention.py:141-225) obtains from
+// two FlashAttention backward calls on the global O and LSE.
 //
-// KV-stationary: one CTA owns a block of 128 keys of one (chunk, kv head) and walks over every
-// 128-row query tile that attends it - the causal tiles of the own chunk for each query head of
-// the group, then the gathered rows of the expert list.  dK and dV of the block accumulate in
-// tensor memory across the walk and are written once (no cross-CTA reduction); dQ of every tile
-// is reduced into an FP32 buffer with vector atomics and converted to bf16 at the end.
-//
-// Per query tile:  S = Q K^T, dP = dO V^T (TMEM)  ->  P = exp2(S*c - LSE), dS = P (dP - delta) / sqrt(D)
-// (registers, written as bf16 tiles)  ->  dV += P^T dO, dK += dS^T Q, dQ = dS K.
-// The same swizzled shared-memory image of a tile serves as K-major and as MN-major operand, so
-// no transposes are materialised.
+// Launch sequence: dq_acc = 0, delta = rowsum(dO * O), pack dO / LSE / delta per query tile, the KV-stationary main
+// kernel (prefill_attn_bwd_ws.cu for head_dim <= 64, prefill_attn_bwd_ws128.cu above that: dK and dV of a key block
+// accumulate in tensor memory and are written once, dQ of every tile is reduced into the FP32 buffer with vector
+// atomics), dq = bf16(dq_acc).
 #include "prefill_bwd.cuh"
 
 namespace moba {
@@ -51,239 +44,6 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
       make_uint4(bwd_pack_bf16(a.x, a.y), bwd_pack_bf16(a.z, a.w), bwd_pack_bf16(b.x, b.y), bwd_pack_bf16(b.z, b.w));
 }
 
-template <int DPAD>
-__global__ void __launch_bounds__(128, 1) attn_bwd_kernel(BwdArgs a) {
-  constexpr int UPR = DPAD / 8;
-  constexpr int TILE_BYTES = kTile * DPAD * 2;
-  constexpr int PT_BYTES = kTile * kTile * 2;
-  constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 256 + DPAD, COL_DQ = 0;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t& bar1 = *reinterpret_cast<uint64_t*>(smem);
-  uint64_t& bar2 = *reinterpret_cast<uint64_t*>(smem + 8);
-  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(smem + 16);
-  int* s_rowth = reinterpret_cast<int*>(smem + 64);
-  uint8_t* sK = smem + 1024;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sQ = sV + TILE_BYTES;
-  uint8_t* sdO = sQ + TILE_BYTES;
-  uint8_t* sP = sdO + TILE_BYTES;
-  uint8_t* sdS = sP + PT_BYTES;
-
-  const PrefillView& pv = a.pv;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int D = pv.D;
-  const int kblock = a.kv_order[blockIdx.x];
-  const int g = blockIdx.y;
-  const int c = pv.qtile_chunk[kblock];
-  const int k0 = pv.qtile_tok0[kblock];
-  const int chunk_begin = pv.chunk_start[c], chunk_end = pv.chunk_start[c + 1];
-  const int nkeys = min(kTile, chunk_end - k0);
-  const int kb = (k0 - chunk_begin) / kTile;
-  const int tiles_in_chunk = (chunk_end - chunk_begin + kTile - 1) / kTile;
-  const int n_self = tiles_in_chunk - kb;
-  int remote_begin = 0, remote_rows = 0;
-  if (pv.R > 0) {
-    remote_begin = a.seg_base[c * pv.Hq + g * pv.G];
-    remote_rows = a.seg_base[c * pv.Hq + (g + 1) * pv.G] - remote_begin;
-  }
-  const int n_remote = (remote_rows + kTile - 1) / kTile;
-  const int n_iter = pv.G * n_self + n_remote;
-
-  if ((smem_u32(smem) & 1023u) != 0) {
-    if (tid == 0) atomicOr(a.status, kErrBadIndex);
-    return;
-  }
-  if (tid == 0) {
-    mbar_init(&bar1, 1);
-    mbar_init(&bar2, 1);
-    mbar_fence_init();
-  }
-  if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
-
-  // stationary K and V tiles of the key block
-  {
-    const __nv_bfloat16* kbase = a.k + (long long)g * pv.k_sh;
-    const __nv_bfloat16* vbase = a.v + (long long)g * pv.v_sh;
-    for (int i = tid; i < kTile * UPR; i += 128) {
-      const int r = i / UPR, u = i - r * UPR;
-      const bool ok = r < nkeys && u * 8 < D;
-      cp_async16(smem_u32(sK) + sw128_offset(kTile, r, u), ok ? kbase + (long long)(k0 + r) * pv.k_st + u * 8 : kbase, ok);
-      cp_async16(smem_u32(sV) + sw128_offset(kTile, r, u), ok ? vbase + (long long)(k0 + r) * pv.v_st + u * 8 : vbase, ok);
-    }
-    cp_async_commit();
-  }
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_slot;
-  const uint32_t tlane = tmem + (uint32_t(warp * 32) << 16);
-  const uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
-  const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 1, 1);
-  const uint32_t idesc_dq = umma_idesc_bf16(128, DPAD, 0, 1);
-  uint32_t phase = 0;
-  bool alive = true;
-
-  for (int it = 0; it < n_iter; ++it) {
-    // ---- rows of this query tile
-    int th = -1;        // t*Hq+h of this thread's row
-    bool diag = false;  // causal mask inside the tile
-    if (it < pv.G * n_self) {
-      const int hl = it / n_self, i = kb + (it - hl * n_self);
-      const int tok = chunk_begin + i * kTile + tid;
-      if (tok < chunk_end) th = tok * pv.Hq + g * pv.G + hl;
-      diag = i == kb;
-    } else {
-      const int idx = (it - pv.G * n_self) * kTile + tid;
-      if (idx < remote_rows) {
-        th = a.rowlist[remote_begin + idx] / pv.R;
-        if (th < 0 || th >= pv.T * pv.Hq) { atomicOr(a.status, kErrBadIndex); th = -1; }
-      }
-    }
-    s_rowth[tid] = th;
-    float lse2 = INFINITY, delta = 0.f;
-    if (th >= 0) {
-      lse2 = a.lse[th] * 1.4426950408889634f;
-      delta = a.delta[th];
-    }
-    __syncthreads();  // row ids visible; previous tile's MMAs were awaited by every thread
-    for (int i = tid; i < kTile * UPR; i += 128) {
-      const int r = i / UPR, u = i - r * UPR;
-      const int rth = s_rowth[r];
-      const bool ok = rth >= 0 && u * 8 < D;
-      const int t = rth / pv.Hq, h = rth - t * pv.Hq;
-      cp_async16(smem_u32(sQ) + sw128_offset(kTile, r, u),
-                 ok ? a.q + (long long)t * pv.q_st + (long long)h * pv.q_sh + u * 8 : a.q, ok);
-      cp_async16(smem_u32(sdO) + sw128_offset(kTile, r, u), ok ? a.dout + (long long)rth * D + u * 8 : a.dout, ok);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int kk = 0; kk < DPAD; kk += 16)
-        umma_ss(tmem + COL_S, umma_desc_kmajor(smem_u32(sQ), kTile, kk), umma_desc_kmajor(smem_u32(sK), kTile, kk), idesc_qk, kk > 0);
-#pragma unroll
-      for (int kk = 0; kk < DPAD; kk += 16)
-        umma_ss(tmem + COL_DP, umma_desc_kmajor(smem_u32(sdO), kTile, kk), umma_desc_kmajor(smem_u32(sV), kTile, kk), idesc_qk, kk > 0);
-      umma_commit(&bar1);
-    }
-    if (alive) alive = mbar_wait(&bar1, phase, a.status);
-    tc_fence_after_sync();
-
-    // ---- P and dS of this thread's row
-    int klimit = nkeys;
-    if (diag) klimit = min(klimit, tid + 1);
-#pragma unroll
-    for (int pc = 0; pc < 4; ++pc) {
-      uint32_t s[32], dp[32];
-      tmem_ld32(tlane + COL_S + pc * 32, s);
-      tmem_ld32(tlane + COL_DP + pc * 32, dp);
-      tmem_ld_wait();
-      uint32_t pp[16], ds[16];
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float p0 = bwd_exp2(fmaf(__uint_as_float(s[i]), a.scale_log2, -lse2));
-        float p1 = bwd_exp2(fmaf(__uint_as_float(s[i + 1]), a.scale_log2, -lse2));
-        if (pc * 32 + i >= klimit) p0 = 0.f;
-        if (pc * 32 + i + 1 >= klimit) p1 = 0.f;
-        const float d0 = p0 * (__uint_as_float(dp[i]) - delta) * a.scale;
-        const float d1 = p1 * (__uint_as_float(dp[i + 1]) - delta) * a.scale;
-        pp[i >> 1] = bwd_pack_bf16(p0, p1);
-        ds[i >> 1] = bwd_pack_bf16(d0, d1);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        *reinterpret_cast<uint4*>(sP + sw128_offset(kTile, tid, pc * 4 + u)) = make_uint4(pp[4 * u], pp[4 * u + 1], pp[4 * u + 2], pp[4 * u + 3]);
-        *reinterpret_cast<uint4*>(sdS + sw128_offset(kTile, tid, pc * 4 + u)) = make_uint4(ds[4 * u], ds[4 * u + 1], ds[4 * u + 2], ds[4 * u + 3]);
-      }
-    }
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after_sync();
-#pragma unroll
-      for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO  (contraction over the tile's query rows)
-        umma_ss(tmem + COL_DV, umma_desc_mnmajor(smem_u32(sP), kTile, kk, 0), umma_desc_mnmajor(smem_u32(sdO), kTile, kk, 0),
-                idesc_kv, (it > 0) || (kk > 0));
-#pragma unroll
-      for (int kk = 0; kk < kTile; kk += 16)  // dK += dS^T Q
-        umma_ss(tmem + COL_DK, umma_desc_mnmajor(smem_u32(sdS), kTile, kk, 0), umma_desc_mnmajor(smem_u32(sQ), kTile, kk, 0),
-                idesc_kv, (it > 0) || (kk > 0));
-#pragma unroll
-      for (int kk = 0; kk < kTile; kk += 16)  // dQ = dS K  (contraction over the block's keys)
-        umma_ss(tmem + COL_DQ, umma_desc_kmajor(smem_u32(sdS), kTile, kk), umma_desc_mnmajor(smem_u32(sK), kTile, kk, 0),
-                idesc_dq, kk > 0);
-      umma_commit(&bar2);
-    }
-    if (alive) alive = mbar_wait(&bar2, phase, a.status);
-    tc_fence_after_sync();
-    phase ^= 1;
-    {
-      // every thread issues the warp-wide TMEM loads; padding rows drop their dQ row
-      const bool ok = th >= 0 && alive;
-      float* dst = a.dq_acc + (long long)(ok ? th : 0) * D;
-#pragma unroll
-      for (int pc = 0; pc < DPAD / 32; ++pc) {
-        uint32_t r[32];
-        tmem_ld32(tlane + COL_DQ + pc * 32, r);
-        tmem_ld_wait();
-        if (ok) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            if (pc * 32 + i < D)
-              red_add_v4(dst + pc * 32 + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                         __uint_as_float(r[i + 3]));
-        }
-      }
-    }
-    tc_fence_before_sync();
-  }
-
-  // ---- dK, dV of the key block: thread = key row
-  __syncthreads();
-  tc_fence_after_sync();
-  {
-    const bool ok = tid < nkeys && alive;
-    __nv_bfloat16* dkrow = a.dk + ((long long)(k0 + tid) * pv.Hkv + g) * D;
-    __nv_bfloat16* dvrow = a.dv + ((long long)(k0 + tid) * pv.Hkv + g) * D;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-#pragma unroll
-      for (int pc = 0; pc < DPAD / 32; ++pc) {
-        uint32_t r[32];
-        tmem_ld32(tlane + (which == 0 ? COL_DK : COL_DV) + pc * 32, r);
-        tmem_ld_wait();
-        if (ok) {
-          __nv_bfloat16* dst = which == 0 ? dkrow : dvrow;
-#pragma unroll
-          for (int i = 0; i < 32; i += 8)
-            if (pc * 32 + i < D)
-              *reinterpret_cast<uint4*>(dst + pc * 32 + i) =
-                  make_uint4(bwd_pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
-                             bwd_pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
-                             bwd_pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
-                             bwd_pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
-        }
-      }
-    }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_free(tmem, TMEM_COLS);
-}
-
-template <int DPAD>
-static cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t st) {
-  const size_t smem = 1024 + (size_t)kTile * DPAD * 2 * 4 + (size_t)kTile * kTile * 2 * 2;
-  cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<DPAD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  attn_bwd_kernel<DPAD><<<dim3(a.pv.n_qtiles, a.pv.Hkv), 128, smem, st>>>(a);
-  return cudaGetLastError();
-}
-
 }  // namespace moba
 
 using namespace moba;
@@ -293,7 +53,7 @@ extern "C" size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d) {
   if (validate_desc(d) != MOBA_OK) return 0;
   const size_t rows = (size_t)d->total_tokens * d->hq;
   size_t bytes = align256(rows * 4) + align256(rows * d->dim * 4);
-  if (d->dim <= 128 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP)) {
+  {
     const size_t tiles = (size_t)pack_q_tiles(*d);
     bytes += align256(tiles * kTile * pack_dpad(*d) * 2) + 2 * align256(tiles * kTile * 4);
   }
@@ -350,8 +110,7 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.status = status;
   a.scale = (float)(1.0 / sqrt((double)d->dim));
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)d->dim));
-  const bool ws = d->dim <= 128 && !(d->flags & MOBA_BWD_SINGLE_WARPGROUP);
-  if (ws) {
+  {
     const size_t tiles = (size_t)pack_q_tiles(*d);
     char* p = reinterpret_cast<char*>(dq_acc) + align256((size_t)rows * d->dim * 4);
     void* dopack = p; p += align256(tiles * kTile * pack_dpad(*d) * 2);
@@ -365,8 +124,7 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
     a.lsepack = lsepack; a.deltapack = deltapack;
   }
   prof_begin(kProfBwdMain, st);
-  cudaError_t e = ws ? (d->dim > 64 ? launch_bwd_ws128(a, st) : launch_bwd_ws(a, st))
-                     : (d->dim > 64 ? launch_bwd<128>(a, st) : launch_bwd<64>(a, st));
+  cudaError_t e = d->dim > 64 ? launch_bwd_ws128(a, st) : launch_bwd_ws(a, st);
   prof_end(kProfBwdMain, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
   const long long n8 = rows * d->dim / 8;
