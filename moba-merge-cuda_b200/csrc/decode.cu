@@ -539,42 +539,49 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int hl = 0; hl < G; ++hl) {
+  // One warp per head.  The partials of a head are (slot, part) pairs, j = slot * parts + part; lanes share them for
+  // the maximum and the weights (kept in shared memory), then share the head dimension for the weighted sum, whose
+  // loads are independent of each other.  Order of summation is fixed, so the result is bit-repeatable.
+  float* s_w = reinterpret_cast<float*>(s_pipe) + warp * 1024;
+  for (int hl = warp; hl < G; hl += 4) {
     const int h = g * G + hl;
     const long long hbase = ((long long)row * a.Hq + h) * a.ns;
     const int nslots = dense ? cur + 1 : a.ns;
+    const int total = nslots * a.parts;
+    const long long p0 = hbase * a.parts;
+    auto valid = [&](int j) {
+      const int sl = j / a.parts, pt = j - sl * a.parts;
+      const int c = dense ? sl : a.selected[hbase + sl];
+      return c >= 0 && pt < (c == cur ? cur_parts : a.parts);
+    };
     float big = -INFINITY;
-    for (int s = 0; s < nslots; ++s) {
-      const int c = dense ? s : a.selected[hbase + s];
-      if (c < 0) continue;
-      const int np = c == cur ? cur_parts : a.parts;
-      for (int p = 0; p < np; ++p) big = fmaxf(big, __ldcg(a.pm + (hbase + s) * a.parts + p));
-    }
+    for (int j = lane; j < total; j += 32)
+      if (valid(j)) big = fmaxf(big, __ldcg(a.pm + p0 + j));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xFFFFFFFFu, big, o));
     float lsum = 0.f;
-    for (int s = 0; s < nslots; ++s) {
-      const int c = dense ? s : a.selected[hbase + s];
-      if (c < 0) continue;
-      const int np = c == cur ? cur_parts : a.parts;
-      for (int p = 0; p < np; ++p) {
-        const long long pidx = (hbase + s) * a.parts + p;
-        lsum += __ldcg(a.pl + pidx) * dec_exp2(__ldcg(a.pm + pidx) - big);
-      }
+    for (int j = lane; j < total; j += 32) {
+      const float w = valid(j) ? dec_exp2(__ldcg(a.pm + p0 + j) - big) : 0.f;
+      if (j < 1024) s_w[j] = w;
+      if (w != 0.f) lsum = fmaf(__ldcg(a.pl + p0 + j), w, lsum);
     }
-    for (int d = tid; d < D; d += 128) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
+    __syncwarp();
+    const float inv = 1.f / lsum;
+    for (int d = lane; d < D; d += 32) {
       float v = 0.f;
-      for (int s = 0; s < nslots; ++s) {
-        const int c = dense ? s : a.selected[hbase + s];
-        if (c < 0) continue;
-        const int np = c == cur ? cur_parts : a.parts;
-        for (int p = 0; p < np; ++p) {
-          const long long pidx = (hbase + s) * a.parts + p;
-          v += __ldcg(a.pacc + pidx * D + d) * dec_exp2(__ldcg(a.pm + pidx) - big);
-        }
+#pragma unroll 4
+      for (int j = 0; j < total; ++j) {
+        const float w = j < 1024 ? s_w[j] : (valid(j) ? dec_exp2(__ldcg(a.pm + p0 + j) - big) : 0.f);
+        if (w != 0.f) v = fmaf(__ldcg(a.pacc + (p0 + j) * D + d), w, v);
       }
-      a.out[((long long)row * a.Hq + h) * D + d] = __float2bfloat16_rn(v / lsum);
+      a.out[((long long)row * a.Hq + h) * D + d] = __float2bfloat16_rn(v * inv);
     }
-    if (tid == 0) a.lse[(long long)row * a.Hq + h] = (big + log2f(lsum)) * 0.6931471805599453f;
+    if (lane == 0) a.lse[(long long)row * a.Hq + h] = (big + log2f(lsum)) * 0.6931471805599453f;
+    __syncwarp();
   }
+  __syncthreads();
   if (tid == 0) a.counters[rowg] = 0;  // ready for the next launch (graph replay included)
 }
 
