@@ -32,17 +32,15 @@ def lib():
         L.moba_selftest_umma.argtypes = [ctypes.c_int, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int, c_vp, c_vp]
         for name in ("moba_prefill_route_state_bytes", "moba_prefill_route_scratch_bytes",
                      "moba_prefill_fwd_scratch_bytes", "moba_prefill_bwd_scratch_bytes"):
-            fn = getattr(L, name, None)
-            if fn is not None:
-                fn.restype, fn.argtypes = c_sz, [P]
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = c_sz, [P]
         L.moba_profile_events.argtypes = [ctypes.c_int, c_vp, c_vp]
         L.moba_prefill_route.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]
         L.moba_prefill_route_static.argtypes = [P, c_vp, c_vp, c_vp, c_vp]
         L.moba_prefill_route_static_capacity.restype = c_sz
         L.moba_prefill_route_static_capacity.argtypes = []
         L.moba_prefill_fwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp]
-        if hasattr(L, "moba_prefill_bwd"):
-            L.moba_prefill_bwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, c_vp]
+        L.moba_prefill_bwd.argtypes = [P, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp, c_vp, c_vp, c_vp, c_vp]
         L.moba_merge_scratch_bytes.restype = c_sz
         L.moba_merge_scratch_bytes.argtypes = [ctypes.c_longlong, ctypes.c_int]
         L.moba_merge_forward.argtypes = [c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_int,
