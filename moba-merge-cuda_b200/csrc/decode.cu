@@ -539,47 +539,74 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // One warp per head.  The partials of a head are (slot, part) pairs, j = slot * parts + part; lanes share them for
-  // the maximum and the weights (kept in shared memory), then share the head dimension for the weighted sum, whose
-  // loads are independent of each other.  Order of summation is fixed, so the result is bit-repeatable.
-  float* s_w = reinterpret_cast<float*>(s_pipe) + warp * 1024;
+  // The partials of a head are (slot, part) pairs, j = slot * parts + part.  First one warp per head finds the
+  // maximum and the weights (kept in shared memory) and the denominator; then every thread takes four dimensions
+  // of one head and sums over the partials with loads that do not depend on each other or on the weights, so the
+  // latency of the loads is paid once per eight partials, not once per partial.  Order of summation is fixed, so
+  // the result is bit-repeatable.
+  const int nslots = dense ? cur + 1 : a.ns;
+  const int total = nslots * a.parts;
+  const int cap = min(1024, (int)(kStages * STAGE_BYTES / 4) / G);  // weights of a head that fit in shared memory
+  float* s_w = reinterpret_cast<float*>(s_pipe);
+  __shared__ float s_big[32], s_inv[32];
+  auto valid = [&](long long hbase, int j) {
+    const int sl = j / a.parts, pt = j - sl * a.parts;
+    const int c = dense ? sl : a.selected[hbase + sl];
+    return c >= 0 && pt < (c == cur ? cur_parts : a.parts);
+  };
   for (int hl = warp; hl < G; hl += 4) {
     const int h = g * G + hl;
     const long long hbase = ((long long)row * a.Hq + h) * a.ns;
-    const int nslots = dense ? cur + 1 : a.ns;
-    const int total = nslots * a.parts;
     const long long p0 = hbase * a.parts;
-    auto valid = [&](int j) {
-      const int sl = j / a.parts, pt = j - sl * a.parts;
-      const int c = dense ? sl : a.selected[hbase + sl];
-      return c >= 0 && pt < (c == cur ? cur_parts : a.parts);
-    };
     float big = -INFINITY;
-    for (int j = lane; j < total; j += 32)
-      if (valid(j)) big = fmaxf(big, __ldcg(a.pm + p0 + j));
+    for (int j = lane; j < total; j += 32) {
+      const float m = valid(hbase, j) ? __ldcg(a.pm + p0 + j) : -INFINITY;
+      if (j < cap) s_w[hl * cap + j] = m;
+      big = fmaxf(big, m);
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xFFFFFFFFu, big, o));
     float lsum = 0.f;
     for (int j = lane; j < total; j += 32) {
-      const float w = valid(j) ? dec_exp2(__ldcg(a.pm + p0 + j) - big) : 0.f;
-      if (j < 1024) s_w[j] = w;
+      const float m = j < cap ? s_w[hl * cap + j] : (valid(hbase, j) ? __ldcg(a.pm + p0 + j) : -INFINITY);
+      const float w = m == -INFINITY ? 0.f : dec_exp2(m - big);
+      if (j < cap) s_w[hl * cap + j] = w;
       if (w != 0.f) lsum = fmaf(__ldcg(a.pl + p0 + j), w, lsum);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
-    __syncwarp();
-    const float inv = 1.f / lsum;
-    for (int d = lane; d < D; d += 32) {
-      float v = 0.f;
-#pragma unroll 4
-      for (int j = 0; j < total; ++j) {
-        const float w = j < 1024 ? s_w[j] : (valid(j) ? dec_exp2(__ldcg(a.pm + p0 + j) - big) : 0.f);
-        if (w != 0.f) v = fmaf(__ldcg(a.pacc + (p0 + j) * D + d), w, v);
-      }
-      a.out[((long long)row * a.Hq + h) * D + d] = __float2bfloat16_rn(v * inv);
+    if (lane == 0) {
+      s_big[hl] = big;
+      s_inv[hl] = 1.f / lsum;
+      a.lse[(long long)row * a.Hq + h] = (big + log2f(lsum)) * 0.6931471805599453f;
     }
-    if (lane == 0) a.lse[(long long)row * a.Hq + h] = (big + log2f(lsum)) * 0.6931471805599453f;
-    __syncwarp();
+  }
+  __syncthreads();
+  const int d4n = D >> 2;  // the head dimension is a multiple of 8
+  for (int item = tid; item < G * d4n; item += 128) {
+    const int hl = item / d4n, d = (item - hl * d4n) * 4;
+    const int h = g * G + hl;
+    const long long hbase = ((long long)row * a.Hq + h) * a.ns;
+    const long long p0 = hbase * a.parts;
+    const float big = s_big[hl];
+    const float4* src = reinterpret_cast<const float4*>(a.pacc + p0 * D + d);
+    const int stride4 = D >> 2;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int j = 0; j < total; ++j) {
+      const float w = j < cap ? s_w[hl * cap + j] : (valid(hbase, j) ? dec_exp2(__ldcg(a.pm + p0 + j) - big) : 0.f);
+      const float4 x = __ldcg(src + (long long)j * stride4);  // always inside the buffer; unused if w == 0
+      if (w != 0.f) {
+        v.x = fmaf(x.x, w, v.x); v.y = fmaf(x.y, w, v.y);
+        v.z = fmaf(x.z, w, v.z); v.w = fmaf(x.w, w, v.w);
+      }
+    }
+    const float inv = s_inv[hl];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv, v.y * inv), hi = __floats2bfloat162_rn(v.z * inv, v.w * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(a.out + ((long long)row * a.Hq + h) * D + d) = pk;
   }
   __syncthreads();
   if (tid == 0) a.counters[rowg] = 0;  // ready for the next launch (graph replay included)

@@ -277,6 +277,18 @@ def test_chunk_size_extremes(chunk, dim, length, page):
     check(cache, cache.attend(q, sequence_ids=[0], mode="dense"), q)
 
 
+@pytest.mark.parametrize("hq,dim,chunk,length", [(32, 32, 4, 700), (8, 64, 1, 1100), (7, 64, 2, 300)])
+def test_dense_merge_over_more_partials_than_fit_in_shared_memory(hq, dim, chunk, length):
+    """The merge keeps the weights of a head's partials in shared memory up to a capacity that shrinks with the
+    group size; the partials beyond it take the recomputing path.  (32 heads, dim 32: capacity 128 of 176
+    partials; 8 heads, dim 64: 1024 of 1101; the last case stays inside the capacity.)"""
+    from moba_opt import PagedKVCache
+    cache = PagedKVCache(1, length + 1, 1, dim, page_size=16, chunk_size=chunk)
+    cache.append(rand((length, 1, dim), 271), rand((length, 1, dim), 272), sequence_ids=[0], cu_seqlens=[0, length])
+    q = rand((1, hq, dim), 273)
+    check(cache, cache.attend(q, sequence_ids=[0], mode="dense"), q)
+
+
 def test_extreme_logits_use_stable_online_softmax():
     from moba_opt import PagedKVCache
     cache = PagedKVCache(1, 16, 1, 8, page_size=3, chunk_size=4)
