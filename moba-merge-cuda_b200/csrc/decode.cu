@@ -263,17 +263,32 @@ struct AttendArgs {
   float scale_log2;
 };
 
+#ifdef MOBA_DEC_TRACE
+// Phase stamps for tuning (thread 0 of every CTA; [cta][16] entries: even = SM clock, slot 15 = global timer at entry).
+__device__ long long* g_dec_trace = nullptr;
+__device__ __forceinline__ long long dec_gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define DEC_TRACE_INIT long long* const trace_buf = g_dec_trace; const int trace_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; \
+  if (trace_buf && threadIdx.x == 0 && trace_cta < 256) trace_buf[trace_cta * 16 + 15] = dec_gtime()
+#define DEC_TRACE(i) do { if (trace_buf && threadIdx.x == 0 && trace_cta < 256) trace_buf[trace_cta * 16 + (i)] = clock64(); } while (0)
+#else
+#define DEC_TRACE_INIT do {} while (0)
+#define DEC_TRACE(i) do {} while (0)
+#endif
+
 constexpr int kHeadBlock = 16;    // query heads of a group processed together (MMA M dimension)
 constexpr int kStageTokens = 64;  // tokens per pipeline stage: 16 per warp
 // Two 32 KB stages (D <= 128) and 160 registers let three CTAs share an SM; measured faster than three
-// stages with two CTAs.
+// stages with two CTAs when the grid fills the GPU.  A grid of at most one CTA per SM (a batch of one or two
+// requests) is bound by latency instead: each stage then costs one trip to memory, so that case runs a deep
+// ring that has up to a whole 512-token part in flight.
 #ifndef MOBA_DEC_STAGES
 #define MOBA_DEC_STAGES 2
 #endif
 #ifndef MOBA_DEC_MINBLOCKS
 #define MOBA_DEC_MINBLOCKS 3
 #endif
-constexpr int kStages = MOBA_DEC_STAGES;  // cp.async stages in flight per CTA
+constexpr int kStages = MOBA_DEC_STAGES;  // cp.async stages in flight per CTA, throughput variant
+constexpr int deep_stages(int dp) { return dp <= 64 ? 8 : dp <= 128 ? 4 : 3; }  // latency variant
 
 // Shared-memory K/V stage: row = one token, DP bf16 values; the 16-byte units of a row are
 // XOR-permuted by (token & 7) so that ldmatrix reads of 8 consecutive tokens are conflict-free.
@@ -284,16 +299,15 @@ __device__ __forceinline__ uint32_t kv_unit_offset(int tok, int unit) {
   return (uint32_t)(tok * DP * 2 + sw * 16);
 }
 
-// Row base (element offset of the token's K/V row of kv head g, or -1) of one token of a stage.  The
-// lookup goes through the page table; it is issued one stage ahead of the copy that needs it.
-__device__ __forceinline__ long long attend_row_base(const CacheView& cv, int sid, int g, int t, int t_end, unsigned* status) {
-  if (t >= t_end) return -1;
-  const int physical = __ldg(cv.table + (long long)sid * cv.width + t / cv.page);
-  if (physical < 0 || physical >= cv.num_pages) {
-    atomicOr(status, kErrBadIndex);
-    return -1;
-  }
-  return (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * cv.D;
+// Row base (element offset of the K/V row of kv head g, or -1) of the token at offset r of logical page pg.  The
+// lookup goes through the page table; it is issued one stage ahead of the copy that needs it.  No branch depends
+// on the table entry, so several lookups can be in flight; a bad entry is recorded in `bad` and reported later.
+__device__ __forceinline__ long long attend_row_base(const CacheView& cv, int sid, int g, int pg, int r, bool exists,
+                                                     bool& bad) {
+  const int physical = exists ? __ldg(cv.table + (long long)sid * cv.width + pg) : 0;
+  const bool wrong = physical < 0 || physical >= cv.num_pages;
+  bad |= wrong;
+  return exists && !wrong ? (((long long)physical * cv.page + r) * cv.Hkv + g) * cv.D : -1;
 }
 
 // Copies the K and V rows of one stage with cp.async.  Consecutive threads copy consecutive 16-byte
@@ -337,19 +351,68 @@ __device__ __forceinline__ uint32_t dec_pack_bf16(float lo, float hi) {
   return r;
 }
 
+// ---- pieces of the merge that are needed only when a head has more partials than fit in shared memory; they
+// are functions of their own so that the common path stays short.
+struct MergeTail {
+  const int* selected;  // null: dense, slot == chunk
+  const float *pm, *pl, *pacc;
+  int parts, cur, cur_parts, D;
+  __device__ __forceinline__ bool valid(long long hbase, int j) const {
+    const int sl = j / parts, pt = j - sl * parts;
+    const int c = selected ? __ldg(selected + hbase + sl) : sl;
+    return c >= 0 && pt < (c == cur ? cur_parts : parts);
+  }
+};
+// a select, not a branch: stale values where the weight is zero never count and the load stays unconditional
+__device__ __forceinline__ void merge_add(float4& v, const float4& x, float w) {
+  const bool use = w != 0.f;
+  v.x = fmaf(use ? x.x : 0.f, w, v.x); v.y = fmaf(use ? x.y : 0.f, w, v.y);
+  v.z = fmaf(use ? x.z : 0.f, w, v.z); v.w = fmaf(use ? x.w : 0.f, w, v.w);
+}
+__device__ __noinline__ float merge_tail_max(const MergeTail& t, long long hbase, int from, int total, float big) {
+  for (int j = from; j < total; j += 16)
+    if (t.valid(hbase, j)) big = fmaxf(big, __ldcg(t.pm + hbase * t.parts + j));
+  return big;
+}
+__device__ __noinline__ float merge_tail_den(const MergeTail& t, long long hbase, int from, int total, float big, float lsum) {
+  for (int j = from; j < total; j += 16)
+    if (t.valid(hbase, j))
+      lsum = fmaf(__ldcg(t.pl + hbase * t.parts + j), dec_exp2(__ldcg(t.pm + hbase * t.parts + j) - big), lsum);
+  return lsum;
+}
+// partials [from, to) whose weights are in shared memory but whose sums are not
+__device__ __noinline__ float4 merge_rest_acc(const MergeTail& t, long long hbase, int from, int to, int d, const float* wrow,
+                                              float4 v) {
+  const float4* src = reinterpret_cast<const float4*>(t.pacc + hbase * t.parts * t.D + d);
+#pragma unroll 8
+  for (int j = from; j < to; ++j) merge_add(v, __ldcg(src + (long long)j * (t.D >> 2)), wrow[j]);
+  return v;
+}
+// partials [from, total) with nothing in shared memory
+__device__ __noinline__ float4 merge_tail_acc(const MergeTail& t, long long hbase, int from, int total, int d, float big,
+                                              float4 v) {
+  const float4* src = reinterpret_cast<const float4*>(t.pacc + hbase * t.parts * t.D + d);
+  for (int j = from; j < total; ++j)
+    if (t.valid(hbase, j))
+      merge_add(v, __ldcg(src + (long long)j * (t.D >> 2)), dec_exp2(__ldcg(t.pm + hbase * t.parts + j) - big));
+  return v;
+}
+
 // Split-K paged attention for one (query row, kv head, union chunk, part).  The query heads of the
 // GQA group are the 16 rows of m16n8k16 tensor-core tiles (unused rows are zero), so a K/V token read
 // from HBM serves every head at no extra cost and the kernel stays memory bound for any group size.
 // Each warp takes 16 tokens of every 64-token stage and keeps its own running (max, sum, O); the
 // four warps are combined through shared memory at the end.
-template <int DP>
-__global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
+template <int DP, int NS>
+__global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
   constexpr int KSTEPS = DP / 16;
   constexpr int DT = DP / 8;  // 8-column output tiles
   constexpr int STAGE_BYTES = 2 * kStageTokens * DP * 2;
-  extern __shared__ __align__(128) uint8_t s_pipe[];  // kStages stages; reused for the cross-warp reduction
-  __shared__ int s_last;
-  __shared__ long long s_rowbase[kStages][kStageTokens];
+  extern __shared__ __align__(128) uint8_t s_pipe[];  // NS stages; reused for the cross-warp reduction
+  __shared__ int s_last, s_slot[kHeadBlock];
+  __shared__ long long s_rowbase[NS][kStageTokens];
+  DEC_TRACE_INIT;
+  DEC_TRACE(0);
   const CacheView& cv = a.cv;
   const int D = cv.D, G = a.Hq / cv.Hkv;
   const int rowg = blockIdx.z, row = rowg / cv.Hkv, g = rowg - row * cv.Hkv;
@@ -371,10 +434,31 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
   const int cur_parts = (visible - cur * cv.C + a.part_tokens - 1) / a.part_tokens;
   const int expected = (ucount - 1) * a.parts + cur_parts;
   const int ntiles = (t_end - t_begin + kStageTokens - 1) / kStageTokens;
+  DEC_TRACE(1);
 
   for (int hb = 0; hb < G; hb += kHeadBlock) {
     const unsigned active = (mask >> hb) & 0xFFFFu;
     if (!active) continue;
+    // row bases of the tokens of the stages about to be copied (ring of NS slots).  A thread looks up one token
+    // of every stage; from stage to stage the token advances by kStageTokens, so page and offset are stepped
+    // instead of divided anew.
+    int look_t = t_begin + tid, look_pg = 0, look_r = 0, step_pg = 0, step_r = 0;
+    bool look_bad = false;
+    if (tid < kStageTokens) {
+      look_pg = look_t / cv.page; look_r = look_t - look_pg * cv.page;
+      step_pg = kStageTokens / cv.page; step_r = kStageTokens - step_pg * cv.page;
+    }
+    auto lookup = [&]() {
+      const long long base = attend_row_base(cv, sid, g, look_pg, look_r, look_t < t_end, look_bad);
+      look_t += kStageTokens; look_pg += step_pg; look_r += step_r;
+      if (look_r >= cv.page) { look_r -= cv.page; ++look_pg; }
+      return base;
+    };
+    long long first_base[NS];  // issued before the query loads below, stored after them
+    if (tid < kStageTokens) {
+#pragma unroll
+      for (int s = 0; s < NS; ++s) first_base[s] = lookup();
+    }
     // Q fragments (A operand): rows qr and qr+8 of the head block, all k-steps
     uint32_t qf[KSTEPS][4];
     {
@@ -396,35 +480,34 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows qr and qr+8; l: this thread's columns only
 
     __syncthreads();  // the previous head block is done with shared memory
-    // row bases of the tokens of the stages about to be copied (ring of kStages slots)
     if (tid < kStageTokens) {
 #pragma unroll
-      for (int s = 0; s < kStages; ++s)
-        s_rowbase[s][tid] = attend_row_base(cv, sid, g, t_begin + s * kStageTokens + tid, t_end, a.status);
+      for (int s = 0; s < NS; ++s) s_rowbase[s][tid] = first_base[s];
     }
     __syncthreads();
+    DEC_TRACE(2);
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
+    for (int s = 0; s < NS - 1; ++s) {
       if (s < ntiles) attend_load_stage<DP>(cv, s_pipe + s * STAGE_BYTES, s_rowbase[s]);
       cp_async_commit();
     }
     for (int i = 0; i < ntiles; ++i) {
-      cp_async_wait<kStages - 2>();
+      cp_async_wait<NS - 2>();
       __syncthreads();  // tile i has landed; every warp finished tile i-1, whose buffer is refilled next
-      const int nx = i + kStages - 1;
-      if (nx < ntiles) attend_load_stage<DP>(cv, s_pipe + (nx % kStages) * STAGE_BYTES, s_rowbase[nx % kStages]);
+      if (i == 0) DEC_TRACE(3);
+      const int nx = i + NS - 1;
+      if (nx < ntiles) attend_load_stage<DP>(cv, s_pipe + (nx % NS) * STAGE_BYTES, s_rowbase[nx % NS]);
       cp_async_commit();
-      // look up the rows of tile nx+1 now, publish them after this tile's math (slot i % kStages is free)
+      // look up the rows of tile nx+1 now, publish them after this tile's math (slot i % NS is free)
       long long next_base = -1;
-      if (tid < kStageTokens && nx + 1 < ntiles)
-        next_base = attend_row_base(cv, sid, g, t_begin + (nx + 1) * kStageTokens + tid, t_end, a.status);
+      if (tid < kStageTokens && nx + 1 < ntiles) next_base = lookup();
       const int tok0 = warp * 16;                                 // this warp's tokens inside the stage
       const int nvalid = t_end - (t_begin + i * kStageTokens + tok0);  // tokens of the warp tile that exist
       if (nvalid <= 0) {                                          // warp-uniform
-        if (tid < kStageTokens) s_rowbase[i % kStages][tid] = next_base;
+        if (tid < kStageTokens) s_rowbase[i % NS][tid] = next_base;
         continue;
       }
-      const uint32_t kbase = smem_u32(s_pipe + (i % kStages) * STAGE_BYTES);
+      const uint32_t kbase = smem_u32(s_pipe + (i % NS) * STAGE_BYTES);
       const uint32_t vbase = kbase + kStageTokens * DP * 2;
       // ---- S = Q K^T for 16 tokens: two 8-token column tiles
       float sc[2][4];
@@ -479,9 +562,11 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
           mma_bf16_16816(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
         }
       }
-      if (tid < kStageTokens) s_rowbase[i % kStages][tid] = next_base;
+      if (tid < kStageTokens) s_rowbase[i % NS][tid] = next_base;
     }
+    if (look_bad) atomicOr(a.status, kErrBadIndex);
     // ---- combine the four warps, then write one partial per active head
+    DEC_TRACE(4);
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
@@ -498,38 +583,49 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
       s_ml[((size_t)warp * 16 + qr) * 2] = m0; s_ml[((size_t)warp * 16 + qr) * 2 + 1] = l0;
       s_ml[((size_t)warp * 16 + qr + 8) * 2] = m1; s_ml[((size_t)warp * 16 + qr + 8) * 2 + 1] = l1;
     }
-    __syncthreads();
-    for (int hh = 0; hh < kHeadBlock; ++hh) {
-      if (!((active >> hh) & 1u) || hb + hh >= G) continue;
-      const int h = g * G + hb + hh;
-      int slot = dense ? chunk : -1;
-      if (!dense) {
-        for (int s = 0; s < a.ns; ++s)
-          if (a.selected[((long long)row * a.Hq + h) * a.ns + s] == chunk) { slot = s; break; }
+    // slot of this chunk in each head's route (all candidate slots are read before any is compared)
+    const int nh = min(kHeadBlock, G - hb);
+    if (tid < kHeadBlock) {
+      int slot = -1;
+      if (tid < nh && ((active >> tid) & 1u)) {
+        if (dense) {
+          slot = chunk;
+        } else {
+          const int* sel = a.selected + ((long long)row * a.Hq + g * G + hb + tid) * a.ns;
+#pragma unroll 4
+          for (int s2 = a.ns - 1; s2 >= 0; --s2)
+            if (__ldg(sel + s2) == chunk) slot = s2;
+        }
       }
+      s_slot[tid] = slot;
+    }
+    __syncthreads();
+    // every thread takes two dimensions of one head
+    const int d2n = D >> 1;
+    for (int item = tid; item < nh * d2n; item += 128) {
+      const int hh = item / d2n, d = (item - hh * d2n) * 2;
+      const int slot = s_slot[hh];
       if (slot < 0) continue;
+      const int h = g * G + hb + hh;
       const long long pidx = (((long long)row * a.Hq + h) * a.ns + slot) * a.parts + part;
-      float big = -INFINITY;
+      float mw[4], big = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) big = fmaxf(big, s_ml[((size_t)w * 16 + hh) * 2]);
-      float wgt[4], lsum = 0.f;
+      for (int w = 0; w < 4; ++w) { mw[w] = s_ml[((size_t)w * 16 + hh) * 2]; big = fmaxf(big, mw[w]); }
+      float lsum = 0.f, v0 = 0.f, v1 = 0.f;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const float mw = s_ml[((size_t)w * 16 + hh) * 2];
-        wgt[w] = mw == -INFINITY ? 0.f : dec_exp2(mw - big);   // a warp that saw no token contributes nothing
-        lsum += s_ml[((size_t)w * 16 + hh) * 2 + 1] * wgt[w];
+        const float wgt = mw[w] == -INFINITY ? 0.f : dec_exp2(mw[w] - big);  // a warp that saw no token adds nothing
+        lsum += s_ml[((size_t)w * 16 + hh) * 2 + 1] * wgt;
+        const float2 x = *reinterpret_cast<const float2*>(s_o + ((size_t)w * 16 + hh) * DP + d);
+        v0 += x.x * wgt; v1 += x.y * wgt;
       }
-      for (int d = tid; d < D; d += 128) {
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) v += s_o[((size_t)w * 16 + hh) * DP + d] * wgt[w];
-        a.pacc[pidx * D + d] = v;
-      }
-      if (tid == 0) { a.pm[pidx] = big; a.pl[pidx] = lsum; }
+      *reinterpret_cast<float2*>(a.pacc + pidx * D + d) = make_float2(v0, v1);
+      if (d == 0) { a.pm[pidx] = big; a.pl[pidx] = lsum; }
     }
   }
 
   // ---- ticket: the last CTA of this (query, kv head) merges every partial of the group's heads
+  DEC_TRACE(5);
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -537,70 +633,96 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
     s_last = ticket == expected - 1;
   }
   __syncthreads();
+  DEC_TRACE(6);
   if (!s_last) return;
   __threadfence();
-  // The partials of a head are (slot, part) pairs, j = slot * parts + part.  First one warp per head finds the
-  // maximum and the weights (kept in shared memory) and the denominator; then every thread takes four dimensions
-  // of one head and sums over the partials with loads that do not depend on each other or on the weights, so the
-  // latency of the loads is paid once per eight partials, not once per partial.  Order of summation is fixed, so
-  // the result is bit-repeatable.
+  // The partials of a head are (slot, part) pairs, j = slot * parts + part, and lie one after the other.  All
+  // threads first start asynchronous copies of the partial sums into shared memory, as many partials per head as
+  // fit, and read the maxima and denominators of every head's partials, all with accesses that do not depend on
+  // each other: one trip to L2 for the whole merge.  One warp per head then finds the maximum, the weights and the
+  // denominator; finally every thread takes four dimensions of one head and sums over the partials.  What does not
+  // fit in shared memory is read from global memory in the same fixed order, so the result is bit-repeatable.
   const int nslots = dense ? cur + 1 : a.ns;
   const int total = nslots * a.parts;
-  const int cap = min(1024, (int)(kStages * STAGE_BYTES / 4) / G);  // weights of a head that fit in shared memory
-  float* s_w = reinterpret_cast<float*>(s_pipe);
+  const int pipe_floats = NS * STAGE_BYTES / 4;
+  const int cap = min(min(1024, (total + 3) & ~3), (pipe_floats / (2 * G)) & ~3);  // maxima / weights kept per head
+  const int tc = min(total, cap);
+  const int pb = min(tc, (pipe_floats - 2 * G * cap) / (G * D));                   // partial sums kept per head
+  float* s_w = reinterpret_cast<float*>(s_pipe);  // [G][cap] maxima, then weights
+  float* s_l = s_w + G * cap;                       // [G][cap] denominators
+  float* s_acc = s_l + G * cap;                     // [G][pb][D] partial sums
   __shared__ float s_big[32], s_inv[32];
-  auto valid = [&](long long hbase, int j) {
-    const int sl = j / a.parts, pt = j - sl * a.parts;
-    const int c = dense ? sl : a.selected[hbase + sl];
-    return c >= 0 && pt < (c == cur ? cur_parts : a.parts);
-  };
-  for (int hl = warp; hl < G; hl += 4) {
-    const int h = g * G + hl;
-    const long long hbase = ((long long)row * a.Hq + h) * a.ns;
-    const long long p0 = hbase * a.parts;
+  const int d4n = D >> 2;  // the head dimension is a multiple of 8
+  const long long gbase = ((long long)row * a.Hq + g * G) * a.ns;  // first slot of the group's first head
+  for (int hl = 0; hl < G; ++hl) {
+    const float* src = a.pacc + (gbase + (long long)hl * a.ns) * a.parts * D;
+    const uint32_t dst = smem_u32(s_acc + (size_t)hl * pb * D);
+    for (int u = tid; u < pb * d4n; u += 128) cp_async16(dst + u * 16, src + u * 4, true);
+  }
+  cp_async_commit();
+  // This code runs once per launch in one CTA per group, from a cold instruction cache: it is kept short (little
+  // unrolling; the rarely needed paths sit in functions of their own) because fetching it costs more than running it.
+  const MergeTail tail{a.selected, a.pm, a.pl, a.pacc, a.parts, cur, cur_parts, D};
+#pragma unroll 2
+  for (int idx = tid; idx < G * tc; idx += 128) {
+    const int hl = idx / tc, j = idx - hl * tc;
+    const long long hbase = gbase + (long long)hl * a.ns;
+    const float m = __ldcg(a.pm + hbase * a.parts + j), l = __ldcg(a.pl + hbase * a.parts + j);
+    const bool ok = tail.valid(hbase, j);
+    s_w[hl * cap + j] = ok ? m : -INFINITY;
+    s_l[hl * cap + j] = ok ? l : 0.f;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  // half a warp per head
+  const int sub = lane & 15;
+#pragma unroll 1
+  for (int hl = warp * 2 + (lane >> 4); hl < ((G + 7) & ~7); hl += 8) {
+    const bool live = hl < G;  // the shuffles below need every lane
+    const int hc = live ? hl : 0;
+    const int h = g * G + hc;
+    const long long hbase = gbase + (long long)hc * a.ns;
     float big = -INFINITY;
-    for (int j = lane; j < total; j += 32) {
-      const float m = valid(hbase, j) ? __ldcg(a.pm + p0 + j) : -INFINITY;
-      if (j < cap) s_w[hl * cap + j] = m;
-      big = fmaxf(big, m);
+    if (live) {
+#pragma unroll 1
+      for (int j = sub; j < tc; j += 16) big = fmaxf(big, s_w[hc * cap + j]);
+      if (total > cap) big = merge_tail_max(tail, hbase, cap + sub, total, big);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xFFFFFFFFu, big, o));
+    for (int o = 8; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xFFFFFFFFu, big, o));
     float lsum = 0.f;
-    for (int j = lane; j < total; j += 32) {
-      const float m = j < cap ? s_w[hl * cap + j] : (valid(hbase, j) ? __ldcg(a.pm + p0 + j) : -INFINITY);
-      const float w = m == -INFINITY ? 0.f : dec_exp2(m - big);
-      if (j < cap) s_w[hl * cap + j] = w;
-      if (w != 0.f) lsum = fmaf(__ldcg(a.pl + p0 + j), w, lsum);
+    if (live) {
+#pragma unroll 1
+      for (int j = sub; j < tc; j += 16) {
+        const float m = s_w[hc * cap + j];
+        const float w = m == -INFINITY ? 0.f : dec_exp2(m - big);
+        s_w[hc * cap + j] = w;
+        lsum = fmaf(s_l[hc * cap + j], w, lsum);
+      }
+      if (total > cap) lsum = merge_tail_den(tail, hbase, cap + sub, total, big, lsum);
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
-    if (lane == 0) {
-      s_big[hl] = big;
-      s_inv[hl] = 1.f / lsum;
+    for (int o = 8; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
+    if (live && sub == 0) {
+      s_big[hc] = big;
+      s_inv[hc] = 1.f / lsum;
       a.lse[(long long)row * a.Hq + h] = (big + log2f(lsum)) * 0.6931471805599453f;
     }
   }
   __syncthreads();
-  const int d4n = D >> 2;  // the head dimension is a multiple of 8
+  DEC_TRACE(7);
+#pragma unroll 1
   for (int item = tid; item < G * d4n; item += 128) {
     const int hl = item / d4n, d = (item - hl * d4n) * 4;
     const int h = g * G + hl;
-    const long long hbase = ((long long)row * a.Hq + h) * a.ns;
-    const long long p0 = hbase * a.parts;
-    const float big = s_big[hl];
-    const float4* src = reinterpret_cast<const float4*>(a.pacc + p0 * D + d);
-    const int stride4 = D >> 2;
+    const long long hbase = gbase + (long long)hl * a.ns;
+    const float* wrow = s_w + hl * cap;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (int j = 0; j < total; ++j) {
-      const float w = j < cap ? s_w[hl * cap + j] : (valid(hbase, j) ? dec_exp2(__ldcg(a.pm + p0 + j) - big) : 0.f);
-      const float4 x = __ldcg(src + (long long)j * stride4);  // always inside the buffer; unused if w == 0
-      if (w != 0.f) {
-        v.x = fmaf(x.x, w, v.x); v.y = fmaf(x.y, w, v.y);
-        v.z = fmaf(x.z, w, v.z); v.w = fmaf(x.w, w, v.w);
-      }
-    }
+    const float4* sacc = reinterpret_cast<const float4*>(s_acc + (size_t)hl * pb * D + d);
+#pragma unroll 4
+    for (int j = 0; j < pb; ++j) merge_add(v, sacc[(size_t)j * d4n], wrow[j]);
+    if (tc > pb) v = merge_rest_acc(tail, hbase, pb, tc, d, wrow, v);
+    if (total > cap) v = merge_tail_acc(tail, hbase, cap, total, d, s_big[hl], v);
     const float inv = s_inv[hl];
     __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv, v.y * inv), hi = __floats2bfloat162_rn(v.z * inv, v.w * inv);
     uint2 pk;
@@ -609,12 +731,31 @@ __global__ void __launch_bounds__(128, (DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) dec
     *reinterpret_cast<uint2*>(a.out + ((long long)row * a.Hq + h) * D + d) = pk;
   }
   __syncthreads();
+  DEC_TRACE(8);
   if (tid == 0) a.counters[rowg] = 0;  // ready for the next launch (graph replay included)
 }
 
 }  // namespace moba
 
 using namespace moba;
+
+#ifdef MOBA_DEC_TRACE
+extern "C" int moba_debug_set_dec_trace(long long* buf) {
+  return cudaMemcpyToSymbol(moba::g_dec_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
+}
+#endif
+
+static int decode_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 extern "C" int moba_decode_metadata(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta,
                                     int rows, int append, void* stream) {
@@ -723,21 +864,29 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)c->dim));
   const int dp = c->dim <= 32 ? 32 : c->dim <= 64 ? 64 : c->dim <= 128 ? 128 : 256;
   const size_t red_bytes = (size_t)4 * 16 * (dp + 2) * 4;
-  const size_t pipe_bytes = (size_t)kStages * 2 * kStageTokens * dp * 2;
-  const size_t smem = red_bytes > pipe_bytes ? red_bytes : pipe_bytes;
   const dim3 grid(a.umax, a.parts, rows * c->hkv);
+  const bool deep = (long long)grid.x * grid.y * grid.z <= decode_sm_count();
+  const int stages = deep ? deep_stages(dp) : kStages;
+  const size_t pipe_bytes = (size_t)stages * 2 * kStageTokens * dp * 2;
+  const size_t smem = red_bytes > pipe_bytes ? red_bytes : pipe_bytes;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
   prof_begin(kProfDecodeAttend, st);
+#define MOBA_LAUNCH_ATTEND_NS(L, NS)                                                                               \
+  do {                                                                                                             \
+    e = cudaFuncSetAttribute(decode_attend_kernel<L, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) decode_attend_kernel<L, NS><<<grid, 128, smem, st>>>(a);                                 \
+  } while (0)
 #define MOBA_LAUNCH_ATTEND(L)                                                                                      \
   do {                                                                                                             \
-    e = cudaFuncSetAttribute(decode_attend_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    if (e == cudaSuccess) decode_attend_kernel<L><<<grid, 128, smem, st>>>(a);                                     \
+    if (deep) MOBA_LAUNCH_ATTEND_NS(L, deep_stages(L));                                                            \
+    else MOBA_LAUNCH_ATTEND_NS(L, kStages);                                                                        \
   } while (0)
   if (dp == 32) MOBA_LAUNCH_ATTEND(32);
   else if (dp == 64) MOBA_LAUNCH_ATTEND(64);
   else if (dp == 128) MOBA_LAUNCH_ATTEND(128);
   else MOBA_LAUNCH_ATTEND(256);
+#undef MOBA_LAUNCH_ATTEND_NS
 #undef MOBA_LAUNCH_ATTEND
   prof_end(kProfDecodeAttend, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
