@@ -189,6 +189,18 @@ int moba_rope_split(const void* qkv, const void* cosv, const void* sinv, long lo
                     void* v, void* stream);
 int moba_silu_mul(const void* gate_up, long long rows, int ffn, void* out, void* stream);
 
+/* Linear layer of a one-token decode step: y [n] = weight [n, k] x (+ bias), bf16 in and out, FP32 accumulation; the
+ * weight is read once with all loads of a thread in flight, which is what bounds a batch-1 step.
+ *   input: either x [k], or h_in [k] with norm_weight [k] (then x = norm_weight * rmsnorm(h_in + delta, eps), delta
+ *          may be null, and h_out, if given, receives h_in + delta: the residual add and the RMSNorm that precede the
+ *          projection in the layer run inside the same launch);
+ *   epilogue 0: y [n] = W x + bias (bias may be null);
+ *   epilogue 1: weight is [2 n, k], gate rows then up rows, y [n] = silu(gate) * up (no bias).
+ * k a multiple of 8, at most 16384 (8192 with epilogue 1); weight and x 16-byte aligned.  No reference counterpart
+ * (the reference's session calls the Hugging Face modules: examples/full_qwen2.py:76-90, 160-190). */
+int moba_decode_linear(const void* x, const void* h_in, const void* delta, const void* norm_weight, float eps, void* h_out,
+                       const void* weight, const void* bias, int k, int n, int epilogue, void* y, void* stream);
+
 /* Profiling aid (no reference counterpart): record the given CUDA events right before and after one
  * kernel on its launch stream. which: 1 forward remote pass, 2 forward self pass, 3 backward main
  * kernel, 4 decode attention. Null events switch it off. Process-wide, not thread-safe. */

@@ -75,6 +75,116 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __re
   out[row * ffn + i] = __float2bfloat16_rn(bf(g / (1.f + expf(-g))) * u);
 }
 
+
+// ---- batch-1 linear layers of the decode step -----------------------------------------------------------------
+// y = W x (+ bias) for one token: W [N, K] bf16 row-major is read once from HBM, which is all the step costs, so
+// the kernel is built to have every byte of its rows in flight at once: a group of 32..256 threads owns one output
+// (or one gate/up pair), each thread issues all of its 16-byte weight loads before anything else, and only then
+// the CTA prepares x in shared memory - either a plain copy, or the residual add + RMSNorm that precedes the
+// projection in the layer (recomputed by every CTA: 2 KB of input, cheaper than a launch of its own; CTA 0 writes
+// the new residual).  FP32 accumulation, one rounding to bf16 at the end as in a bf16 GEMM.
+struct LinearArgs {
+  const __nv_bfloat16 *x, *h_in, *delta, *norm_w, *W, *bias;
+  __nv_bfloat16 *h_out, *y;
+  float eps;
+  int K, N;  // N outputs; with PAIR the weight has 2 N rows (gate rows, then up rows)
+};
+
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+  const uint32_t wv[4] = {w.x, w.y, w.z, w.w}, xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc = fmaf(__uint_as_float(wv[i] << 16), __uint_as_float(xv[i] << 16), acc);
+    acc = fmaf(__uint_as_float(wv[i] & 0xFFFF0000u), __uint_as_float(xv[i] & 0xFFFF0000u), acc);
+  }
+  return acc;
+}
+
+template <int TPR, bool PAIR>
+__global__ void __launch_bounds__(256) decode_linear_kernel(LinearArgs a) {
+  constexpr int CH = PAIR ? 4 : 8;     // 16-byte loads per thread and weight row
+  constexpr int GROUPS = 256 / TPR;    // outputs per CTA
+  extern __shared__ __align__(16) uint8_t s_raw[];
+  __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(s_raw);
+  __shared__ float s_part[8], s_red[2][8];
+  const int tid = threadIdx.x, t = tid % TPR, group = tid / TPR;
+  const int out = blockIdx.x * GROUPS + group;
+  const int chunks = a.K >> 3;
+  // 1. every weight byte of this thread in flight
+  uint4 w0[CH], w1[PAIR ? CH : 1];
+  {
+    const bool live = out < a.N;
+    const uint4* r0 = reinterpret_cast<const uint4*>(a.W + (long long)(live ? out : 0) * a.K);
+    const uint4* r1 = reinterpret_cast<const uint4*>(a.W + ((long long)(live ? out : 0) + a.N) * a.K);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int c = t + i * TPR;
+      w0[i] = live && c < chunks ? __ldcs(r0 + c) : make_uint4(0u, 0u, 0u, 0u);
+      if (PAIR) w1[i] = live && c < chunks ? __ldcs(r1 + c) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  // 2. x into shared memory
+  if (a.h_in) {
+    float sum = 0.f;
+    for (int i = tid; i < a.K; i += 256) {
+      float v = __bfloat162float(a.h_in[i]);
+      if (a.delta) v = bf(v + __bfloat162float(a.delta[i]));
+      const __nv_bfloat16 vb = __float2bfloat16_rn(v);
+      s_x[i] = vb;
+      if (a.h_out && blockIdx.x == 0) a.h_out[i] = vb;
+      sum = fmaf(v, v, sum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    if ((tid & 31) == 0) s_part[tid >> 5] = sum;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) total += s_part[i];
+    const float r = rsqrtf(total / (float)a.K + a.eps);
+    for (int i = tid; i < a.K; i += 256)  // the same thread wrote s_x[i]
+      s_x[i] = __float2bfloat16_rn(__bfloat162float(a.norm_w[i]) * bf(__bfloat162float(s_x[i]) * r));
+  } else {
+    for (int c = tid; c < chunks; c += 256)
+      reinterpret_cast<uint4*>(s_x)[c] = __ldg(reinterpret_cast<const uint4*>(a.x) + c);
+  }
+  __syncthreads();
+  // 3. dot products
+  float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    const int c = t + i * TPR;
+    if (c < chunks) {
+      const uint4 xv = reinterpret_cast<const uint4*>(s_x)[c];
+      acc0 = dot8(w0[i], xv, acc0);
+      if (PAIR) acc1 = dot8(w1[i], xv, acc1);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, o);
+    if (PAIR) acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, o);
+  }
+  if (TPR > 32) {
+    if ((tid & 31) == 0) { s_red[0][tid >> 5] = acc0; s_red[1][tid >> 5] = acc1; }
+    __syncthreads();
+    if (t == 0) {
+      acc0 = 0.f; acc1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < TPR / 32; ++i) { acc0 += s_red[0][group * (TPR / 32) + i]; acc1 += s_red[1][group * (TPR / 32) + i]; }
+    }
+  }
+  // 4. epilogue
+  if (t == 0 && out < a.N) {
+    if (PAIR) {
+      const float g = bf(acc0), u = bf(acc1);
+      a.y[out] = __float2bfloat16_rn(bf(g / (1.f + expf(-g))) * u);
+    } else {
+      a.y[out] = __float2bfloat16_rn(a.bias ? acc0 + __bfloat162float(a.bias[out]) : acc0);
+    }
+  }
+}
+
 }  // namespace
 }  // namespace moba
 
@@ -102,5 +212,40 @@ extern "C" int moba_silu_mul(const void* gate_up, long long rows, int ffn, void*
   if (!gate_up || !out || rows < 1 || ffn < 1) return MOBA_ERR_INVALID;
   silu_mul_kernel<<<dim3((unsigned)((ffn + 255) / 256), (unsigned)rows), 256, 0, (cudaStream_t)stream>>>(
       static_cast<const __nv_bfloat16*>(gate_up), ffn, static_cast<__nv_bfloat16*>(out));
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* delta, const void* norm_weight, float eps, void* h_out,
+                                  const void* weight, const void* bias, int k, int n, int epilogue, void* y, void* stream) {
+  if (!weight || !y || k < 8 || (k & 7) || n < 1 || (epilogue != 0 && epilogue != 1)) return MOBA_ERR_INVALID;
+  if ((h_in == nullptr) == (x == nullptr)) return MOBA_ERR_INVALID;  // exactly one source of the input vector
+  if (h_in && !norm_weight) return MOBA_ERR_INVALID;
+  if (!h_in && (delta || h_out)) return MOBA_ERR_INVALID;
+  if (epilogue == 1 && bias) return MOBA_ERR_INVALID;
+  if (((uintptr_t)weight | (uintptr_t)(x ? x : weight)) & 15) return MOBA_ERR_INVALID;
+  const bool pair = epilogue == 1;
+  const int per_thread = (pair ? 4 : 8) * 8;  // elements of a row one thread can hold
+  int tpr = 32;
+  while (tpr < 256 && tpr * per_thread < k) tpr *= 2;
+  if (tpr * per_thread < k) return MOBA_ERR_UNSUPPORTED;
+  LinearArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(x); a.h_in = static_cast<const __nv_bfloat16*>(h_in);
+  a.delta = static_cast<const __nv_bfloat16*>(delta); a.norm_w = static_cast<const __nv_bfloat16*>(norm_weight);
+  a.W = static_cast<const __nv_bfloat16*>(weight); a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.h_out = static_cast<__nv_bfloat16*>(h_out); a.y = static_cast<__nv_bfloat16*>(y);
+  a.eps = eps; a.K = k; a.N = n;
+  const size_t smem = (size_t)k * 2;
+  cudaStream_t st = (cudaStream_t)stream;
+#define MOBA_LAUNCH_LINEAR(T)                                                                                       \
+  do {                                                                                                              \
+    const unsigned grid = (unsigned)((n + 256 / T - 1) / (256 / T));                                                \
+    if (pair) decode_linear_kernel<T, true><<<grid, 256, smem, st>>>(a);                                            \
+    else decode_linear_kernel<T, false><<<grid, 256, smem, st>>>(a);                                                \
+  } while (0)
+  if (tpr == 32) MOBA_LAUNCH_LINEAR(32);
+  else if (tpr == 64) MOBA_LAUNCH_LINEAR(64);
+  else if (tpr == 128) MOBA_LAUNCH_LINEAR(128);
+  else MOBA_LAUNCH_LINEAR(256);
+#undef MOBA_LAUNCH_LINEAR
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

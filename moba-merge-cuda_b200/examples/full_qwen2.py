@@ -86,12 +86,15 @@ class FullQwen2Session:
             a = layer.self_attn
             bias = None if a.q_proj.bias is None else torch.cat([a.q_proj.bias, a.k_proj.bias, a.v_proj.bias], 0)
             self.packed.append((torch.cat([a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], 0), bias))
-        # Decode-step glue as single launches (moba_add_rmsnorm, moba_rope_split, moba_silu_mul) instead of the
-        # Hugging Face modules' many small ones; needs bf16 and bias-free MLP projections.
+        # Decode step on this package's kernels (moba_decode_linear with the norms and SiLU * up inside, moba_rope_split)
+        # instead of the Hugging Face modules' many small launches; needs bf16 and bias-free gate/up projections.
         if not isinstance(fused_glue, bool):
             raise ValueError("fused_glue must be bool")
         self.fused_glue = fused_glue and self.dtype == torch.bfloat16 and all(
-            l.mlp.gate_proj.bias is None and l.mlp.up_proj.bias is None for l in layers)
+            l.mlp.gate_proj.bias is None and l.mlp.up_proj.bias is None for l in layers) and (
+            cfg.hidden_size % 8 == 0 and cfg.hidden_size <= 8192 and cfg.intermediate_size % 8 == 0
+            and cfg.intermediate_size <= 16384 and (cfg.num_attention_heads * (
+                getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads)) % 8 == 0)
         if self.fused_glue:
             from moba_opt import _ext
             self._lib = _ext.lib()
@@ -99,6 +102,7 @@ class FullQwen2Session:
             hidden, ffn = cfg.hidden_size, cfg.intermediate_size
             new = lambda n: torch.empty((1, n), dtype=self.dtype, device=self.device)
             self._h, self._y, self._act = [new(hidden), new(hidden)], new(hidden), new(ffn)
+            self._qkv, self._att, self._down = new((self.hq + 2 * self.hk) * self.dim), new(hidden), new(hidden)
 
     # ------------------------------------------------------------------ helpers
     def _check(self):
@@ -200,8 +204,10 @@ class FullQwen2Session:
             p._compute(True)
 
     def _compute_step_fused(self):
-        """The same step with the layer glue as single launches: residual add + RMSNorm, rotary embedding + split
-        of the fused q/k/v projection straight into the attention's input buffers, SiLU * up."""
+        """The same step in six launches per layer besides the attention's own: every projection is one
+        `moba_decode_linear` (the weight read once, all loads in flight), with the residual add + RMSNorm in front of
+        the q/k/v and the gate/up projections and SiLU * up behind the latter inside the same launch; rotary embedding
+        + split of q/k/v go straight into the attention's input buffers."""
         import ctypes
         lib, body, cfg = self._lib, self.model.model, self.model.config
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -209,12 +215,16 @@ class FullQwen2Session:
 
         def check(rc):
             if rc:
-                raise RuntimeError("glue kernel launch failed (status %d)" % rc)
+                raise RuntimeError("decode step kernel launch failed (status %d)" % rc)
 
-        def add_norm(h_in, delta, norm, h_out):
-            check(lib.moba_add_rmsnorm(h_in.data_ptr(), None if delta is None else delta.data_ptr(), norm.weight.data_ptr(),
-                                       float(norm.variance_epsilon), 1, hidden, None if h_out is None else h_out.data_ptr(),
-                                       self._y.data_ptr(), st))
+        def ptr(t):
+            return None if t is None else t.data_ptr()
+
+        def linear(x, weight, bias, out, *, norm=None, h_in=None, delta=None, h_out=None, epilogue=0):
+            n = out.shape[-1]
+            check(lib.moba_decode_linear(ptr(x), ptr(h_in), ptr(delta), None if norm is None else norm.weight.data_ptr(),
+                                         0.0 if norm is None else float(norm.variance_epsilon), ptr(h_out), weight.data_ptr(),
+                                         ptr(bias), weight.shape[1], n, epilogue, out.data_ptr(), st))
 
         h = body.embed_tokens(self.input)[0]
         position = self.caches[0]._lengths[:1].to(torch.long)
@@ -222,22 +232,25 @@ class FullQwen2Session:
         cos, sin = cos.contiguous(), sin.contiguous()
         delta, flip = None, 0
         for i, (layer, p) in enumerate(zip(body.layers, self.plans)):
-            if delta is None:
-                add_norm(h, None, layer.input_layernorm, None)
-            else:                                   # h <- h + (MLP output of the previous layer), then normalise
-                add_norm(h, delta, layer.input_layernorm, self._h[flip])
+            weight, bias = self.packed[i]
+            if delta is None:                       # first layer: the embedding is the residual
+                linear(None, weight, bias, self._qkv, norm=layer.input_layernorm, h_in=h)
+            else:                                   # h <- h + (MLP output of the previous layer), normalise, project
+                linear(None, weight, bias, self._qkv, norm=layer.input_layernorm, h_in=h, delta=delta, h_out=self._h[flip])
                 h, flip = self._h[flip], flip ^ 1
-            qkv = F.linear(self._y, *self.packed[i])
-            check(lib.moba_rope_split(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, self.hq, self.hk, self.dim,
+            check(lib.moba_rope_split(self._qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, self.hq, self.hk, self.dim,
                                       p.q.data_ptr(), p.k.data_ptr(), p.v.data_ptr(), st))
             self._attend(p)
-            att = layer.self_attn.o_proj(p.output.reshape(1, -1))
-            add_norm(h, att, layer.post_attention_layernorm, self._h[flip])
+            o = layer.self_attn.o_proj
+            linear(p.output, o.weight, o.bias, self._att)
+            linear(None, self.gate_up[i], None, self._act, norm=layer.post_attention_layernorm, h_in=h, delta=self._att,
+                   h_out=self._h[flip], epilogue=1)
             h, flip = self._h[flip], flip ^ 1
-            gu = F.linear(self._y, self.gate_up[i])
-            check(lib.moba_silu_mul(gu.data_ptr(), 1, ffn, self._act.data_ptr(), st))
-            delta = layer.mlp.down_proj(self._act)
-        add_norm(h, delta, body.norm, None)
+            down = layer.mlp.down_proj
+            linear(self._act, down.weight, down.bias, self._down)
+            delta = self._down
+        check(lib.moba_add_rmsnorm(h.data_ptr(), delta.data_ptr(), body.norm.weight.data_ptr(), float(body.norm.variance_epsilon),
+                                   1, hidden, None, self._y.data_ptr(), st))
         self.logits = self.model.lm_head(self._y)
         self.next_token.copy_(self.logits.argmax(-1, keepdim=True))
         return self.logits

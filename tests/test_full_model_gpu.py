@@ -141,3 +141,67 @@ def test_fused_glue_step_agrees_with_the_module_by_module_step(model):
             logits[fused] = [s.step(int(ids[0, i])).float().clone() for i in range(70, 80)]
     for a, b in zip(logits[False], logits[True]):
         assert _rel_l2(b, a) <= 5e-3
+
+
+@pytest.mark.parametrize("k,n", [(896, 1152), (896, 896), (4864, 896), (128, 40), (8, 1), (1032, 77), (16384, 9)])
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("norm", [False, True])
+def test_decode_linear_matches_torch(k, n, bias, norm):
+    """moba_decode_linear against the module arithmetic it replaces: residual add in bf16, RMSNorm as the Hugging Face
+    module computes it, projection with FP32 accumulation and one rounding."""
+    import ctypes
+    from moba_opt import _ext
+    lib = _ext.lib()
+    g = torch.Generator().manual_seed(k * 31 + n)
+    rnd = lambda *shape: torch.randn(*shape, generator=g).cuda().bfloat16()
+    w, b = rnd(n, k) * k ** -0.5, (rnd(n) if bias else None)
+    h, d, nw = rnd(k), rnd(k), (1 + 0.1 * torch.randn(k, generator=g)).cuda().bfloat16()
+    y, h_out = torch.empty(n, device="cuda", dtype=torch.bfloat16), torch.empty(k, device="cuda", dtype=torch.bfloat16)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if norm:
+        rc = lib.moba_decode_linear(None, h.data_ptr(), d.data_ptr(), nw.data_ptr(), 1e-6, h_out.data_ptr(), w.data_ptr(),
+                                    None if b is None else b.data_ptr(), k, n, 0, y.data_ptr(), st)
+        res = h + d
+        assert rc == 0 and torch.equal(h_out, res)
+        f = res.float()
+        x = nw * (f * torch.rsqrt(f.pow(2).mean() + 1e-6)).bfloat16()
+    else:
+        x = h
+        rc = lib.moba_decode_linear(x.data_ptr(), None, None, None, 0.0, None, w.data_ptr(), None if b is None else b.data_ptr(),
+                                    k, n, 0, y.data_ptr(), st)
+        assert rc == 0
+    want = w.double() @ x.double() + (0 if b is None else b.double())
+    assert _rel_l2(y, want) <= 4e-3
+    np.testing.assert_allclose(y.double().cpu().numpy(), want.cpu().numpy(), atol=0.03, rtol=0.02)
+
+
+@pytest.mark.parametrize("k,ffn", [(896, 4864), (128, 256), (8192, 5), (40, 33)])
+def test_decode_linear_gate_up_epilogue(k, ffn):
+    import ctypes
+    from moba_opt import _ext
+    lib = _ext.lib()
+    g = torch.Generator().manual_seed(k + ffn)
+    w = (torch.randn(2 * ffn, k, generator=g) * k ** -0.5).cuda().bfloat16()
+    x = torch.randn(k, generator=g).cuda().bfloat16()
+    y = torch.empty(ffn, device="cuda", dtype=torch.bfloat16)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.moba_decode_linear(x.data_ptr(), None, None, None, 0.0, None, w.data_ptr(), None, k, ffn, 1, y.data_ptr(), st) == 0
+    gu = (w.double() @ x.double())
+    want = torch.nn.functional.silu(gu[:ffn]) * gu[ffn:]
+    assert _rel_l2(y, want) <= 8e-3
+
+
+def test_decode_linear_contract():
+    import ctypes
+    from moba_opt import _ext
+    lib = _ext.lib()
+    t = torch.zeros(64, 64, device="cuda", dtype=torch.bfloat16)
+    p, st = t.data_ptr(), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    call = lambda *a: lib.moba_decode_linear(*a, st)
+    assert call(p, None, None, None, 0.0, None, p, None, 12, 4, 0, p) != 0          # k not a multiple of 8
+    assert call(p, p, None, p, 0.0, None, p, None, 64, 4, 0, p) != 0                # two input sources
+    assert call(None, None, None, None, 0.0, None, p, None, 64, 4, 0, p) != 0       # none
+    assert call(p, None, None, None, 0.0, None, p, p, 64, 4, 1, p) != 0             # bias with the gate/up epilogue
+    assert call(p, None, None, None, 0.0, None, p, None, 16392, 1, 0, p) != 0       # row longer than a group can hold
+    assert call(p + 2, None, None, None, 0.0, None, p, None, 64, 4, 0, p) != 0      # unaligned input
+    torch.cuda.synchronize()
