@@ -142,6 +142,15 @@ int moba_decode_append(const moba_cache_desc* c, const void* k, const void* v, c
 int moba_decode_means(const moba_cache_desc* c, const int32_t* seqs, const int32_t* chunk_or_pos, int items, int predicated,
                       unsigned* status, void* stream);
 
+/* First launch of an appending decode step: moba_decode_metadata (append != 0), moba_decode_append of one token per
+ * row and the predicated moba_decode_means in one launch, one CTA per row (ops/prepared_decode.py:7-41 are three
+ * kernels).  With qkv == NULL, k and v [rows, hkv, dim] are inputs.  With qkv [rows, (hq + 2 hkv) * dim] (the fused
+ * projection of the new token), the launch also applies the rotate-half rotary embedding with cos, sin [rows, dim]
+ * to the query and key heads and writes q [rows, hq, dim], k, v [rows, hkv, dim] before appending. */
+int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
+                           int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
+                           unsigned* status, void* stream);
+
 /* Routing (ops/paged_decode.py:48-64 scores; ops/prepared_decode.py:45-55,78-94 selection): q [rows,hq,dim];
  * scores [rows,hq,width] fp32 (may be null), -inf for chunks not completed before the query's chunk;
  * selected [rows,hq,1+remote] int32 = (pos/chunk_size, picks in descending score order with the lowest chunk

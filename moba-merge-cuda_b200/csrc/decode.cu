@@ -96,22 +96,8 @@ __global__ void __launch_bounds__(256) decode_append_kernel(CacheView cv, const 
   *reinterpret_cast<uint4*>(cv.vc + dst) = *reinterpret_cast<const uint4*>(v + src);
 }
 
-// --------------------------------------------------------------------------- chunk means (K11, K16)
-// One CTA per (item, kv head).  Explicit mode: item = (sequence, chunk).  Predicated mode: item =
-// a decode row; the mean is computed only when the token just appended completes its chunk.
-__global__ void __launch_bounds__(256) decode_means_kernel(CacheView cv, const int* __restrict__ seqs,
-                                                           const int* __restrict__ chunk_or_pos, int predicated,
-                                                           unsigned* status) {
-  extern __shared__ float s_part[];
-  const int item = blockIdx.x, g = blockIdx.y;
-  const int sid = seqs[item];
-  int chunk = chunk_or_pos[item];
-  if (predicated) {
-    const int pos = chunk;
-    if ((pos + 1) % cv.C != 0) return;
-    chunk = pos / cv.C;
-  }
-  if (chunk < 0 || chunk >= cv.max_chunks) return;
+// Mean of the keys of one (sequence, chunk, kv head) by one CTA of 256 threads; s_part holds (256 / (D / 8)) * D floats.
+__device__ __forceinline__ void chunk_mean_cta(const CacheView& cv, int sid, int chunk, int g, float* s_part, unsigned* status) {
   const int upr = cv.D >> 3, rpi = 256 / upr;
   const int ri = threadIdx.x / upr, u = threadIdx.x - ri * upr;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -137,6 +123,89 @@ __global__ void __launch_bounds__(256) decode_means_kernel(CacheView cv, const i
     float s = 0.f;
     for (int r = 0; r < rpi; ++r) s += s_part[r * cv.D + d];
     cv.means[(((long long)sid * cv.max_chunks + chunk) * cv.Hkv + g) * cv.D + d] = __float2bfloat16_rn(s / (float)cv.C);
+  }
+}
+
+// --------------------------------------------------------------------------- chunk means (K11, K16)
+// One CTA per (item, kv head).  Explicit mode: item = (sequence, chunk).  Predicated mode: item =
+// a decode row; the mean is computed only when the token just appended completes its chunk.
+__global__ void __launch_bounds__(256) decode_means_kernel(CacheView cv, const int* __restrict__ seqs,
+                                                           const int* __restrict__ chunk_or_pos, int predicated,
+                                                           unsigned* status) {
+  extern __shared__ float s_part[];
+  const int item = blockIdx.x, g = blockIdx.y;
+  const int sid = seqs[item];
+  int chunk = chunk_or_pos[item];
+  if (predicated) {
+    const int pos = chunk;
+    if ((pos + 1) % cv.C != 0) return;
+    chunk = pos / cv.C;
+  }
+  if (chunk < 0 || chunk >= cv.max_chunks) return;
+  chunk_mean_cta(cv, sid, chunk, g, s_part, status);
+}
+
+// --------------------------------------------------------------------------- first launch of an appending decode step
+// Metadata, append and the predicated chunk mean of one request per CTA, and, when the caller hands over the fused
+// q/k/v projection instead of separate k and v, the rotary embedding and the split as well: what were four
+// launches whose only cost is the wait from one to the next.  rotate-half rotary embedding with cos, sin [rows, D],
+// rounding to bf16 where the Hugging Face implementation does.
+__global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, const int* __restrict__ ids, int* __restrict__ positions,
+                                                                const int* __restrict__ delta, int b, int Hq,
+                                                                const __nv_bfloat16* __restrict__ qkv,
+                                                                const __nv_bfloat16* __restrict__ cosv,
+                                                                const __nv_bfloat16* __restrict__ sinv, __nv_bfloat16* q,
+                                                                __nv_bfloat16* k, __nv_bfloat16* v, unsigned* status) {
+  extern __shared__ float s_part[];
+  __shared__ int s_sid, s_pos, s_phys;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  if (tid == 0) {
+    const int sid = ids[row];
+    const int logical = delta[row], physical = delta[b + row];
+    if (logical >= 0 && logical < cv.width) cv.table[(long long)sid * cv.width + logical] = physical;
+    const int len = cv.lengths[sid];
+    positions[row] = len;
+    cv.lengths[sid] = len + 1;
+    s_sid = sid; s_pos = len;
+    const int page = len / cv.page;
+    s_phys = page < cv.width ? cv.table[(long long)sid * cv.width + page] : -1;
+  }
+  if (qkv) {
+    const int heads = Hq + 2 * cv.Hkv, D = cv.D, half = D >> 1;
+    const __nv_bfloat16* src = qkv + (long long)row * heads * D;
+    for (int i = tid; i < heads * D; i += 256) {
+      const int h = i / D, d = i - h * D;
+      if (h >= Hq + cv.Hkv) { v[((long long)row * cv.Hkv + (h - Hq - cv.Hkv)) * D + d] = src[i]; continue; }
+      const float x = __bfloat162float(src[i]);
+      const float other = __bfloat162float(src[h * D + (d < half ? d + half : d - half)]);
+      const float rot = d < half ? -other : other;
+      const float c = __bfloat162float(cosv[(long long)row * D + d]), sn = __bfloat162float(sinv[(long long)row * D + d]);
+      const __nv_bfloat16 out = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(x * c)) +
+                                                    __bfloat162float(__float2bfloat16_rn(rot * sn)));
+      if (h < Hq) q[((long long)row * Hq + h) * D + d] = out;
+      else k[((long long)row * cv.Hkv + (h - Hq)) * D + d] = out;
+    }
+  }
+  __syncthreads();  // position and page known; this CTA's k and v rows written
+  const int sid = s_sid, pos = s_pos, physical = s_phys;
+  if (physical < 0 || physical >= cv.num_pages) {
+    if (tid == 0 && status) atomicOr(status, kErrBadIndex);
+    return;
+  }
+  const int upr = cv.D >> 3;
+  for (int i = tid; i < cv.Hkv * upr; i += 256) {
+    const int head = i / upr, u = i - head * upr;
+    const long long dst = (((long long)physical * cv.page + pos % cv.page) * cv.Hkv + head) * cv.D + u * 8;
+    const long long src = ((long long)row * cv.Hkv + head) * cv.D + u * 8;
+    *reinterpret_cast<uint4*>(cv.kc + dst) = *reinterpret_cast<const uint4*>(k + src);
+    *reinterpret_cast<uint4*>(cv.vc + dst) = *reinterpret_cast<const uint4*>(v + src);
+  }
+  if ((pos + 1) % cv.C != 0) return;  // the token does not complete its chunk
+  const int chunk = pos / cv.C;
+  if (chunk >= cv.max_chunks) return;
+  for (int g = 0; g < cv.Hkv; ++g) {
+    __syncthreads();  // the appended row is visible; the previous head is done with the partial sums
+    chunk_mean_cta(cv, sid, chunk, g, s_part, status);
   }
 }
 
@@ -413,6 +482,9 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   __shared__ long long s_rowbase[NS][kStageTokens];
   DEC_TRACE_INIT;
   DEC_TRACE(0);
+  // a successor launched as a programmatic dependent (the output projection of a decode step) may begin its own
+  // independent loads now; it still waits for this grid to complete before it reads the result
+  asm volatile("griddepcontrol.launch_dependents;");
   const CacheView& cv = a.cv;
   const int D = cv.D, G = a.Hq / cv.Hkv;
   const int rowg = blockIdx.z, row = rowg / cv.Hkv, g = rowg - row * cv.Hkv;
@@ -787,6 +859,21 @@ extern "C" int moba_decode_means(const moba_cache_desc* c, const int32_t* seqs, 
   const int rpi = 256 / (c->dim / 8);
   decode_means_kernel<<<dim3(items, c->hkv), 256, (size_t)rpi * c->dim * 4, (cudaStream_t)stream>>>(
       make_cache_view(*c), seqs, chunk_or_pos, predicated, status);
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
+                                      int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
+                                      unsigned* status, void* stream) {
+  int rc = validate_cache(c);
+  if (rc != MOBA_OK) return rc;
+  if (!ids || !positions || !delta || !k || !v || rows < 1) return MOBA_ERR_INVALID;
+  if (qkv && (!cosv || !sinv || !q || hq < 1 || hq % c->hkv || (c->dim & 1))) return MOBA_ERR_INVALID;
+  const int rpi = 256 / (c->dim / 8);
+  decode_step_begin_kernel<<<rows, 256, (size_t)rpi * c->dim * 4, (cudaStream_t)stream>>>(
+      make_cache_view(*c), ids, positions, delta, rows, hq, static_cast<const __nv_bfloat16*>(qkv),
+      static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv), static_cast<__nv_bfloat16*>(q),
+      static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), status);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 

@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "moba_b200.h"
 
@@ -101,18 +102,21 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc)
 }
 
 template <int TPR, bool PAIR>
-__global__ void __launch_bounds__(256) decode_linear_kernel(LinearArgs a) {
+__global__ void __launch_bounds__(256, PAIR ? 5 : 4) decode_linear_kernel(LinearArgs a) {
   constexpr int CH = PAIR ? 4 : 8;     // 16-byte loads per thread and weight row
-  constexpr int GROUPS = 256 / TPR;    // outputs per CTA
+  constexpr int GROUPS = 256 / TPR;    // outputs per CTA and pass
   extern __shared__ __align__(16) uint8_t s_raw[];
   __nv_bfloat16* s_x = reinterpret_cast<__nv_bfloat16*>(s_raw);
   __shared__ float s_part[8], s_red[2][8];
   const int tid = threadIdx.x, t = tid % TPR, group = tid / TPR;
-  const int out = blockIdx.x * GROUPS + group;
   const int chunks = a.K >> 3;
-  // 1. every weight byte of this thread in flight
+  const int stride = gridDim.x * GROUPS;
+  // When the outputs outnumber the groups that can be resident, a CTA makes several passes (the same number for
+  // all of its groups) and x is prepared once.
+  const int passes = (a.N - blockIdx.x * GROUPS + stride - 1) / stride;
+  int out = blockIdx.x * GROUPS + group;
   uint4 w0[CH], w1[PAIR ? CH : 1];
-  {
+  auto load_weights = [&]() {  // every weight byte of this thread in flight
     const bool live = out < a.N;
     const uint4* r0 = reinterpret_cast<const uint4*>(a.W + (long long)(live ? out : 0) * a.K);
     const uint4* r1 = reinterpret_cast<const uint4*>(a.W + ((long long)(live ? out : 0) + a.N) * a.K);
@@ -122,8 +126,14 @@ __global__ void __launch_bounds__(256) decode_linear_kernel(LinearArgs a) {
       w0[i] = live && c < chunks ? __ldcs(r0 + c) : make_uint4(0u, 0u, 0u, 0u);
       if (PAIR) w1[i] = live && c < chunks ? __ldcs(r1 + c) : make_uint4(0u, 0u, 0u, 0u);
     }
-  }
-  // 2. x into shared memory
+  };
+  load_weights();
+  // Programmatic dependent launch: the weights above do not depend on the kernel before this one, so this grid
+  // may start while that one still runs (and lets its own successor do the same); everything below reads what the
+  // predecessor wrote, or writes what it may still read, and waits for it to have completed.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // x into shared memory while the weights are on their way
   if (a.h_in) {
     float sum = 0.f;
     for (int i = tid; i < a.K; i += 256) {
@@ -149,39 +159,42 @@ __global__ void __launch_bounds__(256) decode_linear_kernel(LinearArgs a) {
       reinterpret_cast<uint4*>(s_x)[c] = __ldg(reinterpret_cast<const uint4*>(a.x) + c);
   }
   __syncthreads();
-  // 3. dot products
-  float acc0 = 0.f, acc1 = 0.f;
+  for (int pass = 0; pass < passes; ++pass) {
+    if (pass) load_weights();
+    float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-  for (int i = 0; i < CH; ++i) {
-    const int c = t + i * TPR;
-    if (c < chunks) {
-      const uint4 xv = reinterpret_cast<const uint4*>(s_x)[c];
-      acc0 = dot8(w0[i], xv, acc0);
-      if (PAIR) acc1 = dot8(w1[i], xv, acc1);
+    for (int i = 0; i < CH; ++i) {
+      const int c = t + i * TPR;
+      if (c < chunks) {
+        const uint4 xv = reinterpret_cast<const uint4*>(s_x)[c];
+        acc0 = dot8(w0[i], xv, acc0);
+        if (PAIR) acc1 = dot8(w1[i], xv, acc1);
+      }
     }
-  }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, o);
-    if (PAIR) acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, o);
-  }
-  if (TPR > 32) {
-    if ((tid & 31) == 0) { s_red[0][tid >> 5] = acc0; s_red[1][tid >> 5] = acc1; }
-    __syncthreads();
-    if (t == 0) {
-      acc0 = 0.f; acc1 = 0.f;
+    for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1) {
+      acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, o);
+      if (PAIR) acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, o);
+    }
+    if (TPR > 32) {
+      if (pass) __syncthreads();  // the previous pass's sums have been read
+      if ((tid & 31) == 0) { s_red[0][tid >> 5] = acc0; s_red[1][tid >> 5] = acc1; }
+      __syncthreads();
+      if (t == 0) {
+        acc0 = 0.f; acc1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < TPR / 32; ++i) { acc0 += s_red[0][group * (TPR / 32) + i]; acc1 += s_red[1][group * (TPR / 32) + i]; }
+        for (int i = 0; i < TPR / 32; ++i) { acc0 += s_red[0][group * (TPR / 32) + i]; acc1 += s_red[1][group * (TPR / 32) + i]; }
+      }
     }
-  }
-  // 4. epilogue
-  if (t == 0 && out < a.N) {
-    if (PAIR) {
-      const float g = bf(acc0), u = bf(acc1);
-      a.y[out] = __float2bfloat16_rn(bf(g / (1.f + expf(-g))) * u);
-    } else {
-      a.y[out] = __float2bfloat16_rn(a.bias ? acc0 + __bfloat162float(a.bias[out]) : acc0);
+    if (t == 0 && out < a.N) {
+      if (PAIR) {
+        const float g = bf(acc0), u = bf(acc1);
+        a.y[out] = __float2bfloat16_rn(bf(g / (1.f + expf(-g))) * u);
+      } else {
+        a.y[out] = __float2bfloat16_rn(a.bias ? acc0 + __bfloat162float(a.bias[out]) : acc0);
+      }
     }
+    out += stride;
   }
 }
 
@@ -215,6 +228,12 @@ extern "C" int moba_silu_mul(const void* gate_up, long long rows, int ffn, void*
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
+// Programmatic dependent launch of the decode linears; MOBA_NO_PDL=1 in the environment turns it off (for comparison).
+static bool overlap_launches() {
+  static const bool on = [] { const char* e = getenv("MOBA_NO_PDL"); return !(e && e[0] == '1'); }();
+  return on;
+}
+
 extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* delta, const void* norm_weight, float eps, void* h_out,
                                   const void* weight, const void* bias, int k, int n, int epilogue, void* y, void* stream) {
   if (!weight || !y || k < 8 || (k & 7) || n < 1 || (epilogue != 0 && epilogue != 1)) return MOBA_ERR_INVALID;
@@ -236,16 +255,38 @@ extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* d
   a.eps = eps; a.K = k; a.N = n;
   const size_t smem = (size_t)k * 2;
   cudaStream_t st = (cudaStream_t)stream;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return MOBA_ERR_CUDA;
+#define MOBA_LAUNCH_LINEAR_P(T, P)                                                                                  \
+  do {                                                                                                              \
+    int per_sm = 0;                                                                                                 \
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_linear_kernel<T, P>, 256, smem) != cudaSuccess || per_sm < 1) \
+      return MOBA_ERR_CUDA;                                                                                         \
+    const long long units = (n + 256 / T - 1) / (256 / T), resident = (long long)per_sm * sms;                      \
+    const long long passes = (units + resident - 1) / resident;                                                     \
+    cudaLaunchConfig_t cfg = {};                                                                                    \
+    cfg.gridDim = dim3((unsigned)((units + passes - 1) / passes));                                                  \
+    cfg.blockDim = dim3(256);                                                                                       \
+    cfg.dynamicSmemBytes = smem;                                                                                    \
+    cfg.stream = st;                                                                                                \
+    cudaLaunchAttribute attr[1];                                                                                    \
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                                \
+    attr[0].val.programmaticStreamSerializationAllowed = 1;                                                         \
+    cfg.attrs = attr;                                                                                               \
+    cfg.numAttrs = overlap_launches() ? 1 : 0;                                                                      \
+    if (cudaLaunchKernelEx(&cfg, decode_linear_kernel<T, P>, a) != cudaSuccess) return MOBA_ERR_CUDA;              \
+  } while (0)
 #define MOBA_LAUNCH_LINEAR(T)                                                                                       \
   do {                                                                                                              \
-    const unsigned grid = (unsigned)((n + 256 / T - 1) / (256 / T));                                                \
-    if (pair) decode_linear_kernel<T, true><<<grid, 256, smem, st>>>(a);                                            \
-    else decode_linear_kernel<T, false><<<grid, 256, smem, st>>>(a);                                                \
+    if (pair) MOBA_LAUNCH_LINEAR_P(T, true);                                                                        \
+    else MOBA_LAUNCH_LINEAR_P(T, false);                                                                            \
   } while (0)
   if (tpr == 32) MOBA_LAUNCH_LINEAR(32);
   else if (tpr == 64) MOBA_LAUNCH_LINEAR(64);
   else if (tpr == 128) MOBA_LAUNCH_LINEAR(128);
   else MOBA_LAUNCH_LINEAR(256);
+#undef MOBA_LAUNCH_LINEAR_P
 #undef MOBA_LAUNCH_LINEAR
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

@@ -204,10 +204,11 @@ class FullQwen2Session:
             p._compute(True)
 
     def _compute_step_fused(self):
-        """The same step in six launches per layer besides the attention's own: every projection is one
+        """The same step in six launches per dense layer and seven per MoBA layer: every projection is one
         `moba_decode_linear` (the weight read once, all loads in flight), with the residual add + RMSNorm in front of
         the q/k/v and the gate/up projections and SiLU * up behind the latter inside the same launch; rotary embedding
-        + split of q/k/v go straight into the attention's input buffers."""
+        and split of q/k/v run inside the first launch of the attention step (metadata + append + chunk mean), then
+        routing (MoBA layers) and the attention kernel."""
         import ctypes
         lib, body, cfg = self._lib, self.model.model, self.model.config
         st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
@@ -238,9 +239,12 @@ class FullQwen2Session:
             else:                                   # h <- h + (MLP output of the previous layer), normalise, project
                 linear(None, weight, bias, self._qkv, norm=layer.input_layernorm, h_in=h, delta=delta, h_out=self._h[flip])
                 h, flip = self._h[flip], flip ^ 1
-            check(lib.moba_rope_split(self._qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, self.hq, self.hk, self.dim,
-                                      p.q.data_ptr(), p.k.data_ptr(), p.v.data_ptr(), st))
-            self._attend(p)
+            if self.backend == "attention_graph":   # the plan's own graph starts from its q, k, v buffers
+                check(lib.moba_rope_split(self._qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, self.hq, self.hk, self.dim,
+                                          p.q.data_ptr(), p.k.data_ptr(), p.v.data_ptr(), st))
+                p._run("step", True)
+            else:                                   # rotary embedding + split inside the step's first launch
+                p._compute(True, projected=(self._qkv, cos, sin))
             o = layer.self_attn.o_proj
             linear(p.output, o.weight, o.bias, self._att)
             linear(None, self.gate_up[i], None, self._act, norm=layer.post_attention_layernorm, h_in=h, delta=self._att,

@@ -77,6 +77,7 @@ def _bind(lib):
     lib.moba_decode_metadata.argtypes = [P, vp, vp, vp, i, i, vp]
     lib.moba_decode_append.argtypes = [P, vp, vp, vp, vp, i, vp, vp]
     lib.moba_decode_means.argtypes = [P, vp, vp, i, i, vp, vp]
+    lib.moba_decode_step_begin.argtypes = [P, vp, vp, vp, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.moba_decode_union_capacity.argtypes = [i, i, i, i]
     lib.moba_decode_route.argtypes = [P, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp]
     lib.moba_decode_attend_workspace_bytes.restype = sz

@@ -120,19 +120,23 @@ class PreparedDecode:
         self.delta.copy_(self.delta_host, non_blocking=False)
         self.delta_uploads += 1
 
-    def _compute(self, append):
+    def _compute(self, append, projected=None):
+        """Launches of one step.  `projected` = (qkv [b, (Hq + 2 Hkv) * D], cos, sin [b, D]): the fused q/k/v
+        projection of the new tokens; rotary embedding and split into `q`, `k`, `v` then run inside the first launch."""
         c, lib = self.cache, self._lib
         d = c._desc()
         st = ctypes.c_void_p(torch.cuda.current_stream(c.device).cuda_stream)
         b, h = len(self.ids), self.num_q_heads
         status = c._status.data_ptr()
         ids, pos = self.gpu_ids.data_ptr(), self.positions.data_ptr()
-        _ext.check(lib.moba_decode_metadata(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, int(append), st),
-                   "moba_decode_metadata")
         if append:
-            _ext.check(lib.moba_decode_append(ctypes.byref(d), self.k.data_ptr(), self.v.data_ptr(), ids, pos, b, status, st),
-                       "moba_decode_append")
-            _ext.check(lib.moba_decode_means(ctypes.byref(d), ids, pos, b, 1, status, st), "moba_decode_means")
+            qkv, cos, sin = (None, None, None) if projected is None else (t.data_ptr() for t in projected)
+            _ext.check(lib.moba_decode_step_begin(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, h, qkv, cos, sin,
+                                                  self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), status, st),
+                       "moba_decode_step_begin")
+        else:
+            _ext.check(lib.moba_decode_metadata(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, 0, st),
+                       "moba_decode_metadata")
         sel = None
         if not self.dense:
             _ext.check(lib.moba_decode_route(ctypes.byref(d), self.q.data_ptr(), ids, pos, b, h, self.remote, self.width,
