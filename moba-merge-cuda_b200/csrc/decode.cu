@@ -12,6 +12,7 @@
 // each of them; one CTA handles one part of one chunk for all those heads.  Partial (max, sum,
 // accumulator) triples go to a workspace and the last CTA of a (query, kv head) pair to finish -
 // found with an atomic ticket, nobody waits - merges them in a fixed order.
+#include "launch.cuh"
 #include "moba_b200.h"
 #include "prefill_common.cuh"
 #include "sm100.cuh"
@@ -150,15 +151,18 @@ __global__ void __launch_bounds__(256) decode_means_kernel(CacheView cv, const i
 // q/k/v projection instead of separate k and v, the rotary embedding and the split as well: what were four
 // launches whose only cost is the wait from one to the next.  rotate-half rotary embedding with cos, sin [rows, D],
 // rounding to bf16 where the Hugging Face implementation does.
-__global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, const int* __restrict__ ids, int* __restrict__ positions,
-                                                                const int* __restrict__ delta, int b, int Hq,
-                                                                const __nv_bfloat16* __restrict__ qkv,
-                                                                const __nv_bfloat16* __restrict__ cosv,
-                                                                const __nv_bfloat16* __restrict__ sinv, __nv_bfloat16* q,
-                                                                __nv_bfloat16* k, __nv_bfloat16* v, unsigned* status) {
+__global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, const int* ids, int* positions, const int* delta, int b,
+                                                                int Hq, const __nv_bfloat16* qkv, const __nv_bfloat16* cosv,
+                                                                const __nv_bfloat16* sinv, __nv_bfloat16* q, __nv_bfloat16* k,
+                                                                __nv_bfloat16* v, unsigned* status) {
+  // No pointer here is __restrict__ and nothing is read through the read-only path: this grid may start before the
+  // kernel that produces its inputs has finished, and a load the compiler may treat as invariant could be moved
+  // above the wait below.
   extern __shared__ float s_part[];
   __shared__ int s_sid, s_pos, s_phys;
   const int row = blockIdx.x, tid = threadIdx.x;
+  dependents_may_start();
+  wait_for_predecessor();  // the projection of the new token
   if (tid == 0) {
     const int sid = ids[row];
     const int logical = delta[row], physical = delta[b + row];
@@ -214,12 +218,14 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
 // chunks completed before the query's own chunk, -inf elsewhere; top-`remote` per head in descending
 // score order with the lowest chunk winning exact ties; selected[row, h, :] = (own chunk, picks...,
 // -1 padding); and the group's union list (chunk ascending, bitmask of heads) for the attention kernel.
-__global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const __nv_bfloat16* __restrict__ q,
-                                                           const int* __restrict__ ids, const int* __restrict__ positions,
-                                                           int Hq, int remote, int width, float* __restrict__ scores,
-                                                           int* __restrict__ selected, int* __restrict__ u_chunk,
-                                                           unsigned* __restrict__ u_mask, int* __restrict__ u_count, int umax) {
+__global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const __nv_bfloat16* q, const int* ids, const int* positions,
+                                                           int Hq, int remote, int width, float* scores, int* selected, int* u_chunk,
+                                                           unsigned* u_mask, int* u_count, int umax) {
+  // As in decode_step_begin_kernel: no __restrict__, no read-only loads - positions, the query and the chunk means
+  // come from kernels this grid may overlap with until the wait below.
   extern __shared__ float s_dyn[];
+  dependents_may_start();
+  wait_for_predecessor();  // positions, the query, a chunk mean the step's first launch may just have written
   const int G = Hq / cv.Hkv;
   float* s_scores = s_dyn;                                            // [G][width]
   unsigned* s_mask = reinterpret_cast<unsigned*>(s_dyn + G * width);  // [width + 1]
@@ -245,7 +251,7 @@ __global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const _
       const float* qrow = s_q + hl * cv.D;
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
       for (int u = 0; u < upr; ++u) {
-        const uint4 ma = __ldg(mrow + u);
+        const uint4 ma = __ldcg(mrow + u);
         const float* qq = qrow + u * 8;
         a0 = fmaf(qq[0], bf_lo(ma.x), a0); a1 = fmaf(qq[1], bf_hi(ma.x), a1);
         a2 = fmaf(qq[2], bf_lo(ma.y), a2); a3 = fmaf(qq[3], bf_hi(ma.y), a3);
@@ -373,7 +379,7 @@ __device__ __forceinline__ uint32_t kv_unit_offset(int tok, int unit) {
 // on the table entry, so several lookups can be in flight; a bad entry is recorded in `bad` and reported later.
 __device__ __forceinline__ long long attend_row_base(const CacheView& cv, int sid, int g, int pg, int r, bool exists,
                                                      bool& bad) {
-  const int physical = exists ? __ldg(cv.table + (long long)sid * cv.width + pg) : 0;
+  const int physical = exists ? __ldcg(cv.table + (long long)sid * cv.width + pg) : 0;
   const bool wrong = physical < 0 || physical >= cv.num_pages;
   bad |= wrong;
   return exists && !wrong ? (((long long)physical * cv.page + r) * cv.Hkv + g) * cv.D : -1;
@@ -428,7 +434,7 @@ struct MergeTail {
   int parts, cur, cur_parts, D;
   __device__ __forceinline__ bool valid(long long hbase, int j) const {
     const int sl = j / parts, pt = j - sl * parts;
-    const int c = selected ? __ldg(selected + hbase + sl) : sl;
+    const int c = selected ? __ldcg(selected + hbase + sl) : sl;
     return c >= 0 && pt < (c == cur ? cur_parts : parts);
   }
 };
@@ -482,9 +488,8 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   __shared__ long long s_rowbase[NS][kStageTokens];
   DEC_TRACE_INIT;
   DEC_TRACE(0);
-  // a successor launched as a programmatic dependent (the output projection of a decode step) may begin its own
-  // independent loads now; it still waits for this grid to complete before it reads the result
-  asm volatile("griddepcontrol.launch_dependents;");
+  dependents_may_start();   // e.g. the output projection, whose weight loads need nothing from here
+  wait_for_predecessor();   // routes, positions, the appended row
   const CacheView& cv = a.cv;
   const int D = cv.D, G = a.Hq / cv.Hkv;
   const int rowg = blockIdx.z, row = rowg / cv.Hkv, g = rowg - row * cv.Hkv;
@@ -666,7 +671,7 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
           const int* sel = a.selected + ((long long)row * a.Hq + g * G + hb + tid) * a.ns;
 #pragma unroll 4
           for (int s2 = a.ns - 1; s2 >= 0; --s2)
-            if (__ldg(sel + s2) == chunk) slot = s2;
+            if (__ldcg(sel + s2) == chunk) slot = s2;
         }
       }
       s_slot[tid] = slot;
@@ -870,10 +875,12 @@ extern "C" int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* i
   if (!ids || !positions || !delta || !k || !v || rows < 1) return MOBA_ERR_INVALID;
   if (qkv && (!cosv || !sinv || !q || hq < 1 || hq % c->hkv || (c->dim & 1))) return MOBA_ERR_INVALID;
   const int rpi = 256 / (c->dim / 8);
-  decode_step_begin_kernel<<<rows, 256, (size_t)rpi * c->dim * 4, (cudaStream_t)stream>>>(
-      make_cache_view(*c), ids, positions, delta, rows, hq, static_cast<const __nv_bfloat16*>(qkv),
-      static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv), static_cast<__nv_bfloat16*>(q),
-      static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), status);
+  if (launch_dependent(2u, decode_step_begin_kernel, dim3(rows), dim3(256), (size_t)rpi * c->dim * 4, (cudaStream_t)stream,
+                       make_cache_view(*c), ids, positions, delta, rows, hq, static_cast<const __nv_bfloat16*>(qkv),
+                       static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv),
+                       static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v),
+                       status) != cudaSuccess)
+    return MOBA_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
@@ -899,9 +906,10 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
       cudaFuncSetAttribute(decode_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return MOBA_ERR_CUDA;
   const int umax = moba_decode_union_capacity(hq, c->hkv, remote, width);
-  decode_route_kernel<<<dim3(rows, c->hkv), 128, smem, (cudaStream_t)stream>>>(
-      make_cache_view(*c), static_cast<const __nv_bfloat16*>(q), ids, positions, hq, remote, width, scores, selected, u_chunk, u_mask,
-      u_count, umax);
+  if (launch_dependent(4u, decode_route_kernel, dim3(rows, c->hkv), dim3(128), smem, (cudaStream_t)stream, make_cache_view(*c),
+                       static_cast<const __nv_bfloat16*>(q), ids, positions, hq, remote, width, scores, selected, u_chunk, u_mask,
+                       u_count, umax) != cudaSuccess)
+    return MOBA_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
@@ -962,7 +970,7 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
 #define MOBA_LAUNCH_ATTEND_NS(L, NS)                                                                               \
   do {                                                                                                             \
     e = cudaFuncSetAttribute(decode_attend_kernel<L, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess) decode_attend_kernel<L, NS><<<grid, 128, smem, st>>>(a);                                 \
+    if (e == cudaSuccess) e = launch_dependent(8u, decode_attend_kernel<L, NS>, grid, dim3(128), smem, st, a);         \
   } while (0)
 #define MOBA_LAUNCH_ATTEND(L)                                                                                      \
   do {                                                                                                             \

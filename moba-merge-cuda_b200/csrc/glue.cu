@@ -7,8 +7,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
 
+#include "launch.cuh"
 #include "moba_b200.h"
 
 namespace moba {
@@ -131,8 +131,8 @@ __global__ void __launch_bounds__(256, PAIR ? 5 : 4) decode_linear_kernel(Linear
   // Programmatic dependent launch: the weights above do not depend on the kernel before this one, so this grid
   // may start while that one still runs (and lets its own successor do the same); everything below reads what the
   // predecessor wrote, or writes what it may still read, and waits for it to have completed.
-  asm volatile("griddepcontrol.launch_dependents;");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  dependents_may_start();
+  wait_for_predecessor();
   // x into shared memory while the weights are on their way
   if (a.h_in) {
     float sum = 0.f;
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(256, PAIR ? 5 : 4) decode_linear_kernel(Linear
       s_x[i] = __float2bfloat16_rn(__bfloat162float(a.norm_w[i]) * bf(__bfloat162float(s_x[i]) * r));
   } else {
     for (int c = tid; c < chunks; c += 256)
-      reinterpret_cast<uint4*>(s_x)[c] = __ldg(reinterpret_cast<const uint4*>(a.x) + c);
+      reinterpret_cast<uint4*>(s_x)[c] = __ldcg(reinterpret_cast<const uint4*>(a.x) + c);  // not the read-only path: see above
   }
   __syncthreads();
   for (int pass = 0; pass < passes; ++pass) {
@@ -228,12 +228,6 @@ extern "C" int moba_silu_mul(const void* gate_up, long long rows, int ffn, void*
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
-// Programmatic dependent launch of the decode linears; MOBA_NO_PDL=1 in the environment turns it off (for comparison).
-static bool overlap_launches() {
-  static const bool on = [] { const char* e = getenv("MOBA_NO_PDL"); return !(e && e[0] == '1'); }();
-  return on;
-}
-
 extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* delta, const void* norm_weight, float eps, void* h_out,
                                   const void* weight, const void* bias, int k, int n, int epilogue, void* y, void* stream) {
   if (!weight || !y || k < 8 || (k & 7) || n < 1 || (epilogue != 0 && epilogue != 1)) return MOBA_ERR_INVALID;
@@ -265,17 +259,9 @@ extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* d
       return MOBA_ERR_CUDA;                                                                                         \
     const long long units = (n + 256 / T - 1) / (256 / T), resident = (long long)per_sm * sms;                      \
     const long long passes = (units + resident - 1) / resident;                                                     \
-    cudaLaunchConfig_t cfg = {};                                                                                    \
-    cfg.gridDim = dim3((unsigned)((units + passes - 1) / passes));                                                  \
-    cfg.blockDim = dim3(256);                                                                                       \
-    cfg.dynamicSmemBytes = smem;                                                                                    \
-    cfg.stream = st;                                                                                                \
-    cudaLaunchAttribute attr[1];                                                                                    \
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                                \
-    attr[0].val.programmaticStreamSerializationAllowed = 1;                                                         \
-    cfg.attrs = attr;                                                                                               \
-    cfg.numAttrs = overlap_launches() ? 1 : 0;                                                                      \
-    if (cudaLaunchKernelEx(&cfg, decode_linear_kernel<T, P>, a) != cudaSuccess) return MOBA_ERR_CUDA;              \
+    if (launch_dependent(1u, decode_linear_kernel<T, P>, dim3((unsigned)((units + passes - 1) / passes)), dim3(256), smem, st, \
+                         a) != cudaSuccess)                                                                         \
+      return MOBA_ERR_CUDA;                                                                                         \
   } while (0)
 #define MOBA_LAUNCH_LINEAR(T)                                                                                       \
   do {                                                                                                              \
