@@ -102,7 +102,7 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc)
 }
 
 template <int TPR, bool PAIR>
-__global__ void __launch_bounds__(256, PAIR ? 5 : 4) decode_linear_kernel(LinearArgs a) {
+__global__ void __launch_bounds__(256, 4) decode_linear_kernel(LinearArgs a) {
   constexpr int CH = PAIR ? 4 : 8;     // 16-byte loads per thread and weight row
   constexpr int GROUPS = 256 / TPR;    // outputs per CTA and pass
   extern __shared__ __align__(16) uint8_t s_raw[];
@@ -128,6 +128,13 @@ __global__ void __launch_bounds__(256, PAIR ? 5 : 4) decode_linear_kernel(Linear
     }
   };
   load_weights();
+  // the norm weight is a constant too: the first 1024 entries travel with the projection's weights
+  float nw[4] = {0.f, 0.f, 0.f, 0.f};
+  if (a.h_in) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (tid + j * 256 < a.K) nw[j] = __bfloat162float(a.norm_w[tid + j * 256]);
+  }
   // Programmatic dependent launch: the weights above do not depend on the kernel before this one, so this grid
   // may start while that one still runs (and lets its own successor do the same); everything below reads what the
   // predecessor wrote, or writes what it may still read, and waits for it to have completed.
@@ -152,7 +159,12 @@ __global__ void __launch_bounds__(256, PAIR ? 5 : 4) decode_linear_kernel(Linear
 #pragma unroll
     for (int i = 0; i < 8; ++i) total += s_part[i];
     const float r = rsqrtf(total / (float)a.K + a.eps);
-    for (int i = tid; i < a.K; i += 256)  // the same thread wrote s_x[i]
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {         // the same thread wrote s_x[i]
+      const int i = tid + j * 256;
+      if (i < a.K) s_x[i] = __float2bfloat16_rn(nw[j] * bf(__bfloat162float(s_x[i]) * r));
+    }
+    for (int i = tid + 1024; i < a.K; i += 256)
       s_x[i] = __float2bfloat16_rn(__bfloat162float(a.norm_w[i]) * bf(__bfloat162float(s_x[i]) * r));
   } else {
     for (int c = tid; c < chunks; c += 256)
@@ -258,7 +270,7 @@ extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* d
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_linear_kernel<T, P>, 256, smem) != cudaSuccess || per_sm < 1) \
       return MOBA_ERR_CUDA;                                                                                         \
     const long long units = (n + 256 / T - 1) / (256 / T), resident = (long long)per_sm * sms;                      \
-    const long long passes = (units + resident - 1) / resident;                                                     \
+    const long long passes = units > 4 * resident ? (units + resident - 1) / resident : 1; /* a short tail is cheaper */ \
     if (launch_dependent(1u, decode_linear_kernel<T, P>, dim3((unsigned)((units + passes - 1) / passes)), dim3(256), smem, st, \
                          a) != cudaSuccess)                                                                         \
       return MOBA_ERR_CUDA;                                                                                         \
