@@ -142,6 +142,15 @@ int moba_decode_append(const moba_cache_desc* c, const void* k, const void* v, c
 int moba_decode_means(const moba_cache_desc* c, const int32_t* seqs, const int32_t* chunk_or_pos, int items, int predicated,
                       unsigned* status, void* stream);
 
+/* Prefill hand-off: appends whole prompts, k, v [tokens, hkv, dim] packed by cu_seqlens [num_seqs + 1], to sequences
+ * seqs[i] at positions start[i] .. and writes the mean of every chunk the append completes, in one launch and one
+ * pass over K (the reference appends per layer with cache.append after the prefill attention, examples/full_qwen2.py:109,
+ * kv_cache.py:172-191: a scatter over per-token index arrays, then a second pass for the means).  The page table must
+ * already map the new positions.  max_chunks_touched >= the largest number of chunks one sequence's new tokens fall
+ * into.  Means are bit-identical to moba_decode_means. */
+int moba_prefill_to_cache(const moba_cache_desc* c, const void* k, const void* v, const int32_t* seqs, const int32_t* start,
+                          const int32_t* cu_seqlens, int num_seqs, int max_chunks_touched, unsigned* status, void* stream);
+
 /* First launch of an appending decode step: moba_decode_metadata (append != 0), moba_decode_append of one token per
  * row and the predicated moba_decode_means in one launch, one CTA per row (ops/prepared_decode.py:7-41 are three
  * kernels).  With qkv == NULL, k and v [rows, hkv, dim] are inputs.  With qkv [rows, (hq + 2 hkv) * dim] (the fused

@@ -97,6 +97,24 @@ __global__ void __launch_bounds__(256) decode_append_kernel(CacheView cv, const 
   *reinterpret_cast<uint4*>(cv.vc + dst) = *reinterpret_cast<const uint4*>(v + src);
 }
 
+// Second half of a chunk mean: thread (ri, u) holds the sums of unit u over the rows w = ri, ri + rpi, ... of the chunk;
+// the row groups are added in ascending order and the mean is rounded to bf16.  Every producer of a mean goes through
+// here with the same assignment of rows to threads, so a mean has the same bits whichever call computed it.
+__device__ __forceinline__ void chunk_mean_finish(const CacheView& cv, int sid, int chunk, int g, const float (&acc)[8], float* s_part) {
+  const int upr = cv.D >> 3, rpi = 256 / upr;
+  const int ri = threadIdx.x / upr, u = threadIdx.x - ri * upr;
+  if (ri < rpi) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_part[ri * cv.D + u * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < cv.D; d += 256) {
+    float s = 0.f;
+    for (int r = 0; r < rpi; ++r) s += s_part[r * cv.D + d];
+    cv.means[(((long long)sid * cv.max_chunks + chunk) * cv.Hkv + g) * cv.D + d] = __float2bfloat16_rn(s / (float)cv.C);
+  }
+}
+
 // Mean of the keys of one (sequence, chunk, kv head) by one CTA of 256 threads; s_part holds (256 / (D / 8)) * D floats.
 __device__ __forceinline__ void chunk_mean_cta(const CacheView& cv, int sid, int chunk, int g, float* s_part, unsigned* status) {
   const int upr = cv.D >> 3, rpi = 256 / upr;
@@ -116,15 +134,8 @@ __device__ __forceinline__ void chunk_mean_cta(const CacheView& cv, int sid, int
 #pragma unroll
       for (int i = 0; i < 4; ++i) { acc[2 * i] += bf_lo(wv[i]); acc[2 * i + 1] += bf_hi(wv[i]); }
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s_part[ri * cv.D + u * 8 + i] = acc[i];
   }
-  __syncthreads();
-  for (int d = threadIdx.x; d < cv.D; d += 256) {
-    float s = 0.f;
-    for (int r = 0; r < rpi; ++r) s += s_part[r * cv.D + d];
-    cv.means[(((long long)sid * cv.max_chunks + chunk) * cv.Hkv + g) * cv.D + d] = __float2bfloat16_rn(s / (float)cv.C);
-  }
+  chunk_mean_finish(cv, sid, chunk, g, acc, s_part);
 }
 
 // --------------------------------------------------------------------------- chunk means (K11, K16)
@@ -144,6 +155,73 @@ __global__ void __launch_bounds__(256) decode_means_kernel(CacheView cv, const i
   }
   if (chunk < 0 || chunk >= cv.max_chunks) return;
   chunk_mean_cta(cv, sid, chunk, g, s_part, status);
+}
+
+// --------------------------------------------------------------------------- prefill hand-off
+// Appends whole prompts and writes the means of the chunks they complete in one pass over K: one CTA per (chunk
+// touched, kv head, sequence) stores the chunk's new K and V rows into their pages and adds the K rows up as it
+// goes (rows of the chunk that were cached before are read back), instead of an append launch over per-token
+// (sequence, position) arrays built on the host followed by a second pass over K for the means.
+__global__ void __launch_bounds__(256) prefill_to_cache_kernel(CacheView cv, const __nv_bfloat16* __restrict__ k,
+                                                               const __nv_bfloat16* __restrict__ v, const int* __restrict__ seqs,
+                                                               const int* __restrict__ start, const int* __restrict__ cu,
+                                                               unsigned* status) {
+  extern __shared__ float s_part[];
+  const int s = blockIdx.z, g = blockIdx.y;
+  const int sid = seqs[s], first = start[s], src0 = cu[s], last = first + (cu[s + 1] - cu[s]);
+  const int chunk = first / cv.C + blockIdx.x;
+  const int lo = chunk * cv.C, hi = min(lo + cv.C, last);
+  if (lo >= last) return;
+  const int upr = cv.D >> 3, rpi = 256 / upr;
+  const int ri = threadIdx.x / upr, u = threadIdx.x - ri * upr;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (ri < rpi) {
+    // four rows per round: table entries, then rows, then stores, so that a round costs three trips, not twelve
+    for (int w0 = ri; lo + w0 < hi; w0 += 4 * rpi) {
+      long long dst[4];
+      bool fresh[4];
+      uint4 kr[4], vr[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = lo + w0 + j * rpi;
+        dst[j] = -1;
+        fresh[j] = t >= first;
+        if (t < hi) {
+          const int physical = cv.table[(long long)sid * cv.width + t / cv.page];
+          if (physical < 0 || physical >= cv.num_pages) {
+            if (status) atomicOr(status, kErrBadIndex);
+          } else {
+            dst[j] = (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * cv.D + u * 8;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        kr[j] = vr[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (dst[j] < 0) continue;
+        if (fresh[j]) {
+          const long long src = (((long long)src0 + (lo + w0 + j * rpi - first)) * cv.Hkv + g) * cv.D + u * 8;
+          kr[j] = *reinterpret_cast<const uint4*>(k + src);
+          vr[j] = *reinterpret_cast<const uint4*>(v + src);
+        } else {
+          kr[j] = *reinterpret_cast<const uint4*>(cv.kc + dst[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {  // ascending rows: the order of chunk_mean_cta
+        if (dst[j] < 0) continue;
+        if (fresh[j]) {
+          *reinterpret_cast<uint4*>(cv.kc + dst[j]) = kr[j];
+          *reinterpret_cast<uint4*>(cv.vc + dst[j]) = vr[j];
+        }
+        const uint32_t wv[4] = {kr[j].x, kr[j].y, kr[j].z, kr[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { acc[2 * i] += bf_lo(wv[i]); acc[2 * i + 1] += bf_hi(wv[i]); }
+      }
+    }
+  }
+  if (hi - lo < cv.C || chunk >= cv.max_chunks) return;  // the chunk is still open
+  chunk_mean_finish(cv, sid, chunk, g, acc, s_part);
 }
 
 // --------------------------------------------------------------------------- first launch of an appending decode step
@@ -864,6 +942,20 @@ extern "C" int moba_decode_means(const moba_cache_desc* c, const int32_t* seqs, 
   const int rpi = 256 / (c->dim / 8);
   decode_means_kernel<<<dim3(items, c->hkv), 256, (size_t)rpi * c->dim * 4, (cudaStream_t)stream>>>(
       make_cache_view(*c), seqs, chunk_or_pos, predicated, status);
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" int moba_prefill_to_cache(const moba_cache_desc* c, const void* k, const void* v, const int32_t* seqs, const int32_t* start,
+                                     const int32_t* cu_seqlens, int num_seqs, int max_chunks_touched, unsigned* status,
+                                     void* stream) {
+  int rc = validate_cache(c);
+  if (rc != MOBA_OK) return rc;
+  if (!k || !v || !seqs || !start || !cu_seqlens || num_seqs < 1 || num_seqs > 65535 || max_chunks_touched < 1)
+    return MOBA_ERR_INVALID;
+  const int rpi = 256 / (c->dim / 8);
+  prefill_to_cache_kernel<<<dim3(max_chunks_touched, c->hkv, num_seqs), 256, (size_t)rpi * c->dim * 4, (cudaStream_t)stream>>>(
+      make_cache_view(*c), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), seqs, start, cu_seqlens,
+      status);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 

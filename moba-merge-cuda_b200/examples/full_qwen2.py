@@ -143,7 +143,7 @@ class FullQwen2Session:
         cu = torch.tensor([0, t], device=self.device, dtype=torch.int32)
         for i, layer in enumerate(body.layers):
             q, k, v = self._project(i, layer.input_layernorm(h), cos, sin)
-            self.caches[i].append(k, v, sequence_ids=[0], cu_seqlens=[0, t])
+            self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t])
             dense = self.layer_dense[i] or self.prefill_mode == "dense"
             out = opt_gqa_cuda(q, k, v, cu, t, self.dense_config if dense else self.route_config)
             h = h + layer.self_attn.o_proj(out.reshape(t, -1))

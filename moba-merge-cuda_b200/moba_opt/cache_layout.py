@@ -86,7 +86,8 @@ class PageAllocator:
         return total
 
     # -- planning / publishing ---------------------------------------------------------------
-    def plan_append(self, sequence_ids, counts):
+    def plan_append(self, sequence_ids, counts, tokens=True):
+        """`tokens=False` leaves out the per-token (sequence, position) lists, which a whole-prompt append does not need."""
         ids = self.validate_ids(sequence_ids, unique=True)
         if len(ids) != len(counts):
             raise ValueError("one token count per sequence required")
@@ -102,8 +103,9 @@ class PageAllocator:
             first, last = lengths[sid], lengths[sid] + n
             for logical in range(_ceil_div(first, page), _ceil_div(last, page)):
                 rows[sid][logical] = pool.pop()
-            where_seq.extend(sid for _ in range(n))
-            where_pos.extend(range(first, last))
+            if tokens:
+                where_seq.extend(sid for _ in range(n))
+                where_pos.extend(range(first, last))
             closed.extend((sid, c) for c in range(first // chunk, last // chunk))
             lengths[sid] = last
         tables = tuple(tuple(rows[s]) if s in rows else self.tables[s] for s in range(self.batch_size))

@@ -78,6 +78,7 @@ def _bind(lib):
     lib.moba_decode_append.argtypes = [P, vp, vp, vp, vp, i, vp, vp]
     lib.moba_decode_means.argtypes = [P, vp, vp, i, i, vp, vp]
     lib.moba_decode_step_begin.argtypes = [P, vp, vp, vp, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_prefill_to_cache.argtypes = [P, vp, vp, vp, vp, vp, i, i, vp, vp]
     lib.moba_decode_union_capacity.argtypes = [i, i, i, i]
     lib.moba_decode_route.argtypes = [P, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp]
     lib.moba_decode_attend_workspace_bytes.restype = sz
@@ -230,6 +231,37 @@ class PagedKVCache:
             self._reject_storage_alias(k, v)
             ids, counts = self._append_counts(k.shape[0], sequence_ids, cu_seqlens)
             return self._append_validated(k, v, ids, counts)[0]
+
+    @torch.no_grad()
+    def append_prefill(self, k, v, *, sequence_ids, cu_seqlens=None):
+        """`append` for whole prompts (the hand-off from a prefill pass): same contract and resulting cache state, but
+        one launch writes the pages and the means of the completed chunks in a single pass over K, and the host builds
+        no per-token index arrays.  Returns the new lengths of the given sequences."""
+        with self._lock, torch.cuda.device(self.device):
+            self._check_stream()
+            self._tensor(k, "k", expected_heads=self.num_kv_heads)
+            self._tensor(v, "v", expected_heads=self.num_kv_heads, expected_tokens=k.shape[0])
+            self._reject_storage_alias(k, v)
+            ids, counts = self._append_counts(k.shape[0], sequence_ids, cu_seqlens)
+            starts = [self._layout.lengths[s] for s in ids]
+            plan = self._layout.plan_append(ids, counts, tokens=False)
+            cu = [0]
+            for n in counts:
+                cu.append(cu[-1] + n)
+            table = self._gpu(plan.tables)
+            lengths, seqs, start, cu_dev = self._upload(plan.lengths, ids, starts, cu)
+            self._table.copy_(table)
+            self._lengths.copy_(lengths)
+            c = self.chunk_size
+            touched = max((first + n - 1) // c - first // c + 1 for first, n in zip(starts, counts))
+            d, st = self._desc(), self._cuda_stream()
+            k, v = k.contiguous(), v.contiguous()
+            self._run(self._lib.moba_prefill_to_cache(ctypes.byref(d), k.data_ptr(), v.data_ptr(), seqs.data_ptr(), start.data_ptr(),
+                                                      cu_dev.data_ptr(), len(ids), touched, self._status.data_ptr(), st),
+                      "moba_prefill_to_cache")
+            self._layout.commit(plan)
+            self._candidate_count = self._count_candidates(plan.lengths)
+            return tuple(plan.lengths[s] for s in ids)
 
     def _append_validated(self, k, v, ids, counts):
         """Caller holds the lock and has validated the inputs.  Metadata is staged first, the CPU layout

@@ -289,6 +289,51 @@ def test_dense_merge_over_more_partials_than_fit_in_shared_memory(hq, dim, chunk
     check(cache, cache.attend(q, sequence_ids=[0], mode="dense"), q)
 
 
+@pytest.mark.parametrize("page,chunk,dim,hk", [(16, 32, 64, 2), (7, 24, 40, 3), (48, 128, 128, 1), (3, 1, 8, 2), (16, 512, 64, 2)])
+def test_prefill_hand_off_equals_append(page, chunk, dim, hk):
+    """`append_prefill` (one launch: pages + means in one pass over K) leaves the cache exactly as `append` does:
+    payload, lengths, page table and chunk means bit for bit, for ragged prompts, prompts that continue a sequence in
+    the middle of a chunk, and prompts shorter than a chunk."""
+    from moba_opt import PagedKVCache
+    first = [chunk + 5, 3, 2 * chunk]
+    second = [max(2, 3 * chunk - 7), chunk // 2 + 1, 1]
+    caches = [PagedKVCache(3, sum(map(max, zip(first, second))) * 2 + 4 * chunk, hk, dim, page_size=page, chunk_size=chunk)
+              for _ in range(2)]
+    for round_, counts in enumerate((first, second)):
+        total = sum(counts)
+        k, v = rand((total, hk, dim), 281 + round_), rand((total, hk, dim), 291 + round_)
+        cu = [0]
+        for n in counts:
+            cu.append(cu[-1] + n)
+        order = [2, 0, 1] if round_ else [0, 1, 2]
+        caches[0].append(k, v, sequence_ids=order, cu_seqlens=cu)
+        lengths = caches[1].append_prefill(k, v, sequence_ids=order, cu_seqlens=cu)
+        assert caches[0].lengths == caches[1].lengths and caches[0].page_table == caches[1].page_table
+        assert lengths == tuple(caches[1].lengths[s] for s in order)
+        for sid in range(3):
+            a, b = caches[0].materialize(sid), caches[1].materialize(sid)
+            assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+            closed = caches[0].lengths[sid] // chunk
+            assert torch.equal(caches[0]._means[sid, :closed], caches[1]._means[sid, :closed])
+    q = rand((3, 2 * hk, dim), 299)
+    check(caches[1], caches[1].attend(q, sequence_ids=[0, 1, 2], topk=3), q)
+
+
+def test_prefill_hand_off_errors_do_not_mutate_cache():
+    from moba_opt import PagedKVCache
+    cache = PagedKVCache(1, 64, 1, 8, page_size=4, chunk_size=8)
+    k = rand((10, 1, 8), 301)
+    cache.append_prefill(k, k.clone(), sequence_ids=[0], cu_seqlens=[0, 10])
+    lengths, table = cache.lengths, cache.page_table
+    with pytest.raises(ValueError):
+        cache.append_prefill(rand((60, 1, 8), 302), rand((60, 1, 8), 303), sequence_ids=[0], cu_seqlens=[0, 60])   # over capacity
+    with pytest.raises(ValueError):
+        cache.append_prefill(k, k.clone(), sequence_ids=[0], cu_seqlens=[0, 9])                                    # bad cu_seqlens
+    assert cache.lengths == lengths and cache.page_table == table
+    got = cache.materialize(0)
+    assert torch.equal(got[0], k)
+
+
 def test_extreme_logits_use_stable_online_softmax():
     from moba_opt import PagedKVCache
     cache = PagedKVCache(1, 16, 1, 8, page_size=3, chunk_size=4)
