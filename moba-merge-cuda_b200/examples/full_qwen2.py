@@ -141,6 +141,8 @@ class FullQwen2Session:
         h = body.embed_tokens(ids)[0]
         cos, sin = self._rope(h, torch.arange(t, device=self.device))
         cu = torch.tensor([0, t], device=self.device, dtype=torch.int32)
+        if self.fused_glue:
+            return self._prefill_hidden_fused(h, cos, sin, cu, t)
         for i, layer in enumerate(body.layers):
             q, k, v = self._project(i, layer.input_layernorm(h), cos, sin)
             self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t])
@@ -149,6 +151,50 @@ class FullQwen2Session:
             h = h + layer.self_attn.o_proj(out.reshape(t, -1))
             h = h + layer.mlp(layer.post_attention_layernorm(h))
         return body.norm(h)[None]
+
+    def _prefill_hidden_fused(self, h, cos, sin, cu, t):
+        """The same layers with the elementwise work between the GEMMs as single launches over all rows (residual add +
+        RMSNorm, rotary embedding + q/k/v split, SiLU * up) instead of the modules' chains of small kernels."""
+        import ctypes
+        lib, body, cfg = self._lib, self.model.model, self.model.config
+        st = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        hidden, ffn = cfg.hidden_size, cfg.intermediate_size
+
+        def check(rc):
+            if rc:
+                raise RuntimeError("glue kernel launch failed (status %d)" % rc)
+
+        def add_norm(h_in, delta, norm, h_out, y):
+            check(lib.moba_add_rmsnorm(h_in.data_ptr(), None if delta is None else delta.data_ptr(), norm.weight.data_ptr(),
+                                       float(norm.variance_epsilon), t, hidden, None if h_out is None else h_out.data_ptr(),
+                                       y.data_ptr(), st))
+
+        new = lambda *shape: torch.empty(shape, dtype=self.dtype, device=self.device)
+        h = h.contiguous()
+        cos, sin = cos.contiguous(), sin.contiguous()
+        y, res, act = new(t, hidden), [new(t, hidden), new(t, hidden)], new(t, ffn)
+        q, k, v = new(t, self.hq, self.dim), new(t, self.hk, self.dim), new(t, self.hk, self.dim)
+        delta, flip = None, 0
+        for i, layer in enumerate(body.layers):
+            if delta is None:
+                add_norm(h, None, layer.input_layernorm, None, y)
+            else:
+                add_norm(h, delta, layer.input_layernorm, res[flip], y)
+                h, flip = res[flip], flip ^ 1
+            qkv = F.linear(y, *self.packed[i])
+            check(lib.moba_rope_split(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), t, self.hq, self.hk, self.dim,
+                                      q.data_ptr(), k.data_ptr(), v.data_ptr(), st))
+            self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t])
+            dense = self.layer_dense[i] or self.prefill_mode == "dense"
+            out = opt_gqa_cuda(q, k, v, cu, t, self.dense_config if dense else self.route_config)
+            att = layer.self_attn.o_proj(out.reshape(t, -1))
+            add_norm(h, att, layer.post_attention_layernorm, res[flip], y)
+            h, flip = res[flip], flip ^ 1
+            gu = F.linear(y, self.gate_up[i])
+            check(lib.moba_silu_mul(gu.data_ptr(), t, ffn, act.data_ptr(), st))
+            delta = layer.mlp.down_proj(act)
+        add_norm(h, delta, body.norm, None, y)
+        return y[None]
 
     @torch.no_grad()
     def prefill(self, ids):
