@@ -457,7 +457,8 @@ __device__ __forceinline__ uint32_t kv_unit_offset(int tok, int unit) {
 // on the table entry, so several lookups can be in flight; a bad entry is recorded in `bad` and reported later.
 __device__ __forceinline__ long long attend_row_base(const CacheView& cv, int sid, int g, int pg, int r, bool exists,
                                                      bool& bad) {
-  const int physical = exists ? __ldcg(cv.table + (long long)sid * cv.width + pg) : 0;
+  // an ordinary cached load (a page serves many tokens): not the read-only path, which a dependent launch must avoid
+  const int physical = exists ? cv.table[(long long)sid * cv.width + pg] : 0;
   const bool wrong = physical < 0 || physical >= cv.num_pages;
   bad |= wrong;
   return exists && !wrong ? (((long long)physical * cv.page + r) * cv.Hkv + g) * cv.D : -1;
