@@ -288,6 +288,36 @@ def run_full_model(dev):
                 mode="whole-model CUDA graph, greedy token kept on the device")
 
 
+def run_full_model_only(args):
+    """Profiler runs: the MoBA session of BASELINE configs[4] launch by launch (no graph), prefill and four steps
+    outside, `--only-full-model N` greedy steps inside a cudaProfilerStart/Stop range (`ncu --profile-from-start off`)."""
+    import torch
+    sys.path.insert(0, str(ROOT / "moba-merge-cuda_b200" / "examples"))
+    from full_qwen2 import FullQwen2Session, random_qwen2
+    w = FULL_MODEL
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    model = random_qwen2(device=dev)
+    ids = torch.randint(0, model.config.vocab_size, (1, w["prompt"]), generator=torch.Generator().manual_seed(0)).to(dev)
+    with FullQwen2Session(model, w["prompt"] + 64 + args.only_full_model, chunk=w["chunk"], topk=w["topk"], page=w["page"],
+                          backend="eager", stable_routes=True, mode="moba", dense_layers=w["dense_layers"]) as s:
+        s.prefill(ids)
+        s.prepare()
+        for _ in range(4):
+            s.greedy_step()
+        torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        torch.cuda.profiler.start()
+        e[0].record()
+        for _ in range(args.only_full_model):
+            s.greedy_step()
+        e[1].record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    print(json.dumps(dict(full_model_only=True, workload=w["name"], steps=args.only_full_model, backend="eager",
+                          ms_per_step=e[0].elapsed_time(e[1]) / args.only_full_model)))
+
+
 # ----------------------------------------------------------------------------- GPU arm
 def run_decode_only(args):
     import torch
@@ -517,6 +547,8 @@ def main():
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode leg")
     ap.add_argument("--no-full-model", action="store_true", help="skip the full-model decode leg")
     ap.add_argument("--only-decode", action="store_true", help="run only the paged-decode leg (profiler runs)")
+    ap.add_argument("--only-full-model", type=int, default=0, metavar="N",
+                    help="run only N launch-by-launch decode steps of the full-model session (profiler runs)")
     ap.add_argument("--decode-steps", type=int, default=DECODE["steps"])
     ap.add_argument("--kernels-only", action="store_true", help="skip the host-buffer and CPU legs (profiler runs)")
     args = ap.parse_args()
@@ -526,6 +558,8 @@ def main():
         run_reference(args)
     elif args.only_decode:
         run_decode_only(args)
+    elif args.only_full_model:
+        run_full_model_only(args)
     else:
         run_ours(args)
 
