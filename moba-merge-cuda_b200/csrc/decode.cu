@@ -291,6 +291,8 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
   }
 }
 
+constexpr int kRouteTile = 64;  // chunk means staged in shared memory per round of decode_route_kernel
+
 // --------------------------------------------------------------------------- routing (K12, K13, K17, K18)
 // One CTA (128 threads) per (query row, kv head).  scores[row, h, c] = q . mean[c] in FP32 for the
 // chunks completed before the query's own chunk, -inf elsewhere; top-`remote` per head in descending
@@ -321,25 +323,43 @@ __global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const _
   for (int i = tid; i < G * cv.D; i += 128)
     s_q[i] = __bfloat162float(q[((long long)row * Hq + g * G) * cv.D + i]);
   __syncthreads();
-  for (int pair = tid; pair < G * width; pair += 128) {
-    const int hl = pair / width, c = pair - hl * width;
-    float s = -INFINITY;
-    if (c < nlegal) {
-      const uint4* mrow = reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c) * cv.Hkv + g) * cv.D);
+  // The mean rows of kRouteTile chunks at a time are brought into shared memory by all threads with loads that do not
+  // depend on each other (one trip to L2 per tile); the (head, chunk) pairs are then scored from there.  Rows are
+  // padded to an odd number of 16-byte units so that threads on consecutive chunks hit different banks.
+  const int ustride = upr | 1;
+  uint4* s_tile = reinterpret_cast<uint4*>(s_dyn + ((G * width + width + 1 + G * cv.D + 3) & ~3));
+  for (int c0 = 0; c0 < nlegal; c0 += kRouteTile) {
+    const int nt = min(kRouteTile, nlegal - c0);
+#pragma unroll 4
+    for (int idx = tid; idx < nt * upr; idx += 128) {
+      const int cl = idx / upr, u = idx - cl * upr;
+      s_tile[cl * ustride + u] = __ldcg(
+          reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c0 + cl) * cv.Hkv + g) * cv.D) + u);
+    }
+    __syncthreads();
+    for (int pair = tid; pair < G * nt; pair += 128) {
+      const int hl = pair / nt, cl = pair - hl * nt;
+      const uint4* mrow = s_tile + cl * ustride;
       const float* qrow = s_q + hl * cv.D;
       float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
       for (int u = 0; u < upr; ++u) {
-        const uint4 ma = __ldcg(mrow + u);
+        const uint4 ma = mrow[u];
         const float* qq = qrow + u * 8;
         a0 = fmaf(qq[0], bf_lo(ma.x), a0); a1 = fmaf(qq[1], bf_hi(ma.x), a1);
         a2 = fmaf(qq[2], bf_lo(ma.y), a2); a3 = fmaf(qq[3], bf_hi(ma.y), a3);
         a0 = fmaf(qq[4], bf_lo(ma.z), a0); a1 = fmaf(qq[5], bf_hi(ma.z), a1);
         a2 = fmaf(qq[6], bf_lo(ma.w), a2); a3 = fmaf(qq[7], bf_hi(ma.w), a3);
       }
-      s = (a0 + a1) + (a2 + a3);
+      const float sc = (a0 + a1) + (a2 + a3);
+      s_scores[hl * width + c0 + cl] = sc;
+      if (scores) scores[((long long)row * Hq + g * G + hl) * width + c0 + cl] = sc;
     }
-    s_scores[pair] = s;
-    if (scores) scores[((long long)row * Hq + g * G + hl) * width + c] = s;
+    __syncthreads();
+  }
+  for (int pair = tid; pair < G * (width - nlegal); pair += 128) {  // not a candidate
+    const int hl = pair / (width - nlegal), c = nlegal + pair - hl * (width - nlegal);
+    s_scores[hl * width + c] = -INFINITY;
+    if (scores) scores[((long long)row * Hq + g * G + hl) * width + c] = -INFINITY;
   }
   __syncthreads();
   // top-k: one warp per head, `remote` rounds of (max value, lowest index among equals)
@@ -993,7 +1013,8 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
     return MOBA_ERR_INVALID;
   const int G = hq / c->hkv;
   if (G > 32 || remote > 16) return MOBA_ERR_UNSUPPORTED;
-  const size_t smem = ((size_t)G * width + width + 1 + (size_t)G * c->dim) * 4;
+  const size_t smem = ((((size_t)G * width + width + 1 + (size_t)G * c->dim + 3) & ~(size_t)3)) * 4 +
+                      (size_t)kRouteTile * ((c->dim / 8) | 1) * 16;
   if (smem > 200 * 1024) return MOBA_ERR_UNSUPPORTED;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(decode_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
