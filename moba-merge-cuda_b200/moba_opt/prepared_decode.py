@@ -58,7 +58,11 @@ class PreparedDecode:
             self.gpu_ids = torch.tensor(self.ids, dtype=torch.int32, device=dev)
             self.positions = torch.empty(b, dtype=torch.int32, device=dev)
             self.delta = torch.full((2, b), -1, dtype=torch.int32, device=dev)
-            self.delta_host = torch.empty((2, b), dtype=torch.int32, pin_memory=True)
+            # pinned staging buffers for the page-table delta, used in turn so that an upload need not wait for the copy
+            self._delta_ring = [torch.empty((2, b), dtype=torch.int32, pin_memory=True) for _ in range(4)]
+            self._delta_done = [None] * len(self._delta_ring)
+            self._delta_next = 0
+            self._row_of = {sid: i for i, sid in enumerate(self.ids)}
             self._umax = lib.moba_decode_union_capacity(h, hk, self.remote, self.width)
             self._u_chunk = torch.empty((b, hk, self._umax), dtype=torch.int32, device=dev)
             self._u_mask = torch.empty_like(self._u_chunk)
@@ -108,16 +112,26 @@ class PreparedDecode:
 
     # ------------------------------------------------------------------ device work
     def _upload(self, plan):
-        """Only when some sequence opens a page: a synchronous 2 x b int32 copy (the pinned staging
-        buffer may be rewritten right after it returns)."""
+        """Only when some sequence opens a page: an asynchronous 2 x b int32 copy from one of a few pinned staging
+        buffers; the host waits only if the copy that last used the buffer (four uploads ago) is still pending, so a
+        step that opens a page does not drain the stream."""
         if not plan.updates:
             return
-        row_of = {sid: i for i, sid in enumerate(self.ids)}
-        self.delta_host.fill_(-1)
+        slot = self._delta_next
+        self._delta_next = (slot + 1) % len(self._delta_ring)
+        if self._delta_done[slot] is not None:
+            self._delta_done[slot].synchronize()
+        host = self._delta_ring[slot]
+        view = host.numpy()
+        view.fill(-1)
         for sid, logical, physical in plan.updates:
-            self.delta_host[0, row_of[sid]] = logical
-            self.delta_host[1, row_of[sid]] = physical
-        self.delta.copy_(self.delta_host, non_blocking=False)
+            row = self._row_of[sid]
+            view[0, row] = logical
+            view[1, row] = physical
+        self.delta.copy_(host, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        self._delta_done[slot] = done
         self.delta_uploads += 1
 
     def _compute(self, append, projected=None):
