@@ -207,6 +207,14 @@ int moba_rope_split(const void* qkv, const void* cosv, const void* sinv, long lo
                     void* v, void* stream);
 int moba_silu_mul(const void* gate_up, long long rows, int ffn, void* out, void* stream);
 
+/* Inputs of a decode step in one launch: h [rows, hidden] = embedding[tokens[i]] and the rotary table of each row's
+ * position, cos / sin [rows, dim] = cos / sin(positions[i] * inv_freq[d mod dim/2]) * scaling, FP32 arithmetic rounded
+ * to bf16 (the default-type rotary module of Hugging Face, which the reference's session calls:
+ * examples/full_qwen2.py:160-170).  tokens int64, positions int32, both on the device. */
+int moba_decode_step_inputs(const int64_t* tokens, const void* embedding, int hidden, const int32_t* positions,
+                            const float* inv_freq, float scaling, int dim, long long rows, void* h, void* cosv, void* sinv,
+                            void* stream);
+
 /* Linear layer of a one-token decode step: y [n] = weight [n, k] x (+ bias), bf16 in and out, FP32 accumulation; the
  * weight is read once with all loads of a thread in flight, which is what bounds a batch-1 step.
  *   input: either x [k], or h_in [k] with norm_weight [k] (then x = norm_weight * rmsnorm(h_in + delta, eps), delta

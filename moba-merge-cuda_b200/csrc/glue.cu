@@ -210,6 +210,25 @@ __global__ void __launch_bounds__(256, 4) decode_linear_kernel(LinearArgs a) {
   }
 }
 
+// Inputs of a decode step in one launch: the embedding row of each token and the rotary table of its position,
+// cos / sin [rows, dim] = cos / sin(position * inv_freq[d mod dim/2]) * scaling computed in FP32 and rounded to bf16 -
+// the arithmetic of the Hugging Face rotary module (default rope type), which takes about ten small launches.
+__global__ void __launch_bounds__(256) step_inputs_kernel(const long long* tokens, const __nv_bfloat16* __restrict__ embed, int hidden,
+                                                          const int* positions, const float* __restrict__ inv_freq, float scaling,
+                                                          int dim, __nv_bfloat16* h, __nv_bfloat16* cosv, __nv_bfloat16* sinv) {
+  const long long row = blockIdx.x;
+  const long long tok = tokens[row];
+  const __nv_bfloat16* src = embed + tok * hidden;
+  for (int i = threadIdx.x; i < hidden; i += 256) h[row * hidden + i] = src[i];
+  const float pos = (float)positions[row];
+  const int half = dim >> 1;
+  for (int d = threadIdx.x; d < dim; d += 256) {
+    const float f = inv_freq[d < half ? d : d - half] * pos;
+    cosv[row * dim + d] = __float2bfloat16_rn(cosf(f) * scaling);
+    sinv[row * dim + d] = __float2bfloat16_rn(sinf(f) * scaling);
+  }
+}
+
 }  // namespace
 }  // namespace moba
 
@@ -286,5 +305,16 @@ extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* d
   else MOBA_LAUNCH_LINEAR(256);
 #undef MOBA_LAUNCH_LINEAR_P
 #undef MOBA_LAUNCH_LINEAR
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" int moba_decode_step_inputs(const int64_t* tokens, const void* embedding, int hidden, const int32_t* positions,
+                                       const float* inv_freq, float scaling, int dim, long long rows, void* h, void* cosv, void* sinv,
+                                       void* stream) {
+  if (!tokens || !embedding || !positions || !inv_freq || !h || !cosv || !sinv || hidden < 1 || dim < 2 || (dim & 1) || rows < 1)
+    return MOBA_ERR_INVALID;
+  step_inputs_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const long long*>(tokens), static_cast<const __nv_bfloat16*>(embedding), hidden, positions, inv_freq, scaling, dim,
+      static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(cosv), static_cast<__nv_bfloat16*>(sinv));
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

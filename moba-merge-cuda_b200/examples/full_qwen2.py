@@ -103,6 +103,13 @@ class FullQwen2Session:
             new = lambda n: torch.empty((1, n), dtype=self.dtype, device=self.device)
             self._h, self._y, self._act = [new(hidden), new(hidden)], new(hidden), new(ffn)
             self._qkv, self._att, self._down = new((self.hq + 2 * self.hk) * self.dim), new(hidden), new(hidden)
+            # rotary table inside the step's first launch when the model uses the default rotary type
+            rotary = model.model.rotary_emb
+            self._inv_freq = None
+            if getattr(rotary, "rope_type", "default") == "default" and rotary.inv_freq.numel() * 2 == self.dim:
+                self._inv_freq = rotary.inv_freq.detach().float().contiguous()
+                self._rope_scale = float(getattr(rotary, "attention_scaling", 1.0))
+                self._h0, self._cos, self._sin = new(hidden), new(self.dim), new(self.dim)
 
     # ------------------------------------------------------------------ helpers
     def _check(self):
@@ -273,10 +280,16 @@ class FullQwen2Session:
                                          0.0 if norm is None else float(norm.variance_epsilon), ptr(h_out), weight.data_ptr(),
                                          ptr(bias), weight.shape[1], n, epilogue, out.data_ptr(), st))
 
-        h = body.embed_tokens(self.input)[0]
-        position = self.caches[0]._lengths[:1].to(torch.long)
-        cos, sin = self._rope(h, position)
-        cos, sin = cos.contiguous(), sin.contiguous()
+        if self._inv_freq is not None:              # embedding row + rotary table of the new position: one launch
+            h, cos, sin = self._h0, self._cos, self._sin
+            check(lib.moba_decode_step_inputs(self.input.data_ptr(), body.embed_tokens.weight.data_ptr(), hidden,
+                                              self.caches[0]._lengths.data_ptr(), self._inv_freq.data_ptr(), self._rope_scale,
+                                              self.dim, 1, h.data_ptr(), cos.data_ptr(), sin.data_ptr(), st))
+        else:
+            h = body.embed_tokens(self.input)[0]
+            position = self.caches[0]._lengths[:1].to(torch.long)
+            cos, sin = self._rope(h, position)
+            cos, sin = cos.contiguous(), sin.contiguous()
         delta, flip = None, 0
         for i, (layer, p) in enumerate(zip(body.layers, self.plans)):
             weight, bias = self.packed[i]

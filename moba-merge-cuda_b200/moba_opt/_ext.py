@@ -49,6 +49,8 @@ def lib():
         L.moba_rope_split.argtypes = [c_vp, c_vp, c_vp, ctypes.c_longlong, ctypes.c_int, ctypes.c_int, ctypes.c_int, c_vp, c_vp,
                                       c_vp, c_vp]
         L.moba_silu_mul.argtypes = [c_vp, ctypes.c_longlong, ctypes.c_int, c_vp, c_vp]
+        L.moba_decode_step_inputs.argtypes = [c_vp, c_vp, ctypes.c_int, c_vp, c_vp, ctypes.c_float, ctypes.c_int,
+                                              ctypes.c_longlong, c_vp, c_vp, c_vp, c_vp]
         L.moba_decode_linear.argtypes = [c_vp, c_vp, c_vp, c_vp, ctypes.c_float, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, c_vp, c_vp]
         _lib = L

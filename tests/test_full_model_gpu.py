@@ -205,3 +205,26 @@ def test_decode_linear_contract():
     assert call(p, None, None, None, 0.0, None, p, None, 16392, 1, 0, p) != 0       # row longer than a group can hold
     assert call(p + 2, None, None, None, 0.0, None, p, None, 64, 4, 0, p) != 0      # unaligned input
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("position", [0, 1, 777, 16384, 131071])
+def test_step_inputs_match_the_rotary_module_and_embedding(model, position):
+    """moba_decode_step_inputs against the modules it replaces in a step: embedding row and rotary cos / sin, bit for bit."""
+    import ctypes
+    from moba_opt import _ext
+    lib = _ext.lib()
+    body, cfg = model.model, model.config
+    dim = cfg.hidden_size // cfg.num_attention_heads
+    tok = torch.tensor([[123]], device="cuda")
+    pos = torch.tensor([position], device="cuda", dtype=torch.int32)
+    want_h = body.embed_tokens(tok)[0]
+    cos, sin = body.rotary_emb(want_h[None], pos.long()[None])
+    inv = body.rotary_emb.inv_freq.float().contiguous()
+    h = torch.empty(1, cfg.hidden_size, device="cuda", dtype=torch.bfloat16)
+    c, s_ = torch.empty(1, dim, device="cuda", dtype=torch.bfloat16), torch.empty(1, dim, device="cuda", dtype=torch.bfloat16)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.moba_decode_step_inputs(tok.data_ptr(), body.embed_tokens.weight.data_ptr(), cfg.hidden_size, pos.data_ptr(),
+                                       inv.data_ptr(), float(body.rotary_emb.attention_scaling), dim, 1, h.data_ptr(), c.data_ptr(),
+                                       s_.data_ptr(), st) == 0
+    assert torch.equal(h, want_h)
+    assert torch.equal(c, cos[0].to(torch.bfloat16)) and torch.equal(s_, sin[0].to(torch.bfloat16))
