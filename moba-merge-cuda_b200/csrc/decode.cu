@@ -452,8 +452,9 @@ constexpr int kHeadBlock = 16;    // query heads of a group processed together (
 constexpr int kStageTokens = 64;  // tokens per pipeline stage: 16 per warp
 // Two 32 KB stages (D <= 128) and 160 registers let three CTAs share an SM; measured faster than three
 // stages with two CTAs when the grid fills the GPU.  A grid of at most one CTA per SM (a batch of one or two
-// requests) is bound by latency instead: each stage then costs one trip to memory, so that case runs a deep
-// ring that has up to a whole 512-token part in flight.
+// requests) is bound by latency instead: each stage then costs one trip to memory and one dependent chain of
+// math, so that case runs two teams of four warps, each with a ring of its own over half of the part's stages,
+// which together have up to a whole 512-token part in flight.
 #ifndef MOBA_DEC_STAGES
 #define MOBA_DEC_STAGES 2
 #endif
@@ -461,7 +462,7 @@ constexpr int kStageTokens = 64;  // tokens per pipeline stage: 16 per warp
 #define MOBA_DEC_MINBLOCKS 3
 #endif
 constexpr int kStages = MOBA_DEC_STAGES;  // cp.async stages in flight per CTA, throughput variant
-constexpr int deep_stages(int dp) { return dp <= 64 ? 8 : dp <= 128 ? 4 : 3; }  // latency variant
+constexpr int deep_stages(int dp) { return dp <= 64 ? 4 : dp <= 128 ? 2 : 3; }  // latency variant, per team (two teams up to D = 128)
 
 // Shared-memory K/V stage: row = one token, DP bf16 values; the 16-byte units of a row are
 // XOR-permuted by (token & 7) so that ldmatrix reads of 8 consecutive tokens are conflict-free.
@@ -488,10 +489,10 @@ __device__ __forceinline__ long long attend_row_base(const CacheView& cv, int si
 // units of a row, so every 32-byte sector fetched from L2 is used in full; rows that do not exist
 // and head-dim padding are zero-filled.
 template <int DP>
-__device__ __forceinline__ void attend_load_stage(const CacheView& cv, uint8_t* stage, const long long* row_base) {
+__device__ __forceinline__ void attend_load_stage(const CacheView& cv, uint8_t* stage, const long long* row_base, int ltid) {
   constexpr int UPR = DP / 8;
   constexpr int ROWS_PER_PASS = 128 / UPR;
-  const int u = threadIdx.x % UPR, r0 = threadIdx.x / UPR;
+  const int u = ltid % UPR, r0 = ltid / UPR;  // ltid: thread within its team of 128
   const uint32_t kdst = smem_u32(stage);
   const uint32_t vdst = kdst + kStageTokens * DP * 2;
   const bool uok = u * 8 < cv.D;
@@ -576,15 +577,18 @@ __device__ __noinline__ float4 merge_tail_acc(const MergeTail& t, long long hbas
 // GQA group are the 16 rows of m16n8k16 tensor-core tiles (unused rows are zero), so a K/V token read
 // from HBM serves every head at no extra cost and the kernel stays memory bound for any group size.
 // Each warp takes 16 tokens of every 64-token stage and keeps its own running (max, sum, O); the
-// four warps are combined through shared memory at the end.
-template <int DP, int NS>
-__global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
+// warps are combined through shared memory at the end.  A team is four warps with a copy ring and a barrier of its
+// own; the latency variant runs two teams, each on half of the part's stages, because with one warp per scheduler
+// nothing hides the dependent chain of a stage (ldmatrix, mma, shuffles, exp2, mma).
+template <int DP, int NS, int TEAMS>
+__global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
+  constexpr int NT = 128 * TEAMS, NW = 4 * TEAMS;  // threads and warps of the CTA
   constexpr int KSTEPS = DP / 16;
   constexpr int DT = DP / 8;  // 8-column output tiles
   constexpr int STAGE_BYTES = 2 * kStageTokens * DP * 2;
-  extern __shared__ __align__(128) uint8_t s_pipe[];  // NS stages; reused for the cross-warp reduction
+  extern __shared__ __align__(128) uint8_t s_pipe[];  // NS stages per team; reused for the cross-warp reduction
   __shared__ int s_last, s_slot[kHeadBlock];
-  __shared__ long long s_rowbase[NS][kStageTokens];
+  __shared__ long long s_rowbase_all[TEAMS][NS][kStageTokens];
   DEC_TRACE_INIT;
   DEC_TRACE(0);
   dependents_may_start();   // e.g. the output projection, whose weight loads need nothing from here
@@ -594,6 +598,13 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   const int rowg = blockIdx.z, row = rowg / cv.Hkv, g = rowg - row * cv.Hkv;
   const int k = blockIdx.x, part = blockIdx.y;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int team = warp >> 2, wt = warp & 3, ltid = tid & 127;  // team, warp in the team, thread in the team
+  long long (*s_rowbase)[kStageTokens] = s_rowbase_all[team];
+  uint8_t* const t_pipe = s_pipe + (size_t)team * NS * STAGE_BYTES;
+  auto team_sync = [&]() {
+    if (TEAMS == 1) __syncthreads();
+    else asm volatile("bar.sync %0, 128;" ::"r"(team + 1) : "memory");
+  };
   const int qr = lane >> 2, qc = lane & 3;  // fragment row within 8 and column pair
   const int sid = a.ids[row], pos = a.positions[row];
   const int visible = min(pos + 1, cv.lengths[sid]);  // tokens [0, visible) exist and are not in the future
@@ -609,7 +620,10 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   if (t_begin >= t_end) return;
   const int cur_parts = (visible - cur * cv.C + a.part_tokens - 1) / a.part_tokens;
   const int expected = (ucount - 1) * a.parts + cur_parts;
-  const int ntiles = (t_end - t_begin + kStageTokens - 1) / kStageTokens;
+  const int all_tiles = (t_end - t_begin + kStageTokens - 1) / kStageTokens;
+  const int first_tile = team * ((all_tiles + TEAMS - 1) / TEAMS);           // this team's stages: [first_tile, first_tile + ntiles)
+  const int ntiles = max(0, min(all_tiles - first_tile, (all_tiles + TEAMS - 1) / TEAMS));
+  const int tt_begin = t_begin + first_tile * kStageTokens;                  // first token of the team
   DEC_TRACE(1);
 
   for (int hb = 0; hb < G; hb += kHeadBlock) {
@@ -618,9 +632,9 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
     // row bases of the tokens of the stages about to be copied (ring of NS slots).  A thread looks up one token
     // of every stage; from stage to stage the token advances by kStageTokens, so page and offset are stepped
     // instead of divided anew.
-    int look_t = t_begin + tid, look_pg = 0, look_r = 0, step_pg = 0, step_r = 0;
+    int look_t = tt_begin + ltid, look_pg = 0, look_r = 0, step_pg = 0, step_r = 0;
     bool look_bad = false;
-    if (tid < kStageTokens) {
+    if (ltid < kStageTokens) {
       look_pg = look_t / cv.page; look_r = look_t - look_pg * cv.page;
       step_pg = kStageTokens / cv.page; step_r = kStageTokens - step_pg * cv.page;
     }
@@ -631,7 +645,7 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
       return base;
     };
     long long first_base[NS];  // issued before the query loads below, stored after them
-    if (tid < kStageTokens) {
+    if (ltid < kStageTokens) {
 #pragma unroll
       for (int s = 0; s < NS; ++s) first_base[s] = lookup();
     }
@@ -656,34 +670,34 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows qr and qr+8; l: this thread's columns only
 
     __syncthreads();  // the previous head block is done with shared memory
-    if (tid < kStageTokens) {
+    if (ltid < kStageTokens) {
 #pragma unroll
-      for (int s = 0; s < NS; ++s) s_rowbase[s][tid] = first_base[s];
+      for (int s = 0; s < NS; ++s) s_rowbase[s][ltid] = first_base[s];
     }
-    __syncthreads();
+    team_sync();
     DEC_TRACE(2);
 #pragma unroll
     for (int s = 0; s < NS - 1; ++s) {
-      if (s < ntiles) attend_load_stage<DP>(cv, s_pipe + s * STAGE_BYTES, s_rowbase[s]);
+      if (s < ntiles) attend_load_stage<DP>(cv, t_pipe + s * STAGE_BYTES, s_rowbase[s], ltid);
       cp_async_commit();
     }
     for (int i = 0; i < ntiles; ++i) {
       cp_async_wait<NS - 2>();
-      __syncthreads();  // tile i has landed; every warp finished tile i-1, whose buffer is refilled next
+      team_sync();  // tile i has landed; every warp of the team finished tile i-1, whose buffer is refilled next
       if (i == 0) DEC_TRACE(3);
       const int nx = i + NS - 1;
-      if (nx < ntiles) attend_load_stage<DP>(cv, s_pipe + (nx % NS) * STAGE_BYTES, s_rowbase[nx % NS]);
+      if (nx < ntiles) attend_load_stage<DP>(cv, t_pipe + (nx % NS) * STAGE_BYTES, s_rowbase[nx % NS], ltid);
       cp_async_commit();
       // look up the rows of tile nx+1 now, publish them after this tile's math (slot i % NS is free)
       long long next_base = -1;
-      if (tid < kStageTokens && nx + 1 < ntiles) next_base = lookup();
-      const int tok0 = warp * 16;                                 // this warp's tokens inside the stage
-      const int nvalid = t_end - (t_begin + i * kStageTokens + tok0);  // tokens of the warp tile that exist
+      if (ltid < kStageTokens && nx + 1 < ntiles) next_base = lookup();
+      const int tok0 = wt * 16;                                   // this warp's tokens inside the stage
+      const int nvalid = t_end - (tt_begin + i * kStageTokens + tok0);  // tokens of the warp tile that exist
       if (nvalid <= 0) {                                          // warp-uniform
-        if (tid < kStageTokens) s_rowbase[i % NS][tid] = next_base;
+        if (ltid < kStageTokens) s_rowbase[i % NS][ltid] = next_base;
         continue;
       }
-      const uint32_t kbase = smem_u32(s_pipe + (i % NS) * STAGE_BYTES);
+      const uint32_t kbase = smem_u32(t_pipe + (i % NS) * STAGE_BYTES);
       const uint32_t vbase = kbase + kStageTokens * DP * 2;
       // ---- S = Q K^T for 16 tokens: two 8-token column tiles
       float sc[2][4];
@@ -738,17 +752,17 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
           mma_bf16_16816(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
         }
       }
-      if (tid < kStageTokens) s_rowbase[i % NS][tid] = next_base;
+      if (ltid < kStageTokens) s_rowbase[i % NS][ltid] = next_base;
     }
     if (look_bad) atomicOr(a.status, kErrBadIndex);
-    // ---- combine the four warps, then write one partial per active head
+    // ---- combine the warps, then write one partial per active head
     DEC_TRACE(4);
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
     __syncthreads();
-    float* s_o = reinterpret_cast<float*>(s_pipe);                   // [4 warps][16 rows][DP]
-    float* s_ml = s_o + 4 * 16 * DP;                                  // [4 warps][16 rows][2]
+    float* s_o = reinterpret_cast<float*>(s_pipe);                   // [NW warps][16 rows][DP]
+    float* s_ml = s_o + NW * 16 * DP;                                 // [NW warps][16 rows][2]
 #pragma unroll
     for (int dt = 0; dt < DT; ++dt) {
       float* w0 = s_o + ((size_t)warp * 16 + qr) * DP + dt * 8 + qc * 2;
@@ -778,18 +792,18 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
     __syncthreads();
     // every thread takes two dimensions of one head
     const int d2n = D >> 1;
-    for (int item = tid; item < nh * d2n; item += 128) {
+    for (int item = tid; item < nh * d2n; item += NT) {
       const int hh = item / d2n, d = (item - hh * d2n) * 2;
       const int slot = s_slot[hh];
       if (slot < 0) continue;
       const int h = g * G + hb + hh;
       const long long pidx = (((long long)row * a.Hq + h) * a.ns + slot) * a.parts + part;
-      float mw[4], big = -INFINITY;
+      float mw[NW], big = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) { mw[w] = s_ml[((size_t)w * 16 + hh) * 2]; big = fmaxf(big, mw[w]); }
+      for (int w = 0; w < NW; ++w) { mw[w] = s_ml[((size_t)w * 16 + hh) * 2]; big = fmaxf(big, mw[w]); }
       float lsum = 0.f, v0 = 0.f, v1 = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < NW; ++w) {
         const float wgt = mw[w] == -INFINITY ? 0.f : dec_exp2(mw[w] - big);  // a warp that saw no token adds nothing
         lsum += s_ml[((size_t)w * 16 + hh) * 2 + 1] * wgt;
         const float2 x = *reinterpret_cast<const float2*>(s_o + ((size_t)w * 16 + hh) * DP + d);
@@ -820,7 +834,7 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   // fit in shared memory is read from global memory in the same fixed order, so the result is bit-repeatable.
   const int nslots = dense ? cur + 1 : a.ns;
   const int total = nslots * a.parts;
-  const int pipe_floats = NS * STAGE_BYTES / 4;
+  const int pipe_floats = TEAMS * NS * STAGE_BYTES / 4;
   const int cap = min(min(1024, (total + 3) & ~3), (pipe_floats / (2 * G)) & ~3);  // maxima / weights kept per head
   const int tc = min(total, cap);
   const int pb = min(tc, (pipe_floats - 2 * G * cap) / (G * D));                   // partial sums kept per head
@@ -833,14 +847,14 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   for (int hl = 0; hl < G; ++hl) {
     const float* src = a.pacc + (gbase + (long long)hl * a.ns) * a.parts * D;
     const uint32_t dst = smem_u32(s_acc + (size_t)hl * pb * D);
-    for (int u = tid; u < pb * d4n; u += 128) cp_async16(dst + u * 16, src + u * 4, true);
+    for (int u = tid; u < pb * d4n; u += NT) cp_async16(dst + u * 16, src + u * 4, true);
   }
   cp_async_commit();
   // This code runs once per launch in one CTA per group, from a cold instruction cache: it is kept short (little
   // unrolling; the rarely needed paths sit in functions of their own) because fetching it costs more than running it.
   const MergeTail tail{a.selected, a.pm, a.pl, a.pacc, a.parts, cur, cur_parts, D};
 #pragma unroll 2
-  for (int idx = tid; idx < G * tc; idx += 128) {
+  for (int idx = tid; idx < G * tc; idx += NT) {
     const int hl = idx / tc, j = idx - hl * tc;
     const long long hbase = gbase + (long long)hl * a.ns;
     const float m = __ldcg(a.pm + hbase * a.parts + j), l = __ldcg(a.pl + hbase * a.parts + j);
@@ -853,7 +867,7 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   // half a warp per head
   const int sub = lane & 15;
 #pragma unroll 1
-  for (int hl = warp * 2 + (lane >> 4); hl < ((G + 7) & ~7); hl += 8) {
+  for (int hl = warp * 2 + (lane >> 4); hl < ((G + 2 * NW - 1) / (2 * NW)) * (2 * NW); hl += 2 * NW) {
     const bool live = hl < G;  // the shuffles below need every lane
     const int hc = live ? hl : 0;
     const int h = g * G + hc;
@@ -888,7 +902,7 @@ __global__ void __launch_bounds__(128, (NS == NS && DP <= 128 ? MOBA_DEC_MINBLOC
   __syncthreads();
   DEC_TRACE(7);
 #pragma unroll 1
-  for (int item = tid; item < G * d4n; item += 128) {
+  for (int item = tid; item < G * d4n; item += NT) {
     const int hl = item / d4n, d = (item - hl * d4n) * 4;
     const int h = g * G + hl;
     const long long hbase = gbase + (long long)hl * a.ns;
@@ -1072,24 +1086,25 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
   a.status = status;
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)c->dim));
   const int dp = c->dim <= 32 ? 32 : c->dim <= 64 ? 64 : c->dim <= 128 ? 128 : 256;
-  const size_t red_bytes = (size_t)4 * 16 * (dp + 2) * 4;
   const dim3 grid(a.umax, a.parts, rows * c->hkv);
   const bool deep = (long long)grid.x * grid.y * grid.z <= decode_sm_count();
-  const int stages = deep ? deep_stages(dp) : kStages;
-  const size_t pipe_bytes = (size_t)stages * 2 * kStageTokens * dp * 2;
+  const int teams = deep && dp <= 128 ? 2 : 1;
+  const int stages = deep ? deep_stages(dp) : kStages;  // per team
+  const size_t red_bytes = (size_t)4 * teams * 16 * (dp + 2) * 4;
+  const size_t pipe_bytes = (size_t)teams * stages * 2 * kStageTokens * dp * 2;
   const size_t smem = red_bytes > pipe_bytes ? red_bytes : pipe_bytes;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
   prof_begin(kProfDecodeAttend, st);
-#define MOBA_LAUNCH_ATTEND_NS(L, NS)                                                                               \
-  do {                                                                                                             \
-    e = cudaFuncSetAttribute(decode_attend_kernel<L, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess) e = launch_dependent(8u, decode_attend_kernel<L, NS>, grid, dim3(128), smem, st, a);         \
+#define MOBA_LAUNCH_ATTEND_NS(L, NS, T)                                                                              \
+  do {                                                                                                               \
+    e = cudaFuncSetAttribute(decode_attend_kernel<L, NS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) e = launch_dependent(8u, decode_attend_kernel<L, NS, T>, grid, dim3(128 * T), smem, st, a); \
   } while (0)
 #define MOBA_LAUNCH_ATTEND(L)                                                                                      \
   do {                                                                                                             \
-    if (deep) MOBA_LAUNCH_ATTEND_NS(L, deep_stages(L));                                                            \
-    else MOBA_LAUNCH_ATTEND_NS(L, kStages);                                                                        \
+    if (deep) MOBA_LAUNCH_ATTEND_NS(L, deep_stages(L), (L <= 128 ? 2 : 1));                                        \
+    else MOBA_LAUNCH_ATTEND_NS(L, kStages, 1);                                                                     \
   } while (0)
   if (dp == 32) MOBA_LAUNCH_ATTEND(32);
   else if (dp == 64) MOBA_LAUNCH_ATTEND(64);
