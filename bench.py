@@ -355,6 +355,49 @@ def bind_to_gpu_numa(local):
     return None
 
 
+def probe_host_nodes(dev):
+    """When sysfs does not say which NUMA node the GPU hangs off: pin a 64 MB buffer from the CPUs of each node this
+    process may run on, time host->device copies from it, and stay on the fastest node while the real host buffers
+    are allocated (pinned pages land on the node of the thread that allocates them).  Returns (node, GB/s per node)
+    or (None, {}) when there is nothing to choose from."""
+    import glob
+    import torch
+    try:
+        before = os.sched_getaffinity(0)
+        nodes = {}
+        for path in glob.glob("/sys/devices/system/node/node[0-9]*"):
+            cpus = set()
+            for part in open(path + "/cpulist").read().strip().split(","):
+                if part:
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            if cpus & before:
+                nodes[int(path.rsplit("node", 1)[1])] = cpus & before
+        if len(nodes) < 2:
+            return None, {}
+        n = 64 << 20
+        dst = torch.empty(n, dtype=torch.uint8, device=dev)
+        rates = {}
+        for node, cpus in sorted(nodes.items()):
+            os.sched_setaffinity(0, cpus)
+            src = torch.empty(n, dtype=torch.uint8).pin_memory()
+            src.fill_(1)
+            dst.copy_(src, non_blocking=True)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(4):
+                dst.copy_(src, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            rates[node] = 4 * n / (e0.elapsed_time(e1) * 1e-3) / 1e9
+            del src
+        best = max(rates, key=rates.get)
+        os.sched_setaffinity(0, nodes[best])
+        return best, {k: round(v, 1) for k, v in rates.items()}
+    except Exception:
+        return None, {}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -370,7 +413,10 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _ext.lib()  # fails loudly when the CUDA library is missing
-    numa_node = bind_to_gpu_numa(local) if world > 1 else None
+    affinity = os.sched_getaffinity(0)
+    numa_node, numa_rates = bind_to_gpu_numa(local), {}
+    if numa_node is None:
+        numa_node, numa_rates = probe_host_nodes(dev)
 
     w = WORKLOAD
     T, Hq, Hkv, D = sum(w["lens"]), w["hq"], w["hkv"], w["dim"]
@@ -385,6 +431,9 @@ def run_ours(args):
            "deterministic_merge": True}
     res = {n: t.to(dev) for n, t in host.items()}
     host_out = {n: torch.empty_like(host[src]).pin_memory() for n, src in (("out", "q"), ("dq", "q"), ("dk", "k"), ("dv", "k"))}
+    for t in host_out.values():
+        t.zero_()                       # touch the pages from this node before the affinity is widened again
+    os.sched_setaffinity(0, affinity)   # the CPU legs use every core
 
     def step(q, k, v, do):
         q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
@@ -507,7 +556,8 @@ def run_ours(args):
                     clocks=clocks,
                     e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                              ms_per_step=None if ms_e2e is None else ms_e2e / e2e_steps, steps=e2e_steps,
-                             mode="host copies on their own streams, double-buffered across steps", numa_node=numa_node),
+                             mode="host copies on their own streams, double-buffered across steps", numa_node=numa_node,
+                             numa_h2d_gbs=numa_rates),
                     gpu_launches=13 * args.steps,  # route 5, pack 2, forward 2, backward 4 (memsets not counted)
                     roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel" if D <= 64 else "attn_bwd_ws128_kernel", achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
