@@ -151,6 +151,12 @@ int moba_decode_means(const moba_cache_desc* c, const int32_t* seqs, const int32
 int moba_prefill_to_cache(const moba_cache_desc* c, const void* k, const void* v, const int32_t* seqs, const int32_t* start,
                           const int32_t* cu_seqlens, int num_seqs, int max_chunks_touched, unsigned* status, void* stream);
 
+/* Copies a step's q, k, v into the fixed buffers a captured step reads (prepared_decode.py:150-176 of the reference
+ * does three tensor copies), as one launch.  Sizes in bytes, multiples of 16, pointers 16-byte aligned
+ * (MOBA_ERR_UNSUPPORTED otherwise: copy some other way); a size of 0 skips that tensor. */
+int moba_decode_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, void* k_dst, const void* k_src, size_t k_bytes,
+                             void* v_dst, const void* v_src, size_t v_bytes, void* stream);
+
 /* First launch of an appending decode step: moba_decode_metadata (append != 0), moba_decode_append of one token per
  * row and the predicated moba_decode_means in one launch, one CTA per row (ops/prepared_decode.py:7-41 are three
  * kernels).  With qkv == NULL, k and v [rows, hkv, dim] are inputs.  With qkv [rows, (hq + 2 hkv) * dim] (the fused

@@ -224,6 +224,17 @@ __global__ void __launch_bounds__(256) prefill_to_cache_kernel(CacheView cv, con
   chunk_mean_finish(cv, sid, chunk, g, acc, s_part);
 }
 
+// --------------------------------------------------------------------------- staging of a step's inputs
+// Copies the caller's q, k, v of a step into the fixed buffers a captured step reads, as one launch of 16-byte units.
+__global__ void __launch_bounds__(256) stage_inputs_kernel(uint4* dq, const uint4* __restrict__ sq, long long nq, uint4* dk,
+                                                           const uint4* __restrict__ sk, long long nk, uint4* dv,
+                                                           const uint4* __restrict__ sv, long long nv) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i < nq) dq[i] = sq[i];
+  else if (i < nq + nk) dk[i - nq] = sk[i - nq];
+  else if (i < nq + nk + nv) dv[i - nq - nk] = sv[i - nq - nk];
+}
+
 // --------------------------------------------------------------------------- first launch of an appending decode step
 // Metadata, append and the predicated chunk mean of one request per CTA, and, when the caller hands over the fused
 // q/k/v projection instead of separate k and v, the rotary embedding and the split as well: what were four
@@ -991,6 +1002,22 @@ extern "C" int moba_prefill_to_cache(const moba_cache_desc* c, const void* k, co
   prefill_to_cache_kernel<<<dim3(max_chunks_touched, c->hkv, num_seqs), 256, (size_t)rpi * c->dim * 4, (cudaStream_t)stream>>>(
       make_cache_view(*c), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), seqs, start, cu_seqlens,
       status);
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" int moba_decode_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, void* k_dst, const void* k_src, size_t k_bytes,
+                                        void* v_dst, const void* v_src, size_t v_bytes, void* stream) {
+  if ((q_bytes && (!q_dst || !q_src)) || (k_bytes && (!k_dst || !k_src)) || (v_bytes && (!v_dst || !v_src)))
+    return MOBA_ERR_INVALID;
+  if ((q_bytes | k_bytes | v_bytes) & 15) return MOBA_ERR_UNSUPPORTED;
+  if (((uintptr_t)q_dst | (uintptr_t)q_src | (uintptr_t)k_dst | (uintptr_t)k_src | (uintptr_t)v_dst | (uintptr_t)v_src) & 15)
+    return MOBA_ERR_UNSUPPORTED;
+  const long long nq = (long long)(q_bytes >> 4), nk = (long long)(k_bytes >> 4), nv = (long long)(v_bytes >> 4);
+  const long long total = nq + nk + nv;
+  if (total == 0) return MOBA_OK;
+  stage_inputs_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<uint4*>(q_dst), static_cast<const uint4*>(q_src), nq, static_cast<uint4*>(k_dst), static_cast<const uint4*>(k_src), nk,
+      static_cast<uint4*>(v_dst), static_cast<const uint4*>(v_src), nv);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 

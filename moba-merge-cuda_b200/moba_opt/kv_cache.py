@@ -78,6 +78,7 @@ def _bind(lib):
     lib.moba_decode_append.argtypes = [P, vp, vp, vp, vp, i, vp, vp]
     lib.moba_decode_means.argtypes = [P, vp, vp, i, i, vp, vp]
     lib.moba_decode_step_begin.argtypes = [P, vp, vp, vp, i, i, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.moba_decode_stage_inputs.argtypes = [vp, vp, ctypes.c_size_t, vp, vp, ctypes.c_size_t, vp, vp, ctypes.c_size_t, vp]
     lib.moba_prefill_to_cache.argtypes = [P, vp, vp, vp, vp, vp, i, i, vp, vp]
     lib.moba_decode_union_capacity.argtypes = [i, i, i, i]
     lib.moba_decode_route.argtypes = [P, vp, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp]

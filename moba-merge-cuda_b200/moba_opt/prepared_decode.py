@@ -111,6 +111,23 @@ class PreparedDecode:
             raise ValueError(f"{name} contains NaN/Inf")
 
     # ------------------------------------------------------------------ device work
+    def _stage(self, pairs):
+        """Caller's tensors into the fixed buffers: one launch for all of them when they are contiguous and 16-byte
+        aligned, tensor copies otherwise."""
+        todo = [(t, target) for t, target in pairs if t is not target]
+        if not todo:
+            return
+        if all(t.is_contiguous() and t.dtype == target.dtype and t.data_ptr() % 16 == 0 and target.data_ptr() % 16 == 0
+               and (t.numel() * t.element_size()) % 16 == 0 for t, target in todo):
+            args = []
+            for t, target in todo + [(None, None)] * (3 - len(todo)):
+                args += [None, None, 0] if t is None else [target.data_ptr(), t.data_ptr(), t.numel() * t.element_size()]
+            st = ctypes.c_void_p(torch.cuda.current_stream(self.cache.device).cuda_stream)
+            if self._lib.moba_decode_stage_inputs(*args, st) == 0:
+                return
+        for t, target in todo:
+            target.copy_(t)
+
     def _upload(self, plan):
         """Only when some sequence opens a page: an asynchronous 2 x b int32 copy from one of a few pinned staging
         buffers; the host waits only if the copy that last used the buffer (four uploads ago) is still pending, so a
@@ -202,9 +219,7 @@ class PreparedDecode:
             if use_graph and "step" not in self._graphs:
                 raise ValueError("capture('step') first")
             plan = self._state.plan()
-            for tensor, target in ((q, self.q), (k, self.k), (v, self.v)):
-                if tensor is not target:
-                    target.copy_(tensor)
+            self._stage(((q, self.q), (k, self.k), (v, self.v)))
             self._upload(plan)
             self._run("step", use_graph)
             self._state.commit(plan)
