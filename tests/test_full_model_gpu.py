@@ -143,7 +143,8 @@ def test_fused_glue_step_agrees_with_the_module_by_module_step(model):
         assert _rel_l2(b, a) <= 5e-3
 
 
-@pytest.mark.parametrize("k,n", [(896, 1152), (896, 896), (4864, 896), (128, 40), (8, 1), (1032, 77), (16384, 9)])
+@pytest.mark.parametrize("k,n", [(896, 1152), (896, 896), (4864, 896), (128, 40), (8, 1), (1032, 77), (16384, 9),
+                                 (64, 40000), (4864, 6000)])   # the last two: more outputs than fit in four resident waves
 @pytest.mark.parametrize("bias", [False, True])
 @pytest.mark.parametrize("norm", [False, True])
 def test_decode_linear_matches_torch(k, n, bias, norm):
