@@ -72,6 +72,27 @@ def _check_qkv(q, k, v):
         _fail("q, k and v must share one device and one dtype")
 
 
+_CU_MEMO = {}   # id(tensor) -> (weak reference, version counter, offsets)
+
+
+def _known_offsets(cu_seqlens):
+    """cu_seqlens as a Python list.  Reading it is the call's only device-to-host copy, and it waits for everything
+    already enqueued on the stream; a caller that passes the same, unmodified tensor again (every layer of a model,
+    every step of a loop) gets the list remembered from the first call instead, so the host keeps running ahead of the
+    device.  The tensor's version counter, which every in-place write through torch increments, guards the memo."""
+    import weakref
+    entry = _CU_MEMO.get(id(cu_seqlens))
+    if entry is not None and entry[0]() is cu_seqlens and entry[1] == cu_seqlens._version:
+        return entry[2]
+    offsets = cu_seqlens.tolist()
+    for key in [k for k, e in _CU_MEMO.items() if e[0]() is None]:
+        del _CU_MEMO[key]
+    if len(_CU_MEMO) >= 32:
+        _CU_MEMO.pop(next(iter(_CU_MEMO)))
+    _CU_MEMO[id(cu_seqlens)] = (weakref.ref(cu_seqlens), cu_seqlens._version, offsets)
+    return offsets
+
+
 def _check_cu_seqlens(cu_seqlens, q):
     if not isinstance(cu_seqlens, torch.Tensor):
         _fail("cu_seqlens must be a torch.Tensor")
@@ -79,7 +100,7 @@ def _check_cu_seqlens(cu_seqlens, q):
         _fail("cu_seqlens must be an int32 tensor on q's CUDA device")
     if cu_seqlens.dim() != 1 or cu_seqlens.numel() < 2 or not cu_seqlens.is_contiguous():
         _fail("cu_seqlens must be a contiguous 1-D tensor of B+1 >= 2 offsets")
-    offsets = cu_seqlens.tolist()  # the call's only device-to-host read
+    offsets = _known_offsets(cu_seqlens)
     increasing = all(b > a for a, b in zip(offsets, offsets[1:]))
     if offsets[0] != 0 or offsets[-1] != q.shape[0] or not increasing:
         _fail(f"cu_seqlens must run from 0 to T in strictly increasing steps, got {offsets}")
