@@ -240,3 +240,24 @@ def test_full_size_config2_properties():
     v3[cu[1]:] = (torch.randn(total - cu[1], hkv, dim, generator=rng) * dim ** -0.5).bfloat16()
     out3, _, _, _ = _run(q, k3, v3, cu, chunk, topk)
     assert torch.equal(out3[:cu[1]], out[:cu[1]])
+
+
+def test_remembered_offsets_follow_in_place_changes_of_cu_seqlens():
+    """The offsets of a cu_seqlens tensor are read from the device once and reused while the tensor's version counter
+    stands; an in-place change must be seen by the next call (here: it makes the offsets invalid, then valid again
+    with a different split, whose result must equal a fresh tensor's)."""
+    import moba_opt
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(96, h, 16, generator=g).bfloat16().cuda() for h in (4, 2, 2))
+    cfg = {"chunk_size": 16, "topk": 2}
+    cu = torch.tensor([0, 48, 96], dtype=torch.int32, device="cuda")
+    first = moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, 48, cfg)
+    assert torch.equal(first, moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, 48, cfg))
+    cu[1] = 200
+    with pytest.raises(ValueError):
+        moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, 48, cfg)
+    cu[1] = 32
+    fresh = torch.tensor([0, 32, 96], dtype=torch.int32, device="cuda")
+    assert torch.equal(moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, 64, cfg),
+                       moba_opt.run_impl("opt_gqa_cuda", q, k, v, fresh, 64, cfg))
+    assert not torch.equal(first, moba_opt.run_impl("opt_gqa_cuda", q, k, v, fresh, 64, cfg))
