@@ -152,7 +152,7 @@ class FullQwen2Session:
             return self._prefill_hidden_fused(h, cos, sin, cu, t)
         for i, layer in enumerate(body.layers):
             q, k, v = self._project(i, layer.input_layernorm(h), cos, sin)
-            self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t])
+            self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t], check_finite=False)
             dense = self.layer_dense[i] or self.prefill_mode == "dense"
             out = opt_gqa_cuda(q, k, v, cu, t, self.dense_config if dense else self.route_config)
             h = h + layer.self_attn.o_proj(out.reshape(t, -1))
@@ -191,7 +191,7 @@ class FullQwen2Session:
             qkv = F.linear(y, *self.packed[i])
             check(lib.moba_rope_split(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), t, self.hq, self.hk, self.dim,
                                       q.data_ptr(), k.data_ptr(), v.data_ptr(), st))
-            self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t])
+            self.caches[i].append_prefill(k, v, sequence_ids=[0], cu_seqlens=[0, t], check_finite=False)
             dense = self.layer_dense[i] or self.prefill_mode == "dense"
             out = opt_gqa_cuda(q, k, v, cu, t, self.dense_config if dense else self.route_config)
             att = layer.self_attn.o_proj(out.reshape(t, -1))

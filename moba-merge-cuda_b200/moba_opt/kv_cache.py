@@ -164,7 +164,7 @@ class PagedKVCache:
         if torch.cuda.current_stream(self.device).cuda_stream != self._stream:
             raise ValueError("cross-stream cache access is unsupported")
 
-    def _tensor(self, tensor, name, *, expected_heads=None, expected_tokens=None):
+    def _tensor(self, tensor, name, *, expected_heads=None, expected_tokens=None, check_finite=True):
         if not isinstance(tensor, torch.Tensor) or tensor.dim() != 3:
             raise ValueError(f"{name} must be [N,H,D]")
         if tensor.device != self.device or tensor.dtype != self.dtype:
@@ -180,7 +180,7 @@ class PagedKVCache:
             raise ValueError(f"{name} KV head count differs from cache")
         if expected_tokens is not None and n != expected_tokens:
             raise ValueError(f"{name} token count differs")
-        if not bool(torch.isfinite(tensor).all()):
+        if check_finite and not bool(torch.isfinite(tensor).all()):   # reads a flag back: waits for the stream
             raise ValueError(f"{name} contains NaN/Inf")
 
     def _reject_storage_alias(self, *tensors):
@@ -234,14 +234,16 @@ class PagedKVCache:
             return self._append_validated(k, v, ids, counts)[0]
 
     @torch.no_grad()
-    def append_prefill(self, k, v, *, sequence_ids, cu_seqlens=None):
+    def append_prefill(self, k, v, *, sequence_ids, cu_seqlens=None, check_finite=True):
         """`append` for whole prompts (the hand-off from a prefill pass): same contract and resulting cache state, but
         one launch writes the pages and the means of the completed chunks in a single pass over K, and the host builds
-        no per-token index arrays.  Returns the new lengths of the given sequences."""
+        no per-token index arrays.  `check_finite=False` leaves out the NaN/Inf check of k and v, which reads a flag
+        back from the device and so makes the host wait for everything enqueued before (as `prepare_decode` offers
+        for decode steps).  Returns the new lengths of the given sequences."""
         with self._lock, torch.cuda.device(self.device):
             self._check_stream()
-            self._tensor(k, "k", expected_heads=self.num_kv_heads)
-            self._tensor(v, "v", expected_heads=self.num_kv_heads, expected_tokens=k.shape[0])
+            self._tensor(k, "k", expected_heads=self.num_kv_heads, check_finite=check_finite)
+            self._tensor(v, "v", expected_heads=self.num_kv_heads, expected_tokens=k.shape[0], check_finite=check_finite)
             self._reject_storage_alias(k, v)
             ids, counts = self._append_counts(k.shape[0], sequence_ids, cu_seqlens)
             starts = [self._layout.lengths[s] for s in ids]
