@@ -621,10 +621,13 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
   const int visible = min(pos + 1, cv.lengths[sid]);  // tokens [0, visible) exist and are not in the future
   const int cur = pos / cv.C;
   const bool dense = a.selected == nullptr;
+  // the union entry of this CTA is read together with the count (k < umax always), not after the test on the count
+  const int listed = dense ? 0 : a.u_chunk[(long long)rowg * a.umax + k];
+  const unsigned listed_mask = dense ? 0u : a.u_mask[(long long)rowg * a.umax + k];
   const int ucount = dense ? cur + 1 : a.u_count[rowg];
   if (k >= ucount) return;
-  const int chunk = dense ? k : a.u_chunk[(long long)rowg * a.umax + k];
-  const unsigned mask = dense ? (G >= 32 ? 0xFFFFFFFFu : ((1u << G) - 1u)) : a.u_mask[(long long)rowg * a.umax + k];
+  const int chunk = dense ? k : listed;
+  const unsigned mask = dense ? (G >= 32 ? 0xFFFFFFFFu : ((1u << G) - 1u)) : listed_mask;
   const int limit = min((chunk + 1) * cv.C, visible);
   const int t_begin = chunk * cv.C + part * a.part_tokens;
   const int t_end = min(t_begin + a.part_tokens, limit);
