@@ -115,3 +115,19 @@ def test_incremental_failures_do_not_mutate():
     old.commit(old.plan_append([0], [1]))
     with pytest.raises(ValueError, match="max_seq_len"):
         IncrementalLayout(old, [0]).plan()
+
+
+@pytest.mark.parametrize("page", [3, 4, 7])
+def test_plan_without_token_lists_is_the_same_plan(page):
+    """A whole-prompt append (append_prefill) plans without the per-token (sequence, position) lists; everything else
+    of the plan - tables, lengths, pool, completed chunks - is what the full plan gives."""
+    a = PageAllocator(3, 40, page, 40, 8)
+    a.commit(a.plan_append([2], [5]))
+    full = a.plan_append([0, 2, 1], [13, 9, 1])
+    light = a.plan_append([0, 2, 1], [13, 9, 1], tokens=False)
+    assert light.token_sequences == () and light.token_positions == ()
+    assert len(full.token_sequences) == 23
+    for field in ("version", "tables", "lengths", "free_pages", "completed_chunks"):
+        assert getattr(full, field) == getattr(light, field)
+    a.commit(light)
+    assert a.lengths == (13, 1, 14)
