@@ -77,6 +77,108 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __re
 }
 
 
+// ---- the same three operations over many rows (a prefill), eight elements per thread -----------------------------
+__device__ __forceinline__ void unpack8(const uint4& r, float (&f)[8]) {
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&p);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One warp per row, the row kept in registers between the sum of squares and the scaling (hidden <= 8 * 32 * 8).
+__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(const __nv_bfloat16* __restrict__ h_in, const __nv_bfloat16* __restrict__ delta,
+                                                               const __nv_bfloat16* __restrict__ weight, float eps, long long rows,
+                                                               int hidden, __nv_bfloat16* __restrict__ h_out,
+                                                               __nv_bfloat16* __restrict__ y) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31, chunks = hidden >> 3;
+  float v[8][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = lane + j * 32;
+    if (c < chunks) {
+      unpack8(*reinterpret_cast<const uint4*>(h_in + row * hidden + c * 8), v[j]);
+      if (delta) {
+        float d[8];
+        unpack8(*reinterpret_cast<const uint4*>(delta + row * hidden + c * 8), d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j][i] = bf(v[j][i] + d[i]);
+      }
+      if (h_out) *reinterpret_cast<uint4*>(h_out + row * hidden + c * 8) = pack8(v[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum = fmaf(v[j][i], v[j][i], sum);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  const float r = rsqrtf(sum / (float)hidden + eps);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = lane + j * 32;
+    if (c < chunks) {
+      float w[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(weight + c * 8), w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = w[i] * bf(v[j][i] * r);
+      *reinterpret_cast<uint4*>(y + row * hidden + c * 8) = pack8(o);
+    }
+  }
+}
+
+// One thread per 8 consecutive dimensions of a head; the rotation partner is the chunk half a head away.
+__global__ void __launch_bounds__(256) rope_split_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ cosv,
+                                                              const __nv_bfloat16* __restrict__ sinv, long long rows, int hq, int hk,
+                                                              int dim, __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ k,
+                                                              __nv_bfloat16* __restrict__ v) {
+  const int cpd = dim >> 3, heads = hq + 2 * hk;
+  const long long item = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (item >= rows * heads * cpd) return;
+  const int c = (int)(item % cpd);
+  const int h = (int)((item / cpd) % heads);
+  const long long row = item / ((long long)cpd * heads);
+  const __nv_bfloat16* src = qkv + (row * heads + h) * dim;
+  const uint4 own = *reinterpret_cast<const uint4*>(src + c * 8);
+  if (h >= hq + hk) {
+    *reinterpret_cast<uint4*>(v + (row * hk + (h - hq - hk)) * dim + c * 8) = own;
+    return;
+  }
+  const bool low = c < (cpd >> 1);
+  float x[8], other[8], cs[8], sn[8], o[8];
+  unpack8(own, x);
+  unpack8(*reinterpret_cast<const uint4*>(src + (low ? c + (cpd >> 1) : c - (cpd >> 1)) * 8), other);
+  unpack8(*reinterpret_cast<const uint4*>(cosv + row * dim + c * 8), cs);
+  unpack8(*reinterpret_cast<const uint4*>(sinv + row * dim + c * 8), sn);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = bf(x[i] * cs[i]) + bf((low ? -other[i] : other[i]) * sn[i]);
+  __nv_bfloat16* dst = h < hq ? q + (row * hq + h) * dim : k + (row * hk + (h - hq)) * dim;
+  *reinterpret_cast<uint4*>(dst + c * 8) = pack8(o);
+}
+
+__global__ void __launch_bounds__(256) silu_mul_rows_kernel(const __nv_bfloat16* __restrict__ gu, long long rows, int ffn,
+                                                            __nv_bfloat16* __restrict__ out) {
+  const int cpr = ffn >> 3;
+  const long long item = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (item >= rows * cpr) return;
+  const long long row = item / cpr;
+  const int c = (int)(item - row * cpr);
+  float g[8], u[8], o[8];
+  unpack8(*reinterpret_cast<const uint4*>(gu + row * 2 * ffn + c * 8), g);
+  unpack8(*reinterpret_cast<const uint4*>(gu + row * 2 * ffn + ffn + c * 8), u);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = bf(g[i] / (1.f + expf(-g[i]))) * u[i];
+  *reinterpret_cast<uint4*>(out + row * ffn + c * 8) = pack8(o);
+}
+
 // ---- batch-1 linear layers of the decode step -----------------------------------------------------------------
 // y = W x (+ bias) for one token: W [N, K] bf16 row-major is read once from HBM, which is all the step costs, so
 // the kernel is built to have every byte of its rows in flight at once: a group of 32..256 threads owns one output
@@ -237,6 +339,13 @@ using namespace moba;
 extern "C" int moba_add_rmsnorm(const void* h_in, const void* delta, const void* weight, float eps, long long rows, int hidden,
                                 void* h_out, void* y, void* stream) {
   if (!h_in || !weight || !y || rows < 1 || hidden < 1) return MOBA_ERR_INVALID;
+  const bool aligned = !(((uintptr_t)h_in | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)h_out | (uintptr_t)y) & 15);
+  if (rows >= 64 && hidden % 8 == 0 && hidden <= 2048 && aligned) {  // many rows: a warp per row, 16-byte accesses
+    add_rmsnorm_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+        static_cast<const __nv_bfloat16*>(h_in), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight),
+        eps, rows, hidden, static_cast<__nv_bfloat16*>(h_out), static_cast<__nv_bfloat16*>(y));
+    return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+  }
   add_rmsnorm_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
       static_cast<const __nv_bfloat16*>(h_in), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight), eps,
       hidden, static_cast<__nv_bfloat16*>(h_out), static_cast<__nv_bfloat16*>(y));
@@ -246,6 +355,14 @@ extern "C" int moba_add_rmsnorm(const void* h_in, const void* delta, const void*
 extern "C" int moba_rope_split(const void* qkv, const void* cosv, const void* sinv, long long rows, int hq, int hk, int dim, void* q,
                                void* k, void* v, void* stream) {
   if (!qkv || !cosv || !sinv || !q || !k || !v || rows < 1 || hq < 1 || hk < 1 || dim < 2 || (dim & 1)) return MOBA_ERR_INVALID;
+  if (rows >= 64 && dim % 16 == 0 &&
+      !(((uintptr_t)qkv | (uintptr_t)cosv | (uintptr_t)sinv | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15)) {
+    const long long items = rows * (hq + 2 * hk) * (dim / 8);
+    rope_split_rows_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv), rows,
+        hq, hk, dim, static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v));
+    return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+  }
   rope_split_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
       static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv), hq, hk,
       dim, static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v));
@@ -254,6 +371,12 @@ extern "C" int moba_rope_split(const void* qkv, const void* cosv, const void* si
 
 extern "C" int moba_silu_mul(const void* gate_up, long long rows, int ffn, void* out, void* stream) {
   if (!gate_up || !out || rows < 1 || ffn < 1) return MOBA_ERR_INVALID;
+  if (rows >= 64 && ffn % 8 == 0 && !(((uintptr_t)gate_up | (uintptr_t)out) & 15)) {
+    const long long items = rows * (ffn / 8);
+    silu_mul_rows_kernel<<<(unsigned)((items + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        static_cast<const __nv_bfloat16*>(gate_up), rows, ffn, static_cast<__nv_bfloat16*>(out));
+    return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+  }
   silu_mul_kernel<<<dim3((unsigned)((ffn + 255) / 256), (unsigned)rows), 256, 0, (cudaStream_t)stream>>>(
       static_cast<const __nv_bfloat16*>(gate_up), ffn, static_cast<__nv_bfloat16*>(out));
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;

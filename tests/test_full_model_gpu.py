@@ -229,3 +229,45 @@ def test_step_inputs_match_the_rotary_module_and_embedding(model, position):
                                        s_.data_ptr(), st) == 0
     assert torch.equal(h, want_h)
     assert torch.equal(c, cos[0].to(torch.bfloat16)) and torch.equal(s_, sin[0].to(torch.bfloat16))
+
+
+def test_row_wise_glue_kernels_agree_with_the_single_row_forms():
+    """moba_add_rmsnorm, moba_rope_split and moba_silu_mul switch to 16-byte accesses from 64 rows on; the results must
+    be those of the small-batch kernels (rotary embedding and SiLU*up bit for bit, the norm within one bf16 step, its
+    sum of squares being taken in another order)."""
+    import ctypes
+    from moba_opt import _ext
+    lib = _ext.lib()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    g = torch.Generator().manual_seed(11)
+    rnd = lambda *shape: torch.randn(*shape, generator=g).cuda().bfloat16()
+    rows, hidden, hq, hk, dim, ffn = 100, 896, 14, 2, 64, 4864
+    ptr = lambda t: t.data_ptr()
+
+    def halves(call, *outs):
+        """Runs `call(first_row, count)` over all rows at once and as two halves of 50 (the small-batch path)."""
+        call(0, rows)
+        big = [o.clone() for o in outs]
+        for o in outs:
+            o.zero_()
+        call(0, 50)
+        call(50, 50)
+        return big, outs
+
+    h, d, w = rnd(rows, hidden), rnd(rows, hidden), rnd(hidden)
+    h_out, y = torch.empty_like(h), torch.empty_like(h)
+    big, small = halves(lambda r0, n: lib.moba_add_rmsnorm(ptr(h[r0:]), ptr(d[r0:]), ptr(w), 1e-6, n, hidden, ptr(h_out[r0:]),
+                                                          ptr(y[r0:]), st), h_out, y)
+    assert torch.equal(big[0], small[0])
+    diff = (big[1].float() - small[1].float()).abs()
+    assert float((diff / small[1].float().abs().clamp_min(1e-3)).max()) <= 2 ** -7
+
+    qkv, cos, sin = rnd(rows, (hq + 2 * hk) * dim), rnd(rows, dim), rnd(rows, dim)
+    q, k, v = torch.empty(rows, hq, dim, device="cuda", dtype=torch.bfloat16), torch.empty(rows, hk, dim, device="cuda", dtype=torch.bfloat16), torch.empty(rows, hk, dim, device="cuda", dtype=torch.bfloat16)
+    big, small = halves(lambda r0, n: lib.moba_rope_split(ptr(qkv[r0:]), ptr(cos[r0:]), ptr(sin[r0:]), n, hq, hk, dim, ptr(q[r0:]),
+                                                         ptr(k[r0:]), ptr(v[r0:]), st), q, k, v)
+    assert all(torch.equal(a, b) for a, b in zip(big, small))
+
+    gu, act = rnd(rows, 2 * ffn), torch.empty(rows, ffn, device="cuda", dtype=torch.bfloat16)
+    big, small = halves(lambda r0, n: lib.moba_silu_mul(ptr(gu[r0:]), n, ffn, ptr(act[r0:]), st), act)
+    assert torch.equal(big[0], small[0])
