@@ -302,14 +302,15 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
   }
 }
 
-constexpr int kRouteTile = 64;  // chunk means staged in shared memory per round of decode_route_kernel
+constexpr int kRouteTile = 64;      // chunk means staged in shared memory per round of decode_route_kernel
+constexpr int kRouteThreads = 256;  // eight warps: a group of up to eight heads is ranked in one round
 
 // --------------------------------------------------------------------------- routing (K12, K13, K17, K18)
-// One CTA (128 threads) per (query row, kv head).  scores[row, h, c] = q . mean[c] in FP32 for the
+// One CTA (kRouteThreads threads) per (query row, kv head).  scores[row, h, c] = q . mean[c] in FP32 for the
 // chunks completed before the query's own chunk, -inf elsewhere; top-`remote` per head in descending
 // score order with the lowest chunk winning exact ties; selected[row, h, :] = (own chunk, picks...,
 // -1 padding); and the group's union list (chunk ascending, bitmask of heads) for the attention kernel.
-__global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const __nv_bfloat16* q, const int* ids, const int* positions,
+__global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView cv, const __nv_bfloat16* q, const int* ids, const int* positions,
                                                            int Hq, int remote, int width, float* scores, int* selected, int* u_chunk,
                                                            unsigned* u_mask, int* u_count, int umax) {
   // As in decode_step_begin_kernel: no __restrict__, no read-only loads - positions, the query and the chunk means
@@ -327,11 +328,11 @@ __global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const _
   const int nlegal = min(min(cur, width), cv.max_chunks);
   const int upr = cv.D >> 3;
 
-  for (int i = tid; i <= width; i += 128) s_mask[i] = 0u;
+  for (int i = tid; i <= width; i += kRouteThreads) s_mask[i] = 0u;
   // stage the group's query rows as FP32, then one thread per (head, chunk) pair: the loads of all
   // pairs are independent, so their latencies overlap instead of adding up
   float* s_q = reinterpret_cast<float*>(s_mask + width + 1);  // [G][D]
-  for (int i = tid; i < G * cv.D; i += 128)
+  for (int i = tid; i < G * cv.D; i += kRouteThreads)
     s_q[i] = __bfloat162float(q[((long long)row * Hq + g * G) * cv.D + i]);
   __syncthreads();
   // The mean rows of kRouteTile chunks at a time are brought into shared memory by all threads with loads that do not
@@ -342,13 +343,13 @@ __global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const _
   for (int c0 = 0; c0 < nlegal; c0 += kRouteTile) {
     const int nt = min(kRouteTile, nlegal - c0);
 #pragma unroll 4
-    for (int idx = tid; idx < nt * upr; idx += 128) {
+    for (int idx = tid; idx < nt * upr; idx += kRouteThreads) {
       const int cl = idx / upr, u = idx - cl * upr;
       s_tile[cl * ustride + u] = __ldcg(
           reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c0 + cl) * cv.Hkv + g) * cv.D) + u);
     }
     __syncthreads();
-    for (int pair = tid; pair < G * nt; pair += 128) {
+    for (int pair = tid; pair < G * nt; pair += kRouteThreads) {
       const int hl = pair / nt, cl = pair - hl * nt;
       const uint4* mrow = s_tile + cl * ustride;
       const float* qrow = s_q + hl * cv.D;
@@ -367,14 +368,14 @@ __global__ void __launch_bounds__(128) decode_route_kernel(CacheView cv, const _
     }
     __syncthreads();
   }
-  for (int pair = tid; pair < G * (width - nlegal); pair += 128) {  // not a candidate
+  for (int pair = tid; pair < G * (width - nlegal); pair += kRouteThreads) {  // not a candidate
     const int hl = pair / (width - nlegal), c = nlegal + pair - hl * (width - nlegal);
     s_scores[hl * width + c] = -INFINITY;
     if (scores) scores[((long long)row * Hq + g * G + hl) * width + c] = -INFINITY;
   }
   __syncthreads();
   // top-k: one warp per head, `remote` rounds of (max value, lowest index among equals)
-  for (int hl = warp; hl < G; hl += 4) {
+  for (int hl = warp; hl < G; hl += kRouteThreads / 32) {
     float* sc = s_scores + hl * width;
     int* out = selected + ((long long)row * Hq + g * G + hl) * (remote + 1);
     if (lane == 0) out[0] = cur;
@@ -1064,7 +1065,7 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
       cudaFuncSetAttribute(decode_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return MOBA_ERR_CUDA;
   const int umax = moba_decode_union_capacity(hq, c->hkv, remote, width);
-  if (launch_dependent(4u, decode_route_kernel, dim3(rows, c->hkv), dim3(128), smem, (cudaStream_t)stream, make_cache_view(*c),
+  if (launch_dependent(4u, decode_route_kernel, dim3(rows, c->hkv), dim3(kRouteThreads), smem, (cudaStream_t)stream, make_cache_view(*c),
                        static_cast<const __nv_bfloat16*>(q), ids, positions, hq, remote, width, scores, selected, u_chunk, u_mask,
                        u_count, umax) != cudaSuccess)
     return MOBA_ERR_CUDA;
