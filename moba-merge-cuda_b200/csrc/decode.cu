@@ -332,9 +332,23 @@ __global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView c
   // stage the group's query rows as FP32, then one thread per (head, chunk) pair: the loads of all
   // pairs are independent, so their latencies overlap instead of adding up
   float* s_q = reinterpret_cast<float*>(s_mask + width + 1);  // [G][D]
-  for (int i = tid; i < G * cv.D; i += kRouteThreads)
-    s_q[i] = __bfloat162float(q[((long long)row * Hq + g * G) * cv.D + i]);
-  __syncthreads();
+  // the query loads are issued here and stored after the first tile of means has been requested, so that the two
+  // trips to L2 overlap (a store to shared memory would make the warp wait for its load first)
+  const __nv_bfloat16* qsrc = q + ((long long)row * Hq + g * G) * cv.D;
+  float qreg[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = tid + j * kRouteThreads;
+    qreg[j] = i < G * cv.D ? __bfloat162float(qsrc[i]) : 0.f;
+  }
+  auto store_q = [&]() {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = tid + j * kRouteThreads;
+      if (i < G * cv.D) s_q[i] = qreg[j];
+    }
+    for (int i = tid + 4 * kRouteThreads; i < G * cv.D; i += kRouteThreads) s_q[i] = __bfloat162float(qsrc[i]);
+  };
   // The mean rows of kRouteTile chunks at a time are brought into shared memory by all threads with loads that do not
   // depend on each other (one trip to L2 per tile); the (head, chunk) pairs are then scored from there.  Rows are
   // padded to an odd number of 16-byte units so that threads on consecutive chunks hit different banks.
@@ -348,6 +362,7 @@ __global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView c
       s_tile[cl * ustride + u] = __ldcg(
           reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c0 + cl) * cv.Hkv + g) * cv.D) + u);
     }
+    if (c0 == 0) store_q();
     __syncthreads();
     for (int pair = tid; pair < G * nt; pair += kRouteThreads) {
       const int hl = pair / nt, cl = pair - hl * nt;
