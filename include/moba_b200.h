@@ -221,6 +221,13 @@ int moba_decode_step_inputs(const int64_t* tokens, const void* embedding, int hi
                             const float* inv_freq, float scaling, int dim, long long rows, void* h, void* cosv, void* sinv,
                             void* stream);
 
+/* Greedy token of a decode step: index of the largest of n bf16 logits, the lowest index among equal maxima (NaN never
+ * wins), written as int64 to out.  workspace: moba_argmax_workspace_bytes() bytes, 16-byte aligned, zeroed once
+ * before the first call (the kernel leaves it ready for the next); logits 16-byte aligned.  The reference takes
+ * logits.argmax on the host side of its greedy loop (scripts/evaluate_full_model.py:283-288). */
+size_t moba_argmax_workspace_bytes(void);
+int moba_argmax_bf16(const void* logits, int n, void* workspace, size_t workspace_bytes, int64_t* out, void* stream);
+
 /* Linear layer of a one-token decode step: y [n] = weight [n, k] x (+ bias), bf16 in and out, FP32 accumulation; the
  * weight is read once with all loads of a thread in flight, which is what bounds a batch-1 step.
  *   input: either x [k], or h_in [k] with norm_weight [k] (then x = norm_weight * rmsnorm(h_in + delta, eps), delta

@@ -331,6 +331,78 @@ __global__ void __launch_bounds__(256) step_inputs_kernel(const long long* token
   }
 }
 
+// ---- greedy token: arg-max over one row of bf16 logits, lowest index among equal maxima ---------------------------
+// kArgmaxCtas CTAs scan slices with 16-byte loads and leave one candidate each; the CTA that finishes last (atomic
+// ticket, nobody waits) picks among the candidates, writes the int64 index and clears the ticket for the next launch.
+constexpr int kArgmaxCtas = 148;
+
+__device__ __forceinline__ void argmax_pick(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+__global__ void __launch_bounds__(256) argmax_kernel(const __nv_bfloat16* logits, int n, float* cand_v, int* cand_i, unsigned* ticket,
+                                                     long long* out) {
+  __shared__ float s_v[8];
+  __shared__ int s_i[8];
+  __shared__ bool s_last;
+  dependents_may_start();
+  wait_for_predecessor();  // the logits
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float bv = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  const int chunks = n >> 3;
+  for (int c = blockIdx.x * 256 + tid; c < chunks; c += gridDim.x * 256) {
+    const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(logits) + c);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      argmax_pick(bv, bi, __uint_as_float(w[j] << 16), c * 8 + 2 * j);
+      argmax_pick(bv, bi, __uint_as_float(w[j] & 0xFFFF0000u), c * 8 + 2 * j + 1);
+    }
+  }
+  if (blockIdx.x == 0)
+    for (int i = (chunks << 3) + tid; i < n; i += 256) argmax_pick(bv, bi, __bfloat162float(logits[i]), i);
+  auto reduce = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+      argmax_pick(bv, bi, ov, oi);
+    }
+    if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+      bv = lane < 8 ? s_v[lane] : -INFINITY;
+      bi = lane < 8 ? s_i[lane] : 0x7FFFFFFF;
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+        const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        argmax_pick(bv, bi, ov, oi);
+      }
+    }
+  };
+  reduce();
+  if (tid == 0) {
+    cand_v[blockIdx.x] = bv;
+    cand_i[blockIdx.x] = bi;
+    __threadfence();
+    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  bv = -INFINITY;
+  bi = 0x7FFFFFFF;
+  for (int c = tid; c < (int)gridDim.x; c += 256) argmax_pick(bv, bi, __ldcg(cand_v + c), __ldcg(cand_i + c));
+  __syncthreads();  // s_v / s_i of the first reduction have been read
+  reduce();
+  if (tid == 0) {
+    *out = bi == 0x7FFFFFFF ? 0 : bi;  // a row of NaN or -inf only: index 0
+    *ticket = 0u;
+  }
+}
+
 }  // namespace
 }  // namespace moba
 
@@ -439,5 +511,23 @@ extern "C" int moba_decode_step_inputs(const int64_t* tokens, const void* embedd
   step_inputs_kernel<<<(unsigned)rows, 256, 0, (cudaStream_t)stream>>>(
       reinterpret_cast<const long long*>(tokens), static_cast<const __nv_bfloat16*>(embedding), hidden, positions, inv_freq, scaling, dim,
       static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(cosv), static_cast<__nv_bfloat16*>(sinv));
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
+
+extern "C" size_t moba_argmax_workspace_bytes(void) { return 256 + (size_t)kArgmaxCtas * 8; }
+
+extern "C" int moba_argmax_bf16(const void* logits, int n, void* workspace, size_t workspace_bytes, int64_t* out, void* stream) {
+  if (!logits || !workspace || !out || n < 1) return MOBA_ERR_INVALID;
+  if (workspace_bytes < moba_argmax_workspace_bytes()) return MOBA_ERR_WORKSPACE;
+  if (((uintptr_t)logits & 15) || ((uintptr_t)workspace & 15)) return MOBA_ERR_INVALID;
+  char* p = static_cast<char*>(workspace);
+  unsigned* ticket = reinterpret_cast<unsigned*>(p);
+  float* cand_v = reinterpret_cast<float*>(p + 256);
+  int* cand_i = reinterpret_cast<int*>(p + 256 + kArgmaxCtas * 4);
+  const int chunks = n >> 3;
+  const int ctas = chunks >= 256 * kArgmaxCtas ? kArgmaxCtas : (chunks + 255) / 256 > 0 ? (chunks + 255) / 256 : 1;
+  if (launch_dependent(16u, argmax_kernel, dim3(ctas), dim3(256), 0, (cudaStream_t)stream, static_cast<const __nv_bfloat16*>(logits), n,
+                       cand_v, cand_i, ticket, reinterpret_cast<long long*>(out)) != cudaSuccess)
+    return MOBA_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

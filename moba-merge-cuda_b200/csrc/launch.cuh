@@ -6,7 +6,7 @@
 // wait (seen: a stale position, one chunk early, exactly at chunk boundaries).  Both calls do nothing in a kernel
 // that was launched the ordinary way.  MOBA_NO_PDL=1 in the environment makes every launch ordinary (for
 // comparison); MOBA_PDL_MASK=<bits> keeps the dependent form only for the kinds whose bit is set (1 projections,
-// 2 a step's first launch, 4 routing, 8 attention), which is how the rule above was found.
+// 2 a step's first launch, 4 routing, 8 attention, 16 arg-max), which is how the rule above was found.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdlib.h>

@@ -103,6 +103,7 @@ class FullQwen2Session:
             new = lambda n: torch.empty((1, n), dtype=self.dtype, device=self.device)
             self._h, self._y, self._act = [new(hidden), new(hidden)], new(hidden), new(ffn)
             self._qkv, self._att, self._down = new((self.hq + 2 * self.hk) * self.dim), new(hidden), new(hidden)
+            self._argmax_ws = torch.zeros(self._lib.moba_argmax_workspace_bytes(), dtype=torch.uint8, device=self.device)
             # rotary table inside the step's first launch when the model uses the default rotary type
             rotary = model.model.rotary_emb
             self._inv_freq = None
@@ -315,7 +316,11 @@ class FullQwen2Session:
         check(lib.moba_add_rmsnorm(h.data_ptr(), delta.data_ptr(), body.norm.weight.data_ptr(), float(body.norm.variance_epsilon),
                                    1, hidden, None, self._y.data_ptr(), st))
         self.logits = self.model.lm_head(self._y)
-        self.next_token.copy_(self.logits.argmax(-1, keepdim=True))
+        if self.logits.dtype == torch.bfloat16 and self.logits.is_contiguous():
+            check(lib.moba_argmax_bf16(self.logits.data_ptr(), self.logits.shape[-1], self._argmax_ws.data_ptr(),
+                                       self._argmax_ws.numel(), self.next_token.data_ptr(), st))
+        else:
+            self.next_token.copy_(self.logits.argmax(-1, keepdim=True))
         return self.logits
 
     @torch.no_grad()

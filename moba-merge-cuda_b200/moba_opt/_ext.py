@@ -51,6 +51,9 @@ def lib():
         L.moba_silu_mul.argtypes = [c_vp, ctypes.c_longlong, ctypes.c_int, c_vp, c_vp]
         L.moba_decode_step_inputs.argtypes = [c_vp, c_vp, ctypes.c_int, c_vp, c_vp, ctypes.c_float, ctypes.c_int,
                                               ctypes.c_longlong, c_vp, c_vp, c_vp, c_vp]
+        L.moba_argmax_workspace_bytes.restype = c_sz
+        L.moba_argmax_workspace_bytes.argtypes = []
+        L.moba_argmax_bf16.argtypes = [c_vp, ctypes.c_int, c_vp, c_sz, c_vp, c_vp]
         L.moba_decode_linear.argtypes = [c_vp, c_vp, c_vp, c_vp, ctypes.c_float, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, c_vp, c_vp]
         _lib = L

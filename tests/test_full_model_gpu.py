@@ -271,3 +271,26 @@ def test_row_wise_glue_kernels_agree_with_the_single_row_forms():
     gu, act = rnd(rows, 2 * ffn), torch.empty(rows, ffn, device="cuda", dtype=torch.bfloat16)
     big, small = halves(lambda r0, n: lib.moba_silu_mul(ptr(gu[r0:]), n, ffn, ptr(act[r0:]), st), act)
     assert torch.equal(big[0], small[0])
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 300, 4099, 151936, 1 << 20])
+def test_argmax_matches_torch_and_takes_the_lowest_index_among_ties(n):
+    import ctypes
+    from moba_opt import _ext
+    lib = _ext.lib()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    ws = torch.zeros(lib.moba_argmax_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    out = torch.full((1,), -1, dtype=torch.long, device="cuda")
+    g = torch.Generator().manual_seed(n)
+    for trial in range(3):      # the workspace is left ready for the next call
+        x = torch.randn(n, generator=g).cuda().bfloat16()
+        if trial == 1 and n > 8:
+            top = float(x.float().max()) + 1.0
+            x[n - 1], x[n // 2], x[n // 3] = top, top, top          # ties: the lowest index wins
+        if trial == 2 and n > 8:
+            x[0] = float("nan")                                     # NaN never wins
+        assert lib.moba_argmax_bf16(x.data_ptr(), n, ws.data_ptr(), ws.numel(), out.data_ptr(), st) == 0
+        ref = x.float().clone()
+        ref[ref.isnan()] = -float("inf")
+        want = int((ref == ref.max()).nonzero()[0, 0])
+        assert int(out[0]) == want
