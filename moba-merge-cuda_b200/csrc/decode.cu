@@ -253,17 +253,70 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
   dependents_may_start();
   wait_for_predecessor();  // the projection of the new token
   if (tid == 0) {
+    // two trips to memory, not three: the page of the new token is guessed from the previous step's position and
+    // its table entry is read together with the length; the guess is checked against the length afterwards
     const int sid = ids[row];
+    const int guess_page = (positions[row] + 1) / cv.page;  // whatever the buffer holds before the first step is checked below
+    const bool guessed = positions[row] >= 0 && guess_page < cv.width;
     const int logical = delta[row], physical = delta[b + row];
-    if (logical >= 0 && logical < cv.width) cv.table[(long long)sid * cv.width + logical] = physical;
     const int len = cv.lengths[sid];
+    const int spec = guessed ? cv.table[(long long)sid * cv.width + guess_page] : -1;
+    if (logical >= 0 && logical < cv.width) cv.table[(long long)sid * cv.width + logical] = physical;
     positions[row] = len;
     cv.lengths[sid] = len + 1;
     s_sid = sid; s_pos = len;
     const int page = len / cv.page;
-    s_phys = page < cv.width ? cv.table[(long long)sid * cv.width + page] : -1;
+    int phys = -1;
+    if (page < cv.width) {
+      if (page == logical) phys = physical;                      // opened by this step's delta
+      else if (guessed && page == guess_page) phys = spec;
+      else phys = cv.table[(long long)sid * cv.width + page];
+    }
+    s_phys = phys;
   }
-  if (qkv) {
+  // rotary embedding + split.  With head dimensions that are multiples of 16 a thread takes 8 dimensions of a head
+  // (one trip for its four 16-byte loads) and the new K and V rows also stay in shared memory for the append below.
+  const int upr = cv.D >> 3;
+  const bool vec = qkv && (cv.D & 15) == 0 &&
+                   !(((uintptr_t)qkv | (uintptr_t)cosv | (uintptr_t)sinv | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15);
+  const bool staged = vec && cv.Hkv * cv.D <= 2048;  // 2 * Hkv * D bf16 fit the 8 KB of s_part
+  uint4* s_kv = reinterpret_cast<uint4*>(s_part);    // [K, V][Hkv][D / 8]
+  if (vec) {
+    const int heads = Hq + 2 * cv.Hkv, D = cv.D;
+    const __nv_bfloat16* src = qkv + (long long)row * heads * D;
+    for (int item = tid; item < heads * upr; item += 256) {
+      const int h = item / upr, c = item - h * upr;
+      const uint4 own = *reinterpret_cast<const uint4*>(src + h * D + c * 8);
+      if (h >= Hq + cv.Hkv) {
+        *reinterpret_cast<uint4*>(v + ((long long)row * cv.Hkv + (h - Hq - cv.Hkv)) * D + c * 8) = own;
+        if (staged) s_kv[(cv.Hkv + h - Hq - cv.Hkv) * upr + c] = own;
+        continue;
+      }
+      const bool low = c < (upr >> 1);
+      const uint4 oth = *reinterpret_cast<const uint4*>(src + h * D + (low ? c + (upr >> 1) : c - (upr >> 1)) * 8);
+      const uint4 cs = *reinterpret_cast<const uint4*>(cosv + (long long)row * D + c * 8);
+      const uint4 sn = *reinterpret_cast<const uint4*>(sinv + (long long)row * D + c * 8);
+      const uint32_t xw[4] = {own.x, own.y, own.z, own.w}, ow[4] = {oth.x, oth.y, oth.z, oth.w};
+      const uint32_t cw[4] = {cs.x, cs.y, cs.z, cs.w}, sw[4] = {sn.x, sn.y, sn.z, sn.w};
+      uint32_t out[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float lo = __bfloat162float(__float2bfloat16_rn(bf_lo(xw[i]) * bf_lo(cw[i]))) +
+                         __bfloat162float(__float2bfloat16_rn((low ? -bf_lo(ow[i]) : bf_lo(ow[i])) * bf_lo(sw[i])));
+        const float hi = __bfloat162float(__float2bfloat16_rn(bf_hi(xw[i]) * bf_hi(cw[i]))) +
+                         __bfloat162float(__float2bfloat16_rn((low ? -bf_hi(ow[i]) : bf_hi(ow[i])) * bf_hi(sw[i])));
+        const __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+        out[i] = *reinterpret_cast<const uint32_t*>(&pk);
+      }
+      const uint4 res = make_uint4(out[0], out[1], out[2], out[3]);
+      if (h < Hq) {
+        *reinterpret_cast<uint4*>(q + ((long long)row * Hq + h) * D + c * 8) = res;
+      } else {
+        *reinterpret_cast<uint4*>(k + ((long long)row * cv.Hkv + (h - Hq)) * D + c * 8) = res;
+        if (staged) s_kv[(h - Hq) * upr + c] = res;
+      }
+    }
+  } else if (qkv) {
     const int heads = Hq + 2 * cv.Hkv, D = cv.D, half = D >> 1;
     const __nv_bfloat16* src = qkv + (long long)row * heads * D;
     for (int i = tid; i < heads * D; i += 256) {
@@ -285,13 +338,12 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
     if (tid == 0 && status) atomicOr(status, kErrBadIndex);
     return;
   }
-  const int upr = cv.D >> 3;
   for (int i = tid; i < cv.Hkv * upr; i += 256) {
     const int head = i / upr, u = i - head * upr;
     const long long dst = (((long long)physical * cv.page + pos % cv.page) * cv.Hkv + head) * cv.D + u * 8;
     const long long src = ((long long)row * cv.Hkv + head) * cv.D + u * 8;
-    *reinterpret_cast<uint4*>(cv.kc + dst) = *reinterpret_cast<const uint4*>(k + src);
-    *reinterpret_cast<uint4*>(cv.vc + dst) = *reinterpret_cast<const uint4*>(v + src);
+    *reinterpret_cast<uint4*>(cv.kc + dst) = staged ? s_kv[i] : *reinterpret_cast<const uint4*>(k + src);
+    *reinterpret_cast<uint4*>(cv.vc + dst) = staged ? s_kv[cv.Hkv * upr + i] : *reinterpret_cast<const uint4*>(v + src);
   }
   if ((pos + 1) % cv.C != 0) return;  // the token does not complete its chunk
   const int chunk = pos / cv.C;
