@@ -280,7 +280,7 @@ int validate_desc(const moba_prefill_desc* d) {
   if (d->total_tokens < 1 || d->num_seqs < 1 || d->hq < 1 || d->hkv < 1 || d->hq % d->hkv) return MOBA_ERR_INVALID;
   if (d->dim < 8 || d->dim > 256 || d->dim % 8) return MOBA_ERR_INVALID;
   if (d->chunk_size < 1 || d->remote_k < 0 || d->num_chunks < 1 || d->num_qtiles < 1) return MOBA_ERR_INVALID;
-  if (d->remote_k > 16) return MOBA_ERR_UNSUPPORTED;
+  if (d->remote_k > 16 || d->dim > 128) return MOBA_ERR_UNSUPPORTED;  // prefill kernels: head_dim up to 128
   if ((long long)d->total_tokens * d->hq * (d->remote_k > 0 ? d->remote_k : 1) >= (1ll << 31)) return MOBA_ERR_UNSUPPORTED;
   if (d->max_chunks_per_seq > 4096) return MOBA_ERR_UNSUPPORTED;
   if (!d->cu_seqlens || !d->chunk_start || !d->chunk_seq || !d->chunk_local || !d->qtile_chunk || !d->qtile_tok0 ||

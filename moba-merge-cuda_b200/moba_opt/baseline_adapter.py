@@ -2,16 +2,18 @@
 
 Behaviourally the checks of the reference (src/moba_opt/baseline_adapter.py:23-76): every violation
 is a ValueError raised before any device work, and `validate_shapes` / `validate_config` stay usable
-without a CUDA runtime.  Two limits differ on purpose: topk may go up to 17 (reference: 9) because
-the long-context configuration needs 12, and the CUDA kernels take bf16 only (the reference also
-accepts fp16).
+without a CUDA runtime.  Three limits differ on purpose: topk may go up to 17 (reference: 9) because
+the long-context configuration needs 12, the CUDA kernels take bf16 only (the reference also
+accepts fp16), and the prefill kernels take head_dim up to 128 (the reference: 256; the decode
+cache here goes to 256 as well).  Each is refused here, as a ValueError, before anything is launched.
 """
 import numbers
 
 import torch
 
 SUPPORTED_DTYPES = (torch.bfloat16,)
-MAINLINE_HEAD_DIMS = tuple(range(8, 257, 8))
+MAINLINE_HEAD_DIMS = tuple(range(8, 257, 8))      # the reference's envelope; the decode cache accepts all of it
+PREFILL_HEAD_DIMS = tuple(range(8, 129, 8))       # what the prefill kernels are compiled for
 MAX_TOPK = 17
 
 
@@ -25,7 +27,7 @@ def _as_count(value, what):
     return int(value) if ok else _fail(f"{what}: expected a positive integer, got {value!r}")
 
 
-def validate_shapes(q_shape, k_shape, v_shape, allow_gqa=False):
+def validate_shapes(q_shape, k_shape, v_shape, allow_gqa=False, head_dims=PREFILL_HEAD_DIMS):
     """Checks [T,H,D] shapes and returns the group size Hq // Hkv (baseline_adapter.py:23-34)."""
     shapes = {"q": tuple(q_shape), "k": tuple(k_shape), "v": tuple(v_shape)}
     for name, shape in shapes.items():
@@ -36,8 +38,8 @@ def validate_shapes(q_shape, k_shape, v_shape, allow_gqa=False):
         _fail(f"k and v must have the same shape, got {shapes['k']} and {shapes['v']}")
     if tq != tk or dq != dk:
         _fail(f"q and k must agree on tokens and head_dim, got {shapes['q']} and {shapes['k']}")
-    if dq not in MAINLINE_HEAD_DIMS:
-        _fail(f"head_dim {dq} unsupported: need a multiple of 8 between 8 and 256")
+    if dq not in head_dims:
+        _fail(f"head_dim {dq} unsupported: need a multiple of 8 between {head_dims[0]} and {head_dims[-1]}")
     if hq % hk:
         _fail(f"{hq} query heads cannot be grouped over {hk} KV heads")
     if hq != hk and not allow_gqa:

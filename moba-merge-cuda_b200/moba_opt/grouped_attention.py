@@ -225,7 +225,7 @@ def moba_prefill(q, k, v, cu_seqlens, max_seqlen, config, *, return_lse=False):
     """opt_gqa_cuda plus optional access to the global LSE [T,Hq] (fp32, natural log)."""
     cu = _validate(q, k, v, cu_seqlens, allow_gqa=True, max_seqlen=max_seqlen, config=config)
     chunk_size = int(config["chunk_size"])
-    precision = config.get("route_precision", "fp32")
+    precision = config.get("route_precision", "upstream")   # the reference's default (grouped_attention.py:35)
     deterministic = config.get("deterministic_merge", True)
     stable = config.get("stable_routes", True)
     if precision not in ("upstream", "fp32"):
@@ -247,8 +247,10 @@ def opt_gqa_cuda(q, k, v, cu_seqlens, max_seqlen, config):
     """Drop-in for the reference entry point; differentiable w.r.t. q, k, v.
     The gate is always FP32 with the lowest-chunk tie rule and the merge is always order-deterministic
     (the reference's stable_routes=True, deterministic_merge=True behaviour; both flags are accepted
-    and type-checked).  route_precision defaults to 'fp32'; 'upstream' rounds the chunk means to bf16
-    before the gate, as grouped_attention.py:52 does."""
+    and type-checked; where the reference's default stable_routes=False leaves the order among exactly
+    tied scores to torch.topk, the lowest chunk wins here).  route_precision defaults to 'upstream' as in
+    the reference (grouped_attention.py:35): the chunk means are rounded to bf16 before the gate
+    (grouped_attention.py:52); 'fp32' keeps them in FP32."""
     return moba_prefill(q, k, v, cu_seqlens, max_seqlen, config)
 
 

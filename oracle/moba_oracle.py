@@ -133,23 +133,7 @@ def selected_from_sel(sel, filtered, T, Hq):
 
 
 # ----------------------------------------------------------------------------- prefill attention
-def _row_mask(seq_start, seq_end, rows, cu_chunk, chunk_of_token, sel_rows):
-    """Boolean [n_rows, seq_len] mask of attended keys for packed-token rows `rows` of one head.
-    Key set: own chunk up to and including the row (causal) plus every selected chunk in full.
-    reference/fixed_route_attention.py:93-113, reference/grouped_reference.py:19-31."""
-    length = seq_end - seq_start
-    keys = np.arange(seq_start, seq_end)
-    kc = chunk_of_token[keys]
-    rc = chunk_of_token[rows]
-    mask = (kc[None, :] == rc[:, None]) & (keys[None, :] <= rows[:, None])
-    for s in range(sel_rows.shape[1]):
-        c = sel_rows[:, s]
-        mask |= (c[:, None] >= 0) & (kc[None, :] == c[:, None])
-    assert mask.shape == (rows.size, length)
-    return mask
-
-
-def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, rows=None, row_block=512):
+def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, rows=None, row_block=512, key_range=None):
     """FP64 MoBA attention under a fixed route, optionally with gradients, in query blocks (the
     reference oracle builds whole [L,L] masks; this is the same math tiled over queries).
 
@@ -160,6 +144,9 @@ def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, r
     sel [T,Hq,R]: global chunk ids per row (-1 padded); R may be 0.
     rows: optional 1-D array of packed token indices to evaluate; default all.  With `rows`, d_out is
     [len(rows),Hq,D] and dq/dk/dv hold only the contributions of those rows.
+    key_range: optional (lo, hi) of packed key tokens.  With it, only dk[lo:hi] and dv[lo:hi] are formed (returned as
+    arrays of hi-lo rows) and dq is left out: the gradient of one key block costs the forward of the rows that attend
+    it plus two small products, which is what makes a block of a 128K-token sequence checkable on a CPU.
     Returns dict(out [n,Hq,D], lse [n,Hq]) and, when d_out is given, dq, dk, dv (full size).
     """
     q = np.asarray(q, dtype=np.float64)
@@ -178,9 +165,14 @@ def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, r
     lse = np.zeros((all_rows.size, Hq))
     if want_grad:
         d_out = np.asarray(d_out, dtype=np.float64)
-        dq = np.zeros_like(q)
-        dk = np.zeros_like(k)
-        dv = np.zeros_like(v)
+        if key_range is None:
+            dq = np.zeros_like(q)
+            dk = np.zeros_like(k)
+            dv = np.zeros_like(v)
+        else:
+            k_lo, k_hi = int(key_range[0]), int(key_range[1])
+            dk = np.zeros((k_hi - k_lo,) + k.shape[1:])
+            dv = np.zeros((k_hi - k_lo,) + v.shape[1:])
     seq_of_row = np.searchsorted(cu, all_rows, side="right") - 1
     for b in np.unique(seq_of_row):
         s0, s1 = int(cu[b]), int(cu[b + 1])
@@ -188,28 +180,54 @@ def attention_fixed_route(q, k, v, cu_seqlens, sel, chunk_size, *, d_out=None, r
         for lo in range(0, local.size, row_block):
             idx = local[lo:lo + row_block]
             r = all_rows[idx]
+            own_chunk = chunk_of_token[r]
             for h in range(Hq):
                 g = h // G
-                mask = _row_mask(s0, s1, r, cu_chunk, chunk_of_token, sel[r, h])
-                logits = (q[r, h] @ k[s0:s1, g].T) * scale
-                logits = np.where(mask, logits, NEG_INF)
-                m = logits.max(axis=1, keepdims=True)
-                p = np.exp(logits - m)
-                z = p.sum(axis=1, keepdims=True)
-                p /= z
-                o = p @ v[s0:s1, g]
+                # Key set of a row (reference/fixed_route_attention.py:93-113, reference/grouped_reference.py:19-31):
+                # its own chunk up to and including the row, plus every selected chunk in full.  The reference builds
+                # a dense [L, L] mask; here the same set is walked chunk by chunk, so the cost follows the attended
+                # pairs and a 128K-token sequence stays checkable.
+                attended = np.concatenate([own_chunk[:, None], sel[r, h]], axis=1)
+                pieces = []
+                m = np.full(r.size, NEG_INF)
+                for c in np.unique(attended[attended >= 0]).tolist():
+                    ridx = np.nonzero((attended == c).any(axis=1))[0]
+                    k0, k1 = int(cu_chunk[c]), int(cu_chunk[c + 1])
+                    logits = (q[r[ridx], h] @ k[k0:k1, g].T) * scale
+                    causal = own_chunk[ridx] == c
+                    if causal.any():
+                        future = np.arange(k0, k1)[None, :] > r[ridx][:, None]
+                        logits = np.where(causal[:, None] & future, NEG_INF, logits)
+                    m[ridx] = np.maximum(m[ridx], logits.max(axis=1))
+                    pieces.append((k0, k1, ridx, logits))
+                z = np.zeros(r.size)
+                o = np.zeros((r.size, D))
+                for i, (k0, k1, ridx, logits) in enumerate(pieces):
+                    p = np.exp(logits - m[ridx, None])
+                    z[ridx] += p.sum(axis=1)
+                    o[ridx] += p @ v[k0:k1, g]
+                    pieces[i] = (k0, k1, ridx, p)
+                o /= z[:, None]
                 out[idx, h] = o
-                lse[idx, h] = (m + np.log(z))[:, 0]
+                lse[idx, h] = m + np.log(z)
                 if want_grad:
                     do = d_out[idx, h]
-                    dp = do @ v[s0:s1, g].T
-                    delta = (do * o).sum(axis=1, keepdims=True)
-                    ds = p * (dp - delta) * scale
-                    dq[r, h] = ds @ k[s0:s1, g]
-                    dk[s0:s1, g] += ds.T @ q[r, h]
-                    dv[s0:s1, g] += p.T @ do
+                    delta = (do * o).sum(axis=1)
+                    for k0, k1, ridx, p in pieces:
+                        lo_k, hi_k = (k0, k1) if key_range is None else (max(k0, k_lo), min(k1, k_hi))
+                        if lo_k >= hi_k:
+                            continue
+                        pn = p[:, lo_k - k0:hi_k - k0] / z[ridx, None]
+                        ds = pn * (do[ridx] @ v[lo_k:hi_k, g].T - delta[ridx, None]) * scale
+                        base = 0 if key_range is None else k_lo
+                        dk[lo_k - base:hi_k - base, g] += ds.T @ q[r[ridx], h]
+                        dv[lo_k - base:hi_k - base, g] += pn.T @ do[ridx]
+                        if key_range is None:
+                            dq[r[ridx], h] += ds @ k[lo_k:hi_k, g]
     res = dict(out=out, lse=lse)
-    if want_grad:
+    if want_grad and key_range is not None:
+        res.update(dk=dk, dv=dv)
+    elif want_grad:
         res.update(dq=dq, dk=dk, dv=dv)
     return res
 

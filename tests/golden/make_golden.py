@@ -6,8 +6,9 @@ Run where a checkout of the reference project is available:
 What is executed from the reference (never copied):
   * routing: src/moba_opt/grouped_attention.py::opt_gqa_cuda on CPU tensors with its CUDA-only
     input check disabled and the attention launch intercepted, so the ROUTE_HOOK tensor is the
-    reference's own block selection (route_precision='fp32', stable_routes=True, and the
-    torch.topk variant);
+    reference's own block selection (route_precision='fp32' with stable_routes=True and with the
+    torch.topk variant, and route_precision='upstream', the reference's default, whose chunk means
+    are rounded to bf16 before the gate);
   * reference/fixed_route_attention.py, reference/grouped_reference.py (+ torch autograd for the
     gradients), reference/decode_reference.py, reference/merge_reference.py.
 The un-vendored upstream `moba` package the reference imports is satisfied in memory from the
@@ -111,11 +112,12 @@ def prefill_cases(ref, out_dir):
         q, k, v, g, cu = make_inputs(lens, hq, hkv, dim, seed, torch.bfloat16)
         rec = dict(lens=np.asarray(lens), hq=hq, hkv=hkv, dim=dim, chunk=chunk, topk=topk, seed=seed,
                    q=bits(q), k=bits(k), v=bits(v), g=bits(g))
-        for tag, stable in (("stable", True), ("topk", False)):
-            cfg = {"chunk_size": chunk, "topk": topk, "route_precision": "fp32", "stable_routes": stable}
+        for tag, precision, stable in (("stable", "fp32", True), ("topk", "fp32", False), ("upstream", "upstream", True),
+                                       ("upstream_topk", "upstream", False)):
+            cfg = {"chunk_size": chunk, "topk": topk, "route_precision": precision, "stable_routes": stable}
             route = reference_route(grouped, q, k, v, cu, max(lens), cfg)
             rec[f"selected_{tag}"] = route["selected"].numpy()
-            if stable:
+            if tag == "stable":
                 rec["cu_chunk"] = route["cu_chunk"].numpy()
                 rec["filtered"] = route["filtered_chunk_indices"].numpy()
                 rec["chunk_to_batch"] = route["chunk_to_batch"].numpy()
@@ -129,6 +131,31 @@ def prefill_cases(ref, out_dir):
                     rec.update(out_fixed=f32(o2), lse=f32(lse))
         np.savez_compressed(out_dir / f"{name}.npz", **rec)
         print(name, "selected pairs", int(rec["selected_stable"].sum()))
+
+
+ROUTE_CASES = [
+    # name, lens, hq, hkv, dim, chunk, topk, seed: many candidates and chunk sizes that are not powers of two, so that
+    # rounding the chunk means to bf16 (route_precision='upstream') changes some rows' selection
+    ("r_upstream_gqa", (700, 500), 6, 2, 128, 40, 5, 68),
+    ("r_upstream_mqa", (1500,), 4, 1, 64, 24, 4, 69),
+]
+
+
+def route_cases(ref, out_dir):
+    """Route-only fixtures: inputs and the reference's selection under both route precisions (bit-packed)."""
+    grouped = ref[0]
+    for name, lens, hq, hkv, dim, chunk, topk, seed in ROUTE_CASES:
+        q, k, v, _, cu = make_inputs(lens, hq, hkv, dim, seed, torch.bfloat16)
+        rec = dict(lens=np.asarray(lens), hq=hq, hkv=hkv, dim=dim, chunk=chunk, topk=topk, seed=seed, q=bits(q), k=bits(k))
+        for tag, precision in (("stable", "fp32"), ("upstream", "upstream")):
+            cfg = {"chunk_size": chunk, "topk": topk, "route_precision": precision, "stable_routes": True}
+            route = reference_route(grouped, q, k, v, cu, max(lens), cfg)
+            rec[f"selected_{tag}_packed"] = np.packbits(route["selected"].numpy())
+            rec["selected_shape"] = np.asarray(route["selected"].shape)
+            rec["filtered"] = route["filtered_chunk_indices"].numpy()
+        differ = int((np.unpackbits(rec["selected_stable_packed"]) != np.unpackbits(rec["selected_upstream_packed"])).sum())
+        np.savez_compressed(out_dir / f"{name}.npz", **rec)
+        print(name, "selection bits that differ between the two precisions:", differ)
 
 
 def config1_case(ref, out_dir):
@@ -217,6 +244,7 @@ def main():
     torch.set_num_threads(8)
     ref = load_reference(Path(args.reference))
     prefill_cases(ref, HERE)
+    route_cases(ref, HERE)
     config1_case(ref, HERE)
     decode_cases(ref, HERE)
     merge_case(ref, HERE)

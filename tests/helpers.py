@@ -7,10 +7,17 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 
 PREFILL_GOLDENS = ["p_gqa_small", "p_mha_tail", "p_mqa_multi", "p_k9", "p_one_chunk", "p_gqa_256"]
 DECODE_GOLDENS = ["d_small", "d_d128", "d_mha"]
+ROUTE_GOLDENS = ["r_upstream_gqa", "r_upstream_mqa"]
 
 
 def load(name):
     return dict(np.load(GOLDEN / f"{name}.npz"))
+
+
+def unpack_selected(g, tag):
+    """[F,Hq,T] bool selection stored bit-packed as selected_<tag>_packed + selected_shape."""
+    shape = g["selected_shape"]
+    return np.unpackbits(g[f"selected_{tag}_packed"])[:int(np.prod(shape))].reshape(shape).astype(bool)
 
 
 def bf16_bits_to_f64(bits):

@@ -7,7 +7,7 @@ from pathlib import Path
 import pytest
 
 from moba_opt import api
-from moba_opt.baseline_adapter import MAX_TOPK, validate_config, validate_shapes
+from moba_opt.baseline_adapter import MAINLINE_HEAD_DIMS, MAX_TOPK, validate_config, validate_shapes
 
 ROOT = Path(__file__).resolve().parents[1]
 
@@ -19,7 +19,15 @@ def test_grouped_shapes(hq, hkv):
 
 @pytest.mark.parametrize("dim", range(8, 257, 8))
 def test_head_dimensions(dim):
-    assert validate_shapes((3, 2, dim), (3, 2, dim), (3, 2, dim)) == 1
+    """The prefill kernels go to head_dim 128: anything above is a ValueError from the shape check itself, i.e. before
+    any launch (the reference's envelope, up to 256, is what the decode cache accepts)."""
+    shapes = ((3, 2, dim),) * 3
+    assert validate_shapes(*shapes, head_dims=MAINLINE_HEAD_DIMS) == 1
+    if dim <= 128:
+        assert validate_shapes(*shapes) == 1
+    else:
+        with pytest.raises(ValueError, match="head_dim"):
+            validate_shapes(*shapes)
 
 
 @pytest.mark.parametrize("qs,ks,vs", [

@@ -3,8 +3,8 @@ import numpy as np
 import pytest
 
 from oracle import moba_oracle as mo
-from helpers import (DECODE_GOLDENS, PREFILL_GOLDENS, bf16_bits_to_f64, config1_inputs, cu_from_lens, load,
-                     torch_to_f64)
+from helpers import (DECODE_GOLDENS, PREFILL_GOLDENS, ROUTE_GOLDENS, bf16_bits_to_f64, config1_inputs, cu_from_lens, load,
+                     torch_to_f64, unpack_selected)
 
 
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
@@ -30,6 +30,24 @@ def test_route_matches_reference_bit_exact(name):
     assert np.array_equal(mo.sel_from_selected(g["selected_stable"], g["filtered"], R), r["sel"])
     back = mo.selected_from_sel(r["sel"], g["filtered"], q.shape[0], q.shape[1]) if R else r["selected"]
     assert np.array_equal(back, g["selected_stable"])
+
+
+@pytest.mark.parametrize("name", PREFILL_GOLDENS + ROUTE_GOLDENS)
+def test_upstream_route_matches_reference_bit_exact(name):
+    """route_precision='upstream' (the reference's default, src/moba_opt/grouped_attention.py:35,52): chunk means
+    rounded to bf16 before the gate.  The route-only fixtures are shaped so that this changes some rows."""
+    g = load(name)
+    q, k = bf16_bits_to_f64(g["q"]), bf16_bits_to_f64(g["k"])
+    cu = cu_from_lens(g["lens"])
+    r = mo.route_prefill(q, k, cu, int(g["chunk"]), int(g["topk"]), mean_rounding=mo.bf16_round)
+    if name in ROUTE_GOLDENS:
+        want, fp32 = unpack_selected(g, "upstream"), unpack_selected(g, "stable")
+        assert (want != fp32).any()                                  # the fixture does discriminate the two precisions
+        assert np.array_equal(mo.route_prefill(q, k, cu, int(g["chunk"]), int(g["topk"]))["selected"], fp32)
+    else:
+        want = g["selected_upstream"]
+        assert np.array_equal(g["selected_upstream_topk"], want)     # no exact ties: torch.topk picks the same set
+    assert np.array_equal(r["selected"], want)
 
 
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)

@@ -11,7 +11,8 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import PREFILL_GOLDENS, bf16_bits_to_torch, config1_inputs, cu_from_lens, load, rel_rms, torch_to_f64
+from helpers import (PREFILL_GOLDENS, ROUTE_GOLDENS, bf16_bits_to_torch, config1_inputs, cu_from_lens, load, rel_rms,
+                     torch_to_f64, unpack_selected)
 from oracle import moba_oracle as mo
 
 pytestmark = pytest.mark.gpu
@@ -43,9 +44,11 @@ def _run(q, k, v, cu, chunk, topk, d_out=None, **flags):
 def _check_close(name, got, ref):
     got, ref = np.asarray(got, dtype=np.float64), np.asarray(ref, dtype=np.float64)
     assert np.isfinite(got).all(), name
-    err = np.abs(got - ref).max() / max(1.0, np.abs(ref).max())
+    plain = np.abs(got - ref).max()
+    err = plain / max(1.0, np.abs(ref).max())
     rr = rel_rms(got, ref)
-    assert err <= MAX_ABS and rr <= REL_RMS, f"{name}: scaled max-abs {err:.3e} rel-rms {rr:.3e}"
+    print(f"{name}: max-abs {plain:.3e}, |ref|max {np.abs(ref).max():.3e}, scaled max-abs {err:.3e}, rel-rms {rr:.3e}")
+    assert err <= MAX_ABS and rr <= REL_RMS, f"{name}: max-abs {plain:.3e} scaled {err:.3e} rel-rms {rr:.3e}"
 
 
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
@@ -64,6 +67,41 @@ def test_routes_bit_exact_and_forward_matches_reference(name):
     _check_close("out", torch_to_f64(out), g["out"])
     if "lse" in g:
         np.testing.assert_allclose(torch_to_f64(lse), g["lse"], atol=5e-4, rtol=2e-5)
+
+
+@pytest.mark.parametrize("name", PREFILL_GOLDENS + ROUTE_GOLDENS)
+@pytest.mark.parametrize("precision", ["upstream", "fp32"])
+def test_routes_bit_exact_under_both_route_precisions(name, precision):
+    """Selection equal to the reference's own ROUTE_HOOK tensor for route_precision='upstream' (its default: chunk
+    means rounded to bf16, src/moba_opt/grouped_attention.py:35,52) and 'fp32'.  The route-only fixtures have chunk
+    sizes 40 and 24 (mean = FP32 sum / C, not a shift) and rows on which the two precisions choose differently."""
+    g = load(name)
+    q, k = (bf16_bits_to_torch(g[x]) for x in ("q", "k"))
+    cu = cu_from_lens(g["lens"])
+    _, _, captured, _ = _run(q, k, k, cu, int(g["chunk"]), int(g["topk"]), route_precision=precision)
+    tag = "upstream" if precision == "upstream" else "stable"
+    want = unpack_selected(g, tag) if name in ROUTE_GOLDENS else g[f"selected_{tag}"]
+    if want.shape[0]:
+        assert torch.equal(captured["selected"], torch.from_numpy(want))
+    else:
+        assert not captured
+
+
+def test_default_config_routes_like_the_reference_default():
+    """A caller that passes only chunk_size and topk gets route_precision='upstream', as in the reference."""
+    import moba_opt
+    import moba_opt.grouped_attention as ga
+    g = load("r_upstream_mqa")
+    q, k = (bf16_bits_to_torch(g[x]).cuda() for x in ("q", "k"))
+    cu = torch.tensor(cu_from_lens(g["lens"]), dtype=torch.int32, device="cuda")
+    captured = {}
+    ga.ROUTE_HOOK = lambda **kw: captured.update(kw)
+    try:
+        moba_opt.run_impl("opt_gqa_cuda", q, k, k, cu, int(g["lens"].max()), {"chunk_size": int(g["chunk"]), "topk": int(g["topk"])})
+    finally:
+        ga.ROUTE_HOOK = None
+    ga.check_status()
+    assert torch.equal(captured["selected"], torch.from_numpy(unpack_selected(g, "upstream")))
 
 
 def test_config1_routes_and_forward():
@@ -197,7 +235,9 @@ def test_non_contiguous_inputs_and_sequence_isolation():
 def test_full_size_config2_properties():
     """BASELINE configs[1] at full size (4 x 32768 tokens, 14/2 heads, D=64, chunk 2048, topk 3), checked
     through properties that do not need the whole oracle: (a) sampled query rows of sequence 0 / KV group 0
-    against the FP64 oracle under the kernel's own routes (output and dQ rows); (b) the forward is
+    against the FP64 oracle under the kernel's own routes (output and dQ rows), and dK / dV of one whole 128-key
+    block (the last block of chunk 14 of sequence 0: every query that attends it lies behind it in chunks 14 and
+    15, so an oracle run over those rows gives the block's complete gradient); (b) the forward is
     bit-repeatable; (c) <Q, dQ> = <K, dK> per sequence (the loss depends on Q and K only through Q K^T,
     so the two inner products are the same sum of S * dS); (d) gradients are linear in dO; (e) another
     sequence's tokens do not change a sequence's rows."""
@@ -227,6 +267,12 @@ def test_full_size_config2_properties():
                                    row_block=64)
     _check_close("out rows", torch_to_f64(out.cpu()[rows, :G]), ref["out"])
     _check_close("dq rows", dq[rows, :G].numpy(), ref["dq"][rows])
+    lo, hi = 15 * chunk - 128, 15 * chunk
+    rows = np.arange(lo, L)
+    ref = mo.attention_fixed_route(qs, ks, vs, np.array([0, L]), sel, chunk, d_out=torch_to_f64(do[rows, :G]), rows=rows,
+                                   row_block=256, key_range=(lo, hi))
+    _check_close("dk block", dk[lo:hi, :1].numpy(), ref["dk"])
+    _check_close("dv block", dv[lo:hi, :1].numpy(), ref["dv"])
     # (d) linearity in dO and (e) isolation, on the forward/backward of the same batch
     do2 = torch.randn(total, hq, dim, generator=rng).bfloat16()
     _, _, _, g2 = _run(q, k, v, cu, chunk, topk, d_out=do2)
