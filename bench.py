@@ -13,10 +13,16 @@ One JSON line is printed by rank 0.  `value` times the step with inputs resident
 the same call with pinned host buffers, including the host->device copies of q, k, v, dO and the
 device->host copies of out, dq, dk, dv.  `roofline` is the backward main kernel (the dominant
 kernel) timed with CUDA events recorded around its launch inside the timed region.  `cpu_baseline`
-times the FP64 CPU oracle on a bounded sample of the same workload.
+times the reference's FP64 CPU oracle on a bounded sample of the same workload.
 
---impl reference times the CPU implementation of the path (the oracle port of the reference's FP64
-CPU code; the reference itself is Python and is not present on the GPU box) on all host threads.
+At every N the line also carries `long_prefill`: the long-context configuration (131072 tokens, 32 / 8
+heads, D=128, chunk 4096, topk 12) split by KV-head group over the N ranks (strong scaling: N = 1 runs
+all 8 groups), with the NCCL all-gather of the forward output inside the timed region; and `decode`:
+64 paged-decode requests spread over the ranks by context length.
+
+--impl reference times the CPU implementation of the path on all host threads: the reference's own
+reference/grouped_reference.py (forward + autograd backward, FP64) when oracle/make_ref.py has put it
+under oracle/_ref, else the numpy port of it.
 """
 import argparse
 import json
@@ -45,8 +51,7 @@ WORKLOADS = {
                        unit_variance=True),
 }
 WORKLOAD = WORKLOADS["cfg2"]
-# DRAM bytes of one backward launch on one 32768-token sequence, from the committed ncu summary
-BWD_DRAM_BYTES_PER_SEQUENCE = 581.2e6 + 183.5e6
+TRAFFIC_TABLE = ROOT / "profiles" / "dram_traffic.txt"
 METRIC = "moba_prefill_fwd_bwd_attended_tflops"
 UNIT = "TFLOP/s"
 
@@ -63,6 +68,32 @@ def attended_pairs(lens, chunk, topk):
 
 def step_flops(w):
     return 14.0 * w["dim"] * attended_pairs(w["lens"], w["chunk"], w["topk"]) * w["hq"]
+
+
+def kernel_source_digest(*names):
+    """sha256 (16 hex digits) over the named files of the kernel sources: ties a profiled figure to the code it was
+    taken from."""
+    import hashlib
+    h = hashlib.sha256()
+    for name in names:
+        h.update((ROOT / "moba-merge-cuda_b200" / "csrc" / name).read_bytes())
+    return h.hexdigest()[:16]
+
+
+def measured_traffic(kernel, sources, units):
+    """DRAM bytes per launch (ncu dram__bytes_read.sum + dram__bytes_write.sum) of `kernel` from the table of
+    profiled figures, scaled by `units` (the table is per unit, e.g. per 32768-token sequence), or None when the
+    kernel's sources have changed since the figure was taken."""
+    if not TRAFFIC_TABLE.exists():
+        return None, "no profiled figure"
+    digest = kernel_source_digest(*sources)
+    for line in TRAFFIC_TABLE.read_text().splitlines():
+        f = line.split()
+        if len(f) >= 4 and not line.startswith("#") and f[0] == kernel:
+            if f[1] == digest:
+                return float(f[2]) * units, "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on %s, times %d" % (" ".join(f[3:]), units)
+            return None, "kernel sources changed since the profiled figure was taken"
+    return None, "no profiled figure"
 
 
 def peaks():
@@ -110,29 +141,81 @@ class ClockSampler(threading.Thread):
 
 
 # ----------------------------------------------------------------------------- CPU arm
+CPU_SAMPLE_TOKENS = 6144
+
+
 def cpu_sample(threads):
-    """FP64 oracle (routing + forward + backward) on a bounded sample of the workload: sequence 0,
-    KV group 0 (7 query heads), query slabs of 256 tokens in chunks 1, 8 and 15.  Returns
-    (TFLOP/s on attended FLOPs, description, seconds)."""
+    """The CPU implementation of the path on a bounded sample of the workload: the first 6144 tokens (three chunks, so
+    rows with 0, 1 and 2 routed blocks) of sequence 0 with KV head 0 and its 7 query heads.  Attention is causal, so
+    this prefix is computed exactly as inside the full batch.  Routing (numpy port of the reference's torch routing,
+    which has no CPU entry point of its own) + the reference's reference/grouped_reference.py forward + autograd
+    backward in FP64 when oracle/_ref holds it, else the numpy port of that oracle.
+    Returns (TFLOP/s on attended FLOPs, description, seconds, kind)."""
+    import torch
     from oracle import moba_oracle as mo
+    from oracle.make_ref import load_ref
     w = WORKLOAD
-    L, G, D, C = w["lens"][0], w["hq"] // w["hkv"], w["dim"], w["chunk"]
+    L, G, D, C = min(CPU_SAMPLE_TOKENS, w["lens"][0]), w["hq"] // w["hkv"], w["dim"], w["chunk"]
     rng = np.random.default_rng(0)
     bf = mo.bf16_round
-    q = bf(rng.standard_normal((L, G, D)) * D ** -0.5)
-    k = bf(rng.standard_normal((L, 1, D)) * D ** -0.5)
-    v = bf(rng.standard_normal((L, 1, D)) * D ** -0.5)
-    rows = np.concatenate([np.arange(c * C, c * C + 256) for c in (1, 8, 15)])
-    do = bf(rng.standard_normal((rows.size, G, D)))
+    scale = 1.0 if w.get("unit_variance") else D ** -0.5
+    q = bf(rng.standard_normal((L, G, D)) * scale)
+    k = bf(rng.standard_normal((L, 1, D)) * scale)
+    v = bf(rng.standard_normal((L, 1, D)) * scale)
+    do = bf(rng.standard_normal((L, G, D)))
     cu = np.array([0, L])
+    ref = load_ref()
+    torch.set_num_threads(threads)
     t0 = time.perf_counter()
     r = mo.route_prefill(q, k, cu, C, w["topk"])
-    mo.attention_fixed_route(q, k, v, cu, r["sel"], C, d_out=do, rows=rows, row_block=256)
+    if ref is not None:
+        grouped_reference = ref[0]
+        route = dict(cu_chunk=torch.from_numpy(r["cu_chunk"]), chunk_to_batch=torch.from_numpy(r["chunk_to_batch"]),
+                     filtered_chunk_indices=torch.from_numpy(r["filtered"]), selected=torch.from_numpy(r["selected"]),
+                     cu_seqlens=torch.from_numpy(cu))
+        qt, kt, vt = (torch.from_numpy(x).requires_grad_(True) for x in (q, k, v))
+        out = grouped_reference(qt, kt, vt, torch.from_numpy(cu), route)
+        torch.autograd.grad(out, (qt, kt, vt), grad_outputs=torch.from_numpy(do))
+        kind, what = "reference", "the reference's reference/grouped_reference.py forward + autograd backward (FP64 torch)"
+    else:
+        mo.attention_fixed_route(q, k, v, cu, r["sel"], C, d_out=do)
+        kind, what = "port", "numpy FP64 port of the reference's grouped_reference oracle, forward + backward"
     dt = time.perf_counter() - t0
-    pairs = sum((t % C + 1) + min(w["topk"] - 1, t // C) * C for t in rows.tolist())
-    flops = 14.0 * D * pairs * G
-    return flops / dt / 1e12, ("FP64 numpy oracle: route + fwd + bwd for 768 query rows (256-token slabs in chunks 1, 8, 15) "
-                               "x 7 query heads of sequence 0 / KV group 0"), dt
+    flops = 14.0 * D * attended_pairs((L,), C, w["topk"]) * G
+    desc = ("first %d tokens of sequence 0, KV head 0 with its %d query heads: routing (numpy port) + %s" % (L, G, what))
+    return flops / dt / 1e12, desc, dt, kind
+
+
+def cpu_decode_sample(threads):
+    """CPU baseline of the decode leg: the reference's reference/decode_reference.py (per-(row, head) FP64 loop; the
+    numpy port of it when oracle/_ref is absent) on the first 4 requests of the decode workload, routed by the numpy
+    port of the reference's decode routing.  Returns dict(tokens_per_s, requests, seconds, kind)."""
+    import torch
+    from oracle import moba_oracle as mo
+    from oracle.make_ref import load_ref
+    w = DECODE
+    rng = np.random.default_rng(0)
+    lens = [int(x) for x in rng.integers(w["lo"], w["hi"] + 1, size=w["requests"])][:4]
+    bf = mo.bf16_round
+    keys = [bf(rng.standard_normal((n, w["hkv"], w["dim"]))) for n in lens]
+    values = [bf(rng.standard_normal((n, w["hkv"], w["dim"]))) for n in lens]
+    q = bf(rng.standard_normal((len(lens), w["hq"], w["dim"])))
+    ids, pos = list(range(len(lens))), [n - 1 for n in lens]
+    ref = load_ref()
+    torch.set_num_threads(threads)
+    t0 = time.perf_counter()
+    means = [mo.chunk_means(kk, w["chunk"], rounding=bf) for kk in keys]
+    sel = mo.decode_route(q, means, ids, pos, w["chunk"], w["topk"])["selected"]
+    if ref is not None:
+        ref[1](torch.from_numpy(q), [torch.from_numpy(x) for x in keys], [torch.from_numpy(x) for x in values], ids, pos,
+               chunk_size=w["chunk"], selected_blocks=torch.from_numpy(sel))
+        kind = "reference"
+    else:
+        mo.decode_attend(q, keys, values, ids, pos, w["chunk"], sel)
+        kind = "port"
+    dt = time.perf_counter() - t0
+    return dict(tokens_per_s=len(lens) / dt, requests=len(lens), seconds=dt, kind=kind, cores=threads,
+                sample="first 4 requests: chunk means + routing (numpy port) + decode_reference (FP64)")
 
 
 def run_reference(args):
@@ -142,20 +225,21 @@ def run_reference(args):
     threads = os.cpu_count() or 1
     vals = []
     for i in range(args.warmup + args.steps):
-        val, sample, dt = cpu_sample(threads)
+        val, sample, dt, kind = cpu_sample(threads)
         if i >= args.warmup:
             vals.append((val, dt))
-        if sum(d for _, d in vals) > 150:  # keep the whole run within a few minutes
+        if sum(d for _, d in vals) > 100 or (i + 1) * dt > 160:  # keep the whole run within a few minutes
+            if not vals:
+                vals.append((val, dt))
             break
     value = float(np.mean([v for v, _ in vals]))
     ms = float(np.mean([d for _, d in vals])) * 1e3
     line = dict(impl="reference", metric=METRIC, value=value, unit=UNIT, n_gpus=args.gpus, steps=len(vals),
                 warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64",
                 data="synthetic", config=dict(workload=WORKLOAD["name"], sample=sample),
-                cpu_baseline=dict(value=value, unit=UNIT, cores=threads, kind="port", sample=sample),
+                cpu_baseline=dict(value=value, unit=UNIT, cores=threads, kind=kind, sample=sample),
                 e2e=dict(value=value, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
     print(json.dumps(line))
-
 
 
 # ----------------------------------------------------------------------------- decode leg
@@ -164,17 +248,23 @@ DECODE = dict(name="paged_decode_64req_ctx4k-64k_page48_c2048_k4_h12kv2_d128", r
 
 
 def run_decode(dev, rank, world, steps, lib):
-    """BASELINE configs[3]: 64 requests (64/world per rank, request i on rank i mod world), context
-    lengths uniform in [4096, 65536] from seed 0, page 48, chunk 2048, topk 4, 12/2 heads, D=128, K/V ~
-    N(0,1) in randomly permuted physical pages; one new token per request per step under
-    prepare_decode + CUDA graph.  Returns tokens/s, algorithmic HBM bytes per step (union of attended
-    tokens per (request, kv head), K and V, from the actual selected tables) and timings."""
+    """BASELINE configs[3]: 64 requests spread over the ranks (independent shards, each rank its own cache and
+    captured step), context lengths uniform in [4096, 65536] from seed 0, page 48, chunk 2048, topk 4, 12/2 heads,
+    D=128, K/V ~ N(0,1) in randomly permuted physical pages; one new token per request per step under
+    prepare_decode + CUDA graph.  Requests go to ranks by the bytes a step is expected to read for them
+    (sharding.balance_requests over sharding.expected_decode_tokens), not round-robin: the step time of the job is
+    the slowest rank's.  Returns tokens/s, algorithmic HBM bytes per step (union of attended tokens per (request,
+    kv head), K and V, from the actual selected tables) and timings, among them the step with the all-gather of
+    the step's outputs to every rank (sharding.gather_assigned) included."""
     import torch
-    from moba_opt import PagedKVCache
+    import torch.distributed as dist
+    from moba_opt import PagedKVCache, sharding
     w = DECODE
     rng = np.random.default_rng(0)
-    all_lens = rng.integers(w["lo"], w["hi"] + 1, size=w["requests"])
-    lens = [int(x) for i, x in enumerate(all_lens) if i % world == rank]
+    all_lens = [int(x) for x in rng.integers(w["lo"], w["hi"] + 1, size=w["requests"])]
+    costs = [sharding.expected_decode_tokens(n, w["chunk"], w["topk"], w["hq"] // w["hkv"]) for n in all_lens]
+    assignment = sharding.balance_requests(costs, world)
+    lens = [all_lens[i] for i in assignment[rank]]
     b = len(lens)
     max_len = w["hi"] + steps + 64
     pages = sum(-(-(n + steps + 64) // w["page"]) for n in lens)
@@ -237,9 +327,141 @@ def run_decode(dev, rank, world, steps, lib):
         torch.cuda.synchronize()
         att.append(a0.elapsed_time(a1))
     lib.moba_profile_events(4, None, None)
+    # the same steps with every rank receiving all outputs, in request order, after each step
+    gather_ms = None
+    if world > 1:
+        n = min(steps, 128)
+        for _ in range(3):
+            sharding.gather_assigned(plan.step(qs[0], ks[0], vs[0], use_graph=True).output, assignment)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(n):
+            sharding.gather_assigned(plan.step(qs[i % 8], ks[i % 8], vs[i % 8], use_graph=True).output, assignment)
+        e1.record()
+        torch.cuda.synchronize()
+        gather_ms = e0.elapsed_time(e1) / n
     plan.close()
     return dict(ms_per_step=ms, requests=b, bytes_per_step=float(np.mean(sampled_bytes)), attend_ms=float(np.median(att)),
-                context_tokens=int(sum(lens)))
+                context_tokens=int(sum(lens)), gather_ms_per_step=gather_ms)
+
+
+# ----------------------------------------------------------------------------- long-prefill leg
+LONG_PREFILL = dict(name="gqa_prefill_1x131072_h32kv8_d128_c4096_k12_by_kv_group", tokens=131072, hq=32, hkv=8, dim=128,
+                    chunk=4096, topk=12)
+
+
+def run_long_prefill(dev, rank, world, steps, warmup, with_host_leg=True):
+    """BASELINE configs[2]: one sequence of 131072 tokens, 32 query / 8 KV heads, D=128, chunk 4096, topk 12, bf16
+    Q/K/V ~ N(0,1), split by KV-head group: rank r owns 8/world KV heads and their query heads (world = 1 runs all
+    eight).  One step = routing + forward + backward on the rank's heads, and the all-gather of the forward output
+    [T, Hq/world, D] of every rank into [T, Hq, D] on every rank (NCCL over NVLink), issued on a second stream as
+    soon as the forward is done so that it runs beside the backward; the step ends when both are done.  Gradients
+    stay with the heads they belong to (dK, dV of a KV head live wholly on its rank), so nothing else is exchanged.
+    Timed on the device, maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    import moba_opt
+    import moba_opt.grouped_attention as ga
+    from moba_opt import sharding
+    w = LONG_PREFILL
+    if w["hkv"] % world:
+        return None
+    T, D, G = w["tokens"], w["dim"], w["hq"] // w["hkv"]
+    qs, ks = sharding.kv_group_slices(w["hq"], w["hkv"], world, rank)
+    groups = range(ks.start, ks.stop)
+    parts = {"q": [], "k": [], "v": [], "do": []}
+    for g in groups:                              # data of a KV group does not depend on how many ranks there are
+        gen = torch.Generator(device=dev).manual_seed(500 + g)
+        for name, h in (("q", G), ("k", 1), ("v", 1), ("do", G)):
+            parts[name].append(torch.randn(T, h, D, device=dev, generator=gen).bfloat16())
+    res = {n: torch.cat(p, dim=1).contiguous() for n, p in parts.items()}
+    del parts
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    cfg = {"chunk_size": w["chunk"], "topk": w["topk"], "route_precision": "fp32", "stable_routes": True}
+    hq_local = G * len(groups)
+    gathered = torch.empty(world, T, hq_local, D, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    full = torch.empty(T, w["hq"], D, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    side = torch.cuda.Stream(dev)
+    main = torch.cuda.current_stream(dev)
+
+    def gather(out):
+        """[T, Hq/world, D] of every rank -> [T, Hq, D] in head order on this rank."""
+        dist.all_gather_into_tensor(gathered, out)
+        full.view(T, world, hq_local, D).copy_(gathered.permute(1, 0, 2, 3))
+
+    def step(t, overlap=True):
+        q, k, v = (t[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
+        out = moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, T, cfg)
+        if world > 1:
+            det = out.detach()
+            if overlap:
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    det.record_stream(side)
+                    gather(det)
+            else:
+                gather(det)
+        grads = torch.autograd.grad(out, (q, k, v), grad_outputs=t["do"])
+        if world > 1 and overlap:
+            main.wait_stream(side)
+        return (out.detach() if world == 1 else full,) + grads
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for _ in range(max(1, warmup)):
+        step(res)
+    ms = timed(lambda: step(res), steps)
+    ga.check_status()
+    ms_serial = gather_ms = None
+    if world > 1:
+        ms_serial = timed(lambda: step(res, overlap=False), steps)      # gather between forward and backward
+        probe = res["q"]                                                # same shape and dtype as the forward output
+        gather(probe)
+        gather_ms = timed(lambda: gather(probe), 5)                    # the collective (and the reorder) alone
+    flops = 14.0 * D * attended_pairs((T,), w["chunk"], w["topk"]) * w["hq"]
+    out = dict(workload=w["name"], scaling="strong", kv_groups_per_rank=len(groups), steps=steps, ms_per_step=ms,
+               tflops=flops / (ms * 1e-3) / 1e12, flops_per_step=flops,
+               gather=dict(collective="nccl all_gather_into_tensor of the forward output, on a second stream beside the backward",
+                           bytes_received_per_rank=(world - 1) * T * hq_local * D * 2 if world > 1 else 0,
+                           ms_alone=gather_ms, ms_per_step_with_gather_in_line=ms_serial))
+    if with_host_leg:
+        # the same step fed from pinned host memory: this rank's heads only go up (q, k, v, dO) and come back (out of
+        # its heads, dq, dk, dv); the gathered output stays on the device
+        host = {n: t.cpu().pin_memory() for n, t in res.items()}
+        back = {n: torch.empty_like(host[src]) .pin_memory() for n, src in (("out", "q"), ("dq", "q"), ("dk", "k"), ("dv", "k"))}
+        dev_in = {n: torch.empty_like(t) for n, t in res.items()}
+
+        def host_step():
+            for n, t in host.items():
+                dev_in[n].copy_(t, non_blocking=True)
+            outs = step(dev_in)
+            local = outs[0] if world == 1 else outs[0][:, qs]
+            for dst, src in zip(("out", "dq", "dk", "dv"), (local,) + outs[1:]):
+                back[dst].copy_(src, non_blocking=True)
+
+        host_step()
+        ms_host = timed(host_step, max(2, steps // 2))
+        out["e2e"] = dict(ms_per_step=ms_host, tflops=flops / (ms_host * 1e-3) / 1e12,
+                          h2d_bytes_per_step_per_rank=sum(t.numel() * 2 for t in host.values()),
+                          d2h_bytes_per_step_per_rank=sum(t.numel() * 2 for t in back.values()))
+    return out
 
 # ----------------------------------------------------------------------------- full-model leg
 FULL_MODEL = dict(name="qwen2_0.5b_random_prompt16384_greedy256_moba12of24_c512_k4", prompt=16384, steps=256, chunk=512, topk=4,
@@ -529,12 +751,22 @@ def run_ours(args):
     if not args.kernels_only and not args.no_decode:
         dec = run_decode(dev, rank, world, args.decode_steps, lib)
         ga.check_status()
+        dec["per_rank"] = [dict(requests=dec["requests"], context_tokens=dec["context_tokens"], ms_per_step=dec["ms_per_step"])]
         if world > 1:
-            t = torch.tensor([dec["ms_per_step"], dec["attend_ms"]], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            tot = torch.tensor([dec["bytes_per_step"], float(dec["requests"])], device=dev)
-            dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-            dec.update(ms_per_step=float(t[0]), attend_ms=float(t[1]), bytes_per_step=float(tot[0]), requests=int(tot[1]))
+            mine = torch.tensor([dec["ms_per_step"], dec["attend_ms"], dec["gather_ms_per_step"], dec["bytes_per_step"],
+                                 float(dec["requests"]), float(dec["context_tokens"])], device=dev, dtype=torch.float64)
+            every = torch.empty(world, mine.numel(), device=dev, dtype=torch.float64)
+            dist.all_gather_into_tensor(every, mine)
+            every = every.cpu().numpy()
+            dec.update(ms_per_step=float(every[:, 0].max()), attend_ms=float(every[:, 1].max()),
+                       gather_ms_per_step=float(every[:, 2].max()), bytes_per_step=float(every[:, 3].sum()),
+                       requests=int(every[:, 4].sum()),
+                       per_rank=[dict(requests=int(r[4]), context_tokens=int(r[5]), ms_per_step=float(r[0])) for r in every])
+
+    long_leg = None
+    if not args.kernels_only and not args.no_long_prefill:
+        long_leg = run_long_prefill(dev, rank, world, args.long_steps, 2)
+        ga.check_status()
 
     flops = step_flops(w)
     value = world * flops / (ms_total / args.steps * 1e-3) / 1e12
@@ -545,13 +777,20 @@ def run_ours(args):
         pk = peaks()
         bwd_flops = flops * 10.0 / 14.0
         achieved = bwd_flops / (bwd_ms * 1e-3) / 1e12
-        cpu_val, cpu_desc, cpu_dt = (cpu_sample(os.cpu_count() or 1) if world == 1 and not args.kernels_only
-                                     else (None, None, None))
+        cpu_val, cpu_desc, cpu_dt, cpu_kind = (cpu_sample(os.cpu_count() or 1) if world == 1 and not args.kernels_only
+                                               else (None, None, None, None))
+        bwd_sources = (("prefill_attn_bwd_ws.cu", "prefill_bwd.cuh", "prefill_common.cuh", "sm100.cuh") if D <= 64 else
+                       ("prefill_attn_bwd_ws128.cu", "prefill_bwd.cuh", "prefill_common.cuh", "sm100.cuh"))
+        bwd_kernel = "attn_bwd_ws_kernel" if D <= 64 else "attn_bwd_ws128_kernel"
+        traffic, traffic_source = (measured_traffic(bwd_kernel, bwd_sources, len(w["lens"])) if w["lens"][0] == 32768 and D == 64
+                                   else (None, "no profiled figure for this workload"))
         line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
                     ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="bf16", data="synthetic",
                     config=dict(workload=w["name"], sequences=len(w["lens"]), seq_len=w["lens"][0], hq=Hq, hkv=Hkv,
-                                head_dim=D, chunk=w["chunk"], topk=w["topk"], per_rank="one full batch per GPU, no collective",
+                                head_dim=D, chunk=w["chunk"], topk=w["topk"],
+                                per_rank="one full batch per GPU, no collective (the split by KV-head group with its "
+                                         "output gather is the long_prefill leg, the split by request the decode leg)",
                                 l2="inputs (q, k, v, dO, out: %.2f GB per step) exceed the 126 MB L2, no flush needed" % (T * (3 * Hq + 2 * Hkv) * D * 2 / 1e9)),
                     clocks=clocks,
                     e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
@@ -559,11 +798,9 @@ def run_ours(args):
                              mode="host copies on their own streams, double-buffered across steps", numa_node=numa_node,
                              numa_h2d_gbs=numa_rates),
                     gpu_launches=13 * args.steps,  # route 5, pack 2, forward 2, backward 4 (memsets not counted)
-                    roofline=dict(bound="tensor", kernel="attn_bwd_ws_kernel" if D <= 64 else "attn_bwd_ws128_kernel", achieved=achieved, peak=pk["tflops"],
+                    roofline=dict(bound="tensor", kernel=bwd_kernel, achieved=achieved, peak=pk["tflops"],
                                   unit="TFLOP/s", frac=achieved / pk["tflops"], peak_source=pk["source"] + " (sustained bf16)",
-                                  traffic=BWD_DRAM_BYTES_PER_SEQUENCE * len(w["lens"]) if w["name"].startswith("gqa_prefill_") and w["lens"][0] == 32768 else None,
-                                  traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on one 32768-token "
-                                                 "sequence (profiles/attn_bwd_ws_kernel_d64_1x32768.md), times the number of sequences",
+                                  traffic=traffic, traffic_source=traffic_source,
                                   ms_per_launch=bwd_ms, flops_per_launch=bwd_flops))
         if dec is not None:
             sec = dec["ms_per_step"] * 1e-3
@@ -573,14 +810,22 @@ def run_ours(args):
                                   frac_of_hbm_peak=dec["bytes_per_step"] / sec / 1e9 / pk["hbm"] / world, hbm_peak=pk["hbm"],
                                   attend_kernel_ms=dec["attend_ms"],
                                   attend_kernel_gbs=dec["bytes_per_step"] / (dec["attend_ms"] * 1e-3) / 1e9,
-                                  mode="prepare_decode + CUDA graph, one token per request per step")
+                                  mode="prepare_decode + CUDA graph, one token per request per step",
+                                  placement="requests spread over the ranks by expected bytes per step, largest first",
+                                  per_rank=dec["per_rank"],
+                                  ms_per_step_with_output_gather=dec["gather_ms_per_step"])
+            if world == 1 and not args.kernels_only:
+                line["decode"]["cpu_baseline"] = cpu_decode_sample(os.cpu_count() or 1)
+        if long_leg is not None:
+            long_leg["frac_of_tensor_peak"] = long_leg["tflops"] / world / pk["tflops"]
+            line["long_prefill"] = long_leg
         if world == 1 and not args.kernels_only and not args.no_full_model:
             try:
                 line["full_model"] = run_full_model(dev)
             except Exception as exc:  # the optional leg must not take the line with it
                 line["full_model"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
         if cpu_val is not None:
-            line["cpu_baseline"] = dict(value=cpu_val, unit=UNIT, cores=os.cpu_count() or 1, kind="port", sample=cpu_desc,
+            line["cpu_baseline"] = dict(value=cpu_val, unit=UNIT, cores=os.cpu_count() or 1, kind=cpu_kind, sample=cpu_desc,
                                         seconds=cpu_dt)
         print(json.dumps(line))
     if world > 1:
@@ -596,6 +841,8 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-decode", action="store_true", help="skip the paged-decode leg")
     ap.add_argument("--no-full-model", action="store_true", help="skip the full-model decode leg")
+    ap.add_argument("--no-long-prefill", action="store_true", help="skip the long-prefill leg (split by KV-head group)")
+    ap.add_argument("--long-steps", type=int, default=4, help="timed steps of the long-prefill leg")
     ap.add_argument("--only-decode", action="store_true", help="run only the paged-decode leg (profiler runs)")
     ap.add_argument("--only-full-model", type=int, default=0, metavar="N",
                     help="run only N launch-by-launch decode steps of the full-model session (profiler runs)")

@@ -2,7 +2,10 @@
  *
  * Every entry point takes raw device pointers, explicit sizes and a CUDA stream, allocates
  * nothing, never synchronises the host, and returns an int status (MOBA_OK or a MOBA_ERR_*).
- * The caller owns every buffer, so a sequence of calls can be captured in a CUDA graph.
+ * The caller owns every buffer, so a sequence of calls can be captured in a CUDA graph, and the
+ * entry points of this header keep no mutable state between calls (moba_prefill_route_static, which
+ * says so, is the one exception).  Profiling and self-test hooks, which do keep process-wide
+ * state, are declared apart in moba_b200_debug.h.
  */
 #ifndef MOBA_B200_H_
 #define MOBA_B200_H_
@@ -86,7 +89,9 @@ int moba_prefill_route(const moba_prefill_desc* d, const void* q, const void* k,
  * the process exits. Same inputs, outputs and results as moba_prefill_route; it allocates nothing.
  *   - Returns MOBA_ERR_WORKSPACE when moba_prefill_route_scratch_bytes(d) exceeds the array.
  *   - The first call on each device looks up the array's device address (with that device current);
- *     make that first call before starting any stream capture.
+ *     make that first call before starting any stream capture.  The address is remembered per device
+ *     ordinal for the life of the process: a process that destroys its CUDA context and creates a new
+ *     one must not call this entry point again afterwards (a new context may place the array elsewhere).
  *   - All calls on a device share the one array: two calls whose kernels may overlap on the GPU
  *     (different streams, no ordering between them) race. Order them, or use moba_prefill_route. */
 #define MOBA_ROUTE_STATIC_SCRATCH_BYTES (8u << 20)
@@ -239,14 +244,6 @@ int moba_argmax_bf16(const void* logits, int n, void* workspace, size_t workspac
  * (the reference's session calls the Hugging Face modules: examples/full_qwen2.py:76-90, 160-190). */
 int moba_decode_linear(const void* x, const void* h_in, const void* delta, const void* norm_weight, float eps, void* h_out,
                        const void* weight, const void* bias, int k, int n, int epilogue, void* y, void* stream);
-
-/* Profiling aid (no reference counterpart): record the given CUDA events right before and after one
- * kernel on its launch stream. which: 1 forward remote pass, 2 forward self pass, 3 backward main
- * kernel, 4 decode attention. Null events switch it off. Process-wide, not thread-safe. */
-int moba_profile_events(int which, void* start, void* stop);
-
-/* Device self-test of the tcgen05 tile primitives (see csrc/selftest.cu). No reference counterpart. */
-int moba_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int k, unsigned* status, void* stream);
 
 #ifdef __cplusplus
 }

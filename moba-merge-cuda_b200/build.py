@@ -53,7 +53,7 @@ def build(force=False, verbose=False):
         if verbose or "warning" in out:
             sys.stderr.write(out)
         objs.append(str(obj))
-    cmd = [NVCC, "-shared", "-o", str(OUT), *objs, "-lcudart"]
+    cmd = [NVCC, "-shared", "-Wno-deprecated-gpu-targets", "-o", str(OUT), *objs, "-lcudart"]
     subprocess.run(cmd, check=True)
     STAMP.write_text(digest)
     return OUT

@@ -15,6 +15,7 @@ extern "C" const char* moba_status_string(int status) {
 // Profiling aid: events a caller registers are recorded on the launch stream immediately before and
 // after the named kernel, so its duration can be read with cudaEventElapsedTime without a profiler.
 // Process-wide and not thread-safe; pass null events to switch it off.
+#include "moba_b200_debug.h"
 #include "prefill_common.cuh"
 namespace moba {
 static cudaEvent_t g_prof[kProfSlots][2];

@@ -515,18 +515,6 @@ struct AttendArgs {
   float scale_log2;
 };
 
-#ifdef MOBA_DEC_TRACE
-// Phase stamps for tuning (thread 0 of every CTA; [cta][16] entries: even = SM clock, slot 15 = global timer at entry).
-__device__ long long* g_dec_trace = nullptr;
-__device__ __forceinline__ long long dec_gtime() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define DEC_TRACE_INIT long long* const trace_buf = g_dec_trace; const int trace_cta = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x; \
-  if (trace_buf && threadIdx.x == 0 && trace_cta < 256) trace_buf[trace_cta * 16 + 15] = dec_gtime()
-#define DEC_TRACE(i) do { if (trace_buf && threadIdx.x == 0 && trace_cta < 256) trace_buf[trace_cta * 16 + (i)] = clock64(); } while (0)
-#else
-#define DEC_TRACE_INIT do {} while (0)
-#define DEC_TRACE(i) do {} while (0)
-#endif
-
 constexpr int kHeadBlock = 16;    // query heads of a group processed together (MMA M dimension)
 constexpr int kStageTokens = 64;  // tokens per pipeline stage: 16 per warp
 // Two 32 KB stages (D <= 128) and 160 registers let three CTAs share an SM; measured faster than three
@@ -668,8 +656,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
   extern __shared__ __align__(128) uint8_t s_pipe[];  // NS stages per team; reused for the cross-warp reduction
   __shared__ int s_last, s_slot[kHeadBlock];
   __shared__ long long s_rowbase_all[TEAMS][NS][kStageTokens];
-  DEC_TRACE_INIT;
-  DEC_TRACE(0);
   dependents_may_start();   // e.g. the output projection, whose weight loads need nothing from here
   wait_for_predecessor();   // routes, positions, the appended row
   const CacheView& cv = a.cv;
@@ -706,7 +692,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
   const int first_tile = team * ((all_tiles + TEAMS - 1) / TEAMS);           // this team's stages: [first_tile, first_tile + ntiles)
   const int ntiles = max(0, min(all_tiles - first_tile, (all_tiles + TEAMS - 1) / TEAMS));
   const int tt_begin = t_begin + first_tile * kStageTokens;                  // first token of the team
-  DEC_TRACE(1);
 
   for (int hb = 0; hb < G; hb += kHeadBlock) {
     const unsigned active = (mask >> hb) & 0xFFFFu;
@@ -757,7 +742,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
       for (int s = 0; s < NS; ++s) s_rowbase[s][ltid] = first_base[s];
     }
     team_sync();
-    DEC_TRACE(2);
 #pragma unroll
     for (int s = 0; s < NS - 1; ++s) {
       if (s < ntiles) attend_load_stage<DP>(cv, t_pipe + s * STAGE_BYTES, s_rowbase[s], ltid);
@@ -766,7 +750,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
     for (int i = 0; i < ntiles; ++i) {
       cp_async_wait<NS - 2>();
       team_sync();  // tile i has landed; every warp of the team finished tile i-1, whose buffer is refilled next
-      if (i == 0) DEC_TRACE(3);
       const int nx = i + NS - 1;
       if (nx < ntiles) attend_load_stage<DP>(cv, t_pipe + (nx % NS) * STAGE_BYTES, s_rowbase[nx % NS], ltid);
       cp_async_commit();
@@ -838,7 +821,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
     }
     if (look_bad) atomicOr(a.status, kErrBadIndex);
     // ---- combine the warps, then write one partial per active head
-    DEC_TRACE(4);
     cp_async_wait<0>();
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
@@ -897,7 +879,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
   }
 
   // ---- ticket: the last CTA of this (query, kv head) merges every partial of the group's heads
-  DEC_TRACE(5);
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -905,7 +886,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
     s_last = ticket == expected - 1;
   }
   __syncthreads();
-  DEC_TRACE(6);
   if (!s_last) return;
   __threadfence();
   // The partials of a head are (slot, part) pairs, j = slot * parts + part, and lie one after the other.  All
@@ -982,7 +962,6 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
     }
   }
   __syncthreads();
-  DEC_TRACE(7);
 #pragma unroll 1
   for (int item = tid; item < G * d4n; item += NT) {
     const int hl = item / d4n, d = (item - hl * d4n) * 4;
@@ -1003,19 +982,12 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
     *reinterpret_cast<uint2*>(a.out + ((long long)row * a.Hq + h) * D + d) = pk;
   }
   __syncthreads();
-  DEC_TRACE(8);
   if (tid == 0) a.counters[rowg] = 0;  // ready for the next launch (graph replay included)
 }
 
 }  // namespace moba
 
 using namespace moba;
-
-#ifdef MOBA_DEC_TRACE
-extern "C" int moba_debug_set_dec_trace(long long* buf) {
-  return cudaMemcpyToSymbol(moba::g_dec_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
-}
-#endif
 
 static int decode_sm_count() {
   static int cached[64] = {0};

@@ -20,19 +20,6 @@
 
 namespace moba {
 
-#ifdef MOBA_BWD_TRACE
-// Debug build only: per-tile clock stamps of one CTA, for finding where a tile's time goes.
-__device__ long long* g_bwd_trace = nullptr;
-#define WS_TRACE_INIT long long* const trace_buf = (blockIdx.x == 40 && blockIdx.y == 0) ? g_bwd_trace : nullptr
-#define WS_TRACE(role, it, slot)                                                                           \
-  do {                                                                                                     \
-    if (trace_buf && (it) < 256) trace_buf[((it) * 4 + (role)) * 8 + (slot)] = clock64();                  \
-  } while (0)
-#else
-#define WS_TRACE_INIT do {} while (0)
-#define WS_TRACE(role, it, slot) do {} while (0)
-#endif
-
 // ---------------------------------------------------------------------------------------------
 // Backward packing pass: dO rows, LSE (log2 domain) and delta / sqrt(D) of every query tile, in the
 // tile order of the forward's Q pack (row ids come from its rowpack), as contiguous swizzled images.
@@ -161,7 +148,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   tc_fence_after_sync();
   const uint32_t tmem = cb.tmem_slot;
   bool alive = true;
-  WS_TRACE_INIT;
 
   if (warp >= 12) {
     // ================================================================== dQ drain (warps 12-15)
@@ -187,7 +173,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       tmem_ld_wait();
       tc_fence_before_sync();
       warp_arrive(&cb.dq_free);
-#ifndef MOBA_BWD_NODRAIN
       const int c4 = lane & 7;
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
@@ -210,7 +195,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         }
         __syncwarp();
       }
-#endif
     }
   } else if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
@@ -345,10 +329,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       const bool diag = it >= n_remote && ((it - n_remote) % n_self) == 0;
       const int qmin = r >= nkeys ? kTile : (diag ? r : 0);
       const bool unmasked = __all_sync(0xFFFFFFFFu, qmin <= half * 64);
-      if (tid == 0) WS_TRACE(0, it, 0);
       alive = warp_wait(&cb.qdo_full[ms], (it / kWsRing) & 1, a.status, alive);  // the tile's metadata is in the slot
       alive = warp_wait(&cb.st_full, it & 1, a.status, alive);
-      if (tid == 0) WS_TRACE(0, it, 1);
       tc_fence_after_sync();
       float p[64];
       {
@@ -358,7 +340,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         tmem_ld_wait();
         tc_fence_before_sync();
         warp_arrive(&cb.st_free);  // S^T of the next tile may be formed
-        if (tid == 0) WS_TRACE(0, it, 2);
         const float4* lse4 = reinterpret_cast<const float4*>(&cb.lse2[ms][half * 64]);
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
 #pragma unroll
@@ -385,10 +366,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       tmem_st_wait();
       tc_fence_before_sync();
       warp_arrive(&cb.p_ready);
-      if (tid == 0) WS_TRACE(0, it, 3);
 
       alive = warp_wait(&cb.dpt_full, it & 1, a.status, alive);
-      if (tid == 0) WS_TRACE(0, it, 4);
       tc_fence_after_sync();
       const float4* del4 = reinterpret_cast<const float4*>(&cb.delta_s[ms][half * 64]);
 #pragma unroll
@@ -408,7 +387,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
           pk[pc * 16 + (i >> 1) + 1] = bwd_pack_bf16(d1.x, d1.y);
         }
       }
-      if (tid == 0) WS_TRACE(0, it, 5);
       // dS^T: over the first 32 of this thread's own dP^T columns for the dK product, and as a tile row
       // in shared memory for the dQ product (whose previous run must be over)
       tmem_st32(tlane + COL_DPT + half * 64, pk);
@@ -420,7 +398,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       fence_async_smem();
       tc_fence_before_sync();
       warp_arrive(&cb.ds_ready);
-      if (tid == 0) WS_TRACE(0, it, 6);
     }
     if (n_iter > 0) {
       alive = warp_wait(&cb.dq_done, (n_iter - 1) & 1, a.status, alive);
@@ -460,9 +437,3 @@ cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st) {
 }
 
 }  // namespace moba
-
-#ifdef MOBA_BWD_TRACE
-extern "C" int moba_debug_set_bwd_trace(long long* buf) {
-  return cudaMemcpyToSymbol(moba::g_bwd_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
-}
-#endif

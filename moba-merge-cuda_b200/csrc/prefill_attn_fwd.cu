@@ -24,19 +24,6 @@
 
 namespace moba {
 
-#ifdef MOBA_FWD_TRACE
-// Debug build only: per-tile clock stamps of one CTA, for finding where a tile's time goes.
-__device__ long long* g_fwd_trace = nullptr;
-#define FWD_TRACE_INIT long long* const trace_buf = blockIdx.x == 40 ? g_fwd_trace : nullptr
-#define FWD_TRACE(role, it, slot)                                                     \
-  do {                                                                                \
-    if (trace_buf && (it) < 256) trace_buf[((it) * 4 + (role)) * 8 + (slot)] = clock64(); \
-  } while (0)
-#else
-#define FWD_TRACE_INIT do {} while (0)
-#define FWD_TRACE(role, it, slot) do {} while (0)
-#endif
-
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -217,7 +204,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
   tc_fence_after_sync();
   const uint32_t tmem = cb.tmem_slot;
   bool alive = true;
-  FWD_TRACE_INIT;
 
   // The softmax warpgroups keep a whole row of S in registers; the third warpgroup gives them its share.
   if (warp >= 8) {
@@ -390,10 +376,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         int klimit = key_end - k0;                     // keys of the tile that exist
         if (SELF) klimit = min(klimit, tok - k0 + 1);  // causal inside the own chunk
         const bool need_mask = __any_sync(0xFFFFFFFFu, klimit < kTile);
-        if (row == 0) FWD_TRACE(l, tc, 0);
         if (alive) alive = mbar_wait(&cb.s_full[l], tc & 1, a.status);
         tc_fence_after_sync();
-        if (row == 0) FWD_TRACE(l, tc, 1);
         uint32_t s0[32], s1[32], s2[32], s3[32];
         tmem_ld32(tS, s0);
         tmem_ld32(tS + 32, s1);
@@ -405,7 +389,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           __syncwarp();
           if (lane_id == 0) mbar_arrive(&cb.s_free[l]);
         }
-        if (row == 0) FWD_TRACE(l, tc, 2);
         if (need_mask) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -451,7 +434,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           }
           l_run *= alpha;
         }
-        if (row == 0) FWD_TRACE(l, tc, 3);
         // two elements per instruction where the hardware has a packed form (scale-and-shift, row sum)
         float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), neg2 = make_float2(-m_used, -m_used);
@@ -482,12 +464,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         }
         tmem_st32(tP + 32, pk);
         l_run += (sum0.x + sum0.y) + (sum1.x + sum1.y);
-        if (row == 0) FWD_TRACE(l, tc, 4);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane_id == 0) mbar_arrive(&cb.p_ready[l]);
-        if (row == 0) FWD_TRACE(l, tc, 5);
       }
 
       // ---- epilogue: O of the row leaves tensor memory, then the lane's accumulator is free again
@@ -596,12 +576,6 @@ static cudaError_t launch_fwd(const FwdArgs& a, long long items, cudaStream_t st
 }
 
 }  // namespace moba
-
-#ifdef MOBA_FWD_TRACE
-extern "C" int moba_debug_set_fwd_trace(long long* buf) {
-  return cudaMemcpyToSymbol(moba::g_fwd_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : 2;
-}
-#endif
 
 using namespace moba;
 

@@ -6,6 +6,7 @@
 //   mode 2:  D[128,N]  = A[K,128]^T * B[K,N]     (both operands MN-major;  dV = P^T dO, dK = dS^T Q)
 //   mode 3:  D[128,N]  = A[128,K] * B[K,N]       (A in tensor memory as packed bf16 pairs, B MN-major; O = P V)
 #include "moba_b200.h"
+#include "moba_b200_debug.h"
 #include "sm100.cuh"
 
 namespace moba {
@@ -96,7 +97,29 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(int mode, const __nv
   if (warp == 0) tmem_free(tmem, ncols);
 }
 
+// The way every kernel here gives up on a barrier: one thread waits, with the given limit, for a phase of an
+// mbarrier that nothing will ever complete.  The wait must run out, set the time-out bit of the status word and let
+// the kernel return normally, leaving the context usable.
+__global__ void wait_selftest_kernel(long long limit_clocks, unsigned* status, int* returned) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait_for(&bar, 0, status, limit_clocks);
+  __syncthreads();
+  if (threadIdx.x == 0 && returned) *returned = ok ? 1 : 2;
+}
+
 }  // namespace moba
+
+extern "C" int moba_selftest_wait(long long limit_clocks, unsigned* status, int* returned, void* stream) {
+  if (limit_clocks < 1 || limit_clocks > moba::kWaitLimitClocks || !status) return MOBA_ERR_INVALID;
+  moba::wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_clocks, status, returned);
+  return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
+}
 
 extern "C" int moba_selftest_umma(int mode, const void* a, const void* b, float* d, int n, int k, unsigned* status,
                                   void* stream) {

@@ -55,18 +55,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false (and records kErrBarrierTimeout) after about a second of SM
-// clocks instead of spinning forever, so a protocol bug cannot hang the GPU.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned* status) {
+// Bounded wait: returns false (and records kErrBarrierTimeout) after `limit_clocks` SM clocks instead
+// of spinning forever, so a protocol bug cannot hang the GPU.  Kernels use mbar_wait (about a second).
+constexpr long long kWaitLimitClocks = 2000000000ll;
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, unsigned* status, long long limit_clocks) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
     for (int it = 0; it < 64; ++it)
       if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > 2000000000ll) break;
+    if (clock64() - t0 > limit_clocks) break;
   }
   if (status) atomicOr(status, kErrBarrierTimeout);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned* status) {
+  return mbar_wait_for(bar, parity, status, kWaitLimitClocks);
 }
 
 // ----------------------------------------------------------------------------- fences

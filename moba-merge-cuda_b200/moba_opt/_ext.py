@@ -30,6 +30,7 @@ def lib():
         L.moba_status_string.restype = ctypes.c_char_p
         L.moba_status_string.argtypes = [ctypes.c_int]
         L.moba_selftest_umma.argtypes = [ctypes.c_int, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int, c_vp, c_vp]
+        L.moba_selftest_wait.argtypes = [ctypes.c_longlong, c_vp, c_vp, c_vp]
         for name in ("moba_prefill_route_state_bytes", "moba_prefill_route_scratch_bytes",
                      "moba_prefill_fwd_scratch_bytes", "moba_prefill_bwd_scratch_bytes"):
             fn = getattr(L, name)

@@ -6,7 +6,8 @@ per group), and decode requests never interact at all.  So each rank works on it
 single-GPU kernels and the only collective is the optional gather of outputs at the end.
 
   prefill  KV-head groups: rank r owns kv heads [r*Hkv/N, (r+1)*Hkv/N) and their query heads
-  decode   requests:       request i lives on rank i mod N (its own cache, its own prepared plan)
+  decode   requests:       request i lives on rank i mod N, or - when the contexts differ a lot in length - on the
+                           rank `balance_requests` gives it (its own cache, its own prepared plan either way)
 """
 import torch
 import torch.distributed as dist
@@ -29,6 +30,50 @@ def requests_of_rank(num_requests, world, rank):
     if not 0 <= rank < world:
         raise ValueError("rank outside the group")
     return list(range(rank, num_requests, world))
+
+
+def expected_decode_tokens(context, chunk_size, topk, group_heads):
+    """Tokens a routed decode step reads for one (request, KV head): the current, partial chunk plus the expected union
+    of the topk-1 earlier chunks that each of the `group_heads` query heads of the group picks (independent picks among
+    the n complete chunks: n * (1 - (1 - r/n) ** heads) with r = min(topk-1, n))."""
+    n = (context - 1) // chunk_size if context > 0 else 0
+    r = min(topk - 1, n)
+    union = n * (1.0 - (1.0 - r / n) ** group_heads) if n else 0.0
+    return union * chunk_size + (context - n * chunk_size)
+
+
+def balance_requests(costs, world):
+    """Spreads requests of unequal cost over `world` ranks: in order of decreasing cost (ties: lower index first), each
+    request goes to the rank with the smallest total so far (ties: lower rank).  Deterministic, so every rank
+    computes the same assignment without talking.  Returns one ascending list of request indices per rank."""
+    if world < 1:
+        raise ValueError("world must be positive")
+    totals = [0.0] * world
+    owned = [[] for _ in range(world)]
+    for i in sorted(range(len(costs)), key=lambda i: (-float(costs[i]), i)):
+        r = min(range(world), key=lambda r: (totals[r], r))
+        totals[r] += float(costs[i])
+        owned[r].append(i)
+    return [sorted(rows) for rows in owned]
+
+
+def gather_assigned(local, assignment, group=None):
+    """All-gathers per-rank request rows back into request order, for an arbitrary assignment (one list of request
+    indices per rank, as `balance_requests` returns; rank r's local rows are in the order of assignment[r])."""
+    world = dist.get_world_size(group)
+    if len(assignment) != world:
+        raise ValueError("one list of requests per rank required")
+    if world == 1:
+        return local
+    width = max(len(rows) for rows in assignment)
+    padded = local.new_zeros((width,) + tuple(local.shape[1:]))
+    padded[: local.shape[0]] = local
+    parts = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(parts, padded, group=group)
+    out = local.new_empty((sum(len(rows) for rows in assignment),) + tuple(local.shape[1:]))
+    for r, rows in enumerate(assignment):
+        out[torch.as_tensor(rows, dtype=torch.long, device=out.device)] = parts[r][: len(rows)]
+    return out
 
 
 def gather_heads(local, group=None):

@@ -1,4 +1,5 @@
-"""tcgen05 tile primitives: one-CTA matrix products in every operand-major combination."""
+"""tcgen05 tile primitives: one-CTA matrix products in every operand-major combination; and the bounded barrier wait
+running out the way it would on a protocol fault: status bit, RuntimeError on the host, context still usable."""
 import ctypes
 
 import pytest
@@ -29,3 +30,28 @@ def test_umma_selftest(mode, n, k):
     torch.cuda.synchronize()
     assert rc == 0 and int(status.item()) == 0
     assert (d - ref).abs().max().item() < 1e-3
+
+
+def test_bounded_wait_runs_out_and_the_host_sees_it():
+    """A barrier wait that nothing satisfies ends by itself after its limit (here 2e6 SM clocks, about a millisecond;
+    the kernels use 2e9), the kernel returns, and the error surfaces as RuntimeError from check_status() - after
+    which the same context runs the next kernel normally."""
+    from moba_opt import _ext
+    import moba_opt.grouped_attention as ga
+    lib = _ext.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ga.check_status()
+    status = ga._status_word(dev)
+    returned = torch.zeros(1, dtype=torch.int32, device=dev)
+    assert lib.moba_selftest_wait(0, status.data_ptr(), returned.data_ptr(), None) == 1       # limit outside 1..2e9
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    assert lib.moba_selftest_wait(2_000_000, status.data_ptr(), returned.data_ptr(), None) == 0
+    t1.record()
+    torch.cuda.synchronize()
+    assert int(returned.item()) == 2                     # the wait gave up, the kernel ran to its end
+    assert 0.2 < t0.elapsed_time(t1) < 200.0             # and it did wait, for about the limit
+    with pytest.raises(RuntimeError, match="status bits 0x1"):
+        ga.check_status()
+    ga.check_status()                                    # the word is cleared by the report
+    test_umma_selftest(0, 128, 64)                       # the context is intact

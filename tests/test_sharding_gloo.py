@@ -48,7 +48,12 @@ def _worker(rank, world, port, results):
         local = torch.tensor([[float(i), float(i * i)] for i in mine])
         rows = sharding.gather_rows(local, 7)
         ok_rows = torch.equal(rows, torch.tensor([[float(i), float(i * i)] for i in range(7)]))
-        results[rank] = (ok_prefill, ok_rows, (qs.start, qs.stop, ks.start, ks.stop), mine)
+        # decode rows under a cost-balanced assignment (unequal numbers of requests per rank)
+        assignment = sharding.balance_requests([9, 1, 1, 1, 8, 1, 1], world)
+        local = torch.tensor([[float(i), float(i * i)] for i in assignment[rank]])
+        ok_assigned = torch.equal(sharding.gather_assigned(local, assignment),
+                                  torch.tensor([[float(i), float(i * i)] for i in range(7)]))
+        results[rank] = (ok_prefill, ok_rows and ok_assigned, (qs.start, qs.stop, ks.start, ks.stop), mine)
     finally:
         dist.destroy_process_group()
 
@@ -77,3 +82,20 @@ def test_partition_contract():
         sharding.requests_of_rank(8, 2, 2)
     covered = sorted(i for r in range(4) for i in sharding.requests_of_rank(64, 4, r))
     assert covered == list(range(64))
+
+
+def test_balanced_request_assignment():
+    from moba_opt import sharding
+    costs = [int(x) for x in np.random.default_rng(0).integers(4096, 65537, size=64)]
+    for world in (1, 2, 4, 8):
+        owned = sharding.balance_requests(costs, world)
+        assert sorted(i for rows in owned for i in rows) == list(range(64))
+        totals = [sum(costs[i] for i in rows) for rows in owned]
+        assert max(totals) - min(totals) <= max(costs)              # greedy bound: no rank is a whole request ahead
+        naive = [sum(costs[i] for i in range(r, 64, world)) for r in range(world)]
+        assert max(totals) <= max(naive)
+    assert sharding.balance_requests([5, 5, 5], 2) == [[0, 2], [1]]    # ties: lower index first, lower rank first
+    # cost model of a routed decode step: bounded by the context, saturating once the heads' picks cover the chunks
+    assert sharding.expected_decode_tokens(100, 2048, 4, 6) == 100
+    assert sharding.expected_decode_tokens(3 * 2048 + 7, 2048, 4, 6) == 3 * 2048 + 7        # 3 chunks, all picked
+    assert 8 * 2048 < sharding.expected_decode_tokens(65536, 2048, 4, 6) < 18 * 2048 + 2048

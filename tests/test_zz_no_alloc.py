@@ -69,6 +69,33 @@ def test_static_scratch_routing_matches_twice_in_a_row():
     assert torch.equal(first[1], again[1])
 
 
+def test_static_scratch_call_allocates_nothing():
+    """What the entry point is for: once the first call on the device has looked up the built-in array, a call
+    changes neither the device's free memory (cudaMemGetInfo: it sees every allocation of the process, the caching
+    allocator's included) nor torch's own count of allocated and reserved bytes."""
+    from moba_opt import _ext
+    import moba_opt.grouped_attention as ga
+    lib = _ext.lib()
+    dev = torch.device("cuda", 0)
+    rng = torch.Generator().manual_seed(13)
+    q = torch.randn(2048, 4, 64, generator=rng).bfloat16().to(dev)
+    k = torch.randn(2048, 2, 64, generator=rng).bfloat16().to(dev)
+    plan = ga.get_plan([0, 2048], 256, dev)
+    with torch.cuda.device(dev):
+        d = plan.desc(q, k, k, 2)
+        state = torch.zeros(lib.moba_prefill_route_state_bytes(ctypes.byref(d)), dtype=torch.uint8, device=dev)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        call = lambda: lib.moba_prefill_route_static(ctypes.byref(d), q.data_ptr(), k.data_ptr(), state.data_ptr(), stream)
+        assert call() == 0                                 # first call on the device: address look-up
+        torch.cuda.synchronize()
+        before = (torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev))
+        for _ in range(3):
+            assert call() == 0
+        torch.cuda.synchronize()
+        after = (torch.cuda.mem_get_info(dev)[0], torch.cuda.memory_allocated(dev), torch.cuda.memory_reserved(dev))
+    assert after == before
+
+
 def test_static_scratch_rejects_oversized_problem():
     from moba_opt import _ext
     import moba_opt.grouped_attention as ga
