@@ -3,202 +3,222 @@
 // (src/moba_opt/grouped_attention.py:48-94): nothing of size [F, Hq, T] is materialised, there
 // is no host synchronisation, and every list is produced in a fixed order (head in group, token).
 //
-// Passes (all on one stream):
-//   1. chunk_mean_kernel     means[c, g, :] = mean over the tokens of chunk c (FP32 accumulation)
-//   2. gate_topk_kernel      per (token, q head): scores against the earlier chunks of the same
+// Passes (all on one stream, four launches):
+//   1. chunk_mean_kernel     partial sums of K over 256-token slices of a chunk (one CTA each, so the pass
+//                            has enough loads in flight to run at memory speed); the CTA that finishes a
+//                            (chunk, kv head) last adds the slices in slice order and writes the mean
+//   2. gate_topk_kernel      per (token, q head): FP32 scores against the earlier chunks of the same
 //                            sequence, top-R with "lowest chunk wins ties", sel[T,Hq,R] ascending;
 //                            per (query tile, q head, chunk) selection counts
-//   3. segment_scan_kernel   per (chunk, q head): exclusive scan of the counts over query tiles
-//   4. plan_kernel           segment bases and per-expert tile bases (exclusive scans)
-//   5. fill_kernel           writes slot ids into rowlist at base + tile offset + rank in tile
+//   3. segment_scan_kernel   per (chunk, q head): exclusive scan of the counts over query tiles; the block
+//                            that finishes last turns the totals into segment bases and per-expert tile bases
+//   4. fill_kernel           writes slot ids into rowlist at base + tile offset + rank in tile
 #include "prefill_common.cuh"
 #include "sm100.cuh"
 
 namespace moba {
 
-constexpr int kCandBatch = 32;  // candidate means staged in shared memory per pass
+constexpr int kCandBatch = 32;   // candidate means staged in shared memory per pass
+constexpr int kMeanRows = 256;   // tokens per CTA of the mean pass
 
 // --------------------------------------------------------------------------- 1. chunk means
-__global__ void __launch_bounds__(256) chunk_mean_kernel(PrefillView pv, const __nv_bfloat16* __restrict__ k,
-                                                         float* __restrict__ means, int round_bf16) {
+// grid (chunk, kv head, slice).  part [n_chunks*Hkv][splits][D] FP32, tickets [n_chunks*Hkv] zero on entry (and
+// left zero).  Every sum has a fixed order - rows of a slice by (row mod rows-per-pass, then pass), slices
+// ascending - so the means are bit-repeatable whichever CTA happens to finish last.
+__global__ void __launch_bounds__(256) chunk_mean_kernel(PrefillView pv, const __nv_bfloat16* __restrict__ k, float* part,
+                                                         float* __restrict__ means, int* tickets, int round_bf16, int splits) {
   extern __shared__ float s_part[];  // [rows_per_iter][D]
-  const int c = blockIdx.x, g = blockIdx.y;
-  const int t0 = pv.chunk_start[c], t1 = pv.chunk_start[c + 1];
+  __shared__ int s_last;
+  const int c = blockIdx.x, g = blockIdx.y, sl = blockIdx.z;
+  const int c0 = pv.chunk_start[c], c1 = pv.chunk_start[c + 1];
+  const int t0 = min(c1, c0 + sl * kMeanRows), t1 = min(c1, t0 + kMeanRows);
   const int upr = pv.D >> 3;
   const int rpi = 256 / upr;
   const int ri = threadIdx.x / upr, u = threadIdx.x - ri * upr;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   if (ri < rpi) {
-    for (int t = t0 + ri; t < t1; t += rpi) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(k + (long long)t * pv.k_st + (long long)g * pv.k_sh + u * 8);
+    const __nv_bfloat16* base = k + (long long)g * pv.k_sh + u * 8;
+    auto add = [&](const uint4& raw) {
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         acc[2 * i] += __uint_as_float(w[i] << 16);
         acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
       }
+    };
+    int t = t0 + ri;
+    for (; t + 3 * rpi < t1; t += 4 * rpi) {   // four rows in flight per thread
+      uint4 raw[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) raw[j] = *reinterpret_cast<const uint4*>(base + (long long)(t + j * rpi) * pv.k_st);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) add(raw[j]);
     }
+    for (; t < t1; t += rpi) add(*reinterpret_cast<const uint4*>(base + (long long)t * pv.k_st));
 #pragma unroll
     for (int i = 0; i < 8; ++i) s_part[ri * pv.D + u * 8 + i] = acc[i];
   }
   __syncthreads();
+  const long long seg = (long long)c * pv.Hkv + g;
   for (int d = threadIdx.x; d < pv.D; d += 256) {
     float s = 0.f;
     for (int r = 0; r < rpi; ++r) s += s_part[r * pv.D + d];
-    float m = s / (float)(t1 - t0);
-    if (round_bf16) m = __bfloat162float(__float2bfloat16_rn(m));
-    means[((long long)c * pv.Hkv + g) * pv.D + d] = m;
+    part[(seg * splits + sl) * pv.D + d] = s;
   }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&tickets[seg], 1) == splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int d = threadIdx.x; d < pv.D; d += 256) {
+    float s = 0.f;
+    for (int j = 0; j < splits; ++j) s += __ldcg(part + (seg * splits + j) * pv.D + d);
+    float m = s / (float)(c1 - c0);
+    if (round_bf16) m = __bfloat162float(__float2bfloat16_rn(m));
+    means[seg * pv.D + d] = m;
+  }
+  if (threadIdx.x == 0) tickets[seg] = 0;
 }
 
 // --------------------------------------------------------------------------- 2. gate + top-k
-template <int RT>
-__global__ void __launch_bounds__(128) gate_topk_kernel(PrefillView pv, const __nv_bfloat16* __restrict__ q,
-                                                        const float* __restrict__ means, int* __restrict__ sel,
-                                                        int* __restrict__ cnt) {
+// Two FP32 multiply-adds per instruction (packed pairs of lanes 2j, 2j+1 of the dot product).
+__device__ __forceinline__ void fma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  return (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(hi) << 32);
+}
+__device__ __forceinline__ float lo_of(unsigned long long v) { return __uint_as_float((unsigned)v); }
+__device__ __forceinline__ float hi_of(unsigned long long v) { return __uint_as_float((unsigned)(v >> 32)); }
+
+// grid (query tile, query head); 128 * LPR threads: LPR lanes share a row, each holding DH of its DH * LPR (padded)
+// head dimensions as FP32 in registers for the whole launch, converted from bf16 once.  The candidate means sit in
+// shared memory as FP32 and are read as broadcast 16-byte loads, so a candidate costs DH / 2 packed FMAs and DH / 4
+// shared loads per thread and the pass runs at the speed Q arrives from memory.
+template <int RT, int DH, int LPR>
+__global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, const __nv_bfloat16* __restrict__ q,
+                                                              const float* __restrict__ means, int* __restrict__ sel,
+                                                              int* __restrict__ cnt) {
   extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int DP = DH * LPR;
+  constexpr int NT = 128 * LPR;
   const int D = pv.D, R = pv.R;
-  const int qrow_bytes = D * 2 + 16;  // padded so that per-thread row reads are conflict-free
-  float* s_means = reinterpret_cast<float*>(smem);                        // [kCandBatch][D]
-  uint8_t* s_q = smem + (size_t)kCandBatch * D * 4;                       // [128][qrow_bytes]
+  constexpr int qrow_bytes = DP * 2 + 16;  // padded so that per-thread row reads are conflict-free
+  float4* s_means = reinterpret_cast<float4*>(smem);                      // [kCandBatch][DP / 4], 16-byte units interleaved by lane of the row
+  uint8_t* s_q = smem + (size_t)kCandBatch * DP * 4;                      // [128][qrow_bytes]
   int* s_cnt = reinterpret_cast<int*>(s_q + (size_t)kTile * qrow_bytes);  // [ncand]
 
-  const int tile = blockIdx.x, g = blockIdx.y;
+  const int tile = blockIdx.x, h = blockIdx.y, g = h / pv.G;
   const int c = pv.qtile_chunk[tile];
   const int tok0 = pv.qtile_tok0[tile];
   const int ncand = pv.chunk_local[c];
   const int c0 = c - ncand;
-  const int chunk_end = pv.chunk_start[c + 1];
-  const int nrows = min(kTile, chunk_end - tok0);
+  const int nrows = min(kTile, pv.chunk_start[c + 1] - tok0);
   const int tid = threadIdx.x;
-  const int t = tok0 + tid;
-  const bool valid = tid < nrows;
+  const int row = tid / LPR, part = tid - row * LPR;
+  const bool valid = row < nrows;
+  int* out = sel + ((long long)(tok0 + row) * pv.Hq + h) * R;
+  if (ncand == 0) {  // first chunk of a sequence: nothing to route to
+    if (valid && part == 0)
+      for (int s = 0; s < R; ++s) out[s] = -1;
+    return;
+  }
   const int upr = D >> 3;
-  const int tile_local = pv.qtile_local[tile];
+  for (int i = tid; i < nrows * (DP / 8); i += NT) {
+    const int r = i / (DP / 8), u = i - r * (DP / 8);
+    const __nv_bfloat16* src = q + (long long)(tok0 + r) * pv.q_st + (long long)h * pv.q_sh;
+    cp_async16(smem_u32(s_q + (size_t)r * qrow_bytes + u * 16), u < upr ? src + u * 8 : src, u < upr);  // zero fill beyond D
+  }
+  cp_async_commit();
+  for (int i = tid; i < ncand; i += NT) s_cnt[i] = 0;
 
-  for (int hl = 0; hl < pv.G; ++hl) {
-    const int h = g * pv.G + hl;
-    float topv[RT];
-    int topi[RT];
+  unsigned long long qp[DH / 2];
+  float topv[RT];
+  int topi[RT];
 #pragma unroll
-    for (int i = 0; i < RT; ++i) { topv[i] = -INFINITY; topi[i] = -1; }
+  for (int i = 0; i < RT; ++i) { topv[i] = -INFINITY; topi[i] = -1; }
 
-    if (ncand > 0) {
-      __syncthreads();  // previous head's s_q / s_cnt readers are done
-      for (int i = tid; i < nrows * upr; i += 128) {
-        const int r = i / upr, u = i - r * upr;
-        cp_async16(smem_u32(s_q + (size_t)r * qrow_bytes + u * 16),
-                   q + (long long)(tok0 + r) * pv.q_st + (long long)h * pv.q_sh + u * 8, true);
+  for (int cb = 0; cb < ncand; cb += kCandBatch) {
+    const int nb = min(kCandBatch, ncand - cb);
+    if (cb) __syncthreads();  // previous batch consumed
+    for (int i = tid; i < nb * (DP / 4); i += NT) {
+      const int ci = i / (DP / 4), f4 = i - ci * (DP / 4);
+      const int d0 = f4 * 4;
+      float4 mv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (d0 < D) mv = *reinterpret_cast<const float4*>(means + ((long long)(c0 + cb + ci) * pv.Hkv + g) * D + d0);
+      s_means[ci * (DP / 4) + ((d0 % DH) >> 2) * LPR + d0 / DH] = mv;
+    }
+    if (cb == 0) {
+      cp_async_wait<0>();
+      __syncthreads();
+      const uint8_t* qrow = s_q + (size_t)row * qrow_bytes + part * (DH * 2);
+#pragma unroll
+      for (int u = 0; u < DH / 8; ++u) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) raw = *reinterpret_cast<const uint4*>(qrow + u * 16);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) qp[u * 4 + i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
       }
-      cp_async_commit();
-      for (int i = tid; i < ncand; i += 128) s_cnt[i] = 0;
-      for (int cb = 0; cb < ncand; cb += kCandBatch) {
-        const int nb = min(kCandBatch, ncand - cb);
-        __syncthreads();  // previous batch consumed
-        for (int i = tid; i < nb * (D >> 2); i += 128)
-          reinterpret_cast<float4*>(s_means)[i] =
-              *reinterpret_cast<const float4*>(means + ((long long)(c0 + cb + i / (D >> 2)) * pv.Hkv + g) * D + (i % (D >> 2)) * 4);
-        cp_async_wait<0>();
-        __syncthreads();
-        if (valid) {
-          const uint8_t* qrow = s_q + (size_t)tid * qrow_bytes;
-          for (int ci = 0; ci < nb; ++ci) {
-            const float* m = s_means + ci * D;
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-            for (int u = 0; u < upr; ++u) {
-              const uint4 raw = *reinterpret_cast<const uint4*>(qrow + u * 16);
-              const float4 m0 = *reinterpret_cast<const float4*>(m + u * 8);
-              const float4 m1 = *reinterpret_cast<const float4*>(m + u * 8 + 4);
-              a0 = fmaf(__uint_as_float(raw.x << 16), m0.x, a0);
-              a1 = fmaf(__uint_as_float(raw.x & 0xFFFF0000u), m0.y, a1);
-              a2 = fmaf(__uint_as_float(raw.y << 16), m0.z, a2);
-              a3 = fmaf(__uint_as_float(raw.y & 0xFFFF0000u), m0.w, a3);
-              a0 = fmaf(__uint_as_float(raw.z << 16), m1.x, a0);
-              a1 = fmaf(__uint_as_float(raw.z & 0xFFFF0000u), m1.y, a1);
-              a2 = fmaf(__uint_as_float(raw.w << 16), m1.z, a2);
-              a3 = fmaf(__uint_as_float(raw.w & 0xFFFF0000u), m1.w, a3);
-            }
-            const float score = (a0 + a1) + (a2 + a3);
-            // strict '>' keeps the earlier (lower) chunk on exact ties; infinities never enter
-            if (score > topv[RT - 1] && score < INFINITY) {
-              float v = score;
-              int idx = cb + ci;
+    } else {
+      __syncthreads();
+    }
+    for (int ci = 0; ci < nb; ++ci) {
+      const float4* m = s_means + ci * (DP / 4) + part;
+      unsigned long long a0 = 0ull, a1 = 0ull, a2 = 0ull, a3 = 0ull;
 #pragma unroll
-              for (int i = 0; i < RT; ++i) {
-                if (v > topv[i]) {
-                  const float tv = topv[i]; const int ti = topi[i];
-                  topv[i] = v; topi[i] = idx; v = tv; idx = ti;
-                }
-              }
-            }
+      for (int j = 0; j < DH / 4; j += 2) {
+        const float4 m0 = m[j * LPR];
+        const float4 m1 = m[(j + 1) * LPR];
+        fma2(a0, qp[2 * j], pack2(m0.x, m0.y));
+        fma2(a1, qp[2 * j + 1], pack2(m0.z, m0.w));
+        fma2(a2, qp[2 * j + 2], pack2(m1.x, m1.y));
+        fma2(a3, qp[2 * j + 3], pack2(m1.z, m1.w));
+      }
+      float score = ((lo_of(a0) + hi_of(a0)) + (lo_of(a1) + hi_of(a1))) + ((lo_of(a2) + hi_of(a2)) + (lo_of(a3) + hi_of(a3)));
+      if (LPR == 2) score += __shfl_xor_sync(0xFFFFFFFFu, score, 1);   // both lanes of the row get the same bits
+      // strict '>' keeps the earlier (lower) chunk on exact ties; infinities never enter
+      if (score > topv[RT - 1] && score < INFINITY) {
+        float v = score;
+        int idx = cb + ci;
+#pragma unroll
+        for (int i = 0; i < RT; ++i) {
+          if (v > topv[i]) {
+            const float tv = topv[i]; const int ti = topi[i];
+            topv[i] = v; topi[i] = idx; v = tv; idx = ti;
           }
         }
       }
     }
-    // keep the R best, emit them in ascending chunk order
-    if (valid) {
-      int last = -1;
-      int* out = sel + ((long long)t * pv.Hq + h) * R;
-      for (int s = 0; s < R; ++s) {
-        int best = 0x7FFFFFFF;
+  }
+  // keep the R best, emit them in ascending chunk order
+  if (valid && part == 0) {
+    int last = -1;
+    for (int s = 0; s < R; ++s) {
+      int best = 0x7FFFFFFF;
 #pragma unroll
-        for (int i = 0; i < RT; ++i)
-          if (i < R && topi[i] > last && topi[i] < best) best = topi[i];
-        if (best == 0x7FFFFFFF) {
-          out[s] = -1;
-        } else {
-          out[s] = c0 + best;
-          last = best;
-          atomicAdd(&s_cnt[best], 1);
-        }
+      for (int i = 0; i < RT; ++i)
+        if (i < R && topi[i] > last && topi[i] < best) best = topi[i];
+      if (best == 0x7FFFFFFF) {
+        out[s] = -1;
+      } else {
+        out[s] = c0 + best;
+        last = best;
+        atomicAdd(&s_cnt[best], 1);
       }
     }
-    if (ncand > 0) {
-      __syncthreads();
-      for (int i = tid; i < ncand; i += 128)
-        cnt[((long long)(c0 + i) * pv.Hq + h) * pv.max_tiles_per_seq + tile_local] = s_cnt[i];
-    }
   }
+  __syncthreads();
+  const int tile_local = pv.qtile_local[tile];
+  for (int i = tid; i < ncand; i += NT)
+    cnt[((long long)(c0 + i) * pv.Hq + h) * pv.max_tiles_per_seq + tile_local] = s_cnt[i];
 }
 
-// --------------------------------------------------------------------------- 3. scan over query tiles
-__global__ void __launch_bounds__(128) segment_scan_kernel(PrefillView pv, int* __restrict__ cnt, int* __restrict__ seg_count) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= pv.n_chunks * pv.Hq) return;
-  const int c = warp / pv.Hq;
-  const int b = pv.chunk_seq[c];
-  const int len = pv.cu_seqlens[b + 1] - pv.cu_seqlens[b];
-  const int nb = (len + pv.C - 1) / pv.C;
-  const int tpc = (pv.C + kTile - 1) / kTile;
-  const int last = len - (nb - 1) * pv.C;
-  const int ntl = (nb - 1) * tpc + (last + kTile - 1) / kTile;
-  const int j = pv.chunk_local[c];
-  int* row = cnt + (long long)warp * pv.max_tiles_per_seq;
-  int carry = 0;
-  if (j < nb - 1) {
-    for (int base = (j + 1) * tpc; base < ntl; base += 32) {
-      const int i = base + lane;
-      const int v = i < ntl ? row[i] : 0;
-      int incl = v;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += n;
-      }
-      if (i < ntl) row[i] = carry + incl - v;
-      carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
-    }
-  }
-  if (lane == 0) seg_count[warp] = carry;
-}
-
-// --------------------------------------------------------------------------- 4. bases
-// Single block.  seg_base[i] = sum of seg_count[<i]; tile_base[e] = sum over experts < e of
-// ceil(rows(e) / 128) rounded up to even, with expert e = chunk * Hkv + kv head.
-__global__ void __launch_bounds__(1024) plan_kernel(PrefillView pv, const int* __restrict__ seg_count,
-                                                    int* __restrict__ seg_base, int* __restrict__ tile_base) {
-  __shared__ int s_part[1024];
-  __shared__ int s_total;
+// --------------------------------------------------------------------------- 3. scan over query tiles, then the bases
+// Bases, by the block that finishes the scan last.  seg_base[i] = sum of seg_count[<i]; tile_base[e] = sum over
+// experts < e of ceil(rows(e) / 128) rounded up to even, with expert e = chunk * Hkv + kv head.
+__device__ void plan_bases(const PrefillView& pv, const int* seg_count, int* seg_base, int* tile_base, int* s_part, int* s_total) {
   const int tid = threadIdx.x;
   for (int pass = 0; pass < 2; ++pass) {
     const int n = pass == 0 ? pv.n_chunks * pv.Hq : pv.n_chunks * pv.Hkv;
@@ -206,7 +226,7 @@ __global__ void __launch_bounds__(1024) plan_kernel(PrefillView pv, const int* _
     const int per = (n + 1023) / 1024;
     const int lo = min(n, tid * per), hi = min(n, lo + per);
     auto value = [&](int i) {
-      if (pass == 0) return seg_count[i];
+      if (pass == 0) return __ldcg(seg_count + i);
       const int cidx = i / pv.Hkv, g = i - cidx * pv.Hkv;
       const int rows = seg_base[cidx * pv.Hq + (g + 1) * pv.G] - seg_base[cidx * pv.Hq + g * pv.G];
       return ((rows + kTile - 1) / kTile + 1) & ~1;  // even: the forward pairs tiles
@@ -218,15 +238,59 @@ __global__ void __launch_bounds__(1024) plan_kernel(PrefillView pv, const int* _
     if (tid == 0) {
       int run = 0;
       for (int i = 0; i < 1024; ++i) { const int v = s_part[i]; s_part[i] = run; run += v; }
-      s_total = run;
+      *s_total = run;
     }
     __syncthreads();
     int run = s_part[tid];
     for (int i = lo; i < hi; ++i) { out[i] = run; run += value(i); }
-    if (tid == 0) out[n] = s_total;
+    if (tid == 0) out[n] = *s_total;
     __threadfence_block();
     __syncthreads();
   }
+}
+
+// One warp per (chunk, q head); 32 warps per block.  ticket: one zero int on entry (left zero).
+__global__ void __launch_bounds__(1024) segment_scan_kernel(PrefillView pv, int* __restrict__ cnt, int* seg_count,
+                                                            int* seg_base, int* tile_base, int* ticket) {
+  __shared__ int s_part[1024];
+  __shared__ int s_total;
+  __shared__ int s_last;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp < pv.n_chunks * pv.Hq) {
+    const int c = warp / pv.Hq;
+    const int b = pv.chunk_seq[c];
+    const int len = pv.cu_seqlens[b + 1] - pv.cu_seqlens[b];
+    const int nb = (len + pv.C - 1) / pv.C;
+    const int tpc = (pv.C + kTile - 1) / kTile;
+    const int last = len - (nb - 1) * pv.C;
+    const int ntl = (nb - 1) * tpc + (last + kTile - 1) / kTile;
+    const int j = pv.chunk_local[c];
+    int* row = cnt + (long long)warp * pv.max_tiles_per_seq;
+    int carry = 0;
+    if (j < nb - 1) {
+      for (int base = (j + 1) * tpc; base < ntl; base += 32) {
+        const int i = base + lane;
+        const int v = i < ntl ? row[i] : 0;
+        int incl = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+          if (lane >= o) incl += n;
+        }
+        if (i < ntl) row[i] = carry + incl - v;
+        carry += __shfl_sync(0xFFFFFFFFu, incl, 31);
+      }
+    }
+    if (lane == 0) seg_count[warp] = carry;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(ticket, 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  plan_bases(pv, seg_count, seg_base, tile_base, s_part, &s_total);
+  if (threadIdx.x == 0) *ticket = 0;
 }
 
 // --------------------------------------------------------------------------- 5. fill
@@ -289,14 +353,48 @@ int validate_desc(const moba_prefill_desc* d) {
   return MOBA_OK;
 }
 
+template <int RT, int DH, int LPR>
+static cudaError_t launch_gate_as(const PrefillView& pv, const __nv_bfloat16* q, const float* means, int* sel, int* cnt,
+                                  int max_chunks_per_seq, cudaStream_t st) {
+  constexpr int DP = DH * LPR;
+  const size_t smem = (size_t)kCandBatch * DP * 4 + (size_t)kTile * (DP * 2 + 16) + (size_t)max_chunks_per_seq * 4 + 16;
+  cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel<RT, DH, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  gate_topk_kernel<RT, DH, LPR><<<dim3(pv.n_qtiles, pv.Hq), 128 * LPR, smem, st>>>(pv, q, means, sel, cnt);
+  return cudaGetLastError();
+}
+
 template <int RT>
 static cudaError_t launch_gate(const PrefillView& pv, const __nv_bfloat16* q, const float* means, int* sel, int* cnt,
                                int max_chunks_per_seq, cudaStream_t st) {
-  size_t smem = (size_t)kCandBatch * pv.D * 4 + (size_t)kTile * (pv.D * 2 + 16) + (size_t)max_chunks_per_seq * 4 + 16;
-  cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  gate_topk_kernel<RT><<<dim3(pv.n_qtiles, pv.Hkv), 128, smem, st>>>(pv, q, means, sel, cnt);
-  return cudaGetLastError();
+  if (pv.D <= 32) return launch_gate_as<RT, 32, 1>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
+  if (pv.D <= 64) return launch_gate_as<RT, 64, 1>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
+  return launch_gate_as<RT, 64, 2>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
+}
+
+// Layout of the routing scratch.  Only `tickets` has to be zero when a call starts (route_impl clears it).
+struct RouteScratch {
+  float* means;     // [n_chunks][Hkv][D]
+  float* part;      // [n_chunks][Hkv][splits][D] slice sums of the mean pass
+  int* cnt;         // [n_chunks][Hq][max_tiles_per_seq]
+  int* seg_count;   // [n_chunks][Hq]
+  int* tickets;     // [n_chunks * Hkv + 1] arrival counters of the mean pass, then one for the scan pass
+  size_t tickets_bytes, total;
+};
+static int mean_splits(const moba_prefill_desc& d) { return (d.chunk_size + kMeanRows - 1) / kMeanRows; }
+static RouteScratch carve_route_scratch(const moba_prefill_desc& d, void* base) {
+  RouteScratch r;
+  char* p = static_cast<char*>(base);
+  const size_t seg = (size_t)d.num_chunks * d.hkv;
+  r.means = reinterpret_cast<float*>(p); p += align256(seg * d.dim * 4);
+  r.part = reinterpret_cast<float*>(p); p += align256(seg * mean_splits(d) * d.dim * 4);
+  r.cnt = reinterpret_cast<int*>(p); p += align256((size_t)d.num_chunks * d.hq * d.max_tiles_per_seq * 4);
+  r.seg_count = reinterpret_cast<int*>(p); p += align256((size_t)d.num_chunks * d.hq * 4);
+  r.tickets = reinterpret_cast<int*>(p);
+  r.tickets_bytes = (seg + 1) * 4;
+  p += align256(r.tickets_bytes);
+  r.total = (size_t)(p - static_cast<char*>(base));
+  return r;
 }
 
 }  // namespace moba
@@ -310,8 +408,7 @@ extern "C" size_t moba_prefill_route_state_bytes(const moba_prefill_desc* d) {
 
 extern "C" size_t moba_prefill_route_scratch_bytes(const moba_prefill_desc* d) {
   if (validate_desc(d) != MOBA_OK) return 0;
-  return align256((size_t)d->num_chunks * d->hkv * d->dim * 4) +
-         align256((size_t)d->num_chunks * d->hq * d->max_tiles_per_seq * 4) + align256((size_t)d->num_chunks * d->hq * 4);
+  return carve_route_scratch(*d, nullptr).total;
 }
 
 static int route_impl(const moba_prefill_desc* d, const void* q, const void* k, void* route_state, void* scratch,
@@ -319,16 +416,19 @@ static int route_impl(const moba_prefill_desc* d, const void* q, const void* k, 
   if (d->remote_k == 0) return MOBA_OK;  // dense fallback: nothing to route
   const PrefillView pv = make_view(*d);
   RouteState rs = carve_route_state(*d, route_state);
-  char* p = static_cast<char*>(scratch);
-  float* means = reinterpret_cast<float*>(p); p += align256((size_t)d->num_chunks * d->hkv * d->dim * 4);
-  int* cnt = reinterpret_cast<int*>(p); p += align256((size_t)d->num_chunks * d->hq * d->max_tiles_per_seq * 4);
-  int* seg_count = reinterpret_cast<int*>(p);
+  const RouteScratch sc = carve_route_scratch(*d, scratch);
+  float* means = sc.means;
+  int* cnt = sc.cnt;
+  int* seg_count = sc.seg_count;
+  // The arrival counters are the one part of the scratch that must start at zero; everything else is written before
+  // it is read.  (The kernels leave the counters at zero, but a caller's scratch arrives with arbitrary contents.)
+  if (cudaMemsetAsync(sc.tickets, 0, sc.tickets_bytes, st) != cudaSuccess) return MOBA_ERR_CUDA;
   const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
   const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
 
   const int rpi = 256 / (d->dim / 8);
-  chunk_mean_kernel<<<dim3(d->num_chunks, d->hkv), 256, (size_t)rpi * d->dim * 4, st>>>(pv, kb, means,
-                                                                                           d->flags & MOBA_ROUTE_BF16_MEANS);
+  chunk_mean_kernel<<<dim3(d->num_chunks, d->hkv, mean_splits(*d)), 256, (size_t)rpi * d->dim * 4, st>>>(
+      pv, kb, sc.part, means, sc.tickets, d->flags & MOBA_ROUTE_BF16_MEANS, mean_splits(*d));
   if (cudaGetLastError() != cudaSuccess) return MOBA_ERR_CUDA;
   cudaError_t e;
   const int R = d->remote_k;
@@ -340,8 +440,8 @@ static int route_impl(const moba_prefill_desc* d, const void* q, const void* k, 
   else e = launch_gate<16>(pv, qb, means, rs.sel, cnt, d->max_chunks_per_seq, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
   const int segs = d->num_chunks * d->hq;
-  segment_scan_kernel<<<(segs * 32 + 127) / 128, 128, 0, st>>>(pv, cnt, seg_count);
-  plan_kernel<<<1, 1024, 0, st>>>(pv, seg_count, rs.seg_base, rs.tile_base);
+  segment_scan_kernel<<<(segs + 31) / 32, 1024, 0, st>>>(pv, cnt, seg_count, rs.seg_base, rs.tile_base,
+                                                          sc.tickets + (size_t)d->num_chunks * d->hkv);
   fill_kernel<<<dim3(d->num_qtiles, d->hkv), 128, (size_t)4 * d->max_chunks_per_seq * 4 + 16, st>>>(pv, rs.sel, cnt, rs.seg_base,
                                                                                                  rs.rowlist);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
@@ -397,7 +497,8 @@ extern "C" int moba_prefill_route_static(const moba_prefill_desc* d, const void*
     }
     scratch = g_route_scratch_addr[dev];
   }
-  // Nothing in the scratch has to start at zero: every word the later passes read is written by an
-  // earlier pass of the same call, so the previous call's contents are simply overwritten.
+  // The previous call's contents stay in the array.  The arrival counters of the mean and scan passes are the
+  // only words that must start at zero, and route_impl clears them on the stream before the first kernel; every
+  // other word the later passes read is written by an earlier pass of the same call.
   return route_impl(d, q, k, route_state, scratch, (cudaStream_t)stream);
 }
