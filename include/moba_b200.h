@@ -135,6 +135,14 @@ typedef struct moba_cache_desc {
 int moba_decode_metadata(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
                          int append, void* stream);
 
+/* Applies host-planned changes to the device copies of the page table and the lengths, the changed entries only
+ * (the reference re-uploads the whole [batch, width] table and the lengths on every append and reset,
+ * src/moba_opt/kv_cache.py:112-126): edits [n][3] = (sequence, logical page, physical page), then
+ * lengths[ids[j]] = lengths_new[j] for j < m.  clear_rows != 0 (with n == 0) unmaps the whole row of every listed
+ * sequence first: a reset. */
+int moba_cache_update(const moba_cache_desc* c, const int32_t* edits, int n, const int32_t* ids, const int32_t* lengths_new, int m,
+                      int clear_rows, void* stream);
+
 /* Scatter k, v [tokens, hkv, dim] (contiguous) to (table[token_seq[t]][token_pos[t]/page], token_pos[t]%page)
  * (ops/paged_decode.py:11-23). */
 int moba_decode_append(const moba_cache_desc* c, const void* k, const void* v, const int32_t* token_seq,
@@ -166,10 +174,23 @@ int moba_decode_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, voi
  * row and the predicated moba_decode_means in one launch, one CTA per row (ops/prepared_decode.py:7-41 are three
  * kernels).  With qkv == NULL, k and v [rows, hkv, dim] are inputs.  With qkv [rows, (hq + 2 hkv) * dim] (the fused
  * projection of the new token), the launch also applies the rotate-half rotary embedding with cos, sin [rows, dim]
- * to the query and key heads and writes q [rows, hq, dim], k, v [rows, hkv, dim] before appending. */
+ * to the query and key heads and writes q [rows, hq, dim], k, v [rows, hkv, dim] before appending.
+ * positions is read before it is written (the previous step's position is a hint for the page of the new token): it is
+ * in/out, must be readable memory, and may hold anything before the first step (the hint is range-checked). */
 int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
                            int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
                            unsigned* status, void* stream);
+
+/* moba_decode_step_begin followed by moba_decode_route of the same rows, as one launch: the CTA that appends a row
+ * already holds its query (after the rotary embedding) and its position, so it scores the chunk means and ranks them
+ * on the spot, and the step has one launch boundary less.  q is required (an input when qkv == NULL).  remote, width and
+ * the five routing outputs are moba_decode_route's, with the same results bit for bit; umax is
+ * moba_decode_union_capacity(hq, hkv, remote, width).  (ops/prepared_decode.py:7-55,78-94 of the reference: five kernels
+ * and a torch.topk.) */
+int moba_decode_step_begin_routed(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
+                                  int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
+                                  int remote, int width, float* scores, int32_t* selected, int32_t* u_chunk, uint32_t* u_mask,
+                                  int32_t* u_count, unsigned* status, void* stream);
 
 /* Routing (ops/paged_decode.py:48-64 scores; ops/prepared_decode.py:45-55,78-94 selection): q [rows,hq,dim];
  * scores [rows,hq,width] fp32 (may be null), -inf for chunks not completed before the query's chunk;
@@ -237,7 +258,8 @@ int moba_argmax_bf16(const void* logits, int n, void* workspace, size_t workspac
  * weight is read once with all loads of a thread in flight, which is what bounds a batch-1 step.
  *   input: either x [k], or h_in [k] with norm_weight [k] (then x = norm_weight * rmsnorm(h_in + delta, eps), delta
  *          may be null, and h_out, if given, receives h_in + delta: the residual add and the RMSNorm that precede the
- *          projection in the layer run inside the same launch);
+ *          projection in the layer run inside the same launch; h_out must not be h_in or delta - every CTA re-reads
+ *          those while one writes h_out - and equal pointers are refused with MOBA_ERR_INVALID);
  *   epilogue 0: y [n] = W x + bias (bias may be null);
  *   epilogue 1: weight is [2 n, k], gate rows then up rows, y [n] = silu(gate) * up (no bias).
  * k a multiple of 8, at most 16384 (8192 with epilogue 1); weight and x 16-byte aligned.  No reference counterpart

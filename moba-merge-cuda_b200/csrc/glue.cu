@@ -460,6 +460,8 @@ extern "C" int moba_decode_linear(const void* x, const void* h_in, const void* d
   if ((h_in == nullptr) == (x == nullptr)) return MOBA_ERR_INVALID;  // exactly one source of the input vector
   if (h_in && !norm_weight) return MOBA_ERR_INVALID;
   if (!h_in && (delta || h_out)) return MOBA_ERR_INVALID;
+  // every CTA re-reads h_in and delta while the first one writes h_out: in place would hand some CTAs updated rows
+  if (h_out && (h_out == h_in || h_out == delta)) return MOBA_ERR_INVALID;
   if (epilogue == 1 && bias) return MOBA_ERR_INVALID;
   if (((uintptr_t)weight | (uintptr_t)(x ? x : weight)) & 15) return MOBA_ERR_INVALID;
   const bool pair = epilogue == 1;

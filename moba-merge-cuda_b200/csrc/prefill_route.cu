@@ -4,7 +4,7 @@
 // is no host synchronisation, and every list is produced in a fixed order (head in group, token).
 //
 // Passes (all on one stream, four launches):
-//   1. chunk_mean_kernel     partial sums of K over 256-token slices of a chunk (one CTA each, so the pass
+//   1. chunk_mean_kernel     partial sums of K over 128-token slices of a chunk (one CTA each, so the pass
 //                            has enough loads in flight to run at memory speed); the CTA that finishes a
 //                            (chunk, kv head) last adds the slices in slice order and writes the mean
 //   2. gate_topk_kernel      per (token, q head): FP32 scores against the earlier chunks of the same
@@ -19,7 +19,7 @@
 namespace moba {
 
 constexpr int kCandBatch = 32;   // candidate means staged in shared memory per pass
-constexpr int kMeanRows = 256;   // tokens per CTA of the mean pass
+constexpr int kMeanRows = 128;   // tokens per CTA of the mean pass
 
 // --------------------------------------------------------------------------- 1. chunk means
 // grid (chunk, kv head, slice).  part [n_chunks*Hkv][splits][D] FP32, tickets [n_chunks*Hkv] zero on entry (and
@@ -86,11 +86,17 @@ __global__ void __launch_bounds__(256) chunk_mean_kernel(PrefillView pv, const _
 __device__ __forceinline__ void fma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
 }
+// A pair of FP32 values as one 64-bit register pair and back: register moves at most, no arithmetic.
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
-  return (unsigned long long)__float_as_uint(lo) | ((unsigned long long)__float_as_uint(hi) << 32);
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
 }
-__device__ __forceinline__ float lo_of(unsigned long long v) { return __uint_as_float((unsigned)v); }
-__device__ __forceinline__ float hi_of(unsigned long long v) { return __uint_as_float((unsigned)(v >> 32)); }
+__device__ __forceinline__ float sum2(unsigned long long v) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return lo + hi;
+}
 
 // grid (query tile, query head); 128 * LPR threads: LPR lanes share a row, each holding DH of its DH * LPR (padded)
 // head dimensions as FP32 in registers for the whole launch, converted from bf16 once.  The candidate means sit in
@@ -165,18 +171,19 @@ __global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, co
       __syncthreads();
     }
     for (int ci = 0; ci < nb; ++ci) {
-      const float4* m = s_means + ci * (DP / 4) + part;
+      // a 16-byte shared load lands in two aligned register pairs, which are the packed operands as they are
+      const ulonglong2* m = reinterpret_cast<const ulonglong2*>(s_means + ci * (DP / 4) + part);
       unsigned long long a0 = 0ull, a1 = 0ull, a2 = 0ull, a3 = 0ull;
 #pragma unroll
       for (int j = 0; j < DH / 4; j += 2) {
-        const float4 m0 = m[j * LPR];
-        const float4 m1 = m[(j + 1) * LPR];
-        fma2(a0, qp[2 * j], pack2(m0.x, m0.y));
-        fma2(a1, qp[2 * j + 1], pack2(m0.z, m0.w));
-        fma2(a2, qp[2 * j + 2], pack2(m1.x, m1.y));
-        fma2(a3, qp[2 * j + 3], pack2(m1.z, m1.w));
+        const ulonglong2 m0 = m[j * LPR];
+        const ulonglong2 m1 = m[(j + 1) * LPR];
+        fma2(a0, qp[2 * j], m0.x);
+        fma2(a1, qp[2 * j + 1], m0.y);
+        fma2(a2, qp[2 * j + 2], m1.x);
+        fma2(a3, qp[2 * j + 3], m1.y);
       }
-      float score = ((lo_of(a0) + hi_of(a0)) + (lo_of(a1) + hi_of(a1))) + ((lo_of(a2) + hi_of(a2)) + (lo_of(a3) + hi_of(a3)));
+      float score = (sum2(a0) + sum2(a1)) + (sum2(a2) + sum2(a3));
       if (LPR == 2) score += __shfl_xor_sync(0xFFFFFFFFu, score, 1);   // both lanes of the row get the same bits
       // strict '>' keeps the earlier (lower) chunk on exact ties; infinities never enter
       if (score > topv[RT - 1] && score < INFINITY) {

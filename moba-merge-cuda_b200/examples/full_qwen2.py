@@ -253,9 +253,9 @@ class FullQwen2Session:
 
     def _attend(self, p):
         if self.backend == "attention_graph":
-            p._run("step", True)
+            p.replay("step")
         else:
-            p._compute(True)
+            p.launch("step")
 
     def _compute_step_fused(self):
         """The same step in six launches per dense layer and seven per MoBA layer: every projection is one
@@ -302,9 +302,9 @@ class FullQwen2Session:
             if self.backend == "attention_graph":   # the plan's own graph starts from its q, k, v buffers
                 check(lib.moba_rope_split(self._qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), 1, self.hq, self.hk, self.dim,
                                           p.q.data_ptr(), p.k.data_ptr(), p.v.data_ptr(), st))
-                p._run("step", True)
+                p.replay("step")
             else:                                   # rotary embedding + split inside the step's first launch
-                p._compute(True, projected=(self._qkv, cos, sin))
+                p.launch("step", projected=(self._qkv, cos, sin))
             o = layer.self_attn.o_proj
             linear(p.output, o.weight, o.bias, self._att)
             linear(None, self.gate_up[i], None, self._act, norm=layer.post_attention_layernorm, h_in=h, delta=self._att,
@@ -327,37 +327,35 @@ class FullQwen2Session:
     def _capture_model(self):
         """Captures `_compute_step` as one CUDA graph.  The visible state of every cache (page table, lengths,
         means, pending page-table delta) is restored afterwards."""
-        snapshots = [[t.clone() for t in (c._table, c._lengths, c._means, p.delta)] for c, p in zip(self.caches, self.plans)]
-        counters = [p.delta_uploads for p in self.plans]
+        from contextlib import ExitStack
+        from moba_opt.prepared_decode import VisibleState
         main = torch.cuda.current_stream(self.device)
         side = torch.cuda.Stream(device=self.device)
-        try:
-            for p in self.plans:
-                p._upload(p._state.plan())
-            side.wait_stream(main)
-            with torch.cuda.stream(side):
-                for _ in range(2):                      # warm-up outside the capture
+        with ExitStack() as stack:
+            saved = [stack.enter_context(VisibleState(p)) for p in self.plans]
+            try:
+                for p in self.plans:
+                    p.send_delta(p.plan_step())
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    for _ in range(2):                      # warm-up outside the capture
+                        self._compute_step()
+                        for c, state in zip(self.caches, saved):
+                            c._lengths.copy_(state.lengths)
+                main.wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
                     self._compute_step()
-                    for c, snap in zip(self.caches, snapshots):
-                        c._lengths.copy_(snap[1])
-            main.wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                self._compute_step()
-            self.graph = graph
-        finally:
-            main.wait_stream(side)
-            for c, p, snap, n in zip(self.caches, self.plans, snapshots, counters):
-                for target, source in zip((c._table, c._lengths, c._means, p.delta), snap):
-                    target.copy_(source)
-                p.delta_uploads = n
+                self.graph = graph
+            finally:
+                main.wait_stream(side)
 
     def _advance(self):
         if not self.plans:
             raise ValueError("prepare first")
-        plans = [p._state.plan() for p in self.plans]     # raises before anything is modified when a cache is full
+        plans = [p.plan_step() for p in self.plans]     # raises before anything is modified when a cache is full
         for p, plan in zip(self.plans, plans):
-            p._upload(plan)
+            p.send_delta(plan)
         try:
             if self.graph is not None:
                 self.graph.replay()
@@ -366,10 +364,10 @@ class FullQwen2Session:
         except Exception:
             self.failed = True
             for p in self.plans:
-                p.failed = True
+                p.mark_failed()
             raise
         for p, plan in zip(self.plans, plans):
-            p._state.commit(plan)
+            p.commit_step(plan)
         return self.logits
 
     @torch.no_grad()

@@ -34,6 +34,7 @@ class AppendPlan:
     token_sequences: tuple    # sequence id of every appended token, in input order
     token_positions: tuple    # its position inside that sequence
     completed_chunks: tuple   # (sequence id, chunk index) for every chunk this append completes
+    page_edits: tuple = ()    # (sequence id, logical page, physical page) for every page this append maps
 
 
 @dataclass(frozen=True)
@@ -97,12 +98,13 @@ class PageAllocator:
         pool = list(self.free_pages)
         rows = {sid: list(self.tables[sid]) for sid in ids}
         lengths = list(self.lengths)
-        where_seq, where_pos, closed = [], [], []
+        where_seq, where_pos, closed, edits = [], [], [], []
         page, chunk = self.page_size, self.chunk_size
         for sid, n in zip(ids, counts):
             first, last = lengths[sid], lengths[sid] + n
             for logical in range(_ceil_div(first, page), _ceil_div(last, page)):
                 rows[sid][logical] = pool.pop()
+                edits.append((sid, logical, rows[sid][logical]))
             if tokens:
                 where_seq.extend(sid for _ in range(n))
                 where_pos.extend(range(first, last))
@@ -110,7 +112,7 @@ class PageAllocator:
             lengths[sid] = last
         tables = tuple(tuple(rows[s]) if s in rows else self.tables[s] for s in range(self.batch_size))
         return AppendPlan(self.version, tables, tuple(lengths), tuple(pool), tuple(where_seq), tuple(where_pos),
-                          tuple(closed))
+                          tuple(closed), tuple(edits))
 
     def commit(self, plan):
         if plan.version != self.version:

@@ -205,6 +205,10 @@ def test_decode_linear_contract():
     assert call(p, None, None, None, 0.0, None, p, p, 64, 4, 1, p) != 0             # bias with the gate/up epilogue
     assert call(p, None, None, None, 0.0, None, p, None, 16392, 1, 0, p) != 0       # row longer than a group can hold
     assert call(p + 2, None, None, None, 0.0, None, p, None, 64, 4, 0, p) != 0      # unaligned input
+    h, d2, o = t.data_ptr(), t[8:].data_ptr(), t[16:].data_ptr()
+    assert call(None, h, d2, p, 1e-6, h, p, None, 64, 4, 0, o) == 1                 # new residual written in place of h_in
+    assert call(None, h, d2, p, 1e-6, d2, p, None, 64, 4, 0, o) == 1                # ... or of delta
+    assert call(None, h, d2, p, 1e-6, t[24:].data_ptr(), p, None, 64, 4, 0, o) == 0
     torch.cuda.synchronize()
 
 
