@@ -468,16 +468,20 @@ FULL_MODEL = dict(name="qwen2_0.5b_random_prompt16384_greedy256_moba12of24_c512_
                   page=16, dense_layers=tuple(range(0, 24, 2)))
 
 
-def run_full_model(dev):
-    """BASELINE configs[4]: random-init Qwen2-0.5B architecture (24 layers, hidden 896, 14/2 heads, D=64, FFN 4864,
+FULL_MODEL_LONG = dict(FULL_MODEL, name="qwen2_0.5b_random_prompt131072_greedy64_moba12of24_c512_k4", prompt=131072, steps=64)
+
+
+def run_full_model(dev, w=None):
+    """BASELINE configs[4] (and, with w = FULL_MODEL_LONG, the same model on a 131072-token prompt, where a dense layer's
+    K/V is 67 MB per step and attention bytes are what a step waits for): random-init Qwen2-0.5B architecture (24 layers, hidden 896, 14/2 heads, D=64, FFN 4864,
     vocab 151936, N(0, 0.02) bf16), 12 of the 24 layers MoBA (the odd ones; chunk 512, topk 4), batch 1, a prompt of
     16384 uniform-random token ids, then 256 greedy steps under one whole-model CUDA graph, beside the all-dense
     session on the same weights and prompt.  Returns prefill and per-step times (CUDA events)."""
     import torch
     sys.path.insert(0, str(ROOT / "moba-merge-cuda_b200" / "examples"))
     from full_qwen2 import FullQwen2Session, random_qwen2
-    w = FULL_MODEL
-    model = random_qwen2(device=dev)
+    w = w or FULL_MODEL
+    model = random_qwen2(device=dev, max_positions=max(32768, w["prompt"] + w["steps"] + 64))
     ids = torch.randint(0, model.config.vocab_size, (1, w["prompt"]), generator=torch.Generator().manual_seed(0)).to(dev)
     with FullQwen2Session(model, 2048, chunk=w["chunk"], topk=w["topk"], page=w["page"], mode="moba") as s:   # warm-up
         s.prefill(ids[:, :1536])
@@ -822,8 +826,11 @@ def run_ours(args):
         if world == 1 and not args.kernels_only and not args.no_full_model:
             try:
                 line["full_model"] = run_full_model(dev)
+                line["full_model_long"] = run_full_model(dev, FULL_MODEL_LONG)
             except Exception as exc:  # the optional leg must not take the line with it
-                line["full_model"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
+                line.setdefault("full_model", {"error": "%s: %s" % (type(exc).__name__, exc)})
+                if "error" not in line["full_model"]:
+                    line["full_model_long"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
         if cpu_val is not None:
             line["cpu_baseline"] = dict(value=cpu_val, unit=UNIT, cores=os.cpu_count() or 1, kind=cpu_kind, sample=cpu_desc,
                                         seconds=cpu_dt)

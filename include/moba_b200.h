@@ -52,11 +52,14 @@ const char* moba_status_string(int status);
  * expresses the dense fallback of grouped_attention.py:41-46 by passing chunk_size >= max_seqlen).
  */
 #define MOBA_ROUTE_BF16_MEANS 1
+#define MOBA_BWD_DETERMINISTIC 2
 
 typedef struct moba_prefill_desc {
   int32_t total_tokens, num_seqs, hq, hkv, dim, chunk_size, remote_k;
   int32_t num_chunks, num_qtiles, max_tiles_per_seq, max_chunks_per_seq;
-  int32_t flags; /* MOBA_ROUTE_BF16_MEANS: round chunk means to bf16 (route_precision='upstream') */
+  int32_t flags; /* MOBA_ROUTE_BF16_MEANS: round chunk means to bf16 (route_precision='upstream');
+                    MOBA_BWD_DETERMINISTIC: dQ summed in 64-bit fixed point, bit-repeatable (needs the larger scratch
+                    moba_prefill_bwd_scratch_bytes reports for a descriptor with the flag set) */
   int32_t num_self_pairs, reserved0;
   int64_t q_stride_t, q_stride_h, k_stride_t, k_stride_h, v_stride_t, v_stride_h;
   const int32_t* cu_seqlens;
@@ -104,7 +107,9 @@ int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const void* k, c
                      void* scratch, size_t scratch_bytes, void* out, float* lse, unsigned* status, void* stream);
 
 /* Backward (mixed_attention.py:141-225): gradients of out w.r.t. q, k, v with the route held fixed.
- * dq [T,Hq,D], dk/dv [T,Hkv,D] bf16 contiguous. */
+ * dq [T,Hq,D], dk/dv [T,Hkv,D] bf16 contiguous.  dK, dV are bit-repeatable; dQ is summed over key blocks with FP32
+ * reductions in arrival order unless d->flags has MOBA_BWD_DETERMINISTIC (the reference's deterministic=True,
+ * mixed_attention.py:185,220), which costs scalar 64-bit reductions and a scratch twice the size. */
 size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d);
 int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, const void* v, const void* out,
                      const float* lse, const void* dout, const void* route_state, void* scratch, size_t scratch_bytes,
@@ -180,17 +185,6 @@ int moba_decode_stage_inputs(void* q_dst, const void* q_src, size_t q_bytes, voi
 int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
                            int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
                            unsigned* status, void* stream);
-
-/* moba_decode_step_begin followed by moba_decode_route of the same rows, as one launch: the CTA that appends a row
- * already holds its query (after the rotary embedding) and its position, so it scores the chunk means and ranks them
- * on the spot, and the step has one launch boundary less.  q is required (an input when qkv == NULL).  remote, width and
- * the five routing outputs are moba_decode_route's, with the same results bit for bit; umax is
- * moba_decode_union_capacity(hq, hkv, remote, width).  (ops/prepared_decode.py:7-55,78-94 of the reference: five kernels
- * and a torch.topk.) */
-int moba_decode_step_begin_routed(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
-                                  int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
-                                  int remote, int width, float* scores, int32_t* selected, int32_t* u_chunk, uint32_t* u_mask,
-                                  int32_t* u_count, unsigned* status, void* stream);
 
 /* Routing (ops/paged_decode.py:48-64 scores; ops/prepared_decode.py:45-55,78-94 selection): q [rows,hq,dim];
  * scores [rows,hq,width] fp32 (may be null), -inf for chunks not completed before the query's chunk;

@@ -257,105 +257,6 @@ __global__ void __launch_bounds__(256) stage_inputs_kernel(uint4* dq, const uint
   else if (i < nq + nk + nv) dv[i - nq - nk] = sv[i - nq - nk];
 }
 
-constexpr int kStepPartFloats = 2048;  // 8 KB of partial sums / staged K and V rows at the start of the step kernel's shared memory
-
-// Routing outputs of a step whose first launch also routes (remote < 0: it does not).
-struct StepRoute {
-  int remote, width, umax;
-  float* scores;      // [rows, Hq, width] or null
-  int* selected;      // [rows, Hq, 1 + remote]
-  int* u_chunk;       // [rows, Hkv, umax]
-  unsigned* u_mask;
-  int* u_count;       // [rows, Hkv]
-};
-
-// decode_route_kernel's work for one query row, all KV groups at once, by one CTA of 256 threads that already holds
-// the row's query (after the rotary embedding) as FP32 in shared memory and knows its position: a thread per (head,
-// chunk) pair reads the chunk mean straight from L2, a warp ranks a head, a warp builds a group's union list.  The
-// arithmetic - order of the multiply-adds, tie rule, list order - is that kernel's, so both give the same bits.
-__device__ void route_row_cta(const CacheView& cv, int sid, int pos, int row, int Hq, const StepRoute& ro, const float* s_q,
-                              float* s_scores, unsigned* s_mask) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int G = Hq / cv.Hkv, width = ro.width, remote = ro.remote;
-  const int cur = pos / cv.C;
-  const int nlegal = min(min(cur, width), cv.max_chunks);
-  const int upr = cv.D >> 3;
-  for (int i = tid; i < cv.Hkv * (width + 1); i += 256) s_mask[i] = 0u;
-  for (int pair = tid; pair < Hq * width; pair += 256) {
-    const int h = pair / width, c = pair - h * width;
-    float sc = -INFINITY;
-    if (c < nlegal) {
-      const uint4* mrow = reinterpret_cast<const uint4*>(cv.means + (((long long)sid * cv.max_chunks + c) * cv.Hkv + h / G) * cv.D);
-      const float* qrow = s_q + h * cv.D;
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 4
-      for (int u = 0; u < upr; ++u) {
-        const uint4 ma = __ldcg(mrow + u);
-        const float* qq = qrow + u * 8;
-        a0 = fmaf(qq[0], bf_lo(ma.x), a0); a1 = fmaf(qq[1], bf_hi(ma.x), a1);
-        a2 = fmaf(qq[2], bf_lo(ma.y), a2); a3 = fmaf(qq[3], bf_hi(ma.y), a3);
-        a0 = fmaf(qq[4], bf_lo(ma.z), a0); a1 = fmaf(qq[5], bf_hi(ma.z), a1);
-        a2 = fmaf(qq[6], bf_lo(ma.w), a2); a3 = fmaf(qq[7], bf_hi(ma.w), a3);
-      }
-      sc = (a0 + a1) + (a2 + a3);
-    }
-    s_scores[pair] = sc;
-    if (ro.scores) ro.scores[((long long)row * Hq + h) * width + c] = sc;
-  }
-  __syncthreads();
-  for (int h = warp; h < Hq; h += 8) {
-    float* sc = s_scores + h * width;
-    unsigned* mask = s_mask + (h / G) * (width + 1);
-    int* out = ro.selected + ((long long)row * Hq + h) * (remote + 1);
-    if (lane == 0) out[0] = cur;
-    for (int r = 0; r < remote; ++r) {
-      float best = -INFINITY;
-      int idx = 0x7FFFFFFF;
-      for (int c = lane; c < nlegal; c += 32) {
-        const float v = sc[c];
-        if (v > best || (v == best && c < idx && v > -INFINITY)) { best = v; idx = c; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xFFFFFFFFu, best, o);
-        const int oi = __shfl_xor_sync(0xFFFFFFFFu, idx, o);
-        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
-      }
-      const bool found = best > -INFINITY && idx != 0x7FFFFFFF;
-      if (lane == 0) {
-        out[1 + r] = found ? idx : -1;
-        if (found) {
-          sc[idx] = -INFINITY;
-          atomicOr(&mask[idx], 1u << (h % G));
-        }
-      }
-      __syncwarp();
-    }
-  }
-  __syncthreads();
-  for (int g = warp; g < cv.Hkv; g += 8) {  // union list: routed chunks ascending, the own chunk (all heads) last
-    const unsigned* mask = s_mask + g * (width + 1);
-    const long long base = ((long long)row * cv.Hkv + g) * ro.umax;
-    int count = 0;
-    for (int c0 = 0; c0 < nlegal; c0 += 32) {
-      const int c = c0 + lane;
-      const unsigned m = c < nlegal ? mask[c] : 0u;
-      const unsigned bal = __ballot_sync(0xFFFFFFFFu, m != 0u);
-      if (m) {
-        const int at = count + __popc(bal & ((1u << lane) - 1u));
-        if (at < ro.umax - 1) { ro.u_chunk[base + at] = c; ro.u_mask[base + at] = m; }
-      }
-      count += __popc(bal);
-    }
-    if (lane == 0) {
-      count = min(count, ro.umax - 1);
-      ro.u_chunk[base + count] = cur;
-      ro.u_mask[base + count] = G >= 32 ? 0xFFFFFFFFu : ((1u << G) - 1u);
-      ro.u_count[(long long)row * cv.Hkv + g] = count + 1;
-    }
-  }
-}
-
 // --------------------------------------------------------------------------- first launch of an appending decode step
 // Metadata, append and the predicated chunk mean of one request per CTA, and, when the caller hands over the fused
 // q/k/v projection instead of separate k and v, the rotary embedding and the split as well: what were four
@@ -364,7 +265,7 @@ __device__ void route_row_cta(const CacheView& cv, int sid, int pos, int row, in
 __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, const int* ids, int* positions, const int* delta, int b,
                                                                 int Hq, const __nv_bfloat16* qkv, const __nv_bfloat16* cosv,
                                                                 const __nv_bfloat16* sinv, __nv_bfloat16* q, __nv_bfloat16* k,
-                                                                __nv_bfloat16* v, StepRoute ro, unsigned* status) {
+                                                                __nv_bfloat16* v, unsigned* status) {
   // No pointer here is __restrict__ and nothing is read through the read-only path: this grid may start before the
   // kernel that produces its inputs has finished, and a load the compiler may treat as invariant could be moved
   // above the wait below.
@@ -405,13 +306,6 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
                    !(((uintptr_t)qkv | (uintptr_t)cosv | (uintptr_t)sinv | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15);
   const bool staged = vec && cv.Hkv * cv.D <= 2048;  // 2 * Hkv * D bf16 fit the 8 KB of s_part
   uint4* s_kv = reinterpret_cast<uint4*>(s_part);    // [K, V][Hkv][D / 8]
-  // routing region (only with ro.remote >= 0): the query as FP32, the scores, the per-group head masks
-  const bool routed = ro.remote >= 0;
-  float* s_rq = s_part + kStepPartFloats;             // [Hq][D]
-  float* s_scores = s_rq + (routed ? Hq * cv.D : 0);  // [Hq][width]
-  unsigned* s_mask = reinterpret_cast<unsigned*>(s_scores + (routed ? Hq * ro.width : 0));  // [Hkv][width + 1]
-  if (routed && !qkv)
-    for (int i = tid; i < Hq * cv.D; i += 256) s_rq[i] = __bfloat162float(q[(long long)row * Hq * cv.D + i]);
   if (vec) {
     const int heads = Hq + 2 * cv.Hkv, D = cv.D;
     const __nv_bfloat16* src = qkv + (long long)row * heads * D;
@@ -442,10 +336,6 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
       const uint4 res = make_uint4(out[0], out[1], out[2], out[3]);
       if (h < Hq) {
         *reinterpret_cast<uint4*>(q + ((long long)row * Hq + h) * D + c * 8) = res;
-        if (routed) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { s_rq[h * D + c * 8 + 2 * i] = bf_lo(out[i]); s_rq[h * D + c * 8 + 2 * i + 1] = bf_hi(out[i]); }
-        }
       } else {
         *reinterpret_cast<uint4*>(k + ((long long)row * cv.Hkv + (h - Hq)) * D + c * 8) = res;
         if (staged) s_kv[(h - Hq) * upr + c] = res;
@@ -463,7 +353,7 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
       const float c = __bfloat162float(cosv[(long long)row * D + d]), sn = __bfloat162float(sinv[(long long)row * D + d]);
       const __nv_bfloat16 out = __float2bfloat16_rn(__bfloat162float(__float2bfloat16_rn(x * c)) +
                                                     __bfloat162float(__float2bfloat16_rn(rot * sn)));
-      if (h < Hq) { q[((long long)row * Hq + h) * D + d] = out; if (routed) s_rq[h * D + d] = __bfloat162float(out); }
+      if (h < Hq) q[((long long)row * Hq + h) * D + d] = out;
       else k[((long long)row * cv.Hkv + (h - Hq)) * D + d] = out;
     }
   }
@@ -480,9 +370,6 @@ __global__ void __launch_bounds__(256) decode_step_begin_kernel(CacheView cv, co
     *reinterpret_cast<uint4*>(cv.kc + dst) = staged ? s_kv[i] : *reinterpret_cast<const uint4*>(k + src);
     *reinterpret_cast<uint4*>(cv.vc + dst) = staged ? s_kv[cv.Hkv * upr + i] : *reinterpret_cast<const uint4*>(v + src);
   }
-  // Routing of the new query.  Its candidates are the chunks completed before its own chunk, so the mean this launch
-  // may still have to write (below, when the new token completes a chunk) is not among them.
-  if (routed) route_row_cta(cv, sid, pos, row, Hq, ro, s_rq, s_scores, s_mask);
   if ((pos + 1) % cv.C != 0) return;  // the token does not complete its chunk
   const int chunk = pos / cv.C;
   if (chunk >= cv.max_chunks) return;
@@ -1217,47 +1104,21 @@ extern "C" int moba_decode_stage_inputs(void* q_dst, const void* q_src, size_t q
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }
 
-static int step_begin_impl(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows, int hq,
-                           const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v, const StepRoute& ro,
-                           unsigned* status, void* stream) {
+extern "C" int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
+                                      int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
+                                      unsigned* status, void* stream) {
   int rc = validate_cache(c);
   if (rc != MOBA_OK) return rc;
   if (!ids || !positions || !delta || !k || !v || rows < 1) return MOBA_ERR_INVALID;
   if (qkv && (!cosv || !sinv || !q || hq < 1 || hq % c->hkv || (c->dim & 1))) return MOBA_ERR_INVALID;
-  size_t smem = (size_t)kStepPartFloats * 4;
-  if (ro.remote >= 0) {
-    if (!q || hq < 1 || hq % c->hkv || ro.width < 1 || !ro.selected || !ro.u_chunk || !ro.u_mask || !ro.u_count) return MOBA_ERR_INVALID;
-    if (hq / c->hkv > 32 || ro.remote > 16) return MOBA_ERR_UNSUPPORTED;
-    smem += ((size_t)hq * c->dim + (size_t)hq * ro.width + (size_t)c->hkv * (ro.width + 1)) * 4;
-    if (smem > 200 * 1024) return MOBA_ERR_UNSUPPORTED;
-  }
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(decode_step_begin_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-    return MOBA_ERR_CUDA;
-  if (launch_dependent(2u, decode_step_begin_kernel, dim3(rows), dim3(256), smem, (cudaStream_t)stream,
+  const int rpi = 256 / (c->dim / 8);
+  if (launch_dependent(2u, decode_step_begin_kernel, dim3(rows), dim3(256), (size_t)rpi * c->dim * 4, (cudaStream_t)stream,
                        make_cache_view(*c), ids, positions, delta, rows, hq, static_cast<const __nv_bfloat16*>(qkv),
                        static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv),
-                       static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v), ro,
+                       static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v),
                        status) != cudaSuccess)
     return MOBA_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
-}
-
-extern "C" int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta, int rows,
-                                      int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k, void* v,
-                                      unsigned* status, void* stream) {
-  StepRoute none = {};
-  none.remote = -1;
-  return step_begin_impl(c, ids, positions, delta, rows, hq, qkv, cosv, sinv, q, k, v, none, status, stream);
-}
-
-extern "C" int moba_decode_step_begin_routed(const moba_cache_desc* c, const int32_t* ids, int32_t* positions, const int32_t* delta,
-                                             int rows, int hq, const void* qkv, const void* cosv, const void* sinv, void* q, void* k,
-                                             void* v, int remote, int width, float* scores, int32_t* selected, int32_t* u_chunk,
-                                             uint32_t* u_mask, int32_t* u_count, unsigned* status, void* stream) {
-  if (remote < 0 || !c) return MOBA_ERR_INVALID;
-  StepRoute ro = {remote, width, moba_decode_union_capacity(hq, c->hkv, remote, width), scores, selected, u_chunk, u_mask, u_count};
-  return step_begin_impl(c, ids, positions, delta, rows, hq, qkv, cosv, sinv, q, k, v, ro, status, stream);
 }
 
 extern "C" int moba_decode_union_capacity(int hq, int hkv, int remote, int width) {

@@ -5,7 +5,9 @@
 // Launch sequence: dq_acc = 0, delta = rowsum(dO * O), pack dO / LSE / delta per query tile, the KV-stationary main
 // kernel (prefill_attn_bwd_ws.cu for head_dim <= 64, prefill_attn_bwd_ws128.cu above that: dK and dV of a key block
 // accumulate in tensor memory and are written once, dQ of every tile is reduced into the FP32 buffer with vector
-// atomics), dq = bf16(dq_acc).
+// atomics), dq = bf16(dq_acc).  With MOBA_BWD_DETERMINISTIC the accumulator is 64-bit fixed point and the reductions
+// are integer, which makes dQ bit-repeatable like everything else (the reference asks FlashAttention for the same:
+// deterministic=True in both backward calls, mixed_attention.py:185,220).
 #include "prefill_bwd.cuh"
 
 namespace moba {
@@ -44,6 +46,21 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __rest
       make_uint4(bwd_pack_bf16(a.x, a.y), bwd_pack_bf16(a.z, a.w), bwd_pack_bf16(b.x, b.y), bwd_pack_bf16(b.z, b.w));
 }
 
+__global__ void __launch_bounds__(256) bwd_dq_convert_fixed_kernel(const long long* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
+                                                                   long long n8) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n8) return;
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const longlong2 w = reinterpret_cast<const longlong2*>(acc)[4 * i + j];
+    f[2 * j] = (float)((double)w.x * (1.0 / 4294967296.0));
+    f[2 * j + 1] = (float)((double)w.y * (1.0 / 4294967296.0));
+  }
+  reinterpret_cast<uint4*>(dq)[i] =
+      make_uint4(bwd_pack_bf16(f[0], f[1]), bwd_pack_bf16(f[2], f[3]), bwd_pack_bf16(f[4], f[5]), bwd_pack_bf16(f[6], f[7]));
+}
+
 }  // namespace moba
 
 using namespace moba;
@@ -52,7 +69,7 @@ using namespace moba;
 extern "C" size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d) {
   if (validate_desc(d) != MOBA_OK) return 0;
   const size_t rows = (size_t)d->total_tokens * d->hq;
-  size_t bytes = align256(rows * 4) + align256(rows * d->dim * 4);
+  size_t bytes = align256(rows * 4) + align256(rows * d->dim * ((d->flags & MOBA_BWD_DETERMINISTIC) ? 8 : 4));
   {
     const size_t tiles = (size_t)pack_q_tiles(*d);
     bytes += align256(tiles * kTile * pack_dpad(*d) * 2) + 2 * align256(tiles * kTile * 4);
@@ -74,7 +91,9 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   const long long rows = (long long)d->total_tokens * d->hq;
   float* delta = static_cast<float*>(scratch);
   float* dq_acc = reinterpret_cast<float*>(static_cast<char*>(scratch) + align256((size_t)rows * 4));
-  if (cudaMemsetAsync(dq_acc, 0, (size_t)rows * d->dim * 4, st) != cudaSuccess) return MOBA_ERR_CUDA;
+  const bool fixed = (d->flags & MOBA_BWD_DETERMINISTIC) != 0;
+  const size_t acc_bytes = (size_t)rows * d->dim * (fixed ? 8 : 4);
+  if (cudaMemsetAsync(dq_acc, 0, acc_bytes, st) != cudaSuccess) return MOBA_ERR_CUDA;
   {
     const __nv_bfloat16* o16 = static_cast<const __nv_bfloat16*>(out);
     const __nv_bfloat16* do16 = static_cast<const __nv_bfloat16*>(dout);
@@ -105,6 +124,7 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.rowpack = nullptr;
   a.lsepack = a.deltapack = nullptr;
   a.dq_acc = dq_acc;
+  a.dq_fixed = fixed ? reinterpret_cast<unsigned long long*>(dq_acc) : nullptr;
   a.dk = static_cast<__nv_bfloat16*>(dk);
   a.dv = static_cast<__nv_bfloat16*>(dv);
   a.status = status;
@@ -112,7 +132,7 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   a.scale_log2 = (float)(1.4426950408889634 / sqrt((double)d->dim));
   {
     const size_t tiles = (size_t)pack_q_tiles(*d);
-    char* p = reinterpret_cast<char*>(dq_acc) + align256((size_t)rows * d->dim * 4);
+    char* p = reinterpret_cast<char*>(dq_acc) + align256(acc_bytes);
     void* dopack = p; p += align256(tiles * kTile * pack_dpad(*d) * 2);
     float* lsepack = reinterpret_cast<float*>(p); p += align256(tiles * kTile * 4);
     float* deltapack = reinterpret_cast<float*>(p);
@@ -128,6 +148,10 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   prof_end(kProfBwdMain, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;
   const long long n8 = rows * d->dim / 8;
-  bwd_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
+  if (fixed)
+    bwd_dq_convert_fixed_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const long long*>(dq_acc),
+                                                                           static_cast<__nv_bfloat16*>(dq), n8);
+  else
+    bwd_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

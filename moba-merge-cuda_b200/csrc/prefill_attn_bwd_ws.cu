@@ -190,8 +190,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
           const int rth = __shfl_sync(0xFFFFFFFFu, th, rl);
           const uint4 w = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((c4 ^ (rl & 7)) << 4));
           if (rth >= 0 && alive && col < D)
-            red_add_v4(a.dq_acc + (long long)rth * D + col, __uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z),
-                       __uint_as_float(w.w));
+            dq_accumulate(a.dq_acc, a.dq_fixed, (long long)rth * D + col, __uint_as_float(w.x), __uint_as_float(w.y),
+                          __uint_as_float(w.z), __uint_as_float(w.w));
         }
         __syncwarp();
       }

@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
           const int rth = __shfl_sync(0xFFFFFFFFu, piece < 2 ? th0 : th1, qi);
           const float4 w = *reinterpret_cast<const float4*>(stage + ql * 32 + (lane & 7) * 4);
           const int col = quad * 32 + (lane & 7) * 4;
-          if (rth >= 0 && alive && col < D) red_add_v4(a.dq_acc + (long long)rth * D + col, w.x, w.y, w.z, w.w);
+          if (rth >= 0 && alive && col < D) dq_accumulate(a.dq_acc, a.dq_fixed, (long long)rth * D + col, w.x, w.y, w.z, w.w);
         }
         __syncwarp();
       }

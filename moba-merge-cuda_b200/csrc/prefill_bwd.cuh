@@ -19,6 +19,23 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
+// dQ contribution into the accumulator.  Ordinary mode: one FP32 vector reduction (the order in which the key blocks'
+// contributions arrive is not fixed, so the last bit of a sum may differ between runs).  Deterministic mode: the
+// accumulator holds 64-bit fixed-point numbers (32 fractional bits) and integer addition does not care about order,
+// so dQ is bit-repeatable; the reductions are scalar and cost more.
+__device__ __forceinline__ void dq_accumulate(float* acc, unsigned long long* acc_fixed, long long index, float a, float b, float c,
+                                              float d) {
+  if (acc_fixed) {
+    unsigned long long* p = acc_fixed + index;
+    atomicAdd(p, (unsigned long long)__float2ll_rn(a * 4294967296.f));
+    atomicAdd(p + 1, (unsigned long long)__float2ll_rn(b * 4294967296.f));
+    atomicAdd(p + 2, (unsigned long long)__float2ll_rn(c * 4294967296.f));
+    atomicAdd(p + 3, (unsigned long long)__float2ll_rn(d * 4294967296.f));
+  } else {
+    red_add_v4(acc + index, a, b, c, d);
+  }
+}
+
 struct BwdArgs {
   PrefillView pv;
   const __nv_bfloat16* q;
@@ -39,7 +56,8 @@ struct BwdArgs {
   const int* rowpack;           // [tiles][128] t*Hq+h, -1 = padding row
   const float* lsepack;         // [tiles][128] LSE * log2(e), +inf for padding rows
   const float* deltapack;       // [tiles][128] delta / sqrt(D)
-  float* dq_acc;        // [T,Hq,D] fp32, zero-initialised
+  float* dq_acc;        // [T,Hq,D] fp32, zero-initialised (ordinary mode)
+  unsigned long long* dq_fixed;  // [T,Hq,D] 64-bit fixed point, zero-initialised (deterministic mode), else null
   __nv_bfloat16* dk;    // [T,Hkv,D] contiguous
   __nv_bfloat16* dv;
   unsigned* status;

@@ -98,20 +98,24 @@ __device__ __forceinline__ float sum2(unsigned long long v) {
   return lo + hi;
 }
 
-// grid (query tile, query head); 128 * LPR threads: LPR lanes share a row, each holding DH of its DH * LPR (padded)
-// head dimensions as FP32 in registers for the whole launch, converted from bf16 once.  The candidate means sit in
-// shared memory as FP32 and are read as broadcast 16-byte loads, so a candidate costs DH / 2 packed FMAs and DH / 4
-// shared loads per thread and the pass runs at the speed Q arrives from memory.
-template <int RT, int DH, int LPR>
-__global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, const __nv_bfloat16* __restrict__ q,
-                                                              const float* __restrict__ means, int* __restrict__ sel,
-                                                              int* __restrict__ cnt) {
+// grid (query tile, query head).  A group of LPR lanes shares four query rows: each lane keeps DD of the DD * LPR
+// (padded) head dimensions of all four rows as FP32 in registers for the whole launch, converted from bf16 once.  The
+// candidate means sit in shared memory as FP32; one 16-byte broadcast load feeds eight packed FMAs (four rows), which
+// is what keeps the shared-memory pipe below the FMA pipe - with one row per lane it is the limit.  The four partial
+// sums of a lane are combined across the group by a butterfly of three (LPR = 4) or four (LPR = 8) shuffles that
+// leaves every lane with the complete score of one row, for which it then keeps the running top-R.
+//   LPR = 4: 128 threads, 32 rows per warp.  LPR = 8: 256 threads, 16 rows per warp.
+template <int RT, int DD, int LPR>
+__global__ void __launch_bounds__(32 * LPR) gate_topk_kernel(PrefillView pv, const __nv_bfloat16* __restrict__ q,
+                                                             const float* __restrict__ means, int* __restrict__ sel,
+                                                             int* __restrict__ cnt) {
   extern __shared__ __align__(16) uint8_t smem[];
-  constexpr int DP = DH * LPR;
-  constexpr int NT = 128 * LPR;
+  constexpr int DP = DD * LPR;
+  constexpr int NT = 32 * LPR;
+  constexpr int RPW = 128 / LPR;           // rows per warp
   const int D = pv.D, R = pv.R;
-  constexpr int qrow_bytes = DP * 2 + 16;  // padded so that per-thread row reads are conflict-free
-  float4* s_means = reinterpret_cast<float4*>(smem);                      // [kCandBatch][DP / 4], 16-byte units interleaved by lane of the row
+  constexpr int qrow_bytes = DP * 2 + 16;  // padded so that the rows of a warp start in different banks
+  float4* s_means = reinterpret_cast<float4*>(smem);                      // [kCandBatch][DP / 4], 16-byte units interleaved by lane of the group
   uint8_t* s_q = smem + (size_t)kCandBatch * DP * 4;                      // [128][qrow_bytes]
   int* s_cnt = reinterpret_cast<int*>(s_q + (size_t)kTile * qrow_bytes);  // [ncand]
 
@@ -121,12 +125,14 @@ __global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, co
   const int ncand = pv.chunk_local[c];
   const int c0 = c - ncand;
   const int nrows = min(kTile, pv.chunk_start[c + 1] - tok0);
-  const int tid = threadIdx.x;
-  const int row = tid / LPR, part = tid - row * LPR;
-  const bool valid = row < nrows;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int part = lane % LPR;
+  const int row0 = warp * RPW + (lane / LPR) * 4;                         // first of the group's four rows
+  const int row = row0 + (part & 1) * 2 + ((part >> 1) & 1);              // the row whose score this lane ends up with
+  const bool owner = row < nrows && part < 4;
   int* out = sel + ((long long)(tok0 + row) * pv.Hq + h) * R;
   if (ncand == 0) {  // first chunk of a sequence: nothing to route to
-    if (valid && part == 0)
+    if (owner)
       for (int s = 0; s < R; ++s) out[s] = -1;
     return;
   }
@@ -139,7 +145,7 @@ __global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, co
   cp_async_commit();
   for (int i = tid; i < ncand; i += NT) s_cnt[i] = 0;
 
-  unsigned long long qp[DH / 2];
+  unsigned long long qp[4][DD / 2];
   float topv[RT];
   int topi[RT];
 #pragma unroll
@@ -153,19 +159,22 @@ __global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, co
       const int d0 = f4 * 4;
       float4 mv = make_float4(0.f, 0.f, 0.f, 0.f);
       if (d0 < D) mv = *reinterpret_cast<const float4*>(means + ((long long)(c0 + cb + ci) * pv.Hkv + g) * D + d0);
-      s_means[ci * (DP / 4) + ((d0 % DH) >> 2) * LPR + d0 / DH] = mv;
+      s_means[ci * (DP / 4) + ((d0 % DD) >> 2) * LPR + d0 / DD] = mv;
     }
     if (cb == 0) {
       cp_async_wait<0>();
       __syncthreads();
-      const uint8_t* qrow = s_q + (size_t)row * qrow_bytes + part * (DH * 2);
 #pragma unroll
-      for (int u = 0; u < DH / 8; ++u) {
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-        if (valid) raw = *reinterpret_cast<const uint4*>(qrow + u * 16);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      for (int j = 0; j < 4; ++j) {
+        const uint8_t* qrow = s_q + (size_t)(row0 + j) * qrow_bytes + part * (DD * 2);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) qp[u * 4 + i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+        for (int u = 0; u < DD / 8; ++u) {
+          uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+          if (row0 + j < nrows) raw = *reinterpret_cast<const uint4*>(qrow + u * 16);
+          const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) qp[j][u * 4 + i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+        }
       }
     } else {
       __syncthreads();
@@ -175,16 +184,19 @@ __global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, co
       const ulonglong2* m = reinterpret_cast<const ulonglong2*>(s_means + ci * (DP / 4) + part);
       unsigned long long a0 = 0ull, a1 = 0ull, a2 = 0ull, a3 = 0ull;
 #pragma unroll
-      for (int j = 0; j < DH / 4; j += 2) {
-        const ulonglong2 m0 = m[j * LPR];
-        const ulonglong2 m1 = m[(j + 1) * LPR];
-        fma2(a0, qp[2 * j], m0.x);
-        fma2(a1, qp[2 * j + 1], m0.y);
-        fma2(a2, qp[2 * j + 2], m1.x);
-        fma2(a3, qp[2 * j + 3], m1.y);
+      for (int jj = 0; jj < DD / 4; ++jj) {
+        const ulonglong2 mv = m[jj * LPR];
+        fma2(a0, qp[0][2 * jj], mv.x); fma2(a1, qp[1][2 * jj], mv.x); fma2(a2, qp[2][2 * jj], mv.x); fma2(a3, qp[3][2 * jj], mv.x);
+        fma2(a0, qp[0][2 * jj + 1], mv.y); fma2(a1, qp[1][2 * jj + 1], mv.y); fma2(a2, qp[2][2 * jj + 1], mv.y);
+        fma2(a3, qp[3][2 * jj + 1], mv.y);
       }
-      float score = (sum2(a0) + sum2(a1)) + (sum2(a2) + sum2(a3));
-      if (LPR == 2) score += __shfl_xor_sync(0xFFFFFFFFu, score, 1);   // both lanes of the row get the same bits
+      const float s0 = sum2(a0), s1 = sum2(a1), s2 = sum2(a2), s3 = sum2(a3);
+      // butterfly over the group: lanes with an odd index keep rows 2 and 3, then lanes 2, 3 (mod 4) the second of the pair
+      const bool odd = part & 1, upper = part & 2;
+      const float t0 = (odd ? s2 : s0) + __shfl_xor_sync(0xFFFFFFFFu, odd ? s0 : s2, 1);
+      const float t1 = (odd ? s3 : s1) + __shfl_xor_sync(0xFFFFFFFFu, odd ? s1 : s3, 1);
+      float score = (upper ? t1 : t0) + __shfl_xor_sync(0xFFFFFFFFu, upper ? t0 : t1, 2);
+      if (LPR == 8) score += __shfl_xor_sync(0xFFFFFFFFu, score, 4);   // both lanes of the pair get the same bits
       // strict '>' keeps the earlier (lower) chunk on exact ties; infinities never enter
       if (score > topv[RT - 1] && score < INFINITY) {
         float v = score;
@@ -200,7 +212,7 @@ __global__ void __launch_bounds__(128 * LPR) gate_topk_kernel(PrefillView pv, co
     }
   }
   // keep the R best, emit them in ascending chunk order
-  if (valid && part == 0) {
+  if (owner) {
     int last = -1;
     for (int s = 0; s < R; ++s) {
       int best = 0x7FFFFFFF;
@@ -360,23 +372,23 @@ int validate_desc(const moba_prefill_desc* d) {
   return MOBA_OK;
 }
 
-template <int RT, int DH, int LPR>
+template <int RT, int DD, int LPR>
 static cudaError_t launch_gate_as(const PrefillView& pv, const __nv_bfloat16* q, const float* means, int* sel, int* cnt,
                                   int max_chunks_per_seq, cudaStream_t st) {
-  constexpr int DP = DH * LPR;
+  constexpr int DP = DD * LPR;
   const size_t smem = (size_t)kCandBatch * DP * 4 + (size_t)kTile * (DP * 2 + 16) + (size_t)max_chunks_per_seq * 4 + 16;
-  cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel<RT, DH, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(gate_topk_kernel<RT, DD, LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  gate_topk_kernel<RT, DH, LPR><<<dim3(pv.n_qtiles, pv.Hq), 128 * LPR, smem, st>>>(pv, q, means, sel, cnt);
+  gate_topk_kernel<RT, DD, LPR><<<dim3(pv.n_qtiles, pv.Hq), 32 * LPR, smem, st>>>(pv, q, means, sel, cnt);
   return cudaGetLastError();
 }
 
 template <int RT>
 static cudaError_t launch_gate(const PrefillView& pv, const __nv_bfloat16* q, const float* means, int* sel, int* cnt,
                                int max_chunks_per_seq, cudaStream_t st) {
-  if (pv.D <= 32) return launch_gate_as<RT, 32, 1>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
-  if (pv.D <= 64) return launch_gate_as<RT, 64, 1>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
-  return launch_gate_as<RT, 64, 2>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
+  if (pv.D <= 32) return launch_gate_as<RT, 8, 4>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
+  if (pv.D <= 64) return launch_gate_as<RT, 16, 4>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
+  return launch_gate_as<RT, 16, 8>(pv, q, means, sel, cnt, max_chunks_per_seq, st);
 }
 
 // Layout of the routing scratch.  Only `tickets` has to be zero when a call starts (route_impl clears it).

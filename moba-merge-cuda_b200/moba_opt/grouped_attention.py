@@ -167,7 +167,7 @@ class _MobaPrefill(torch.autograd.Function):
     (src/moba_opt/mixed_attention.py:40-225) with routing included."""
 
     @staticmethod
-    def forward(ctx, q, k, v, plan, remote_k, flags):
+    def forward(ctx, q, k, v, plan, remote_k, flags, bwd_flags):
         lib = _ext.lib()
         q, k, v = _aligned(q), _aligned(k), _aligned(v)
         with torch.cuda.device(q.device):
@@ -184,7 +184,7 @@ class _MobaPrefill(torch.autograd.Function):
                                             out.data_ptr(), lse.data_ptr(), _status_word(q.device).data_ptr(),
                                             _stream(q.device)), "moba_prefill_fwd")
         ctx.save_for_backward(q, k, v, out, lse, state)
-        ctx.plan, ctx.remote_k = plan, remote_k
+        ctx.plan, ctx.remote_k, ctx.bwd_flags = plan, remote_k, bwd_flags
         ctx.mark_non_differentiable(lse)
         return out, lse
 
@@ -195,7 +195,7 @@ class _MobaPrefill(torch.autograd.Function):
         plan, remote_k = ctx.plan, ctx.remote_k
         d_out = d_out.contiguous()
         with torch.cuda.device(q.device):
-            d = plan.desc(q, k, v, remote_k)
+            d = plan.desc(q, k, v, remote_k, ctx.bwd_flags)
             nbytes = lib.moba_prefill_bwd_scratch_bytes(ctypes.byref(d))
             scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
             dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
@@ -205,7 +205,7 @@ class _MobaPrefill(torch.autograd.Function):
                                             lse.data_ptr(), d_out.data_ptr(), state.data_ptr(),
                                             scratch.data_ptr(), nbytes, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                                             _status_word(q.device).data_ptr(), _stream(q.device)), "moba_prefill_bwd")
-        return dq, dk, dv, None, None, None
+        return dq, dk, dv, None, None, None, None
 
 
 def _fire_hook(plan, state, total, hq, remote_k):
@@ -228,9 +228,10 @@ def moba_prefill(q, k, v, cu_seqlens, max_seqlen, config, *, return_lse=False):
     precision = config.get("route_precision", "upstream")   # the reference's default (grouped_attention.py:35)
     deterministic = config.get("deterministic_merge", True)
     stable = config.get("stable_routes", True)
+    repeatable_grads = config.get("deterministic_backward", False)
     if precision not in ("upstream", "fp32"):
         raise ValueError("route_precision")
-    if not isinstance(deterministic, bool) or not isinstance(stable, bool):
+    if not isinstance(deterministic, bool) or not isinstance(stable, bool) or not isinstance(repeatable_grads, bool):
         raise ValueError("routing flags must be bool")
     flags = 1 if precision == "upstream" else 0  # MOBA_ROUTE_BF16_MEANS
     plan = get_plan(cu, chunk_size, q.device)
@@ -239,7 +240,7 @@ def moba_prefill(q, k, v, cu_seqlens, max_seqlen, config, *, return_lse=False):
         # K=1 or no routable chunk: dense causal attention over every whole sequence
         # (grouped_attention.py:41-46), expressed as one chunk per sequence.
         plan = get_plan(cu, max(b - a for a, b in zip(cu, cu[1:])), q.device)
-    out, lse = _MobaPrefill.apply(q, k, v, plan, remote_k, flags)
+    out, lse = _MobaPrefill.apply(q, k, v, plan, remote_k, flags, 2 if repeatable_grads else 0)   # MOBA_BWD_DETERMINISTIC
     return (out, lse) if return_lse else out
 
 
@@ -250,7 +251,10 @@ def opt_gqa_cuda(q, k, v, cu_seqlens, max_seqlen, config):
     and type-checked; where the reference's default stable_routes=False leaves the order among exactly
     tied scores to torch.topk, the lowest chunk wins here).  route_precision defaults to 'upstream' as in
     the reference (grouped_attention.py:35): the chunk means are rounded to bf16 before the gate
-    (grouped_attention.py:52); 'fp32' keeps them in FP32."""
+    (grouped_attention.py:52); 'fp32' keeps them in FP32.  One key of this package's own:
+    deterministic_backward (bool, default False) sums dQ in fixed point, so that the gradients are
+    bit-repeatable too (the reference gets that from FlashAttention's deterministic=True,
+    mixed_attention.py:185,220); dK, dV and the forward always are."""
     return moba_prefill(q, k, v, cu_seqlens, max_seqlen, config)
 
 

@@ -53,8 +53,6 @@ _DECODE_ABI = {
     "moba_decode_append": (_I, [_P, _VP, _VP, _VP, _VP, _I, _VP, _VP]),
     "moba_decode_means": (_I, [_P, _VP, _VP, _I, _I, _VP, _VP]),
     "moba_decode_step_begin": (_I, [_P, _VP, _VP, _VP, _I, _I, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
-    "moba_decode_step_begin_routed": (_I, [_P, _VP, _VP, _VP, _I, _I, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP, _VP, _VP, _VP,
-                                           _VP, _VP, _VP]),
     "moba_decode_stage_inputs": (_I, [_VP, _VP, _SZ, _VP, _VP, _SZ, _VP, _VP, _SZ, _VP]),
     "moba_prefill_to_cache": (_I, [_P, _VP, _VP, _VP, _VP, _VP, _I, _I, _VP, _VP]),
     "moba_decode_union_capacity": (_I, [_I, _I, _I, _I]),

@@ -8,10 +8,9 @@ persistent buffers and are overwritten by the next call.
 
 How a step runs here: the host plans the pages (a few integer operations) and, only when some
 sequence opens a new page, sends a 2 x b int32 delta from a ring of pinned buffers; the device work is
-two launches whose shapes were fixed at preparation - `moba_decode_step_begin_routed` (metadata,
-append, predicated chunk mean and the routing of the new query in one kernel) and
-`moba_decode_attend` - or one plus the attention for dense plans.  Fixed shapes, fixed addresses and
-positions read from device memory are what make the step capturable.
+three launches whose shapes were fixed at preparation - `moba_decode_step_begin` (metadata, append and
+predicated chunk mean in one kernel), `moba_decode_route`, `moba_decode_attend` - two for dense plans.
+Fixed shapes, fixed addresses and positions read from device memory are what make the step capturable.
 
 Besides the reference's methods there is a small driver interface for callers that run several plans
 inside one graph of their own (a model session with one plan per layer): `plan_step`, `send_delta`,
@@ -223,19 +222,13 @@ class PreparedDecode:
         if kind == "step":
             qkv, cos, sin = (None, None, None) if projected is None else (t.data_ptr() for t in projected)
             buffers = (self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr())
-            if self.dense:
-                _ext.check(lib.moba_decode_step_begin(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, h, qkv, cos, sin,
-                                                      *buffers, status, st), "moba_decode_step_begin")
-            else:
-                _ext.check(lib.moba_decode_step_begin_routed(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, h, qkv, cos, sin,
-                                                             *buffers, self.remote, self.width, self.scores.data_ptr(),
-                                                             self.selected.data_ptr(), *union, status, st),
-                           "moba_decode_step_begin_routed")
+            _ext.check(lib.moba_decode_step_begin(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, h, qkv, cos, sin,
+                                                  *buffers, status, st), "moba_decode_step_begin")
         else:
             _ext.check(lib.moba_decode_metadata(ctypes.byref(d), ids, pos, self.delta.data_ptr(), b, 0, st), "moba_decode_metadata")
-            if not self.dense:
-                _ext.check(lib.moba_decode_route(ctypes.byref(d), self.q.data_ptr(), ids, pos, b, h, self.remote, self.width,
-                                                 self.scores.data_ptr(), self.selected.data_ptr(), *union, st), "moba_decode_route")
+        if not self.dense:
+            _ext.check(lib.moba_decode_route(ctypes.byref(d), self.q.data_ptr(), ids, pos, b, h, self.remote, self.width,
+                                             self.scores.data_ptr(), self.selected.data_ptr(), *union, st), "moba_decode_route")
         _ext.check(lib.moba_decode_attend(ctypes.byref(d), self.q.data_ptr(), ids, pos, b, h,
                                           None if self.dense else self.selected.data_ptr(), self._slots, *union, self._umax,
                                           self._workspace.data_ptr(), self._ws_bytes, self.output.data_ptr(),

@@ -128,3 +128,36 @@ def test_legacy_names_run_the_same_engine():
         assert torch.equal(moba_opt.run_impl(name, q, k, v, cu, 600, cfg), ref)
     with pytest.raises(ValueError):
         moba_opt.run_impl("opt_merge_cuda", q, k[:, :2], v[:, :2], cu, 600, cfg)
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,chunk,topk,lens", [(8, 2, 64, 64, 3, (300, 212)), (4, 4, 128, 128, 4, (700,)), (6, 1, 32, 16, 9, (200,))])
+def test_merge_stage_fixture_of_the_prefill_forward(heads, kv_heads, dim, chunk, topk, lens):
+    """The merge-stage payload of moba_opt.diagnostic (the counterpart of the reference's MERGE_HOOK dump,
+    scripts/dump_merge_fixtures.py:29-60): the self branch and the per-slot remote rows it lists, merged by the
+    standalone operator and by the FP64 oracle, give the output and LSE the fused forward returned - which pins the
+    epilogue merge of the forward kernel as an operator of its own."""
+    from moba_opt import diagnostic
+    from moba_opt.ops.merge_cuda import merge_forward_cuda
+    payload = diagnostic.dump_merge_fixture(sum(lens), heads, kv_heads, dim, chunk, topk, seq_lens=lens, seed=5)
+    inp, exp = payload["inputs"], payload["expected"]
+    total = sum(lens)
+    assert inp["self_out"].shape == (total, heads, dim) and inp["remote_out"].shape[1:] == (1, dim)
+    counts = torch.bincount(inp["mapping"], minlength=total * heads)
+    per_row = np.concatenate([np.minimum(topk - 1, np.arange(n) // chunk) for n in lens])      # selected chunks per token
+    assert torch.equal(counts.reshape(total, heads), torch.from_numpy(per_row)[:, None].expand(total, heads))
+    want, want_lse = _oracle(inp["self_out"], inp["self_lse"], inp["remote_out"], inp["remote_lse"], inp["mapping"])
+    np.testing.assert_allclose(exp["output"].double().numpy(), want, atol=2e-2, rtol=2e-2)
+    np.testing.assert_allclose(exp["mixed_lse"].double().numpy(), want_lse, atol=2e-3, rtol=2e-5)
+    dev = {k_: v_.cuda() for k_, v_ in inp.items()}
+    out, lse = merge_forward_cuda(dev["self_out"], dev["self_lse"], dev["remote_out"], dev["remote_lse"], dev["mapping"])
+    np.testing.assert_allclose(out.double().cpu().numpy(), exp["output"].double().numpy(), atol=2e-2, rtol=2e-2)
+    np.testing.assert_allclose(lse.double().cpu().numpy(), exp["mixed_lse"].double().numpy(), atol=2e-3, rtol=2e-5)
+    # the hook form: same phases, same tensor names as the reference's diagnostic forward
+    seen = {}
+    diagnostic.MERGE_HOOK = lambda phase, tensors: seen.__setitem__(phase, sorted(tensors))
+    try:
+        q = torch.randn(64, 4, 32, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+        diagnostic.moba_attn_varlen(q, q, q, torch.tensor([0, 64], dtype=torch.int32, device="cuda"), 64, 16, 3)
+    finally:
+        diagnostic.MERGE_HOOK = None
+    assert seen == {"inputs": ["mapping", "remote_lse", "remote_out", "self_lse", "self_out"], "outputs": ["mixed_lse", "output"]}

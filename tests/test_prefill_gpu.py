@@ -213,6 +213,33 @@ def test_gradients_against_oracle_on_seeded_inputs(lens, hq, hkv, dim, chunk, to
         _check_close(key, torch_to_f64(got), ref[key])
 
 
+@pytest.mark.parametrize("lens,hq,hkv,dim,chunk,topk", [((1500, 800), 4, 2, 64, 256, 3), ((1024,), 8, 2, 128, 128, 5)])
+def test_deterministic_backward_is_bit_repeatable(lens, hq, hkv, dim, chunk, topk):
+    """deterministic_backward=True (the counterpart of deterministic=True in the reference's two backward calls,
+    src/moba_opt/mixed_attention.py:185,220): dQ of a row is the sum of the contributions of many key blocks; summed in
+    fixed point it has the same bits run after run, and it still meets the tolerance against the oracle."""
+    rng = torch.Generator().manual_seed(77)
+    total = sum(lens)
+    q, k, v = [torch.randn(total, h, dim, generator=rng).bfloat16() for h in (hq, hkv, hkv)]
+    do = torch.randn(total, hq, dim, generator=rng).bfloat16()
+    cu = cu_from_lens(lens)
+    _, _, captured, first = _run(q, k, v, cu, chunk, topk, d_out=do, deterministic_backward=True)
+    for _ in range(20):
+        _, _, _, again = _run(q, k, v, cu, chunk, topk, d_out=do, deterministic_backward=True)
+        for a, b in zip(first, again):
+            assert torch.equal(a, b)
+    qf, kf, vf, dof = (torch_to_f64(t) for t in (q, k, v, do))
+    r = mo.route_prefill(qf, kf, cu, chunk, topk)
+    sel = mo.sel_from_selected(captured["selected"].numpy(), r["filtered"], r["sel"].shape[-1])
+    ref = mo.attention_fixed_route(qf, kf, vf, cu, sel, chunk, d_out=dof)
+    for key, got in zip(("dq", "dk", "dv"), first):
+        _check_close(key, torch_to_f64(got), ref[key])
+    _, _, _, plain = _run(q, k, v, cu, chunk, topk, d_out=do)
+    assert torch.equal(plain[1], first[1]) and torch.equal(plain[2], first[2])      # dK, dV do not depend on the mode
+    with pytest.raises(ValueError):
+        _run(q, k, v, cu, chunk, topk, d_out=do, deterministic_backward=1)
+
+
 def test_non_contiguous_inputs_and_sequence_isolation():
     """Strided q/k/v views give the same result, and rows of one sequence do not depend on another
     sequence's tokens (tests/test_attention_opt.py causal & sequence isolation in the reference)."""
