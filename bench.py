@@ -255,7 +255,7 @@ def run_decode(dev, rank, world, steps, lib):
     (sharding.balance_requests over sharding.expected_decode_tokens), not round-robin: the step time of the job is
     the slowest rank's.  Returns tokens/s, algorithmic HBM bytes per step (union of attended tokens per (request,
     kv head), K and V, from the actual selected tables) and timings, among them the step with the all-gather of
-    the step's outputs to every rank (sharding.gather_assigned) included."""
+    the step's outputs to every rank (sharding.RowGather) included."""
     import torch
     import torch.distributed as dist
     from moba_opt import PagedKVCache, sharding
@@ -266,8 +266,9 @@ def run_decode(dev, rank, world, steps, lib):
     assignment = sharding.balance_requests(costs, world)
     lens = [all_lens[i] for i in assignment[rank]]
     b = len(lens)
-    max_len = w["hi"] + steps + 64
-    pages = sum(-(-(n + steps + 64) // w["page"]) for n in lens)
+    extra = steps + 5 + 4 + 8 + 3 + min(steps, 128) + 16     # every step this leg takes: warm-up, timed, sampled, eager, gathered
+    max_len = w["hi"] + extra
+    pages = sum(-(-(n + extra) // w["page"]) for n in lens)
     cache = PagedKVCache(b, max_len, w["hkv"], w["dim"], page_size=w["page"], num_pages=pages, chunk_size=w["chunk"])
     free = list(cache._layout.free_pages)
     np.random.default_rng(1 + rank).shuffle(free)          # physical pages in random order
@@ -331,13 +332,14 @@ def run_decode(dev, rank, world, steps, lib):
     gather_ms = None
     if world > 1:
         n = min(steps, 128)
+        gather = sharding.RowGather(assignment, plan.output)
         for _ in range(3):
-            sharding.gather_assigned(plan.step(qs[0], ks[0], vs[0], use_graph=True).output, assignment)
+            gather(plan.step(qs[0], ks[0], vs[0], use_graph=True).output)
         dist.barrier()
         torch.cuda.synchronize()
         e0.record()
         for i in range(n):
-            sharding.gather_assigned(plan.step(qs[i % 8], ks[i % 8], vs[i % 8], use_graph=True).output, assignment)
+            gather(plan.step(qs[i % 8], ks[i % 8], vs[i % 8], use_graph=True).output)
         e1.record()
         torch.cuda.synchronize()
         gather_ms = e0.elapsed_time(e1) / n

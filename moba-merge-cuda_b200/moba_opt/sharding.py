@@ -57,23 +57,44 @@ def balance_requests(costs, world):
     return [sorted(rows) for rows in owned]
 
 
+class RowGather:
+    """Per-step gather of decode outputs to every rank, in request order, for a fixed assignment (one list of request
+    indices per rank, as `balance_requests` returns; rank r's local rows are in the order of assignment[r]).  Buffers
+    and the reordering index are built once; a call is one copy into the send slot, one all-gather and one
+    index-select."""
+
+    def __init__(self, assignment, like, group=None):
+        self.group, self.world = group, dist.get_world_size(group)
+        if len(assignment) != self.world:
+            raise ValueError("one list of requests per rank required")
+        self.assignment = [list(rows) for rows in assignment]
+        self.width = max(len(rows) for rows in self.assignment)
+        tail = tuple(like.shape[1:])
+        self.parts = like.new_zeros((self.world, self.width) + tail)
+        self.mine = self.parts[dist.get_rank(group)]
+        total = sum(len(rows) for rows in self.assignment)
+        where = [0] * total
+        for r, rows in enumerate(self.assignment):
+            for j, request in enumerate(rows):
+                where[request] = r * self.width + j
+        self.where = torch.tensor(where, dtype=torch.long, device=like.device)
+        self.nccl = dist.get_backend(group) == "nccl"
+
+    def __call__(self, local):
+        if self.world == 1:
+            return local
+        send = self.mine if self.nccl else torch.zeros_like(self.mine)
+        send[: local.shape[0]].copy_(local)
+        if self.nccl:      # in place: the send slot is this rank's slice of the receive buffer
+            dist.all_gather_into_tensor(self.parts, send, group=self.group)
+        else:
+            dist.all_gather(list(self.parts.unbind(0)), send, group=self.group)
+        return self.parts.reshape((self.world * self.width,) + tuple(self.parts.shape[2:])).index_select(0, self.where)
+
+
 def gather_assigned(local, assignment, group=None):
-    """All-gathers per-rank request rows back into request order, for an arbitrary assignment (one list of request
-    indices per rank, as `balance_requests` returns; rank r's local rows are in the order of assignment[r])."""
-    world = dist.get_world_size(group)
-    if len(assignment) != world:
-        raise ValueError("one list of requests per rank required")
-    if world == 1:
-        return local
-    width = max(len(rows) for rows in assignment)
-    padded = local.new_zeros((width,) + tuple(local.shape[1:]))
-    padded[: local.shape[0]] = local
-    parts = [torch.empty_like(padded) for _ in range(world)]
-    dist.all_gather(parts, padded, group=group)
-    out = local.new_empty((sum(len(rows) for rows in assignment),) + tuple(local.shape[1:]))
-    for r, rows in enumerate(assignment):
-        out[torch.as_tensor(rows, dtype=torch.long, device=out.device)] = parts[r][: len(rows)]
-    return out
+    """One-off form of `RowGather`."""
+    return RowGather(assignment, local, group)(local)
 
 
 def gather_heads(local, group=None):
