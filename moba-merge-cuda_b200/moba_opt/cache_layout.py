@@ -96,21 +96,24 @@ class PageAllocator:
         if self._pages_needed(ids, counts) > len(self.free_pages):
             raise ValueError("KV page pool exhausted; cache was not modified")
         pool = list(self.free_pages)
-        rows = {sid: list(self.tables[sid]) for sid in ids}
+        rows = {}                                   # only the rows that receive a page are rebuilt
         lengths = list(self.lengths)
         where_seq, where_pos, closed, edits = [], [], [], []
         page, chunk = self.page_size, self.chunk_size
         for sid, n in zip(ids, counts):
             first, last = lengths[sid], lengths[sid] + n
-            for logical in range(_ceil_div(first, page), _ceil_div(last, page)):
-                rows[sid][logical] = pool.pop()
-                edits.append((sid, logical, rows[sid][logical]))
+            lo, hi = _ceil_div(first, page), _ceil_div(last, page)
+            if hi > lo:
+                fresh = [pool.pop() for _ in range(hi - lo)]
+                old = self.tables[sid]
+                rows[sid] = old[:lo] + tuple(fresh) + old[hi:]
+                edits.extend((sid, lo + i, physical) for i, physical in enumerate(fresh))
             if tokens:
                 where_seq.extend(sid for _ in range(n))
                 where_pos.extend(range(first, last))
             closed.extend((sid, c) for c in range(first // chunk, last // chunk))
             lengths[sid] = last
-        tables = tuple(tuple(rows[s]) if s in rows else self.tables[s] for s in range(self.batch_size))
+        tables = tuple(rows.get(s, row) for s, row in enumerate(self.tables)) if rows else self.tables
         return AppendPlan(self.version, tables, tuple(lengths), tuple(pool), tuple(where_seq), tuple(where_pos),
                           tuple(closed), tuple(edits))
 

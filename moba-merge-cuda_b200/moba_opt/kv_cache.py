@@ -234,6 +234,10 @@ class PagedKVCache:
         self._lock = threading.RLock()
         self._life = CacheLife.READY
         self._owner = None                    # the PreparedDecode that holds the lease, if any
+        # The NaN/Inf check of q, k, v (the reference's contract) reads a flag back, so every eager call waits for the
+        # device.  A caller that vouches for its tensors may set this to False, as prepare_decode(check_finite=False)
+        # does for prepared steps; it is an attribute rather than an argument to leave the reference's signatures alone.
+        self.check_finite = True
         self._lib = decode_library()
         with torch.cuda.device(wanted):
             self.device = torch.device("cuda", torch.cuda.current_device())
@@ -317,6 +321,7 @@ class PagedKVCache:
                               stable_routes=stable_routes)
 
     def _checked_kv(self, k, v, check_finite=True):
+        check_finite = check_finite and self.check_finite
         TensorRule("k", heads=self.num_kv_heads, finite=check_finite).check(self, k)
         TensorRule("v", heads=self.num_kv_heads, tokens=k.shape[0], finite=check_finite).check(self, v)
 
@@ -371,7 +376,7 @@ class PagedKVCache:
 
     # ------------------------------------------------------------------ attend
     def _query_rows(self, q, sequence_ids, positions):
-        TensorRule("q").check(self, q)
+        TensorRule("q", finite=self.check_finite).check(self, q)
         if q.shape[1] % self.num_kv_heads:
             raise ValueError("Hq must be a multiple of Hkv")
         ids = self._layout.validate_ids(_ints(sequence_ids, "sequence_ids"))
@@ -448,7 +453,7 @@ class PagedKVCache:
             self._guard()
             dense = wants_dense(mode, topk)
             self._checked_kv(k, v)
-            TensorRule("q", tokens=k.shape[0]).check(self, q)
+            TensorRule("q", tokens=k.shape[0], finite=self.check_finite).check(self, q)
             self._refuse_pool_aliases(q, k, v)
             if q.shape[1] % self.num_kv_heads:
                 raise ValueError("Hq must be a multiple of Hkv")
