@@ -348,6 +348,55 @@ def run_decode(dev, rank, world, steps, lib):
                 context_tokens=int(sum(lens)), gather_ms_per_step=gather_ms)
 
 
+def run_decode_against_reference(dev):
+    """Same-machine GPU baseline of the decode leg: the reference's own PagedKVCache + prepare_decode + CUDA graph (its
+    Triton kernels, from the unmodified copy oracle/make_ref.py puts under oracle/_ref) beside this package's, on one
+    workload both accept - the reference's kernels stop at chunk 1024, so this is the decode configuration with chunk 1024,
+    16 requests and contexts in [2048, 16384].  Returns None where oracle/_ref or triton is missing."""
+    import torch
+    from oracle.make_ref import load_ref_decode
+    from moba_opt import PagedKVCache
+    mods = load_ref_decode()
+    if mods is None:
+        return None
+    w = dict(DECODE, requests=16, lo=2048, hi=16384, chunk=1024, steps=128)
+    lens = [int(x) for x in np.random.default_rng(3).integers(w["lo"], w["hi"] + 1, size=w["requests"])]
+    b, extra = len(lens), w["steps"] + 32
+    out = {}
+    for label, cls in (("ours", PagedKVCache), ("reference", mods[0].PagedKVCache)):
+        cache = cls(b, w["hi"] + extra, w["hkv"], w["dim"], page_size=w["page"], chunk_size=w["chunk"])
+        gen = torch.Generator(device=dev).manual_seed(11)
+        done = [0] * b
+        while any(d < n for d, n in zip(done, lens)):
+            ids = [i for i in range(b) if done[i] < lens[i]]
+            counts = [min(2048, lens[i] - done[i]) for i in ids]
+            k = torch.randn(sum(counts), w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+            v = torch.randn(sum(counts), w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+            cache.append(k, v, sequence_ids=ids, cu_seqlens=[0] + [int(x) for x in np.cumsum(counts)])
+            for i, c in zip(ids, counts):
+                done[i] += c
+        plan = cache.prepare_decode(list(range(b)), w["hq"], topk=w["topk"], check_finite=False, stable_routes=True)
+        plan.capture("step")
+        q = torch.randn(b, w["hq"], w["dim"], device=dev, generator=gen).bfloat16()
+        kn = torch.randn(b, w["hkv"], w["dim"], device=dev, generator=gen).bfloat16()
+        for _ in range(5):
+            plan.step(q, kn, kn, use_graph=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(w["steps"]):
+            plan.step(q, kn, kn, use_graph=True)
+        e1.record()
+        torch.cuda.synchronize()
+        out[label] = e0.elapsed_time(e1) / w["steps"]
+        plan.close()
+        del cache, plan
+    return dict(workload="paged_decode_16req_ctx2k-16k_page48_c1024_k4_h12kv2_d128", steps=w["steps"],
+                ms_per_step=out["ours"], reference_ms_per_step=out["reference"],
+                reference="the reference's PagedKVCache + prepare_decode + CUDA graph (Triton kernels), same inputs, same GPU",
+                speedup=out["reference"] / out["ours"])
+
+
 # ----------------------------------------------------------------------------- long-prefill leg
 LONG_PREFILL = dict(name="gqa_prefill_1x131072_h32kv8_d128_c4096_k12_by_kv_group", tokens=131072, hq=32, hkv=8, dim=128,
                     chunk=4096, topk=12)
@@ -822,6 +871,10 @@ def run_ours(args):
                                   ms_per_step_with_output_gather=dec["gather_ms_per_step"])
             if world == 1 and not args.kernels_only:
                 line["decode"]["cpu_baseline"] = cpu_decode_sample(os.cpu_count() or 1)
+                try:
+                    line["decode"]["reference_gpu"] = run_decode_against_reference(dev)
+                except Exception as exc:      # the reference's Triton kernels are outside this package's control
+                    line["decode"]["reference_gpu"] = {"error": "%s: %s" % (type(exc).__name__, exc)}
         if long_leg is not None:
             long_leg["frac_of_tensor_peak"] = long_leg["tflops"] / world / pk["tflops"]
             line["long_prefill"] = long_leg

@@ -4,7 +4,7 @@
 // is no host synchronisation, and every list is produced in a fixed order (head in group, token).
 //
 // Passes (all on one stream, four launches):
-//   1. chunk_mean_kernel     partial sums of K over 128-token slices of a chunk (one CTA each, so the pass
+//   1. chunk_mean_kernel     partial sums of K over 256-token slices of a chunk (one CTA each, so the pass
 //                            has enough loads in flight to run at memory speed); the CTA that finishes a
 //                            (chunk, kv head) last adds the slices in slice order and writes the mean
 //   2. gate_topk_kernel      per (token, q head): FP32 scores against the earlier chunks of the same
@@ -19,7 +19,7 @@
 namespace moba {
 
 constexpr int kCandBatch = 32;   // candidate means staged in shared memory per pass
-constexpr int kMeanRows = 128;   // tokens per CTA of the mean pass
+constexpr int kMeanRows = 256;   // tokens per CTA of the mean pass
 
 // --------------------------------------------------------------------------- 1. chunk means
 // grid (chunk, kv head, slice).  part [n_chunks*Hkv][splits][D] FP32, tickets [n_chunks*Hkv] zero on entry (and
