@@ -301,8 +301,10 @@ def run_decode(dev, rank, world, steps, lib):
     sampled_bytes = []
     G = w["hq"] // w["hkv"]
     e0.record()
+    h0 = time.perf_counter()
     for i in range(steps):
         r = plan.step(qs[i % 8], ks[i % 8], vs[i % 8], use_graph=True)
+    host_ms = (time.perf_counter() - h0) * 1e3 / steps      # what the host spends enqueueing a step (no wait inside)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
@@ -344,7 +346,8 @@ def run_decode(dev, rank, world, steps, lib):
         torch.cuda.synchronize()
         gather_ms = e0.elapsed_time(e1) / n
     plan.close()
-    return dict(ms_per_step=ms, requests=b, bytes_per_step=float(np.mean(sampled_bytes)), attend_ms=float(np.median(att)),
+    return dict(ms_per_step=ms, host_ms_per_step=host_ms, requests=b, bytes_per_step=float(np.mean(sampled_bytes)),
+                attend_ms=float(np.median(att)),
                 context_tokens=int(sum(lens)), gather_ms_per_step=gather_ms)
 
 
@@ -806,17 +809,19 @@ def run_ours(args):
     if not args.kernels_only and not args.no_decode:
         dec = run_decode(dev, rank, world, args.decode_steps, lib)
         ga.check_status()
-        dec["per_rank"] = [dict(requests=dec["requests"], context_tokens=dec["context_tokens"], ms_per_step=dec["ms_per_step"])]
+        dec["per_rank"] = [dict(requests=dec["requests"], context_tokens=dec["context_tokens"], ms_per_step=dec["ms_per_step"],
+                                host_ms_per_step=dec["host_ms_per_step"])]
         if world > 1:
             mine = torch.tensor([dec["ms_per_step"], dec["attend_ms"], dec["gather_ms_per_step"], dec["bytes_per_step"],
-                                 float(dec["requests"]), float(dec["context_tokens"])], device=dev, dtype=torch.float64)
+                                 float(dec["requests"]), float(dec["context_tokens"]), dec["host_ms_per_step"]], device=dev, dtype=torch.float64)
             every = torch.empty(world, mine.numel(), device=dev, dtype=torch.float64)
             dist.all_gather_into_tensor(every, mine)
             every = every.cpu().numpy()
             dec.update(ms_per_step=float(every[:, 0].max()), attend_ms=float(every[:, 1].max()),
                        gather_ms_per_step=float(every[:, 2].max()), bytes_per_step=float(every[:, 3].sum()),
                        requests=int(every[:, 4].sum()),
-                       per_rank=[dict(requests=int(r[4]), context_tokens=int(r[5]), ms_per_step=float(r[0])) for r in every])
+                       per_rank=[dict(requests=int(r[4]), context_tokens=int(r[5]), ms_per_step=float(r[0]),
+                                      host_ms_per_step=float(r[6])) for r in every])
 
     long_leg = None
     if not args.kernels_only and not args.no_long_prefill:

@@ -1152,6 +1152,9 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
 }
 
 static int attend_part_tokens(const moba_cache_desc* c) {
+#ifdef MOBA_DEC_PART
+  if (c->chunk_size >= MOBA_DEC_PART) return MOBA_DEC_PART;
+#endif
   return c->chunk_size >= 2048 ? 1024 : c->chunk_size >= 512 ? 512 : c->chunk_size;
 }
 static int attend_parts(const moba_cache_desc* c) {

@@ -27,6 +27,16 @@ from .cache_layout import IncrementalLayout, positive_int
 from .kv_cache import CacheLife, DecodeResult, _ints, wants_dense
 
 
+def current_stream_handle(device_index):
+    """The current CUDA stream of the device as an integer handle (the cheapest route torch offers; a step asks twice)."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    return raw(device_index) if raw is not None else torch.cuda.current_stream(device_index).cuda_stream
+
+
+def _storage_address(t):
+    return t.untyped_storage().data_ptr()
+
+
 class PlanLife(enum.Enum):
     OPEN = "open"
     FAILED = "failed"      # a launch or replay raised: buffers and cache contents are undefined
@@ -100,6 +110,11 @@ class PreparedDecode:
             self._delta_done = [None] * len(self._delta_ring)
             self._delta_next = 0
             self._row_of = {sid: i for i, sid in enumerate(self.ids)}
+            # what a caller's q / k / v must not share storage with; the pools and the buffers live as long as the plan
+            self._device_index = dev.index
+            self._pool_storage = frozenset(_storage_address(t) for t in (cache.k_cache, cache.v_cache))
+            self._input_storage = frozenset(_storage_address(t) for t in (self.q, self.k, self.v))
+            self._step_pairs = ((self.q, "q"), (self.k, "k"), (self.v, "v"))
             self._umax = lib.moba_decode_union_capacity(h, hk, self.remote, self.width)
             self._u_chunk = new((b, hk, self._umax), torch.int32)
             self._u_mask = new((b, hk, self._umax), torch.int32)
@@ -137,27 +152,31 @@ class PreparedDecode:
             raise RuntimeError("CUDA execution failed; discard prepared decode and cache")
         if torch.cuda.is_current_stream_capturing():
             raise ValueError("use capture(), not external capture")
-        if torch.cuda.current_stream(self.cache.device).cuda_stream != self.cache._stream:
+        if current_stream_handle(self._device_index) != self.cache._stream:
             raise ValueError("cross-stream cache access is unsupported")
 
     def _accept(self, tensor, target, name):
         """The caller's tensor for the fixed buffer `target`: same shape, device, dtype, contiguous, no gradient, no
-        overlap with the cache pools or with another of the plan's input buffers, finite unless the plan skips that."""
-        if not isinstance(tensor, torch.Tensor) or tensor.shape != target.shape:
-            raise ValueError(f"{name} must have fixed shape {tuple(target.shape)}")
-        if tensor.device != target.device or tensor.dtype != target.dtype or not tensor.is_contiguous():
-            raise ValueError(f"{name} must match device/dtype and be contiguous")
-        if tensor.requires_grad:
-            raise ValueError("prepared decode is inference-only")
-        self.cache._refuse_pool_aliases(tensor)
-        if tensor is not target and tensor.untyped_storage().data_ptr() in {x.untyped_storage().data_ptr() for x in (self.q, self.k, self.v)}:
-            raise ValueError("input aliases another prepared workspace; clone first")
+        overlap with the cache pools or with another of the plan's input buffers, finite unless the plan skips that.
+        The buffer itself passes all but the last by construction."""
+        if tensor is not target:
+            if not isinstance(tensor, torch.Tensor) or tensor.shape != target.shape:
+                raise ValueError(f"{name} must have fixed shape {tuple(target.shape)}")
+            if tensor.device != target.device or tensor.dtype != target.dtype or not tensor.is_contiguous():
+                raise ValueError(f"{name} must match device/dtype and be contiguous")
+            if tensor.requires_grad:
+                raise ValueError("prepared decode is inference-only")
+            where = _storage_address(tensor)
+            if where in self._pool_storage:
+                raise ValueError("append inputs must not alias KV cache storage; clone first")
+            if where in self._input_storage:
+                raise ValueError("input aliases another prepared workspace; clone first")
         if self.check_finite and not bool(torch.isfinite(tensor).all()):
             raise ValueError(f"{name} contains NaN/Inf")
 
     # ------------------------------------------------------------------ driver interface
     def _stream(self):
-        return ctypes.c_void_p(torch.cuda.current_stream(self.cache.device).cuda_stream)
+        return ctypes.c_void_p(current_stream_handle(self._device_index))
 
     def plan_step(self):
         """Positions and page openings of the next one-token step; raises (cache full, pool empty) without side effects."""
@@ -175,12 +194,14 @@ class PreparedDecode:
         todo = [(t, target) for t, target in pairs if t is not target]
         if not todo:
             return
-        fits = all(t.is_contiguous() and t.dtype == target.dtype and t.data_ptr() % 16 == 0 and target.data_ptr() % 16 == 0
-                   and (t.numel() * t.element_size()) % 16 == 0 for t, target in todo)
-        if fits:
-            args = []
-            for t, target in todo + [(None, None)] * (3 - len(todo)):
-                args += [None, None, 0] if t is None else [target.data_ptr(), t.data_ptr(), t.numel() * t.element_size()]
+        args = []
+        for t, target in todo:
+            src, dst, size = t.data_ptr(), target.data_ptr(), t.numel() * t.element_size()
+            if (src | dst | size) & 15 or t.dtype != target.dtype or not t.is_contiguous():
+                break
+            args += (dst, src, size)
+        else:
+            args += (None, None, 0) * (3 - len(todo))
             if self._lib.moba_decode_stage_inputs(*args, self._stream()) == 0:
                 return
         for t, target in todo:
@@ -250,7 +271,7 @@ class PreparedDecode:
     # ------------------------------------------------------------------ the reference's operations
     @torch.no_grad()
     def attend(self, q, *, use_graph=False):
-        with self.cache._lock, torch.cuda.device(self.cache.device):
+        with self.cache._lock, torch.cuda.device(self._device_index):
             self._usable()
             self._accept(q, self.q, "q")
             pos = tuple(self._state.lengths[s] - 1 for s in self.ids)
@@ -266,17 +287,19 @@ class PreparedDecode:
     def step(self, q, k, v, *, use_graph=False):
         """Appends one token per leased sequence and attends with it.  Validation and capacity errors
         are raised before anything is modified."""
-        with self.cache._lock, torch.cuda.device(self.cache.device):
+        with self.cache._lock, torch.cuda.device(self._device_index):
             self._usable()
-            for tensor, target, name in ((q, self.q, "q"), (k, self.k, "k"), (v, self.v, "v")):
+            pairs = ((q, self.q), (k, self.k), (v, self.v))
+            for (tensor, target), (_, name) in zip(pairs, self._step_pairs):
                 self._accept(tensor, target, name)
             if use_graph and "step" not in self._graphs:
                 raise ValueError("capture('step') first")
-            plan = self.plan_step()
-            self.stage_inputs(((q, self.q), (k, self.k), (v, self.v)))
-            self.send_delta(plan)
+            plan = self._state.plan()
+            self.stage_inputs(pairs)
+            if plan.updates:
+                self.send_delta(plan)
             self._execute("step", use_graph)
-            self.commit_step(plan)
+            self._state.commit(plan)
             return self._result(plan.positions)
 
     @torch.no_grad()
