@@ -36,9 +36,9 @@ const char* moba_status_string(int status);
  * merge of OptMixedAttention.forward (src/moba_opt/mixed_attention.py:43-139, ops/merge.cu:27-288)
  * and OptMixedAttention.backward (mixed_attention.py:141-225).
  *
- * Layout: q [T,Hq,D], k/v [T,Hkv,D] bf16 with element strides given in the descriptor (last
+ * Layout: q [T,Hq,D], k/v [T,Hkv,D] bf16 (fp16 with MOBA_INPUT_FP16) with element strides given in the descriptor (last
  * dimension contiguous, strides multiples of 8 elements, base pointers 16-byte aligned);
- * out [T,Hq,D] bf16 contiguous; lse [T,Hq] fp32 (natural log).
+ * out [T,Hq,D] in the input format, contiguous; lse [T,Hq] fp32 (natural log).
  * The int32 metadata arrays are device pointers built by the host from cu_seqlens:
  *   chunk_start[n+1], chunk_seq[n], chunk_local[n]   (chunking of src/moba_opt/diagnostic.py:30-80)
  *   qtile_chunk/qtile_tok0/qtile_local[num_qtiles]   128-token query tiles that never cross a chunk;
@@ -53,13 +53,16 @@ const char* moba_status_string(int status);
  */
 #define MOBA_ROUTE_BF16_MEANS 1
 #define MOBA_BWD_DETERMINISTIC 2
+#define MOBA_INPUT_FP16 4
 
 typedef struct moba_prefill_desc {
   int32_t total_tokens, num_seqs, hq, hkv, dim, chunk_size, remote_k;
   int32_t num_chunks, num_qtiles, max_tiles_per_seq, max_chunks_per_seq;
-  int32_t flags; /* MOBA_ROUTE_BF16_MEANS: round chunk means to bf16 (route_precision='upstream');
+  int32_t flags; /* MOBA_ROUTE_BF16_MEANS: round chunk means to the input format (route_precision='upstream');
                     MOBA_BWD_DETERMINISTIC: dQ summed in 64-bit fixed point, bit-repeatable (needs the larger scratch
-                    moba_prefill_bwd_scratch_bytes reports for a descriptor with the flag set) */
+                    moba_prefill_bwd_scratch_bytes reports for a descriptor with the flag set);
+                    MOBA_INPUT_FP16: q, k, v, dout, out and the gradients are IEEE half instead of bf16 (both are
+                    accepted by baseline_adapter.py:13); everything else about the call is the same */
   int32_t num_self_pairs, reserved0;
   int64_t q_stride_t, q_stride_h, k_stride_t, k_stride_h, v_stride_t, v_stride_h;
   const int32_t* cu_seqlens;
@@ -107,7 +110,7 @@ int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const void* k, c
                      void* scratch, size_t scratch_bytes, void* out, float* lse, unsigned* status, void* stream);
 
 /* Backward (mixed_attention.py:141-225): gradients of out w.r.t. q, k, v with the route held fixed.
- * dq [T,Hq,D], dk/dv [T,Hkv,D] bf16 contiguous.  dK, dV are bit-repeatable; dQ is summed over key blocks with FP32
+ * dq [T,Hq,D], dk/dv [T,Hkv,D] in the input format, contiguous.  dK, dV are bit-repeatable; dQ is summed over key blocks with FP32
  * reductions in arrival order unless d->flags has MOBA_BWD_DETERMINISTIC (the reference's deterministic=True,
  * mixed_attention.py:185,220), which costs scalar 64-bit reductions and a scratch twice the size. */
 size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d);
@@ -121,12 +124,17 @@ int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, c
  * Replaces the Triton kernels behind PagedKVCache / PreparedDecode of the reference
  * (src/moba_opt/ops/paged_decode.py:11-144, src/moba_opt/ops/prepared_decode.py:7-94) and the
  * torch.topk of src/moba_opt/kv_cache.py:208-223. The cache pools stay owned by the caller:
- *   k_cache, v_cache [num_pages, page_size, hkv, dim] bf16      table   [batch_slots, table_width] int32 (-1 unmapped)
- *   means [batch_slots, max_chunks, hkv, dim] bf16               lengths [batch_slots] int32
+ *   k_cache, v_cache [num_pages, page_size, hkv, dim] 16-bit    table   [batch_slots, table_width] int32 (-1 unmapped)
+ *   means [batch_slots, max_chunks, hkv, dim] 16-bit             lengths [batch_slots] int32
  * dim must be a multiple of 8 (<= 256). All functions enqueue on `stream` and return.
  */
+#define MOBA_CACHE_FP16 1
+
 typedef struct moba_cache_desc {
   int32_t batch_slots, max_seq_len, page_size, num_pages, table_width, chunk_size, max_chunks, hkv, dim;
+  int32_t flags; /* MOBA_CACHE_FP16: pools, means, q, k, v and out are IEEE half instead of bf16 (the reference's cache
+                    takes both, src/moba_opt/kv_cache.py:65); the fused q/k/v projection input of
+                    moba_decode_step_begin is bf16 only */
   void* k_cache;
   void* v_cache;
   int32_t* table;
@@ -153,7 +161,7 @@ int moba_cache_update(const moba_cache_desc* c, const int32_t* edits, int n, con
 int moba_decode_append(const moba_cache_desc* c, const void* k, const void* v, const int32_t* token_seq,
                        const int32_t* token_pos, int tokens, unsigned* status, void* stream);
 
-/* Chunk means, FP32 sum / chunk_size rounded to bf16 (ops/paged_decode.py:27-44). predicated == 0: item i is
+/* Chunk means, FP32 sum / chunk_size rounded to the cache's format (ops/paged_decode.py:27-44). predicated == 0: item i is
  * (seqs[i], chunk chunk_or_pos[i]). predicated != 0: chunk_or_pos holds the position of the token just
  * appended to seqs[i]; the mean of its chunk is written only if that token completed the chunk
  * (ops/prepared_decode.py:24-41). */
@@ -198,7 +206,7 @@ int moba_decode_route(const moba_cache_desc* c, const void* q, const int32_t* id
 
 /* Attention (ops/paged_decode.py:68-112): per (row, query head) softmax over the tokens <= positions[row] of the
  * listed chunks (selected != null, slots = 1+remote) or of the whole prefix (selected == null, slots =
- * max_chunks); out [rows,hq,dim] bf16, lse [rows,hq] fp32 natural log. The workspace starts with one int32
+ * max_chunks); out [rows,hq,dim] in the cache's format, lse [rows,hq] fp32 natural log. The workspace starts with one int32
  * counter per (row, kv head) that must be zero before the first call; the kernel leaves it zero. */
 size_t moba_decode_attend_workspace_bytes(const moba_cache_desc* c, int rows, int hq, int slots);
 int moba_decode_attend(const moba_cache_desc* c, const void* q, const int32_t* ids, const int32_t* positions, int rows, int hq,
@@ -212,7 +220,7 @@ int moba_decode_attend(const moba_cache_desc* c, const void* q, const int32_t* i
  * branch and the scattered remote contributions themselves; the prefill path merges in its own epilogue.
  *   self_out [rows, dim], self_lse [rows]; remote_out [remote_rows, dim], remote_lse [remote_rows];
  *   mapping [remote_rows] int64: the row each contribution belongs to; at most kmax (<= 32) per row.
- *   dtype: 0 = bf16, 1 = fp32 (of self_out, remote_out and out); LSE is fp32 natural log.
+ *   dtype: 0 = bf16, 1 = fp32, 2 = fp16 (of self_out, remote_out and out); LSE is fp32 natural log.
  * Contributions are reduced in ascending index order, so the result is bit-repeatable. status bits: 2 = a
  * mapping entry was out of range (skipped), 4 = a row had more than kmax contributions (the excess is skipped). */
 size_t moba_merge_scratch_bytes(long long rows, int kmax);

@@ -21,6 +21,7 @@ namespace moba {
 
 struct CacheView {
   int slots, max_seq_len, page, num_pages, width, C, max_chunks, Hkv, D;
+  int fp16;  // pools, means, q and out are IEEE half (MOBA_CACHE_FP16), else bf16; the pointer types below only address 16-bit elements
   __nv_bfloat16* kc;
   __nv_bfloat16* vc;
   int* table;
@@ -32,6 +33,7 @@ static CacheView make_cache_view(const moba_cache_desc& c) {
   CacheView v;
   v.slots = c.batch_slots; v.max_seq_len = c.max_seq_len; v.page = c.page_size; v.num_pages = c.num_pages;
   v.width = c.table_width; v.C = c.chunk_size; v.max_chunks = c.max_chunks; v.Hkv = c.hkv; v.D = c.dim;
+  v.fp16 = (c.flags & MOBA_CACHE_FP16) ? 1 : 0;
   v.kc = static_cast<__nv_bfloat16*>(c.k_cache); v.vc = static_cast<__nv_bfloat16*>(c.v_cache);
   v.table = c.table; v.lengths = c.lengths; v.means = static_cast<__nv_bfloat16*>(c.means);
   return v;
@@ -49,6 +51,14 @@ static int validate_cache(const moba_cache_desc* c) {
 
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+// one 16-bit value to its bits in the cache's format
+__device__ __forceinline__ uint16_t bits16(float x, bool f16) {
+  return f16 ? __half_as_ushort(__float2half_rn(x)) : __bfloat16_as_ushort(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ float value16(const __nv_bfloat16* p, bool f16) {
+  const uint16_t w = *reinterpret_cast<const uint16_t*>(p);
+  return f16 ? __half2float(__ushort_as_half(w)) : __uint_as_float((uint32_t)w << 16);
+}
 __device__ __forceinline__ float dec_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -120,7 +130,7 @@ __global__ void __launch_bounds__(256) decode_append_kernel(CacheView cv, const 
 }
 
 // Second half of a chunk mean: thread (ri, u) holds the sums of unit u over the rows w = ri, ri + rpi, ... of the chunk;
-// the row groups are added in ascending order and the mean is rounded to bf16.  Every producer of a mean goes through
+// the row groups are added in ascending order and the mean is rounded to the cache's format.  Every producer of a mean goes through
 // here with the same assignment of rows to threads, so a mean has the same bits whichever call computed it.
 __device__ __forceinline__ void chunk_mean_finish(const CacheView& cv, int sid, int chunk, int g, const float (&acc)[8], float* s_part) {
   const int upr = cv.D >> 3, rpi = 256 / upr;
@@ -133,7 +143,8 @@ __device__ __forceinline__ void chunk_mean_finish(const CacheView& cv, int sid, 
   for (int d = threadIdx.x; d < cv.D; d += 256) {
     float s = 0.f;
     for (int r = 0; r < rpi; ++r) s += s_part[r * cv.D + d];
-    cv.means[(((long long)sid * cv.max_chunks + chunk) * cv.Hkv + g) * cv.D + d] = __float2bfloat16_rn(s / (float)cv.C);
+    reinterpret_cast<uint16_t*>(cv.means)[(((long long)sid * cv.max_chunks + chunk) * cv.Hkv + g) * cv.D + d] =
+        bits16(s / (float)cv.C, cv.fp16 != 0);
   }
 }
 
@@ -154,7 +165,10 @@ __device__ __forceinline__ void chunk_mean_cta(const CacheView& cv, int sid, int
           *reinterpret_cast<const uint4*>(cv.kc + (((long long)physical * cv.page + t % cv.page) * cv.Hkv + g) * cv.D + u * 8);
       const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { acc[2 * i] += bf_lo(wv[i]); acc[2 * i + 1] += bf_hi(wv[i]); }
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack16(wv[i], cv.fp16 != 0);
+        acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+      }
     }
   }
   chunk_mean_finish(cv, sid, chunk, g, acc, s_part);
@@ -238,7 +252,10 @@ __global__ void __launch_bounds__(256) prefill_to_cache_kernel(CacheView cv, con
         }
         const uint32_t wv[4] = {kr[j].x, kr[j].y, kr[j].z, kr[j].w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { acc[2 * i] += bf_lo(wv[i]); acc[2 * i + 1] += bf_hi(wv[i]); }
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = unpack16(wv[i], cv.fp16 != 0);
+          acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+        }
       }
     }
   }
@@ -387,6 +404,7 @@ constexpr int kRouteThreads = 256;  // eight warps: a group of up to eight heads
 // chunks completed before the query's own chunk, -inf elsewhere; top-`remote` per head in descending
 // score order with the lowest chunk winning exact ties; selected[row, h, :] = (own chunk, picks...,
 // -1 padding); and the group's union list (chunk ascending, bitmask of heads) for the attention kernel.
+template <bool F16>
 __global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView cv, const __nv_bfloat16* q, const int* ids, const int* positions,
                                                            int Hq, int remote, int width, float* scores, int* selected, int* u_chunk,
                                                            unsigned* u_mask, int* u_count, int umax) {
@@ -416,7 +434,7 @@ __global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView c
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int i = tid + j * kRouteThreads;
-    qreg[j] = i < G * cv.D ? __bfloat162float(qsrc[i]) : 0.f;
+    qreg[j] = i < G * cv.D ? value16(qsrc + i, F16) : 0.f;
   }
   auto store_q = [&]() {
 #pragma unroll
@@ -424,7 +442,7 @@ __global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView c
       const int i = tid + j * kRouteThreads;
       if (i < G * cv.D) s_q[i] = qreg[j];
     }
-    for (int i = tid + 4 * kRouteThreads; i < G * cv.D; i += kRouteThreads) s_q[i] = __bfloat162float(qsrc[i]);
+    for (int i = tid + 4 * kRouteThreads; i < G * cv.D; i += kRouteThreads) s_q[i] = value16(qsrc + i, F16);
   };
   // The mean rows of kRouteTile chunks at a time are brought into shared memory by all threads with loads that do not
   // depend on each other (one trip to L2 per tile); the (head, chunk) pairs are then scored from there.  Rows are
@@ -449,10 +467,11 @@ __global__ void __launch_bounds__(kRouteThreads) decode_route_kernel(CacheView c
       for (int u = 0; u < upr; ++u) {
         const uint4 ma = mrow[u];
         const float* qq = qrow + u * 8;
-        a0 = fmaf(qq[0], bf_lo(ma.x), a0); a1 = fmaf(qq[1], bf_hi(ma.x), a1);
-        a2 = fmaf(qq[2], bf_lo(ma.y), a2); a3 = fmaf(qq[3], bf_hi(ma.y), a3);
-        a0 = fmaf(qq[4], bf_lo(ma.z), a0); a1 = fmaf(qq[5], bf_hi(ma.z), a1);
-        a2 = fmaf(qq[6], bf_lo(ma.w), a2); a3 = fmaf(qq[7], bf_hi(ma.w), a3);
+        const float2 m0 = unpack16<F16>(ma.x), m1 = unpack16<F16>(ma.y), m2 = unpack16<F16>(ma.z), m3 = unpack16<F16>(ma.w);
+        a0 = fmaf(qq[0], m0.x, a0); a1 = fmaf(qq[1], m0.y, a1);
+        a2 = fmaf(qq[2], m1.x, a2); a3 = fmaf(qq[3], m1.y, a3);
+        a0 = fmaf(qq[4], m2.x, a0); a1 = fmaf(qq[5], m2.y, a1);
+        a2 = fmaf(qq[6], m3.x, a2); a3 = fmaf(qq[7], m3.y, a3);
       }
       const float sc = (a0 + a1) + (a2 + a3);
       s_scores[hl * width + c0 + cl] = sc;
@@ -607,15 +626,16 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t dec_pack_bf16(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
+template <bool F16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if (F16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 // ---- pieces of the merge that are needed only when a head has more partials than fit in shared memory; they
@@ -672,7 +692,7 @@ __device__ __noinline__ float4 merge_tail_acc(const MergeTail& t, long long hbas
 // warps are combined through shared memory at the end.  A team is four warps with a copy ring and a barrier of its
 // own; the latency variant runs two teams, each on half of the part's stages, because with one warp per scheduler
 // nothing hides the dependent chain of a stage (ldmatrix, mma, shuffles, exp2, mma).
-template <int DP, int NS, int TEAMS>
+template <int DP, int NS, int TEAMS, bool F16>
 __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_DEC_MINBLOCKS : 1)) decode_attend_kernel(AttendArgs a) {
   constexpr int NT = 128 * TEAMS, NW = 4 * TEAMS;  // threads and warps of the CTA
   constexpr int KSTEPS = DP / 16;
@@ -798,8 +818,8 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
         uint32_t b[4];
         const int mat = lane >> 3, r = lane & 7;
         ldmatrix_x4(kbase + kv_unit_offset<DP>(tok0 + (mat >> 1) * 8 + r, ks * 2 + (mat & 1)), b);
-        mma_bf16_16816(sc[0], qf[ks], b[0], b[1]);
-        mma_bf16_16816(sc[1], qf[ks], b[2], b[3]);
+        mma_16816<F16>(sc[0], qf[ks], b[0], b[1]);
+        mma_16816<F16>(sc[1], qf[ks], b[2], b[3]);
       }
       // ---- online softmax of rows qr / qr+8 (exp2 domain)
 #pragma unroll
@@ -825,8 +845,8 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
         const float p10 = dec_exp2(sc[1][0] - n0), p11 = dec_exp2(sc[1][1] - n0), p12 = dec_exp2(sc[1][2] - n1), p13 = dec_exp2(sc[1][3] - n1);
         l0 = l0 * al0 + (p00 + p01) + (p10 + p11);
         l1 = l1 * al1 + (p02 + p03) + (p12 + p13);
-        pf[0] = dec_pack_bf16(p00, p01); pf[1] = dec_pack_bf16(p02, p03);
-        pf[2] = dec_pack_bf16(p10, p11); pf[3] = dec_pack_bf16(p12, p13);
+        pf[0] = pack16<F16>(p00, p01); pf[1] = pack16<F16>(p02, p03);
+        pf[2] = pack16<F16>(p10, p11); pf[3] = pack16<F16>(p12, p13);
       }
       // ---- O = O * alpha + P V; the running maxima rarely move after the first tiles, and alpha == 1 needs no pass over O
       const bool rescale = __any_sync(0xFFFFFFFFu, al0 != 1.f || al1 != 1.f);
@@ -839,7 +859,7 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
         for (int h2 = 0; h2 < 2; ++h2) {
           float (&acc)[4] = o[dp * 2 + h2];
           if (rescale) { acc[0] *= al0; acc[1] *= al0; acc[2] *= al1; acc[3] *= al1; }
-          mma_bf16_16816(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
+          mma_16816<F16>(acc, pf, b[h2 * 2], b[h2 * 2 + 1]);
         }
       }
       if (ltid < kStageTokens) s_rowbase[i % NS][ltid] = next_base;
@@ -1000,10 +1020,9 @@ __global__ void __launch_bounds__(128 * TEAMS, (TEAMS == 1 && DP <= 128 ? MOBA_D
     if (tc > pb) v = merge_rest_acc(tail, hbase, pb, tc, d, wrow, v);
     if (total > cap) v = merge_tail_acc(tail, hbase, cap, total, d, s_big[hl], v);
     const float inv = s_inv[hl];
-    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * inv, v.y * inv), hi = __floats2bfloat162_rn(v.z * inv, v.w * inv);
     uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    pk.x = pack16<F16>(v.x * inv, v.y * inv);
+    pk.y = pack16<F16>(v.z * inv, v.w * inv);
     *reinterpret_cast<uint2*>(a.out + ((long long)row * a.Hq + h) * D + d) = pk;
   }
   __syncthreads();
@@ -1111,6 +1130,7 @@ extern "C" int moba_decode_step_begin(const moba_cache_desc* c, const int32_t* i
   if (rc != MOBA_OK) return rc;
   if (!ids || !positions || !delta || !k || !v || rows < 1) return MOBA_ERR_INVALID;
   if (qkv && (!cosv || !sinv || !q || hq < 1 || hq % c->hkv || (c->dim & 1))) return MOBA_ERR_INVALID;
+  if (qkv && (c->flags & MOBA_CACHE_FP16)) return MOBA_ERR_UNSUPPORTED;  // the rotary step rounds as the bf16 modules do
   const int rpi = 256 / (c->dim / 8);
   if (launch_dependent(2u, decode_step_begin_kernel, dim3(rows), dim3(256), (size_t)rpi * c->dim * 4, (cudaStream_t)stream,
                        make_cache_view(*c), ids, positions, delta, rows, hq, static_cast<const __nv_bfloat16*>(qkv),
@@ -1140,11 +1160,11 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
   const size_t smem = ((((size_t)G * width + width + 1 + (size_t)G * c->dim + 3) & ~(size_t)3)) * 4 +
                       (size_t)kRouteTile * ((c->dim / 8) | 1) * 16;
   if (smem > 200 * 1024) return MOBA_ERR_UNSUPPORTED;
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(decode_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  const auto kernel = (c->flags & MOBA_CACHE_FP16) ? decode_route_kernel<true> : decode_route_kernel<false>;
+  if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return MOBA_ERR_CUDA;
   const int umax = moba_decode_union_capacity(hq, c->hkv, remote, width);
-  if (launch_dependent(4u, decode_route_kernel, dim3(rows, c->hkv), dim3(kRouteThreads), smem, (cudaStream_t)stream, make_cache_view(*c),
+  if (launch_dependent(4u, kernel, dim3(rows, c->hkv), dim3(kRouteThreads), smem, (cudaStream_t)stream, make_cache_view(*c),
                        static_cast<const __nv_bfloat16*>(q), ids, positions, hq, remote, width, scores, selected, u_chunk, u_mask,
                        u_count, umax) != cudaSuccess)
     return MOBA_ERR_CUDA;
@@ -1152,9 +1172,6 @@ extern "C" int moba_decode_route(const moba_cache_desc* c, const void* q, const 
 }
 
 static int attend_part_tokens(const moba_cache_desc* c) {
-#ifdef MOBA_DEC_PART
-  if (c->chunk_size >= MOBA_DEC_PART) return MOBA_DEC_PART;
-#endif
   return c->chunk_size >= 2048 ? 1024 : c->chunk_size >= 512 ? 512 : c->chunk_size;
 }
 static int attend_parts(const moba_cache_desc* c) {
@@ -1208,11 +1225,17 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
   const size_t smem = red_bytes > pipe_bytes ? red_bytes : pipe_bytes;
   cudaStream_t st = (cudaStream_t)stream;
   cudaError_t e = cudaSuccess;
+  const bool half = (c->flags & MOBA_CACHE_FP16) != 0;
   prof_begin(kProfDecodeAttend, st);
-#define MOBA_LAUNCH_ATTEND_NS(L, NS, T)                                                                              \
-  do {                                                                                                               \
-    e = cudaFuncSetAttribute(decode_attend_kernel<L, NS, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    if (e == cudaSuccess) e = launch_dependent(8u, decode_attend_kernel<L, NS, T>, grid, dim3(128 * T), smem, st, a); \
+#define MOBA_LAUNCH_ATTEND_F(L, NS, T, F)                                                                               \
+  do {                                                                                                                  \
+    e = cudaFuncSetAttribute(decode_attend_kernel<L, NS, T, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) e = launch_dependent(8u, decode_attend_kernel<L, NS, T, F>, grid, dim3(128 * T), smem, st, a); \
+  } while (0)
+#define MOBA_LAUNCH_ATTEND_NS(L, NS, T)             \
+  do {                                              \
+    if (half) MOBA_LAUNCH_ATTEND_F(L, NS, T, true); \
+    else MOBA_LAUNCH_ATTEND_F(L, NS, T, false);     \
   } while (0)
 #define MOBA_LAUNCH_ATTEND(L)                                                                                      \
   do {                                                                                                             \
@@ -1224,6 +1247,7 @@ extern "C" int moba_decode_attend(const moba_cache_desc* c, const void* q, const
   else if (dp == 128) MOBA_LAUNCH_ATTEND(128);
   else MOBA_LAUNCH_ATTEND(256);
 #undef MOBA_LAUNCH_ATTEND_NS
+#undef MOBA_LAUNCH_ATTEND_F
 #undef MOBA_LAUNCH_ATTEND
   prof_end(kProfDecodeAttend, st);
   if (e != cudaSuccess) return MOBA_ERR_CUDA;

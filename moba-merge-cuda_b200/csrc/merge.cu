@@ -8,6 +8,7 @@
 // its at most 32 contribution indices and reduces them in ascending order, so the result does not depend
 // on the ticket order.  HBM-bound: every input byte is read once, every output byte written once.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -29,7 +30,7 @@ __global__ void __launch_bounds__(256) merge_ticket_kernel(const int64_t* __rest
   else atomicOr(status, kErrCapacity);
 }
 
-// 16 bytes of a row as eight (bf16) or four (fp32) FP32 values.
+// 16 bytes of a row as eight (bf16, half) or four (fp32) FP32 values.
 template <typename T> struct Chunk;
 template <> struct Chunk<__nv_bfloat16> {
   static constexpr int N = 8;
@@ -44,6 +45,27 @@ template <> struct Chunk<__nv_bfloat16> {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Chunk<__half> {
+  static constexpr int N = 8;
+  __device__ static void load(const __half* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static void store(__half* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
       w[i] = *reinterpret_cast<const uint32_t*>(&h);
     }
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -175,7 +197,7 @@ extern "C" int moba_merge_forward(const void* self_out, const float* self_lse, c
                                   void* scratch, size_t scratch_bytes, void* out, float* lse, unsigned* status, void* stream) {
   if (rows < 1 || remote_rows < 0 || dim < 1 || !self_out || !self_lse || !out || !lse || !status || !scratch) return MOBA_ERR_INVALID;
   if (remote_rows > 0 && (!remote_out || !remote_lse || !mapping)) return MOBA_ERR_INVALID;
-  if (kmax < 1 || kmax > 32 || (dtype != 0 && dtype != 1)) return MOBA_ERR_UNSUPPORTED;
+  if (kmax < 1 || kmax > 32 || dtype < 0 || dtype > 2) return MOBA_ERR_UNSUPPORTED;
   if (scratch_bytes < moba_merge_scratch_bytes(rows, kmax)) return MOBA_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)stream;
   int* counts = static_cast<int*>(scratch);
@@ -185,6 +207,8 @@ extern "C" int moba_merge_forward(const void* self_out, const float* self_lse, c
     merge_ticket_kernel<<<(unsigned)((remote_rows + 255) / 256), 256, 0, st>>>(mapping, remote_rows, rows, kmax, counts, slots, status);
   if (dtype == 0)
     launch_rows<__nv_bfloat16>(self_out, self_lse, remote_out, remote_lse, counts, slots, rows, dim, kmax, out, lse, st);
+  else if (dtype == 2)
+    launch_rows<__half>(self_out, self_lse, remote_out, remote_lse, counts, slots, rows, dim, kmax, out, lse, st);
   else
     launch_rows<float>(self_out, self_lse, remote_out, remote_lse, counts, slots, rows, dim, kmax, out, lse, st);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;

@@ -5,7 +5,7 @@
 // Launch sequence: dq_acc = 0, delta = rowsum(dO * O), pack dO / LSE / delta per query tile, the KV-stationary main
 // kernel (prefill_attn_bwd_ws.cu for head_dim <= 64, prefill_attn_bwd_ws128.cu above that: dK and dV of a key block
 // accumulate in tensor memory and are written once, dQ of every tile is reduced into the FP32 buffer with vector
-// atomics), dq = bf16(dq_acc).  With MOBA_BWD_DETERMINISTIC the accumulator is 64-bit fixed point and the reductions
+// atomics), dq = dq_acc rounded to the input format.  With MOBA_BWD_DETERMINISTIC the accumulator is 64-bit fixed point and the reductions
 // are integer, which makes dQ bit-repeatable like everything else (the reference asks FlashAttention for the same:
 // deterministic=True in both backward calls, mixed_attention.py:185,220).
 #include "prefill_bwd.cuh"
@@ -17,7 +17,7 @@ namespace moba {
 template <int LPR>
 __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __restrict__ out,
                                                         const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
-                                                        long long rows, int D) {
+                                                        long long rows, int D, bool f16) {
   constexpr int RPW = 32 / LPR;  // rows per warp
   const int lane = threadIdx.x & 31, sub = lane % LPR;
   const long long row = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW + lane / LPR;
@@ -28,8 +28,9 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __r
     const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      s = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), s);
-      s = fmaf(__uint_as_float(aw[i] & 0xFFFF0000u), __uint_as_float(bw[i] & 0xFFFF0000u), s);
+      const float2 x = unpack16(aw[i], f16), y = unpack16(bw[i], f16);
+      s = fmaf(x.x, y.x, s);
+      s = fmaf(x.y, y.y, s);
     }
   }
 #pragma unroll
@@ -38,16 +39,16 @@ __global__ void __launch_bounds__(256) bwd_delta_kernel(const __nv_bfloat16* __r
 }
 
 __global__ void __launch_bounds__(256) bwd_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
-                                                             long long n8) {
+                                                             long long n8, bool f16) {
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= n8) return;
   const float4 a = reinterpret_cast<const float4*>(acc)[2 * i], b = reinterpret_cast<const float4*>(acc)[2 * i + 1];
   reinterpret_cast<uint4*>(dq)[i] =
-      make_uint4(bwd_pack_bf16(a.x, a.y), bwd_pack_bf16(a.z, a.w), bwd_pack_bf16(b.x, b.y), bwd_pack_bf16(b.z, b.w));
+      make_uint4(pack16(a.x, a.y, f16), pack16(a.z, a.w, f16), pack16(b.x, b.y, f16), pack16(b.z, b.w, f16));
 }
 
 __global__ void __launch_bounds__(256) bwd_dq_convert_fixed_kernel(const long long* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
-                                                                   long long n8) {
+                                                                   long long n8, bool f16) {
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= n8) return;
   float f[8];
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(256) bwd_dq_convert_fixed_kernel(const long lo
     f[2 * j + 1] = (float)((double)w.y * (1.0 / 4294967296.0));
   }
   reinterpret_cast<uint4*>(dq)[i] =
-      make_uint4(bwd_pack_bf16(f[0], f[1]), bwd_pack_bf16(f[2], f[3]), bwd_pack_bf16(f[4], f[5]), bwd_pack_bf16(f[6], f[7]));
+      make_uint4(pack16(f[0], f[1], f16), pack16(f[2], f[3], f16), pack16(f[4], f[5], f16), pack16(f[6], f[7], f16));
 }
 
 }  // namespace moba
@@ -98,10 +99,11 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
     const __nv_bfloat16* o16 = static_cast<const __nv_bfloat16*>(out);
     const __nv_bfloat16* do16 = static_cast<const __nv_bfloat16*>(dout);
     const int units = d->dim / 8;
-    if (units <= 4) bwd_delta_kernel<4><<<(unsigned)((rows + 63) / 64), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
-    else if (units <= 8) bwd_delta_kernel<8><<<(unsigned)((rows + 31) / 32), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
-    else if (units <= 16) bwd_delta_kernel<16><<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
-    else bwd_delta_kernel<32><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o16, do16, delta, rows, d->dim);
+    const bool f16 = (d->flags & MOBA_INPUT_FP16) != 0;
+    if (units <= 4) bwd_delta_kernel<4><<<(unsigned)((rows + 63) / 64), 256, 0, st>>>(o16, do16, delta, rows, d->dim, f16);
+    else if (units <= 8) bwd_delta_kernel<8><<<(unsigned)((rows + 31) / 32), 256, 0, st>>>(o16, do16, delta, rows, d->dim, f16);
+    else if (units <= 16) bwd_delta_kernel<16><<<(unsigned)((rows + 15) / 16), 256, 0, st>>>(o16, do16, delta, rows, d->dim, f16);
+    else bwd_delta_kernel<32><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o16, do16, delta, rows, d->dim, f16);
   }
   BwdArgs a;
   a.pv = make_view(*d);
@@ -150,8 +152,8 @@ extern "C" int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const
   const long long n8 = rows * d->dim / 8;
   if (fixed)
     bwd_dq_convert_fixed_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(reinterpret_cast<const long long*>(dq_acc),
-                                                                           static_cast<__nv_bfloat16*>(dq), n8);
+                                                                           static_cast<__nv_bfloat16*>(dq), n8, a.pv.fp16 != 0);
   else
-    bwd_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
+    bwd_dq_convert_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8, a.pv.fp16 != 0);
   return cudaGetLastError() == cudaSuccess ? MOBA_OK : MOBA_ERR_CUDA;
 }

@@ -89,6 +89,7 @@ struct WsSmem {
 };
 static_assert(sizeof(WsSmem) <= 8192, "control block must fit its reservation");
 
+template <bool F16>
 __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   constexpr int DPAD = 64;
   constexpr int TILE_BYTES = kTile * DPAD * 2;
@@ -241,9 +242,9 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       // dP^T, so dP^T of the next tile follows dK of this one in the (in-order) tensor pipe; every other
       // awaited event depends only on instructions issued earlier and has most of a tile of slack.
       const bool leader = bwd_elect_one();
-      const uint32_t idesc_st = umma_idesc_bf16(128, 128, 0, 0);
-      const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 0, 1);   // A from tensor memory, B MN-major
-      const uint32_t idesc_dq = umma_idesc_bf16(128, DPAD, 1, 1);   // A = dS^T tile (MN-major), B = K (MN-major)
+      const uint32_t idesc_st = umma_idesc_16<F16>(128, 128, 0, 0);
+      const uint32_t idesc_kv = umma_idesc_16<F16>(128, DPAD, 0, 1);   // A from tensor memory, B MN-major
+      const uint32_t idesc_dq = umma_idesc_16<F16>(128, DPAD, 1, 1);   // A = dS^T tile (MN-major), B = K (MN-major)
       // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
       // field counts 16-byte units).
       const uint64_t k_km = umma_desc_kmajor(smem_u32(sK), kTile, 0), k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
@@ -360,7 +361,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       }
       uint32_t pk[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) pk[i] = bwd_pack_bf16(p[2 * i], p[2 * i + 1]);
+      for (int i = 0; i < 32; ++i) pk[i] = pack16<F16>(p[2 * i], p[2 * i + 1]);
       if (it > 0) alive = warp_wait(&cb.pt_free, (it - 1) & 1, a.status, alive);  // dV of the previous tile has read P^T
       tmem_st32(tlane + COL_PT + half * 32, pk);
       tmem_st_wait();
@@ -383,8 +384,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
           const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3])), sc, make_float2(dl.z, dl.w));
           const float2 d0 = __fmul2_rn(make_float2(p[pc * 32 + i], p[pc * 32 + i + 1]), e0);
           const float2 d1 = __fmul2_rn(make_float2(p[pc * 32 + i + 2], p[pc * 32 + i + 3]), e1);
-          pk[pc * 16 + (i >> 1)] = bwd_pack_bf16(d0.x, d0.y);
-          pk[pc * 16 + (i >> 1) + 1] = bwd_pack_bf16(d1.x, d1.y);
+          pk[pc * 16 + (i >> 1)] = pack16<F16>(d0.x, d0.y);
+          pk[pc * 16 + (i >> 1) + 1] = pack16<F16>(d1.x, d1.y);
         }
       }
       // dS^T: over the first 32 of this thread's own dP^T columns for the dK product, and as a tile row
@@ -415,10 +416,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
           for (int i = 0; i < 32; i += 8)
             if (pc * 32 + i < D)
               *reinterpret_cast<uint4*>(dst + pc * 32 + i) =
-                  make_uint4(bwd_pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+                  make_uint4(pack16<F16>(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                             pack16<F16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                             pack16<F16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                             pack16<F16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
         }
       }
     }
@@ -430,9 +431,10 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 
 cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st) {
   const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 + 4 * 4096;
-  cudaError_t e = cudaFuncSetAttribute(attn_bwd_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const auto kernel = a.pv.fp16 ? attn_bwd_ws_kernel<true> : attn_bwd_ws_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  attn_bwd_ws_kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kWsThreads, smem, st>>>(a);
+  kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kWsThreads, smem, st>>>(a);
   return cudaGetLastError();
 }
 

@@ -34,6 +34,7 @@ static_assert(sizeof(Smem128) <= 4096, "control block must fit its reservation")
 
 }  // namespace
 
+template <bool F16>
 __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) {
   constexpr int DPAD = 128;
   constexpr int KV_BYTES = kTile * DPAD * 2;      // 32 KB: two 64-column panels of 128 rows
@@ -182,9 +183,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
       // ================================================================== MMA issue
       // Fixed order per step n:  S^T(n+1) | dV(n) | dK(n) | dP^T(n+1) | dQ^T(n).
       const bool leader = bwd_elect_one();
-      const uint32_t idesc_st = umma_idesc_bf16(128, kQRows, 0, 0);   // K-major x K-major, N = 64 queries
-      const uint32_t idesc_kv = umma_idesc_bf16(128, DPAD, 0, 1);     // A from tensor memory, B MN-major, N = 128
-      const uint32_t idesc_dq = umma_idesc_bf16(128, kQRows, 1, 1);   // A = K (MN-major), B = dS^T tile (MN-major)
+      const uint32_t idesc_st = umma_idesc_16<F16>(128, kQRows, 0, 0);   // K-major x K-major, N = 64 queries
+      const uint32_t idesc_kv = umma_idesc_16<F16>(128, DPAD, 0, 1);     // A from tensor memory, B MN-major, N = 128
+      const uint32_t idesc_dq = umma_idesc_16<F16>(128, kQRows, 1, 1);   // A = K (MN-major), B = dS^T tile (MN-major)
       // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
       // field counts 16-byte units): a K-major step of 16 elements is 2 units inside a 64-column panel,
       // an MN-major step of 16 rows is 128 units.
@@ -301,7 +302,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
       }
       uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) pk[i] = bwd_pack_bf16(p[2 * i], p[2 * i + 1]);
+      for (int i = 0; i < 16; ++i) pk[i] = pack16<F16>(p[2 * i], p[2 * i + 1]);
       if (it > 0) alive = warp_wait(&cb.pt_free, (it - 1) & 1, a.status, alive);  // dV of the previous step has read P^T
       tmem_st16(tlane + COL_PT + half * 16, pk);
       tmem_st_wait();
@@ -323,8 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
           const float2 e1 = __ffma2_rn(make_float2(__uint_as_float(t[i + 2]), __uint_as_float(t[i + 3])), sc, make_float2(dl.z, dl.w));
           const float2 d0 = __fmul2_rn(make_float2(p[i], p[i + 1]), e0);
           const float2 d1 = __fmul2_rn(make_float2(p[i + 2], p[i + 3]), e1);
-          pk[i >> 1] = bwd_pack_bf16(d0.x, d0.y);
-          pk[(i >> 1) + 1] = bwd_pack_bf16(d1.x, d1.y);
+          pk[i >> 1] = pack16<F16>(d0.x, d0.y);
+          pk[(i >> 1) + 1] = pack16<F16>(d1.x, d1.y);
         }
       }
       // dS^T: over the first 16 of this thread's own dP^T columns for the dK product, and as a tile row in
@@ -355,10 +356,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
           for (int i = 0; i < 32; i += 8)
             if (pc * 32 + i < D)
               *reinterpret_cast<uint4*>(dst + pc * 32 + i) =
-                  make_uint4(bwd_pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
-                             bwd_pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
+                  make_uint4(pack16<F16>(__uint_as_float(v[i]), __uint_as_float(v[i + 1])),
+                             pack16<F16>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                             pack16<F16>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                             pack16<F16>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])));
         }
       }
     }
@@ -370,9 +371,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
 
 cudaError_t launch_bwd_ws128(const BwdArgs& a, cudaStream_t st) {
   const size_t smem = 4096 + 2 * (size_t)kTile * 128 * 2 + (size_t)kRing * 2 * kQRows * 128 * 2 + (size_t)kTile * kQRows * 2 + 4 * 2048;
-  cudaError_t e = cudaFuncSetAttribute(attn_bwd_ws128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const auto kernel = a.pv.fp16 ? attn_bwd_ws128_kernel<true> : attn_bwd_ws128_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  attn_bwd_ws128_kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kThreads, smem, st>>>(a);
+  kernel<<<dim3(a.pv.n_qtiles, a.pv.Hkv), kThreads, smem, st>>>(a);
   return cudaGetLastError();
 }
 

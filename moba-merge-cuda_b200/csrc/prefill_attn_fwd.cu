@@ -34,11 +34,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
 
 __device__ __forceinline__ bool elect_one_sync() {
   uint32_t pred;
@@ -168,7 +163,7 @@ struct FwdSmem {
 };
 static_assert(sizeof(FwdSmem) <= 1024, "control block must fit its reservation");
 
-template <int DPAD, bool SELF>
+template <int DPAD, bool SELF, bool F16>
 __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
   using Cfg = FwdCfg<DPAD>;
   constexpr int TILE_BYTES = Cfg::TILE_BYTES, QBUFS = Cfg::QBUFS, STAGES = Cfg::STAGES;
@@ -246,8 +241,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
     // awaited event depends only on instructions issued earlier in this order, and each has about a
     // tile of slack, so waiting in a fixed order costs nothing.
     const bool leader = elect_one_sync();
-    const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
-    const uint32_t idesc_o = umma_idesc_bf16(128, DPAD, 0, 1);
+    const uint32_t idesc_s = umma_idesc_16<F16>(128, 128, 0, 0);
+    const uint32_t idesc_o = umma_idesc_16<F16>(128, DPAD, 0, 1);
     // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
     // field counts 16-byte units).
     const uint64_t qd0 = umma_desc_kmajor(smem_u32(sQ), kTile, 0);
@@ -446,8 +441,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
           sum0 = __fadd2_rn(sum0, pa);
           sum1 = __fadd2_rn(sum1, pb);
-          pk[i >> 1] = pack_bf16(pa.x, pa.y);
-          pk[16 + (i >> 1)] = pack_bf16(pb.x, pb.y);
+          pk[i >> 1] = pack16<F16>(pa.x, pa.y);
+          pk[16 + (i >> 1)] = pack16<F16>(pb.x, pb.y);
         }
         if (j > 0 && !rescale && alive) alive = mbar_wait(&cb.o_full[l], (tc - 1) & 1, a.status);
         tmem_st32(tP, pk);
@@ -459,8 +454,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
           const float2 pb = make_float2(fast_exp2(xb.x), fast_exp2(xb.y));
           sum0 = __fadd2_rn(sum0, pa);
           sum1 = __fadd2_rn(sum1, pb);
-          pk[i >> 1] = pack_bf16(pa.x, pa.y);
-          pk[16 + (i >> 1)] = pack_bf16(pb.x, pb.y);
+          pk[i >> 1] = pack16<F16>(pa.x, pa.y);
+          pk[16 + (i >> 1)] = pack16<F16>(pb.x, pb.y);
         }
         tmem_st32(tP + 32, pk);
         l_run += (sum0.x + sum0.y) + (sum1.x + sum1.y);
@@ -493,8 +488,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         for (int u = 0; u < UPR; ++u) {
           if (u * 8 < D)
             *reinterpret_cast<uint4*>(dst + u * 8) =
-                make_uint4(pack_bf16(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack_bf16(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
-                           pack_bf16(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack_bf16(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
+                make_uint4(pack16<F16>(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack16<F16>(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
+                           pack16<F16>(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack16<F16>(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
         }
         a.part_lse[row_id] = m_used + log2f(l_run);
       } else {
@@ -526,8 +521,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
               const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                o_acc[u * 8 + 2 * i] = fmaf(w, __uint_as_float(wv[i] << 16), o_acc[u * 8 + 2 * i]);
-                o_acc[u * 8 + 2 * i + 1] = fmaf(w, __uint_as_float(wv[i] & 0xFFFF0000u), o_acc[u * 8 + 2 * i + 1]);
+                const float2 pv2 = unpack16<F16>(wv[i]);
+                o_acc[u * 8 + 2 * i] = fmaf(w, pv2.x, o_acc[u * 8 + 2 * i]);
+                o_acc[u * 8 + 2 * i + 1] = fmaf(w, pv2.y, o_acc[u * 8 + 2 * i + 1]);
               }
             }
           }
@@ -538,8 +534,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         for (int u = 0; u < UPR; ++u) {
           if (u * 8 < D)
             *reinterpret_cast<uint4*>(dst + u * 8) =
-                make_uint4(pack_bf16(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack_bf16(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
-                           pack_bf16(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack_bf16(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
+                make_uint4(pack16<F16>(o_acc[u * 8] * inv, o_acc[u * 8 + 1] * inv), pack16<F16>(o_acc[u * 8 + 2] * inv, o_acc[u * 8 + 3] * inv),
+                           pack16<F16>(o_acc[u * 8 + 4] * inv, o_acc[u * 8 + 5] * inv), pack16<F16>(o_acc[u * 8 + 6] * inv, o_acc[u * 8 + 7] * inv));
         }
         a.lse[row_id] = (big + log2f(z)) * 0.6931471805599453f;
       }
@@ -563,16 +559,20 @@ static int sm_count() {
   return cached[dev];
 }
 
-template <int DPAD, bool SELF>
-static cudaError_t launch_fwd(const FwdArgs& a, long long items, cudaStream_t st) {
+template <int DPAD, bool SELF, bool F16>
+static cudaError_t launch_fwd_as(const FwdArgs& a, long long items, cudaStream_t st) {
   const int smem = FwdCfg<DPAD>::SMEM;
-  cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<DPAD, SELF>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<DPAD, SELF, F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   const int sms = sm_count();
   if (sms <= 0) return cudaErrorUnknown;
   const int grid = (int)(items < sms ? (items < 1 ? 1 : items) : sms);
-  attn_fwd_kernel<DPAD, SELF><<<grid, kFwdThreads, smem, st>>>(a);
+  attn_fwd_kernel<DPAD, SELF, F16><<<grid, kFwdThreads, smem, st>>>(a);
   return cudaGetLastError();
+}
+template <int DPAD, bool SELF>
+static cudaError_t launch_fwd(const FwdArgs& a, long long items, cudaStream_t st) {
+  return a.pv.fp16 ? launch_fwd_as<DPAD, SELF, true>(a, items, st) : launch_fwd_as<DPAD, SELF, false>(a, items, st);
 }
 
 }  // namespace moba

@@ -15,6 +15,7 @@ constexpr int kTile = 128;  // query rows per tile and keys per tile
 struct PrefillView {
   int T, B, Hq, Hkv, G, D, C, R;
   int n_chunks, n_qtiles, max_tiles_per_seq, n_self_pairs;
+  int fp16;  // q, k, v, out and the gradients are IEEE half (MOBA_INPUT_FP16), else bf16
   long long q_st, q_sh, k_st, k_sh, v_st, v_sh;  // element strides of token and head
   const int* cu_seqlens;   // [B+1]
   const int* chunk_start;  // [n_chunks+1] first packed token of every chunk
@@ -32,6 +33,7 @@ inline PrefillView make_view(const moba_prefill_desc& d) {
   v.T = d.total_tokens; v.B = d.num_seqs; v.Hq = d.hq; v.Hkv = d.hkv; v.G = d.hq / d.hkv; v.D = d.dim;
   v.C = d.chunk_size; v.R = d.remote_k; v.n_chunks = d.num_chunks; v.n_qtiles = d.num_qtiles;
   v.max_tiles_per_seq = d.max_tiles_per_seq; v.n_self_pairs = d.num_self_pairs;
+  v.fp16 = (d.flags & MOBA_INPUT_FP16) ? 1 : 0;
   v.q_st = d.q_stride_t; v.q_sh = d.q_stride_h; v.k_st = d.k_stride_t; v.k_sh = d.k_stride_h;
   v.v_st = d.v_stride_t; v.v_sh = d.v_stride_h;
   v.cu_seqlens = d.cu_seqlens; v.chunk_start = d.chunk_start; v.chunk_seq = d.chunk_seq;

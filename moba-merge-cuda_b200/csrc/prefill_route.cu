@@ -36,14 +36,16 @@ __global__ void __launch_bounds__(256) chunk_mean_kernel(PrefillView pv, const _
   const int rpi = 256 / upr;
   const int ri = threadIdx.x / upr, u = threadIdx.x - ri * upr;
   float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const bool f16 = pv.fp16 != 0;
   if (ri < rpi) {
     const __nv_bfloat16* base = k + (long long)g * pv.k_sh + u * 8;
     auto add = [&](const uint4& raw) {
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        acc[2 * i] += __uint_as_float(w[i] << 16);
-        acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+        const float2 f = unpack16(w[i], f16);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
       }
     };
     int t = t0 + ri;
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(256) chunk_mean_kernel(PrefillView pv, const _
     float s = 0.f;
     for (int j = 0; j < splits; ++j) s += __ldcg(part + (seg * splits + j) * pv.D + d);
     float m = s / (float)(c1 - c0);
-    if (round_bf16) m = __bfloat162float(__float2bfloat16_rn(m));
+    if (round_bf16) m = round16(m, f16);   // to the format of the inputs
     means[seg * pv.D + d] = m;
   }
   if (threadIdx.x == 0) tickets[seg] = 0;
@@ -99,7 +101,7 @@ __device__ __forceinline__ float sum2(unsigned long long v) {
 }
 
 // grid (query tile, query head).  A group of LPR lanes shares four query rows: each lane keeps DD of the DD * LPR
-// (padded) head dimensions of all four rows as FP32 in registers for the whole launch, converted from bf16 once.  The
+// (padded) head dimensions of all four rows as FP32 in registers for the whole launch, converted from the 16-bit inputs once.  The
 // candidate means sit in shared memory as FP32; one 16-byte broadcast load feeds eight packed FMAs (four rows), which
 // is what keeps the shared-memory pipe below the FMA pipe - with one row per lane it is the limit.  The four partial
 // sums of a lane are combined across the group by a butterfly of three (LPR = 4) or four (LPR = 8) shuffles that
@@ -173,7 +175,10 @@ __global__ void __launch_bounds__(32 * LPR) gate_topk_kernel(PrefillView pv, con
           if (row0 + j < nrows) raw = *reinterpret_cast<const uint4*>(qrow + u * 16);
           const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) qp[j][u * 4 + i] = pack2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xFFFF0000u));
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = unpack16(w[i], pv.fp16 != 0);
+            qp[j][u * 4 + i] = pack2(f.x, f.y);
+          }
         }
       }
     } else {

@@ -14,6 +14,7 @@
 //   This is also the image a TMA load with CU_TENSOR_MAP_SWIZZLE_128B produces.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -163,6 +164,34 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t M, uint32_t N, u
                                                        uint32_t b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (a_mn_major << 15) | (b_mn_major << 16) | ((N >> 3) << 17) |
          ((M >> 4) << 24);
+}
+// The same for either 16-bit input format: the operand-format fields (bits 7-9 for A, 10-12 for B) hold 1 for
+// bf16 and 0 for IEEE half.
+template <bool F16>
+__host__ __device__ constexpr uint32_t umma_idesc_16(uint32_t M, uint32_t N, uint32_t a_mn_major, uint32_t b_mn_major) {
+  return umma_idesc_bf16(M, N, a_mn_major, b_mn_major) & (F16 ? ~((1u << 7) | (1u << 10)) : ~0u);
+}
+
+// ----------------------------------------------------------------------------- the two 16-bit input formats
+// Kernels that convert inside their inner loops are compiled once per format (F16 = IEEE half, else bf16).
+template <bool F16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {  // (lo, hi) -> two 16-bit values, lo in the low half
+  uint32_t r;
+  if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <bool F16>
+__device__ __forceinline__ float2 unpack16(uint32_t w) {
+  if (F16) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u));
+}
+// Run-time forms for kernels that convert a few values per thread (the flag is uniform over the launch).
+__device__ __forceinline__ float2 unpack16(uint32_t w, bool f16) { return f16 ? unpack16<true>(w) : unpack16<false>(w); }
+__device__ __forceinline__ uint32_t pack16(float lo, float hi, bool f16) { return f16 ? pack16<true>(lo, hi) : pack16<false>(lo, hi); }
+// x rounded to the 16-bit format and back (what storing and re-reading it would give)
+__device__ __forceinline__ float round16(float x, bool f16) {
+  return f16 ? __half2float(__float2half_rn(x)) : __bfloat162float(__float2bfloat16_rn(x));
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.

@@ -2,16 +2,16 @@
 
 Behaviourally the checks of the reference (src/moba_opt/baseline_adapter.py:23-76): every violation
 is a ValueError raised before any device work, and `validate_shapes` / `validate_config` stay usable
-without a CUDA runtime.  Three limits differ on purpose: topk may go up to 17 (reference: 9) because
-the long-context configuration needs 12, the CUDA kernels take bf16 only (the reference also
-accepts fp16), and the prefill kernels take head_dim up to 128 (the reference: 256; the decode
-cache here goes to 256 as well).  Each is refused here, as a ValueError, before anything is launched.
+without a CUDA runtime.  Two limits differ on purpose: topk may go up to 17 (reference: 9) because
+the long-context configuration needs 12, and the prefill kernels take head_dim up to 128 (the
+reference: 256; the decode cache here goes to 256 as well).  Each is refused here, as a ValueError,
+before anything is launched.  bf16 and fp16 inputs are both taken, as by the reference.
 """
 import numbers
 
 import torch
 
-SUPPORTED_DTYPES = (torch.bfloat16,)
+SUPPORTED_DTYPES = (torch.bfloat16, torch.float16)
 MAINLINE_HEAD_DIMS = tuple(range(8, 257, 8))      # the reference's envelope; the decode cache accepts all of it
 PREFILL_HEAD_DIMS = tuple(range(8, 129, 8))       # what the prefill kernels are compiled for
 MAX_TOPK = 17

@@ -83,7 +83,7 @@ class PrefillPlan:
 
     def desc(self, q, k, v, remote_k, flags=0):
         d = _ext.PrefillDesc()
-        d.flags = flags
+        d.flags = flags | (4 if q.dtype == torch.float16 else 0)    # MOBA_INPUT_FP16
         d.total_tokens, d.num_seqs = self.total_tokens, self.num_seqs
         d.hq, d.hkv, d.dim = q.shape[1], k.shape[1], q.shape[2]
         d.chunk_size, d.remote_k = self.chunk_size, remote_k

@@ -17,8 +17,7 @@ Operations are serialised by a lock and bound to the CUDA stream that was curren
 built; other streams and external graph capture are refused.  Validation failures never modify the
 cache, and the CPU layout is committed only after every launch of a call was accepted.
 
-Differences to the reference, all by design of the CUDA kernels: the cache dtype is bf16 only,
-head_dim must be a multiple of 8 (8..256), chunk_size may be up to 8192 (reference: 1024), topk up
+Differences to the reference, all by design of the CUDA kernels: head_dim must be a multiple of 8 (8..256), chunk_size may be up to 8192 (reference: 1024), topk up
 to 17 (reference: 9), and routing always breaks exact score ties towards the lowest chunk.
 """
 import ctypes
@@ -41,7 +40,7 @@ MAX_TOPK = 17
 class CacheDesc(ctypes.Structure):
     """Mirror of moba_cache_desc in include/moba_b200.h."""
     _fields_ = ([(n, ctypes.c_int32) for n in ("batch_slots", "max_seq_len", "page_size", "num_pages", "table_width",
-                                               "chunk_size", "max_chunks", "hkv", "dim")]
+                                               "chunk_size", "max_chunks", "hkv", "dim", "flags")]
                 + [(n, ctypes.c_void_p) for n in ("k_cache", "v_cache", "table", "lengths", "means")])
 
 
@@ -222,8 +221,8 @@ class PagedKVCache:
         self.chunk_size = positive_int(chunk_size, "chunk_size")
         if self.chunk_size > MAX_CHUNK:
             raise ValueError(f"cache chunk_size must be <={MAX_CHUNK}")
-        if dtype != torch.bfloat16:
-            raise ValueError("cache dtype must be BF16")
+        if dtype not in (torch.bfloat16, torch.float16):
+            raise ValueError("cache dtype must be BF16 or FP16")
         wanted = torch.device(device)
         if wanted.type != "cuda":
             raise ValueError("cache device must be CUDA")
@@ -269,7 +268,7 @@ class PagedKVCache:
     def _desc(self):
         lay = self._layout
         d = CacheDesc(lay.batch_size, lay.max_seq_len, lay.page_size, lay.num_pages, lay.table_width, self.chunk_size,
-                      self._max_chunks, self.num_kv_heads, self.head_dim)
+                      self._max_chunks, self.num_kv_heads, self.head_dim, 1 if self.dtype == torch.float16 else 0)   # MOBA_CACHE_FP16
         d.k_cache, d.v_cache = self.k_cache.data_ptr(), self.v_cache.data_ptr()
         d.table, d.lengths, d.means = self._table.data_ptr(), self._lengths.data_ptr(), self._means.data_ptr()
         return d

@@ -14,7 +14,7 @@ MAX_CONTRIBUTIONS = 32  # per row
 
 def merge_forward_cuda(self_out, self_lse, remote_out, remote_lse, mapping, kmax=None, check_capacity=True,
                        deterministic=False):
-    """self_out [T,H,D] (bf16 or fp32, CUDA); self_lse [T,H] fp32; remote_out [M,1,D] or [M,D];
+    """self_out [T,H,D] (bf16, fp16 or fp32, CUDA); self_lse [T,H] fp32; remote_out [M,1,D] or [M,D];
     remote_lse [M] fp32; mapping [M] int32/int64 with the row t*H+h every contribution belongs to.
     Returns (O like self_out, LSE [T,H] fp32).  Contributions are always reduced in ascending index
     order, so `deterministic` only is type-checked.  With check_capacity a row with more than kmax
@@ -25,8 +25,8 @@ def merge_forward_cuda(self_out, self_lse, remote_out, remote_lse, mapping, kmax
         raise ValueError("mapping must be a 1D int32/int64 tensor")
     if self_out.dim() != 3 or not self_out.is_cuda:
         raise ValueError("self_out must be a CUDA tensor [T,H,D]")
-    if self_out.dtype not in (torch.bfloat16, torch.float32):
-        raise ValueError("self_out must be bf16 or fp32")
+    if self_out.dtype not in (torch.bfloat16, torch.float32, torch.float16):
+        raise ValueError("self_out must be bf16, fp16 or fp32")
     T, H, D = self_out.shape
     P, M = T * H, mapping.numel()
     if remote_out.dtype != self_out.dtype or remote_out.device != self_out.device:
@@ -56,7 +56,7 @@ def merge_forward_cuda(self_out, self_lse, remote_out, remote_lse, mapping, kmax
         status = torch.zeros(1, dtype=torch.int32, device=dev) if check_capacity else _status_word(dev)
         _ext.check(lib.moba_merge_forward(so.data_ptr(), sl.data_ptr(), ro.data_ptr() if M else None,
                                           rl.data_ptr() if M else None, mapping.data_ptr() if M else None, P, M, D, kmax,
-                                          0 if so.dtype == torch.bfloat16 else 1, scratch.data_ptr(), nbytes, out.data_ptr(),
+                                          {torch.bfloat16: 0, torch.float32: 1, torch.float16: 2}[so.dtype], scratch.data_ptr(), nbytes, out.data_ptr(),
                                           lse.data_ptr(), status.data_ptr(), _stream(dev)), "moba_merge_forward")
         if check_capacity:
             bits = int(status.item())

@@ -103,15 +103,21 @@ PREFILL_CASES = [
     ("p_k9", (200,), 4, 2, 64, 16, 9, 64),
     ("p_one_chunk", (9, 12), 4, 2, 16, 16, 4, 65),
     ("p_gqa_256", (180, 140), 14, 2, 64, 64, 3, 66),
+    # IEEE half inputs (the reference takes both 16-bit formats, baseline_adapter.py:13); the record says so in `dtype`
+    ("p_fp16_gqa", (150, 90), 8, 2, 64, 32, 3, 70, torch.float16),
+    ("p_fp16_d128", (260,), 6, 1, 128, 24, 4, 71, torch.float16),
 ]
 
 
 def prefill_cases(ref, out_dir):
     grouped, fixed_route_attention, grouped_reference, _, _ = ref
-    for name, lens, hq, hkv, dim, chunk, topk, seed in PREFILL_CASES:
-        q, k, v, g, cu = make_inputs(lens, hq, hkv, dim, seed, torch.bfloat16)
+    for name, lens, hq, hkv, dim, chunk, topk, seed, *rest in PREFILL_CASES:
+        dtype = rest[0] if rest else torch.bfloat16
+        q, k, v, g, cu = make_inputs(lens, hq, hkv, dim, seed, dtype)
         rec = dict(lens=np.asarray(lens), hq=hq, hkv=hkv, dim=dim, chunk=chunk, topk=topk, seed=seed,
                    q=bits(q), k=bits(k), v=bits(v), g=bits(g))
+        if dtype != torch.bfloat16:
+            rec["dtype"] = np.asarray(str(dtype).replace("torch.", ""))
         for tag, precision, stable in (("stable", "fp32", True), ("topk", "fp32", False), ("upstream", "upstream", True),
                                        ("upstream_topk", "upstream", False)):
             cfg = {"chunk_size": chunk, "topk": topk, "route_precision": precision, "stable_routes": stable}
@@ -191,18 +197,20 @@ DECODE_CASES = [
     ("d_small", (37, 90, 5), 8, 2, 64, 16, 4, 201),
     ("d_d128", (200, 131), 12, 2, 128, 32, 4, 202),
     ("d_mha", (64, 65), 4, 4, 32, 8, 3, 203),
+    ("d_fp16", (150, 47), 12, 2, 64, 16, 4, 204, torch.float16),
 ]
 
 
 def decode_cases(ref, out_dir):
     _, _, _, decode_reference, _ = ref
-    for name, lengths, hq, hkv, dim, chunk, topk, seed in DECODE_CASES:
+    for name, lengths, hq, hkv, dim, chunk, topk, seed, *rest in DECODE_CASES:
+        dtype = rest[0] if rest else torch.bfloat16
         rng = torch.Generator().manual_seed(seed)
-        keys = [torch.randn(n, hkv, dim, generator=rng).bfloat16() for n in lengths]
-        values = [torch.randn(n, hkv, dim, generator=rng).bfloat16() for n in lengths]
+        keys = [torch.randn(n, hkv, dim, generator=rng).to(dtype) for n in lengths]
+        values = [torch.randn(n, hkv, dim, generator=rng).to(dtype) for n in lengths]
         ids = list(range(len(lengths)))
         pos = [n - 1 for n in lengths]
-        q = torch.randn(len(ids), hq, dim, generator=rng).bfloat16()
+        q = torch.randn(len(ids), hq, dim, generator=rng).to(dtype)
         # a legal hand-made route: current chunk first, then the most recent complete chunks per head parity
         R = topk - 1
         selected = torch.full((len(ids), hq, 1 + R), -1, dtype=torch.int32)
@@ -218,6 +226,8 @@ def decode_cases(ref, out_dir):
         rec = dict(lengths=np.asarray(lengths), hq=hq, hkv=hkv, dim=dim, chunk=chunk, topk=topk, q=bits(q),
                    selected=selected.numpy(), out_sparse=out_s.numpy(), lse_sparse=lse_s.numpy(),
                    out_dense=out_d.numpy(), lse_dense=lse_d.numpy())
+        if dtype != torch.bfloat16:
+            rec["dtype"] = np.asarray(str(dtype).replace("torch.", ""))
         for i, (kk, vv) in enumerate(zip(keys, values)):
             rec[f"k{i}"], rec[f"v{i}"] = bits(kk), bits(vv)
         np.savez_compressed(out_dir / f"{name}.npz", **rec)

@@ -1,17 +1,28 @@
-"""Shared test helpers: golden-fixture loading and bf16 <-> numpy conversions."""
+"""Shared test helpers: golden-fixture loading and conversions between stored 16-bit patterns, numpy and torch."""
 from pathlib import Path
 
 import numpy as np
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
-PREFILL_GOLDENS = ["p_gqa_small", "p_mha_tail", "p_mqa_multi", "p_k9", "p_one_chunk", "p_gqa_256"]
-DECODE_GOLDENS = ["d_small", "d_d128", "d_mha"]
+PREFILL_GOLDENS = ["p_gqa_small", "p_mha_tail", "p_mqa_multi", "p_k9", "p_one_chunk", "p_gqa_256", "p_fp16_gqa", "p_fp16_d128"]
+DECODE_GOLDENS = ["d_small", "d_d128", "d_mha", "d_fp16"]
 ROUTE_GOLDENS = ["r_upstream_gqa", "r_upstream_mqa"]
 
 
+class HalfBits(np.ndarray):
+    """uint16 bit patterns of IEEE half values (plain uint16 arrays in a fixture are bf16 patterns)."""
+
+
 def load(name):
-    return dict(np.load(GOLDEN / f"{name}.npz"))
+    """The fixture as a dict; the 16-bit inputs of a fixture whose `dtype` entry says float16 come back as HalfBits,
+    so that bits_to_f64 / bits_to_torch decode them in the right format."""
+    g = dict(np.load(GOLDEN / f"{name}.npz"))
+    if str(g.get("dtype", "bfloat16")) == "float16":
+        for key, value in g.items():
+            if value.dtype == np.uint16:
+                g[key] = value.view(HalfBits)
+    return g
 
 
 def unpack_selected(g, tag):
@@ -20,14 +31,17 @@ def unpack_selected(g, tag):
     return np.unpackbits(g[f"selected_{tag}_packed"])[:int(np.prod(shape))].reshape(shape).astype(bool)
 
 
-def bf16_bits_to_f64(bits):
-    """uint16 bf16 bit patterns -> float64 values."""
+def bits_to_f64(bits):
+    """uint16 bit patterns (bf16, or half when tagged HalfBits) -> float64 values."""
+    if isinstance(bits, HalfBits):
+        return np.asarray(bits).view(np.float16).astype(np.float64)
     return (np.asarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
 
 
-def bf16_bits_to_torch(bits, device="cpu"):
+def bits_to_torch(bits, device="cpu"):
     import torch
-    t = torch.from_numpy(np.asarray(bits, dtype=np.uint16).view(np.int16).copy()).view(torch.bfloat16)
+    dtype = torch.float16 if isinstance(bits, HalfBits) else torch.bfloat16
+    t = torch.from_numpy(np.asarray(bits, dtype=np.uint16).view(np.int16).copy()).view(dtype)
     return t.to(device)
 
 

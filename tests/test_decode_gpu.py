@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import DECODE_GOLDENS, bf16_bits_to_torch, load, torch_to_f64
+from helpers import DECODE_GOLDENS, bits_to_torch, load, torch_to_f64
 from oracle import moba_oracle as mo
 
 pytestmark = pytest.mark.gpu
@@ -33,9 +33,10 @@ def check(cache, result, q):
         values.append(torch_to_f64(v))
         closed = cache.lengths[sid] // C
         if closed:
-            want = mo.chunk_means(keys[-1], C, rounding=mo.bf16_round)
+            half = cache.dtype == torch.float16
+            want = mo.chunk_means(keys[-1], C, rounding=mo.fp16_round if half else mo.bf16_round)
             got = torch_to_f64(cache._means[sid, :closed])
-            np.testing.assert_allclose(got, want, atol=1e-5, rtol=0.01)   # at most one bf16 ulp apart
+            np.testing.assert_allclose(got, want, atol=1e-5, rtol=0.002 if half else 0.01)   # at most one ulp of the format apart
     qf = torch_to_f64(q)
     if result.selected_blocks is not None:
         route = result.selected_blocks.cpu().numpy()
@@ -71,11 +72,11 @@ def test_decode_matches_reference_golden(name):
     g = load(name)
     lengths, hq, hkv, dim, chunk = g["lengths"], int(g["hq"]), int(g["hkv"]), int(g["dim"]), int(g["chunk"])
     n = len(lengths)
-    cache = PagedKVCache(n, int(max(lengths)) + 1, hkv, dim, page_size=5, chunk_size=chunk)
-    ks = [bf16_bits_to_torch(g[f"k{i}"], "cuda") for i in range(n)]
-    vs = [bf16_bits_to_torch(g[f"v{i}"], "cuda") for i in range(n)]
+    ks = [bits_to_torch(g[f"k{i}"], "cuda") for i in range(n)]
+    vs = [bits_to_torch(g[f"v{i}"], "cuda") for i in range(n)]
+    cache = PagedKVCache(n, int(max(lengths)) + 1, hkv, dim, page_size=5, chunk_size=chunk, dtype=ks[0].dtype)
     cache.append(torch.cat(ks), torch.cat(vs), sequence_ids=list(range(n)), cu_seqlens=[0] + [int(x) for x in np.cumsum(lengths)])
-    q = bf16_bits_to_torch(g["q"], "cuda")
+    q = bits_to_torch(g["q"], "cuda")
     dense = cache.attend(q, sequence_ids=list(range(n)), mode="dense")
     np.testing.assert_allclose(torch_to_f64(dense.output), g["out_dense"], atol=0.02, rtol=0.02)
     np.testing.assert_allclose(torch_to_f64(dense.lse), g["lse_dense"], atol=5e-4, rtol=2e-5)
@@ -83,11 +84,15 @@ def test_decode_matches_reference_golden(name):
     check(cache, cache.attend(q, sequence_ids=list(range(n)), topk=int(g["topk"])), q)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
 @pytest.mark.parametrize("kind", ["paged", "contiguous"])
 @pytest.mark.parametrize("hq,hk", [(1, 1), (8, 1), (8, 2), (28, 4), (32, 8)])
-def test_incremental_decode(kind, hq, hk):
+def test_incremental_decode(kind, hq, hk, dtype):
     from moba_opt import ContiguousKVCache, PagedKVCache
-    cache = PagedKVCache(2, 32, hk, 64, chunk_size=4, page_size=3) if kind == "paged" else ContiguousKVCache(2, 32, hk, 64, chunk_size=4)
+    from functools import partial
+    rand = partial(globals()["rand"], dtype=dtype)
+    cache = (PagedKVCache(2, 32, hk, 64, chunk_size=4, page_size=3, dtype=dtype) if kind == "paged"
+             else ContiguousKVCache(2, 32, hk, 64, chunk_size=4, dtype=dtype))
     k, v = rand((9, hk, 64), 101), rand((9, hk, 64), 102)
     cache.append(k, v, sequence_ids=[0, 1], cu_seqlens=[0, 4, 9])
     stored_k, stored_v = [k[:4], k[4:]], [v[:4], v[4:]]
@@ -104,10 +109,13 @@ def test_incremental_decode(kind, hq, hk):
         check(cache, cache.attend(q, sequence_ids=[0, 1], mode="dense"), q)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
 @pytest.mark.parametrize("dim", [8, 16, 24, 40, 64, 80, 96, 128, 136, 192, 256])
-def test_decode_head_dimensions(dim):
+def test_decode_head_dimensions(dim, dtype):
     from moba_opt import PagedKVCache
-    cache = PagedKVCache(2, 64, 2, dim, page_size=7, chunk_size=12)
+    from functools import partial
+    rand = partial(globals()["rand"], dtype=dtype)
+    cache = PagedKVCache(2, 64, 2, dim, page_size=7, chunk_size=12, dtype=dtype)
     k, v = rand((68, 2, dim), 131), rand((68, 2, dim), 132)
     cache.append(k, v, sequence_ids=[0, 1], cu_seqlens=[0, 27, 68])
     assert_payload(cache, 0, k[:27], v[:27])
@@ -375,7 +383,7 @@ def test_append_rejects_aliases_before_mutation(combined):
 
 
 @pytest.mark.parametrize("kwargs", [{"head_dim": 0}, {"head_dim": 264}, {"head_dim": 33}, {"num_kv_heads": 0}, {"page_size": 0},
-                                    {"num_pages": 0}, {"chunk_size": 8193}, {"dtype": torch.float32}, {"dtype": torch.float16},
+                                    {"num_pages": 0}, {"chunk_size": 8193}, {"dtype": torch.float32}, {"dtype": torch.float64},
                                     {"device": "cpu"}])
 def test_cache_contract_violations(kwargs):
     from moba_opt import PagedKVCache

@@ -54,7 +54,9 @@ def test_matches_reference_golden():
 
 
 @pytest.mark.parametrize("T,H,D,M,dtype", [(37, 3, 64, 200, torch.float32), (128, 4, 128, 900, torch.bfloat16),
-                                           (5, 1, 8, 0, torch.float32), (61, 2, 40, 333, torch.bfloat16)])
+                                           (5, 1, 8, 0, torch.float32), (61, 2, 40, 333, torch.bfloat16),
+                                           (128, 4, 128, 900, torch.float16), (61, 2, 40, 333, torch.float16),
+                                           (33, 2, 12, 100, torch.float16)])
 def test_against_oracle(T, H, D, M, dtype):
     from moba_opt.ops.merge_cuda import merge_forward_cuda
     so, sl, ro, rl, mp = _case(T, H, D, M, 7 + M, dtype, kcap=5)

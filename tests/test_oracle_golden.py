@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 from oracle import moba_oracle as mo
-from helpers import (DECODE_GOLDENS, PREFILL_GOLDENS, ROUTE_GOLDENS, bf16_bits_to_f64, config1_inputs, cu_from_lens, load,
+from helpers import (DECODE_GOLDENS, PREFILL_GOLDENS, ROUTE_GOLDENS, bits_to_f64, config1_inputs, cu_from_lens, load,
                      torch_to_f64, unpack_selected)
 
 
@@ -19,7 +19,7 @@ def test_chunk_metadata_matches_reference(name):
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
 def test_route_matches_reference_bit_exact(name):
     g = load(name)
-    q, k = bf16_bits_to_f64(g["q"]), bf16_bits_to_f64(g["k"])
+    q, k = bits_to_f64(g["q"]), bits_to_f64(g["k"])
     r = mo.route_prefill(q, k, cu_from_lens(g["lens"]), int(g["chunk"]), int(g["topk"]))
     assert r["selected"].shape == g["selected_stable"].shape
     # The reference evaluates the gate in FP32; rows whose decision margin is inside an FP32
@@ -35,11 +35,12 @@ def test_route_matches_reference_bit_exact(name):
 @pytest.mark.parametrize("name", PREFILL_GOLDENS + ROUTE_GOLDENS)
 def test_upstream_route_matches_reference_bit_exact(name):
     """route_precision='upstream' (the reference's default, src/moba_opt/grouped_attention.py:35,52): chunk means
-    rounded to bf16 before the gate.  The route-only fixtures are shaped so that this changes some rows."""
+    rounded to the input format before the gate.  The route-only fixtures are shaped so that this changes some rows."""
     g = load(name)
-    q, k = bf16_bits_to_f64(g["q"]), bf16_bits_to_f64(g["k"])
+    q, k = bits_to_f64(g["q"]), bits_to_f64(g["k"])
     cu = cu_from_lens(g["lens"])
-    r = mo.route_prefill(q, k, cu, int(g["chunk"]), int(g["topk"]), mean_rounding=mo.bf16_round)
+    rounding = mo.fp16_round if str(g.get("dtype", "")) == "float16" else mo.bf16_round     # to the format of the inputs
+    r = mo.route_prefill(q, k, cu, int(g["chunk"]), int(g["topk"]), mean_rounding=rounding)
     if name in ROUTE_GOLDENS:
         want, fp32 = unpack_selected(g, "upstream"), unpack_selected(g, "stable")
         assert (want != fp32).any()                                  # the fixture does discriminate the two precisions
@@ -53,7 +54,7 @@ def test_upstream_route_matches_reference_bit_exact(name):
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
 def test_attention_and_gradients_match_reference(name):
     g = load(name)
-    q, k, v, do = (bf16_bits_to_f64(g[x]) for x in ("q", "k", "v", "g"))
+    q, k, v, do = (bits_to_f64(g[x]) for x in ("q", "k", "v", "g"))
     cu = cu_from_lens(g["lens"])
     R = min(int(g["topk"]) - 1, g["filtered"].size)
     sel = mo.sel_from_selected(g["selected_stable"], g["filtered"], R)
@@ -93,9 +94,9 @@ def test_config1_matches_reference():
 def test_decode_attention_matches_reference(name):
     g = load(name)
     n = len(g["lengths"])
-    keys = [bf16_bits_to_f64(g[f"k{i}"]) for i in range(n)]
-    values = [bf16_bits_to_f64(g[f"v{i}"]) for i in range(n)]
-    q = bf16_bits_to_f64(g["q"])
+    keys = [bits_to_f64(g[f"k{i}"]) for i in range(n)]
+    values = [bits_to_f64(g[f"v{i}"]) for i in range(n)]
+    q = bits_to_f64(g["q"])
     ids, pos = list(range(n)), [int(x) - 1 for x in g["lengths"]]
     out, lse = mo.decode_attend(q, keys, values, ids, pos, int(g["chunk"]), g["selected"])
     np.testing.assert_allclose(out, g["out_sparse"], rtol=1e-10, atol=1e-12)

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import (PREFILL_GOLDENS, ROUTE_GOLDENS, bf16_bits_to_torch, config1_inputs, cu_from_lens, load, rel_rms,
+from helpers import (PREFILL_GOLDENS, ROUTE_GOLDENS, bits_to_torch, config1_inputs, cu_from_lens, load, rel_rms,
                      torch_to_f64, unpack_selected)
 from oracle import moba_oracle as mo
 
@@ -54,7 +54,7 @@ def _check_close(name, got, ref):
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
 def test_routes_bit_exact_and_forward_matches_reference(name):
     g = load(name)
-    q, k, v = (bf16_bits_to_torch(g[x]) for x in ("q", "k", "v"))
+    q, k, v = (bits_to_torch(g[x]) for x in ("q", "k", "v"))
     cu = cu_from_lens(g["lens"])
     out, lse, captured, _ = _run(q, k, v, cu, int(g["chunk"]), int(g["topk"]))
     if g["selected_stable"].shape[0]:
@@ -76,7 +76,7 @@ def test_routes_bit_exact_under_both_route_precisions(name, precision):
     means rounded to bf16, src/moba_opt/grouped_attention.py:35,52) and 'fp32'.  The route-only fixtures have chunk
     sizes 40 and 24 (mean = FP32 sum / C, not a shift) and rows on which the two precisions choose differently."""
     g = load(name)
-    q, k = (bf16_bits_to_torch(g[x]) for x in ("q", "k"))
+    q, k = (bits_to_torch(g[x]) for x in ("q", "k"))
     cu = cu_from_lens(g["lens"])
     _, _, captured, _ = _run(q, k, k, cu, int(g["chunk"]), int(g["topk"]), route_precision=precision)
     tag = "upstream" if precision == "upstream" else "stable"
@@ -92,7 +92,7 @@ def test_default_config_routes_like_the_reference_default():
     import moba_opt
     import moba_opt.grouped_attention as ga
     g = load("r_upstream_mqa")
-    q, k = (bf16_bits_to_torch(g[x]).cuda() for x in ("q", "k"))
+    q, k = (bits_to_torch(g[x]).cuda() for x in ("q", "k"))
     cu = torch.tensor(cu_from_lens(g["lens"]), dtype=torch.int32, device="cuda")
     captured = {}
     ga.ROUTE_HOOK = lambda **kw: captured.update(kw)
@@ -169,7 +169,7 @@ def test_forward_is_bit_repeatable():
 @pytest.mark.parametrize("name", PREFILL_GOLDENS)
 def test_gradients_match_reference(name):
     g = load(name)
-    q, k, v, do = (bf16_bits_to_torch(g[x]) for x in ("q", "k", "v", "g"))
+    q, k, v, do = (bits_to_torch(g[x]) for x in ("q", "k", "v", "g"))
     cu = cu_from_lens(g["lens"])
     _, _, _, grads = _run(q, k, v, cu, int(g["chunk"]), int(g["topk"]), d_out=do)
     for key, got in zip(("dq", "dk", "dv"), grads):
@@ -194,11 +194,12 @@ def test_config1_gradients():
     ((2000,), 6, 1, 64, 500, 2),
     ((300, 150), 4, 2, 64, 64, 1),       # dense fallback
 ])
-def test_gradients_against_oracle_on_seeded_inputs(lens, hq, hkv, dim, chunk, topk):
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_gradients_against_oracle_on_seeded_inputs(lens, hq, hkv, dim, chunk, topk, dtype):
     rng = torch.Generator().manual_seed(4321)
     total = sum(lens)
-    q, k, v = [torch.randn(total, h, dim, generator=rng).bfloat16() for h in (hq, hkv, hkv)]
-    do = torch.randn(total, hq, dim, generator=rng).bfloat16()
+    q, k, v = [torch.randn(total, h, dim, generator=rng).to(dtype) for h in (hq, hkv, hkv)]
+    do = torch.randn(total, hq, dim, generator=rng).to(dtype)
     cu = cu_from_lens(lens)
     out, lse, captured, grads = _run(q, k, v, cu, chunk, topk, d_out=do)
     qf, kf, vf, dof = (torch_to_f64(t) for t in (q, k, v, do))

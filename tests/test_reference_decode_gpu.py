@@ -28,8 +28,8 @@ def ref():
     return mods
 
 
-def rand(shape, seed):
-    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)).to("cuda", torch.bfloat16)
+def rand(shape, seed, dtype=torch.bfloat16):
+    return torch.randn(shape, generator=torch.Generator().manual_seed(seed)).to("cuda", dtype)
 
 
 def _same_routes(ours, theirs, q, means, positions, chunk, hk):
@@ -49,19 +49,23 @@ def _same_routes(ours, theirs, q, means, positions, chunk, hk):
     return same
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
 @pytest.mark.parametrize("hq,hk,dim,page,chunk,topk,lens", [
     (12, 2, 128, 48, 256, 4, (1000, 3000, 517)),
     (8, 8, 64, 16, 128, 3, (700,)),
     (14, 2, 64, 7, 64, 9, (333, 90, 1200)),
     (32, 8, 128, 16, 1024, 4, (5000, 2047)),
 ])
-def test_eager_attend_matches_the_reference_cache(ref, hq, hk, dim, page, chunk, topk, lens):
+def test_eager_attend_matches_the_reference_cache(ref, hq, hk, dim, page, chunk, topk, lens, dtype):
     from moba_opt import PagedKVCache
     import moba_opt.grouped_attention as ga
+    from functools import partial
+    rand = partial(globals()["rand"], dtype=dtype)
+    ulp = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
     theirs_mod, _ = ref
     n, cap = len(lens), max(lens) + 8
-    mine = PagedKVCache(n, cap, hk, dim, page_size=page, chunk_size=chunk)
-    theirs = theirs_mod.PagedKVCache(n, cap, hk, dim, page_size=page, chunk_size=chunk)
+    mine = PagedKVCache(n, cap, hk, dim, page_size=page, chunk_size=chunk, dtype=dtype)
+    theirs = theirs_mod.PagedKVCache(n, cap, hk, dim, page_size=page, chunk_size=chunk, dtype=dtype)
     k, v = rand((sum(lens), hk, dim), 11), rand((sum(lens), hk, dim), 12)
     cu = [0] + [int(x) for x in np.cumsum(lens)]
     for cache in (mine, theirs):
@@ -71,7 +75,7 @@ def test_eager_attend_matches_the_reference_cache(ref, hq, hk, dim, page, chunk,
         closed = length // chunk
         if closed:
             a, b = mine._means[sid, :closed].float(), theirs._means[sid, :closed].float()
-            assert ((a - b).abs() <= 2.0 ** -7 * b.abs() + 1e-30).all()          # one bf16 ulp at most
+            assert ((a - b).abs() <= ulp * b.abs() + 1e-7).all()          # one ulp of the format at most
     ids = list(range(n)) + [0]
     positions = [length - 1 for length in lens] + [min(lens[0] - 1, 3 * chunk + 1)]
     q = rand((len(ids), hq, dim), 13)
