@@ -17,8 +17,10 @@ times the reference's FP64 CPU oracle on a bounded sample of the same workload.
 
 At every N the line also carries `long_prefill`: the long-context configuration (131072 tokens, 32 / 8
 heads, D=128, chunk 4096, topk 12) split by KV-head group over the N ranks (strong scaling: N = 1 runs
-all 8 groups), with the NCCL all-gather of the forward output inside the timed region; and `decode`:
-64 paged-decode requests spread over the ranks by context length.
+all 8 groups), with the NCCL all-gather of the forward output inside the timed region; `decode`:
+64 paged-decode requests spread over the ranks by context length; and, at N > 1, `headline_split`: the
+headline configuration itself as one job over the ranks, split by KV head and then by sequence (its 2 KV
+heads x 4 sequences are 8 independent units), outputs all-gathered the same way.
 
 --impl reference times the CPU implementation of the path on all host threads: the reference's own
 reference/grouped_reference.py (forward + autograd backward, FP64) when oracle/make_ref.py has put it
@@ -400,53 +402,73 @@ def run_decode_against_reference(dev):
                 speedup=out["reference"] / out["ours"])
 
 
-# ----------------------------------------------------------------------------- long-prefill leg
-LONG_PREFILL = dict(name="gqa_prefill_1x131072_h32kv8_d128_c4096_k12_by_kv_group", tokens=131072, hq=32, hkv=8, dim=128,
-                    chunk=4096, topk=12)
+# ----------------------------------------------------------------------------- split-prefill legs
+LONG_PREFILL = dict(name="gqa_prefill_1x131072_h32kv8_d128_c4096_k12_by_kv_group", lens=(131072,), hq=32, hkv=8, dim=128,
+                    chunk=4096, topk=12, unit_variance=True)
+# BASELINE configs[1] as one job over the ranks: 2 KV heads x 4 sequences = 8 independent units
+HEADLINE_SPLIT = dict(WORKLOADS["cfg2"], name="gqa_prefill_4x32768_h14kv2_d64_c2048_k3_by_kv_head_and_sequence")
 
 
-def run_long_prefill(dev, rank, world, steps, warmup, with_host_leg=True):
-    """BASELINE configs[2]: one sequence of 131072 tokens, 32 query / 8 KV heads, D=128, chunk 4096, topk 12, bf16
-    Q/K/V ~ N(0,1), split by KV-head group: rank r owns 8/world KV heads and their query heads (world = 1 runs all
-    eight).  One step = routing + forward + backward on the rank's heads, and the all-gather of the forward output
-    [T, Hq/world, D] of every rank into [T, Hq, D] on every rank (NCCL over NVLink), issued on a second stream as
-    soon as the forward is done so that it runs beside the backward; the step ends when both are done.  Gradients
-    stay with the heads they belong to (dK, dV of a KV head live wholly on its rank), so nothing else is exchanged.
-    Timed on the device, maximum over ranks."""
+def run_long_prefill(dev, rank, world, steps, warmup, with_host_leg=True, w=None):
+    """A prefill configuration as ONE job over the ranks (strong scaling), split into its independent units.
+    w = LONG_PREFILL (default), BASELINE configs[2]: one sequence of 131072 tokens, 32 query / 8 KV heads, D=128, chunk
+    4096, topk 12, bf16 Q/K/V ~ N(0,1), split by KV-head group: rank r owns 8/world KV heads and their query heads
+    (world = 1 runs all eight).  w = HEADLINE_SPLIT, BASELINE configs[1]: 4 sequences of 32768 tokens, 14 / 2 heads,
+    D=64, which has only two KV heads, so the ranks beyond two take whole sequences (sharding.unit_slices: 2 ranks = one KV
+    head each, 4 = one KV head of two sequences, 8 = one KV head of one sequence).
+    One step = routing + forward + backward on the rank's units, and the all-gather of the forward output
+    [T/seq parts, Hq/head parts, D] of every rank into [T, Hq, D] on every rank (NCCL over NVLink), issued on a second
+    stream as soon as the forward is done so that it runs beside the backward; the step ends when both are done.
+    Gradients stay with the units they belong to (dK, dV of a KV head of a sequence live wholly on its rank), so nothing
+    else is exchanged.  Timed on the device, maximum over ranks."""
     import torch
     import torch.distributed as dist
     import moba_opt
     import moba_opt.grouped_attention as ga
     from moba_opt import sharding
-    w = LONG_PREFILL
-    if w["hkv"] % world:
+    w = w or LONG_PREFILL
+    lens = w["lens"]
+    try:
+        head_parts, seq_parts = sharding.unit_grid(w["hkv"], len(lens), world)
+    except ValueError:
         return None
-    T, D, G = w["tokens"], w["dim"], w["hq"] // w["hkv"]
-    qs, ks = sharding.kv_group_slices(w["hq"], w["hkv"], world, rank)
+    D, G = w["dim"], w["hq"] // w["hkv"]
+    qs, ks, seqs = sharding.unit_slices(w["hq"], w["hkv"], len(lens), world, rank)
     groups = range(ks.start, ks.stop)
-    parts = {"q": [], "k": [], "v": [], "do": []}
-    for g in groups:                              # data of a KV group does not depend on how many ranks there are
-        gen = torch.Generator(device=dev).manual_seed(500 + g)
-        for name, h in (("q", G), ("k", 1), ("v", 1), ("do", G)):
-            parts[name].append(torch.randn(T, h, D, device=dev, generator=gen).bfloat16())
-    res = {n: torch.cat(p, dim=1).contiguous() for n, p in parts.items()}
-    del parts
-    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    my_lens = [lens[i] for i in seqs]
+    T, T_all = sum(my_lens), sum(lens)
+    if len(set(lens)) != 1:
+        return None                               # the gather below wants equal shapes on every rank
+    scale = 1.0 if w.get("unit_variance") else D ** -0.5
+    per_seq = {"q": [], "k": [], "v": [], "do": []}
+    for sq in seqs:                               # data of a (sequence, KV group) does not depend on how many ranks there are
+        parts = {"q": [], "k": [], "v": [], "do": []}
+        for g in groups:
+            gen = torch.Generator(device=dev).manual_seed(500 + g + 64 * sq)
+            for name, h, sc in (("q", G, scale), ("k", 1, scale), ("v", 1, scale), ("do", G, 1.0)):
+                parts[name].append((torch.randn(lens[sq], h, D, device=dev, generator=gen) * sc).bfloat16())
+        for n in parts:
+            per_seq[n].append(torch.cat(parts[n], dim=1))
+    res = {n: torch.cat(p, dim=0).contiguous() for n, p in per_seq.items()}
+    del per_seq, parts
+    cu = torch.tensor(np.concatenate(([0], np.cumsum(my_lens))), dtype=torch.int32, device=dev)
     cfg = {"chunk_size": w["chunk"], "topk": w["topk"], "route_precision": "fp32", "stable_routes": True}
     hq_local = G * len(groups)
     gathered = torch.empty(world, T, hq_local, D, dtype=torch.bfloat16, device=dev) if world > 1 else None
-    full = torch.empty(T, w["hq"], D, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    full = torch.empty(T_all, w["hq"], D, dtype=torch.bfloat16, device=dev) if world > 1 else None
     side = torch.cuda.Stream(dev)
     main = torch.cuda.current_stream(dev)
 
     def gather(out):
-        """[T, Hq/world, D] of every rank -> [T, Hq, D] in head order on this rank."""
+        """[T/seq parts, Hq/head parts, D] of every rank (rank = sequence part * head parts + head part) -> [T, Hq, D]
+        in token and head order on this rank."""
         dist.all_gather_into_tensor(gathered, out)
-        full.view(T, world, hq_local, D).copy_(gathered.permute(1, 0, 2, 3))
+        full.view(seq_parts, T, head_parts, hq_local, D).copy_(
+            gathered.view(seq_parts, head_parts, T, hq_local, D).permute(0, 2, 1, 3, 4))
 
     def step(t, overlap=True):
         q, k, v = (t[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
-        out = moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, T, cfg)
+        out = moba_opt.run_impl("opt_gqa_cuda", q, k, v, cu, max(my_lens), cfg)
         if world > 1:
             det = out.detach()
             if overlap:
@@ -489,8 +511,9 @@ def run_long_prefill(dev, rank, world, steps, warmup, with_host_leg=True):
         probe = res["q"]                                                # same shape and dtype as the forward output
         gather(probe)
         gather_ms = timed(lambda: gather(probe), 5)                    # the collective (and the reorder) alone
-    flops = 14.0 * D * attended_pairs((T,), w["chunk"], w["topk"]) * w["hq"]
-    out = dict(workload=w["name"], scaling="strong", kv_groups_per_rank=len(groups), steps=steps, ms_per_step=ms,
+    flops = 14.0 * D * attended_pairs(lens, w["chunk"], w["topk"]) * w["hq"]
+    out = dict(workload=w["name"], scaling="strong", kv_groups_per_rank=len(groups), sequences_per_rank=len(my_lens),
+               steps=steps, ms_per_step=ms,
                tflops=flops / (ms * 1e-3) / 1e12, flops_per_step=flops,
                gather=dict(collective="nccl all_gather_into_tensor of the forward output, on a second stream beside the backward",
                            bytes_received_per_rank=(world - 1) * T * hq_local * D * 2 if world > 1 else 0,
@@ -506,7 +529,7 @@ def run_long_prefill(dev, rank, world, steps, warmup, with_host_leg=True):
             for n, t in host.items():
                 dev_in[n].copy_(t, non_blocking=True)
             outs = step(dev_in)
-            local = outs[0] if world == 1 else outs[0][:, qs]
+            local = outs[0] if world == 1 else outs[0].view(seq_parts, T, w["hq"], D)[rank // head_parts][:, qs]
             for dst, src in zip(("out", "dq", "dk", "dv"), (local,) + outs[1:]):
                 back[dst].copy_(src, non_blocking=True)
 
@@ -822,10 +845,22 @@ def run_ours(args):
                        requests=int(every[:, 4].sum()),
                        per_rank=[dict(requests=int(r[4]), context_tokens=int(r[5]), ms_per_step=float(r[0]),
                                       host_ms_per_step=float(r[6])) for r in every])
+            # the same 64 requests on EVERY rank (independent replicas of the whole decode configuration): what the ranks
+            # deliver when each has a full batch, beside the split above where each has an eighth of one
+            full = run_decode(dev, 0, 1, args.decode_steps, lib)
+            ga.check_status()
+            slowest = torch.tensor([full["ms_per_step"]], device=dev, dtype=torch.float64)
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+            dec["replicated"] = dict(requests_per_rank=full["requests"], ms_per_step=float(slowest.item()),
+                                     tokens_per_s=world * full["requests"] / (float(slowest.item()) * 1e-3), scaling="weak")
 
     long_leg = None
     if not args.kernels_only and not args.no_long_prefill:
         long_leg = run_long_prefill(dev, rank, world, args.long_steps, 2)
+        ga.check_status()
+    split_leg = None
+    if world > 1 and not args.kernels_only and not args.no_long_prefill and WORKLOAD is WORKLOADS["cfg2"]:
+        split_leg = run_long_prefill(dev, rank, world, max(args.long_steps, 8), 3, w=HEADLINE_SPLIT)   # the headline config as one job
         ga.check_status()
 
     flops = step_flops(w)
@@ -874,6 +909,9 @@ def run_ours(args):
                                   placement="requests spread over the ranks by expected bytes per step, largest first",
                                   per_rank=dec["per_rank"],
                                   ms_per_step_with_output_gather=dec["gather_ms_per_step"])
+            if "replicated" in dec:
+                line["decode"]["replicated"] = dec["replicated"]
+            line["decode"]["scaling"] = "strong"
             if world == 1 and not args.kernels_only:
                 line["decode"]["cpu_baseline"] = cpu_decode_sample(os.cpu_count() or 1)
                 try:
@@ -883,6 +921,9 @@ def run_ours(args):
         if long_leg is not None:
             long_leg["frac_of_tensor_peak"] = long_leg["tflops"] / world / pk["tflops"]
             line["long_prefill"] = long_leg
+        if split_leg is not None:
+            split_leg["frac_of_tensor_peak"] = split_leg["tflops"] / world / pk["tflops"]
+            line["headline_split"] = split_leg
         if world == 1 and not args.kernels_only and not args.no_full_model:
             try:
                 line["full_model"] = run_full_model(dev)

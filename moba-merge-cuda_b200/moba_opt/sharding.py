@@ -5,7 +5,9 @@ of query heads never interacts with another group (routing, attention, merge and
 per group), and decode requests never interact at all.  So each rank works on its own units with the
 single-GPU kernels and the only collective is the optional gather of outputs at the end.
 
-  prefill  KV-head groups: rank r owns kv heads [r*Hkv/N, (r+1)*Hkv/N) and their query heads
+  prefill  KV-head groups: rank r owns kv heads [r*Hkv/N, (r+1)*Hkv/N) and their query heads; where there are fewer
+           KV heads than ranks the sequences of the batch are the second independent axis (`unit_slices`: rank =
+           sequence part * head parts + head part)
   decode   requests:       request i lives on rank i mod N, or - when the contexts differ a lot in length - on the
                            rank `balance_requests` gives it (its own cache, its own prepared plan either way)
 """
@@ -23,6 +25,26 @@ def kv_group_slices(hq, hkv, world, rank):
         raise ValueError("rank outside the group")
     per, group = hkv // world, hq // hkv
     return slice(rank * per * group, (rank + 1) * per * group), slice(rank * per, (rank + 1) * per)
+
+
+def unit_grid(hkv, num_seqs, world):
+    """(head parts, sequence parts) of a batch of `num_seqs` sequences with `hkv` KV heads over `world` ranks: heads are
+    split as far as they go (the largest common divisor of world and Hkv), whole sequences take the rest."""
+    head_parts = max(d for d in range(1, world + 1) if world % d == 0 and hkv % d == 0)
+    seq_parts = world // head_parts
+    if num_seqs % seq_parts:
+        raise ValueError(f"{hkv} KV heads x {num_seqs} sequences cannot be split evenly over {world} ranks")
+    return head_parts, seq_parts
+
+
+def unit_slices(hq, hkv, num_seqs, world, rank):
+    """(query-head slice, kv-head slice, range of sequences) owned by `rank`; rank = sequence part * head parts + head part."""
+    if not 0 <= rank < world:
+        raise ValueError("rank outside the group")
+    head_parts, seq_parts = unit_grid(hkv, num_seqs, world)
+    qs, ks = kv_group_slices(hq, hkv, head_parts, rank % head_parts)
+    per = num_seqs // seq_parts
+    return qs, ks, range((rank // head_parts) * per, (rank // head_parts + 1) * per)
 
 
 def requests_of_rank(num_requests, world, rank):
@@ -105,6 +127,19 @@ def gather_heads(local, group=None):
     parts = [torch.empty_like(local) for _ in range(world)]
     dist.all_gather(parts, local.contiguous(), group=group)
     return torch.cat(parts, dim=1)
+
+
+def gather_units(local, head_parts, seq_parts, group=None):
+    """All-gathers the outputs [T/seq_parts, H/head_parts, D] of the ranks of a `unit_slices` split (equal shapes: the
+    sequence parts hold the same number of tokens) into [T, H, D]: tokens in sequence order, heads in head order."""
+    world = dist.get_world_size(group)
+    if world != head_parts * seq_parts:
+        raise ValueError("the split does not match the group")
+    if world == 1:
+        return local
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    return torch.cat([torch.cat(parts[s * head_parts:(s + 1) * head_parts], dim=1) for s in range(seq_parts)], dim=0)
 
 
 def gather_rows(local, num_rows, group=None):

@@ -58,6 +58,40 @@ def _worker(rank, world, port, results):
         dist.destroy_process_group()
 
 
+def _unit_worker(rank, world, port, results):
+    """Head x sequence split: 2 KV heads and 2 equal sequences over 4 ranks, one (KV head, sequence) unit each."""
+    for p in (ROOT, ROOT / "moba-merge-cuda_b200"):
+        sys.path.insert(0, str(p))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from moba_opt import sharding
+        g = torch.Generator().manual_seed(5)
+        q, k, v = torch.randn(96, 4, 16, generator=g), torch.randn(96, 2, 16, generator=g), torch.randn(96, 2, 16, generator=g)
+        cu = torch.tensor([0, 48, 96], dtype=torch.int32)
+        cfg = {"chunk_size": 16, "topk": 3}
+        head_parts, seq_parts = sharding.unit_grid(2, 2, world)
+        qs, ks, seqs = sharding.unit_slices(4, 2, 2, world, rank)
+        lo, hi = int(cu[seqs.start]), int(cu[seqs.stop])
+        local = _oracle_attend(q[lo:hi, qs], k[lo:hi, ks], v[lo:hi, ks], cu[seqs.start:seqs.stop + 1] - lo, 48, cfg)
+        full = sharding.gather_units(local, head_parts, seq_parts)
+        results[rank] = (torch.equal(full, _oracle_attend(q, k, v, cu, 48, cfg)), (head_parts, seq_parts),
+                         (qs.start, qs.stop, ks.start, ks.stop, seqs.start, seqs.stop))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_four_rank_head_and_sequence_split():
+    world, port = 4, _free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_unit_worker, args=(world, port, results), nprocs=world, join=True)
+        out = dict(results)
+    assert all(out[r][0] for r in range(world)), "gathered head x sequence split differs from the single-process result"
+    assert out[0][1] == (2, 2)
+    assert [out[r][2] for r in range(world)] == [(0, 2, 0, 1, 0, 1), (2, 4, 1, 2, 0, 1), (0, 2, 0, 1, 1, 2), (2, 4, 1, 2, 1, 2)]
+
+
 def test_two_rank_sharding_and_gather():
     world, port = 2, _free_port()
     with mp.Manager() as manager:
@@ -80,6 +114,12 @@ def test_partition_contract():
         sharding.kv_group_slices(14, 4, 2, 0)
     with pytest.raises(ValueError):
         sharding.requests_of_rank(8, 2, 2)
+    # 2 KV heads x 4 sequences (the headline configuration): heads first, then whole sequences
+    assert [sharding.unit_grid(2, 4, n) for n in (1, 2, 4, 8)] == [(1, 1), (2, 1), (2, 2), (2, 4)]
+    assert sharding.unit_grid(8, 1, 8) == (8, 1)
+    assert sharding.unit_slices(14, 2, 4, 8, 5) == (slice(7, 14), slice(1, 2), range(2, 3))
+    with pytest.raises(ValueError):
+        sharding.unit_grid(2, 4, 16)                # 8 units cannot feed 16 ranks
     covered = sorted(i for r in range(4) for i in sharding.requests_of_rank(64, 4, r))
     assert covered == list(range(64))
 
