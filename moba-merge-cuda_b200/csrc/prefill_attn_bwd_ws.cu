@@ -3,7 +3,8 @@
 // 128-row query tile that attends them.  Scores are formed transposed, keys on the tensor-memory lanes
 // and queries along the columns:
 //     S^T = K Q^T, dP^T = V dO^T     ->  P^T = exp2(S^T c - LSE[q]),  dS^T = P^T (dP^T - delta[q]) / sqrt(D)
-//     dV += P^T dO,  dK += dS^T Q    with P^T and dS^T read by the tensor cores straight from tensor memory
+//     dV += P^T dO,  dK += dS^T Q    with P^T and dS^T read by the tensor cores straight from tensor memory,
+//                                    and so are K and V in the first two products
 //     dQ  = dS K                     with dS^T also stored once as a shared-memory tile
 // so per tile only dS crosses shared memory (the five products of a tile otherwise read every operand
 // from shared memory, which is what bounded the kernel).
@@ -14,8 +15,8 @@
 //                16 KB images, so a tile is five bulk copies into a four-slot ring
 //   warps 12-15  dQ drain: tensor memory -> registers -> 4 KB transposition buffer -> vector reductions
 //                into the FP32 accumulator, behind the next tile's math
-// Tensor memory: S^T 0-127, dP^T 128-255 (dS^T as packed bf16 over its first columns), dV 256-319,
-// dK 320-383, dQ 384-447, P^T 448-511.
+// Tensor memory: S^T 0-127 (P^T as packed 16-bit over the first columns of each thread's range), dP^T 128-255 (dS^T
+// likewise), dV 256-319, dK 320-383, dQ 384-447, K 448-479 and V 480-511 as stationary A operands.
 #include "prefill_bwd.cuh"
 
 namespace moba {
@@ -71,9 +72,8 @@ constexpr int kWsRing = 4;       // Q/dO tiles in shared memory
 
 struct WsSmem {
   uint64_t st_full;    // S^T of the tile is in tensor memory (tcgen05.commit)
-  uint64_t st_free;    // the 8 compute warps have read it: S^T of the next tile may be formed
-  uint64_t p_ready;    // P^T of the tile is in tensor memory (8 warps)
-  uint64_t pt_free;    // dV of the tile is done: P^T may be overwritten
+  uint64_t p_ready;    // P^T of the tile is in tensor memory, over the S^T columns its threads have read (8 warps)
+  uint64_t ka_ready;   // K and V of the key block are in tensor memory as A operands (8 warps)
   uint64_t dpt_full;   // dP^T of the tile is in tensor memory
   uint64_t ds_ready;   // dS^T of the tile is in tensor memory and in shared memory (8 warps)
   uint64_t dq_done;    // dQ (and everything issued before it) of the tile is done
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   constexpr int TILE_BYTES = kTile * DPAD * 2;
   constexpr int PT_BYTES = kTile * kTile * 2;
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_PT = 448;
+  constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_KA = 448, COL_VA = 480;
   extern __shared__ __align__(1024) uint8_t smem[];
   WsSmem& cb = *reinterpret_cast<WsSmem*>(smem);
   uint8_t* sK = smem + 8192;
@@ -132,9 +132,8 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   }
   if (tid == 0) {
     mbar_init(&cb.st_full, 1);
-    mbar_init(&cb.st_free, 8);
     mbar_init(&cb.p_ready, 8);
-    mbar_init(&cb.pt_free, 1);
+    mbar_init(&cb.ka_ready, 8);
     mbar_init(&cb.dpt_full, 1);
     mbar_init(&cb.ds_ready, 8);
     mbar_init(&cb.dq_done, 1);
@@ -238,17 +237,17 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       }
     } else if (warp == 8) {
       // ================================================================== MMA issue
-      // Fixed order per tile n:  S^T(n+1) | dV(n) | dK(n) | dP^T(n+1) | dQ(n).  dS^T lives in the columns of
-      // dP^T, so dP^T of the next tile follows dK of this one in the (in-order) tensor pipe; every other
-      // awaited event depends only on instructions issued earlier and has most of a tile of slack.
+      // Fixed order per tile n:  dV(n) | S^T(n+1) | dK(n) | dP^T(n+1) | dQ(n).  P^T lives in the columns of S^T and
+      // dS^T in those of dP^T, so S^T of the next tile follows dV of this one and dP^T of the next tile follows dK of
+      // this one in the (in-order) tensor pipe; every other awaited event depends only on instructions issued earlier
+      // and has most of a tile of slack.  K and V, which never change, are A operands in tensor memory.
       const bool leader = bwd_elect_one();
       const uint32_t idesc_st = umma_idesc_16<F16>(128, 128, 0, 0);
       const uint32_t idesc_kv = umma_idesc_16<F16>(128, DPAD, 0, 1);   // A from tensor memory, B MN-major
       const uint32_t idesc_dq = umma_idesc_16<F16>(128, DPAD, 1, 1);   // A = dS^T tile (MN-major), B = K (MN-major)
       // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
       // field counts 16-byte units).
-      const uint64_t k_km = umma_desc_kmajor(smem_u32(sK), kTile, 0), k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
-      const uint64_t v_km = umma_desc_kmajor(smem_u32(sV), kTile, 0);
+      const uint64_t k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
       const uint64_t q_km = umma_desc_kmajor(smem_u32(sQ), kTile, 0), q_mn = umma_desc_mnmajor(smem_u32(sQ), kTile, 0, 0);
       const uint64_t o_km = umma_desc_kmajor(smem_u32(sdO), kTile, 0), o_mn = umma_desc_mnmajor(smem_u32(sdO), kTile, 0, 0);
       const uint64_t s_mn = umma_desc_mnmajor(smem_u32(sdS), kTile, 0, 0);
@@ -260,7 +259,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
           const uint64_t su = slot_u(n);
 #pragma unroll
           for (int kk = 0; kk < DPAD; kk += 16)  // K-major step: 16 elements = 32 bytes = 2 units
-            umma_ss(tmem + COL_ST, k_km + (kk >> 3), q_km + su + (kk >> 3), idesc_st, kk > 0);
+            umma_ts(tmem + COL_ST, tmem + COL_KA + (kk >> 1), q_km + su + (kk >> 3), idesc_st, kk > 0);
           umma_commit(&cb.st_full);
         }
         __syncwarp();
@@ -270,32 +269,28 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
           const uint64_t su = slot_u(n);
 #pragma unroll
           for (int kk = 0; kk < DPAD; kk += 16)
-            umma_ss(tmem + COL_DPT, v_km + (kk >> 3), o_km + su + (kk >> 3), idesc_st, kk > 0);
+            umma_ts(tmem + COL_DPT, tmem + COL_VA + (kk >> 1), o_km + su + (kk >> 3), idesc_st, kk > 0);
           umma_commit(&cb.dpt_full);
         }
         __syncwarp();
       };
       if (n_iter > 0) {
-        if (alive) alive = mbar_wait(&cb.kv_ready, 0, a.status);
+        if (alive) alive = mbar_wait(&cb.ka_ready, 0, a.status);
         issue_st(0);
         issue_dpt(0);
       }
       for (int n = 0; n < n_iter; ++n) {
         const uint64_t su = slot_u(n);
         const uint32_t acc = n > 0;
-        if (n + 1 < n_iter) {
-          if (alive) alive = mbar_wait(&cb.st_free, n & 1, a.status);
-          issue_st(n + 1);
-        }
         if (alive) alive = mbar_wait(&cb.p_ready, n & 1, a.status);
         tc_fence_after_sync();
         if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO; B MN-major step: 16 rows = 2048 bytes = 128 units
-            umma_ts(tmem + COL_DV, tmem + COL_PT + (kk >> 1), o_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
-          umma_commit(&cb.pt_free);
+          for (int kk = 0; kk < kTile; kk += 16)  // dV += P^T dO; queries 0-63 at columns 0.., 64-127 at columns 64..; B MN-major step: 16 rows = 128 units
+            umma_ts(tmem + COL_DV, tmem + COL_ST + (kk >> 6) * 64 + ((kk & 63) >> 1), o_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
         }
         __syncwarp();
+        if (n + 1 < n_iter) issue_st(n + 1);
         if (alive) alive = mbar_wait(&cb.ds_ready, n & 1, a.status);
         tc_fence_after_sync();
         if (leader) {
@@ -323,6 +318,22 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     const int quad = warp & 3, half = warp >> 2;
     const int r = quad * 32 + lane;  // key row of this thread
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
+    if (n_iter > 0) {
+      // K (warps 0-3) and V (warps 4-7) of the key block into tensor memory as A operands: thread = key row, one
+      // 32-bit column per pair of dimensions
+      alive = warp_wait(&cb.kv_ready, 0, a.status, alive);
+      const uint8_t* src = half == 0 ? sK : sV;
+      uint32_t kv[32];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint4 w = *reinterpret_cast<const uint4*>(src + sw128_offset(kTile, r, u));
+        kv[4 * u] = w.x; kv[4 * u + 1] = w.y; kv[4 * u + 2] = w.z; kv[4 * u + 3] = w.w;
+      }
+      tmem_st32(tlane + (half == 0 ? COL_KA : COL_VA), kv);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      warp_arrive(&cb.ka_ready);
+    }
     for (int it = 0; it < n_iter; ++it) {
       const int ms = it % kWsRing;
       // queries below qmin are masked for this key: all of them for a key that does not exist, the
@@ -339,8 +350,6 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         tmem_ld32(tlane + COL_ST + half * 64, t0);
         tmem_ld32(tlane + COL_ST + half * 64 + 32, t1);
         tmem_ld_wait();
-        tc_fence_before_sync();
-        warp_arrive(&cb.st_free);  // S^T of the next tile may be formed
         const float4* lse4 = reinterpret_cast<const float4*>(&cb.lse2[ms][half * 64]);
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
 #pragma unroll
@@ -362,8 +371,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       uint32_t pk[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) pk[i] = pack16<F16>(p[2 * i], p[2 * i + 1]);
-      if (it > 0) alive = warp_wait(&cb.pt_free, (it - 1) & 1, a.status, alive);  // dV of the previous tile has read P^T
-      tmem_st32(tlane + COL_PT + half * 32, pk);
+      tmem_st32(tlane + COL_ST + half * 64, pk);  // over the first 32 of this thread's own S^T columns, which it has read
       tmem_st_wait();
       tc_fence_before_sync();
       warp_arrive(&cb.p_ready);

@@ -7,8 +7,8 @@
 //     dQ^T[D, 64 q] = K^T dS^T,
 // with the head dimension on the tensor-memory lanes; the drain warps turn it 16 query rows at a time
 // through a 2 KB buffer so that vector reductions cover whole 128-byte lines of the FP32 accumulator.
-// Tensor memory: S^T 0-63, dP^T 64-127 (dS^T as packed bf16 over the first columns of each thread's own
-// range), dV 128-255, dK 256-383, dQ^T 384-447, P^T 448-479.
+// Tensor memory: S^T 0-63 and dP^T 64-127 (P^T and dS^T as packed 16-bit values over the first columns of each
+// thread's own range), dV 128-255, dK 256-383, dQ^T 384-447, K 448-511 as a stationary A operand.
 // Shared memory: K and V images (32 KB each), a 4-slot ring of (Q, dO) half tiles (64 rows x 128 columns
 // each, 16 KB), the dS^T tile (128 key rows x 64 query columns, 16 KB).
 #include "prefill_bwd.cuh"
@@ -22,7 +22,7 @@ constexpr int kRing = 4;
 constexpr int kQRows = 64;     // query rows per step
 
 struct Smem128 {
-  uint64_t st_full, st_free, p_ready, pt_free, dpt_full, ds_ready, dq_done, dq_free, kv_ready;
+  uint64_t st_full, p_ready, ka_ready, dpt_full, ds_ready, dq_done, dq_free, kv_ready;
   uint64_t qdo_full[kRing], qdo_free[kRing];
   uint32_t tmem_slot;
   uint32_t pad;
@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
   constexpr int PANEL_BYTES = kQRows * 128;       // 8 KB
   constexpr int SLOT_BYTES = 2 * HALF_BYTES;      // Q half tile followed by dO half tile
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256, COL_DQT = 384, COL_PT = 448;
+  constexpr uint32_t COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 256, COL_DQT = 384, COL_KA = 448;
   extern __shared__ __align__(1024) uint8_t smem[];
   Smem128& cb = *reinterpret_cast<Smem128*>(smem);
   uint8_t* sK = smem + 4096;
@@ -76,9 +76,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
   }
   if (tid == 0) {
     mbar_init(&cb.st_full, 1);
-    mbar_init(&cb.st_free, 8);
     mbar_init(&cb.p_ready, 8);
-    mbar_init(&cb.pt_free, 1);
+    mbar_init(&cb.ka_ready, 8);
     mbar_init(&cb.dpt_full, 1);
     mbar_init(&cb.ds_ready, 8);
     mbar_init(&cb.dq_done, 1);
@@ -181,7 +180,8 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
       }
     } else if (warp == 8) {
       // ================================================================== MMA issue
-      // Fixed order per step n:  S^T(n+1) | dV(n) | dK(n) | dP^T(n+1) | dQ^T(n).
+      // Fixed order per step n:  dV(n) | S^T(n+1) | dK(n) | dP^T(n+1) | dQ^T(n): P^T lives in the columns of S^T, dS^T in
+      // those of dP^T, and the tensor pipe runs in issue order.  K is a stationary A operand in tensor memory.
       const bool leader = bwd_elect_one();
       const uint32_t idesc_st = umma_idesc_16<F16>(128, kQRows, 0, 0);   // K-major x K-major, N = 64 queries
       const uint32_t idesc_kv = umma_idesc_16<F16>(128, DPAD, 0, 1);     // A from tensor memory, B MN-major, N = 128
@@ -189,12 +189,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
       // Operand descriptors are built once; a descriptor is its base plus a constant (the start-address
       // field counts 16-byte units): a K-major step of 16 elements is 2 units inside a 64-column panel,
       // an MN-major step of 16 rows is 128 units.
-      const uint64_t k_km = umma_desc_kmajor(smem_u32(sK), kTile, 0), k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
+      const uint64_t k_mn = umma_desc_mnmajor(smem_u32(sK), kTile, 0, 0);
       const uint64_t v_km = umma_desc_kmajor(smem_u32(sV), kTile, 0);
       const uint64_t q_km = umma_desc_kmajor(smem_u32(sQ), kQRows, 0), q_mn = umma_desc_mnmajor(smem_u32(sQ), kQRows, 0, 0);
       const uint64_t o_km = umma_desc_kmajor(smem_u32(sdO), kQRows, 0), o_mn = umma_desc_mnmajor(smem_u32(sdO), kQRows, 0, 0);
       const uint64_t s_mn = umma_desc_mnmajor(smem_u32(sdS), kTile, 0, 0);
-      constexpr uint32_t KV_PANEL_U = (kTile * 128) >> 4, Q_PANEL_U = (kQRows * 128) >> 4;
+      constexpr uint32_t KV_PANEL_U = (kTile * 128) >> 4, Q_PANEL_U = (kQRows * 128) >> 4;  // V is still read from shared memory
       auto slot_u = [&](int n) { return (uint64_t)((n % kRing) * (SLOT_BYTES >> 4)); };
       auto issue_st = [&](int n) {
         if (alive) alive = mbar_wait(&cb.qdo_full[n % kRing], (n / kRing) & 1, a.status);
@@ -203,8 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
           const uint64_t su = slot_u(n);
 #pragma unroll
           for (int kk = 0; kk < DPAD; kk += 16)
-            umma_ss(tmem + COL_ST, k_km + (kk >> 6) * KV_PANEL_U + ((kk & 63) >> 3), q_km + su + (kk >> 6) * Q_PANEL_U + ((kk & 63) >> 3),
-                    idesc_st, kk > 0);
+            umma_ts(tmem + COL_ST, tmem + COL_KA + (kk >> 1), q_km + su + (kk >> 6) * Q_PANEL_U + ((kk & 63) >> 3), idesc_st, kk > 0);
           umma_commit(&cb.st_full);
         }
         __syncwarp();
@@ -221,26 +220,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
         __syncwarp();
       };
       if (n_iter > 0) {
-        if (alive) alive = mbar_wait(&cb.kv_ready, 0, a.status);
+        if (alive) alive = mbar_wait(&cb.ka_ready, 0, a.status);
         issue_st(0);
         issue_dpt(0);
       }
       for (int n = 0; n < n_iter; ++n) {
         const uint32_t acc = n > 0;
         const uint64_t su = slot_u(n);
-        if (n + 1 < n_iter) {
-          if (alive) alive = mbar_wait(&cb.st_free, n & 1, a.status);
-          issue_st(n + 1);
-        }
         if (alive) alive = mbar_wait(&cb.p_ready, n & 1, a.status);
         tc_fence_after_sync();
         if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kQRows; kk += 16)  // dV += P^T dO over the 64 query rows of the step
-            umma_ts(tmem + COL_DV, tmem + COL_PT + (kk >> 1), o_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
-          umma_commit(&cb.pt_free);
+          for (int kk = 0; kk < kQRows; kk += 16)  // dV += P^T dO over the 64 query rows of the step; queries 0-31 at columns 0.., 32-63 at columns 32..
+            umma_ts(tmem + COL_DV, tmem + COL_ST + (kk >> 5) * 32 + ((kk & 31) >> 1), o_mn + su + kk * 8, idesc_kv, acc | (kk > 0));
         }
         __syncwarp();
+        if (n + 1 < n_iter) issue_st(n + 1);
         if (alive) alive = mbar_wait(&cb.ds_ready, n & 1, a.status);
         tc_fence_after_sync();
         if (leader) {
@@ -268,6 +263,21 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
     const int quad = warp & 3, half = warp >> 2;
     const int r = quad * 32 + lane;  // key row of this thread; its query columns are [32 half, 32 half + 32)
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
+    if (n_iter > 0) {
+      // K of the key block into tensor memory as an A operand: thread = key row, one 32-bit column per pair of
+      // dimensions; warps 0-3 take the first 64-column panel, warps 4-7 the second
+      alive = warp_wait(&cb.kv_ready, 0, a.status, alive);
+      uint32_t kv[32];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint4 w = *reinterpret_cast<const uint4*>(sK + sw128_offset(kTile, r, half * 8 + u));
+        kv[4 * u] = w.x; kv[4 * u + 1] = w.y; kv[4 * u + 2] = w.z; kv[4 * u + 3] = w.w;
+      }
+      tmem_st32(tlane + COL_KA + half * 32, kv);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      warp_arrive(&cb.ka_ready);
+    }
     for (int it = 0; it < n_iter; ++it) {
       const int ms = it % kRing, jt = it >> 1, sub = it & 1;
       // queries below qmin (index inside the 128-row tile) are masked for this key
@@ -283,8 +293,6 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
         uint32_t t[32];
         tmem_ld32(tlane + COL_ST + half * 32, t);
         tmem_ld_wait();
-        tc_fence_before_sync();
-        warp_arrive(&cb.st_free);
         const float4* lse4 = reinterpret_cast<const float4*>(&cb.lse2[ms][half * 32]);
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
 #pragma unroll
@@ -303,8 +311,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) pk[i] = pack16<F16>(p[2 * i], p[2 * i + 1]);
-      if (it > 0) alive = warp_wait(&cb.pt_free, (it - 1) & 1, a.status, alive);  // dV of the previous step has read P^T
-      tmem_st16(tlane + COL_PT + half * 16, pk);
+      tmem_st16(tlane + COL_ST + half * 32, pk);  // over the first 16 of this thread's own S^T columns, which it has read
       tmem_st_wait();
       tc_fence_before_sync();
       warp_arrive(&cb.p_ready);
