@@ -13,8 +13,8 @@
 //   warp 9       one thread asks the copy engine for the tiles: a packing pass has gathered the scattered
 //                Q and dO rows, row ids, LSE and delta of every tile into contiguous, already swizzled
 //                16 KB images, so a tile is five bulk copies into a four-slot ring
-//   warps 12-15  dQ drain: tensor memory -> registers -> 4 KB transposition buffer -> vector reductions
-//                into the FP32 accumulator, behind the next tile's math
+//   warps 12-15  dQ drain: tensor memory -> registers -> one row per thread in shared memory -> one bulk reduction
+//                per row into the FP32 accumulator by the copy engine, behind the next tile's math
 // Tensor memory: S^T 0-127 (P^T as packed 16-bit over the first columns of each thread's range), dP^T 128-255 (dS^T
 // likewise), dV 256-319, dK 320-383, dQ 384-447, K 448-479 and V 480-511 as stationary A operands.
 #include "prefill_bwd.cuh"
@@ -69,6 +69,7 @@ cudaError_t launch_bwd_pack(const BwdArgs& a, long long tiles, void* dopack, flo
 
 constexpr int kWsThreads = 512;  // 8 compute warps, MMA warp, producer warp (+2 idle), 4 dQ drain warps
 constexpr int kWsRing = 4;       // Q/dO tiles in shared memory
+constexpr int kStageRow = 272;   // bytes per staged dQ row: 64 floats + 16, so that eight lanes' 16-byte stores hit 32 banks
 
 struct WsSmem {
   uint64_t st_full;    // S^T of the tile is in tensor memory (tcgen05.commit)
@@ -93,18 +94,20 @@ template <bool F16>
 __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   constexpr int DPAD = 64;
   constexpr int TILE_BYTES = kTile * DPAD * 2;
-  constexpr int PT_BYTES = kTile * kTile * 2;
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t COL_ST = 0, COL_DPT = 128, COL_DV = 256, COL_DK = 320, COL_DQ = 384, COL_KA = 448, COL_VA = 480;
   extern __shared__ __align__(1024) uint8_t smem[];
   WsSmem& cb = *reinterpret_cast<WsSmem*>(smem);
   uint8_t* sK = smem + 8192;
   uint8_t* sV = sK + TILE_BYTES;
+  // dQ staging of the drain warps.  It starts on the V image, which is dead once V sits in tensor memory (long before
+  // the first dQ exists): 128 rows of kStageRow bytes for the copy-engine reductions, or 4 x 4 KB transposition buffers
+  // in deterministic mode.
+  uint8_t* sStage = sV;
   constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // ring slot: Q tile followed by dO tile
-  uint8_t* sQ = sV + TILE_BYTES;
+  uint8_t* sQ = sStage + kTile * kStageRow;
   uint8_t* sdO = sQ + TILE_BYTES;
   uint8_t* sdS = sQ + kWsRing * SLOT_BYTES;  // dS^T: 128 key rows x 128 query columns, bf16, two 64-column panels
-  uint8_t* sStage = sdS + PT_BYTES;          // 4 x 4 KB: transposition buffers of the drain warps
 
   const PrefillView& pv = a.pv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -152,14 +155,14 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   if (warp >= 12) {
     // ================================================================== dQ drain (warps 12-15)
     // A warp takes the 32 rows of its tensor-memory lanes: dQ of the finished tile goes to registers at
-    // once (the accumulator is then free for the next tile) and from there, 32 columns at a time, through
-    // a 4 KB transposition buffer into dq_acc with eight lanes per row, so that one red instruction
-    // covers four whole 128-byte lines.  The atomics run at the pace the memory system takes them,
-    // in the background of the next tile's math.
+    // once (the accumulator is then free for the next tile) and from there into the FP32 accumulator, in the
+    // background of the next tile's math.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
     const int quad = warp & 3;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
-    uint8_t* stage = sStage + quad * 4096;
+    const bool fixed = a.dq_fixed != nullptr;
+    uint8_t* stage = sStage + quad * 4096;                          // deterministic mode
+    uint8_t* myrow = sStage + (quad * 32 + lane) * kStageRow;       // ordinary mode: this thread's row
     for (int it = 0; it < n_iter; ++it) {
       const int slot = it % kWsRing;
       alive = warp_wait(&cb.qdo_full[slot], (it / kWsRing) & 1, a.status, alive);
@@ -173,6 +176,25 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
       tmem_ld_wait();
       tc_fence_before_sync();
       warp_arrive(&cb.dq_free);
+      if (!fixed) {
+        // Ordinary mode: the thread writes its row (one query, D floats) to shared memory and asks the copy engine to
+        // add it to the row's place in the FP32 accumulator - one reduction of whole lines per row, carried by the
+        // engine's own path to the L2 cache, so that neither the reductions nor a transposition pass through the
+        // load/store pipe the compute warps need.  A thread only ever touches its own row, so it only has to wait
+        // for its own previous reduction to have read the row before overwriting it.
+        bulk_wait_group_read();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          *reinterpret_cast<uint4*>(myrow + u * 16) = make_uint4(v0[4 * u], v0[4 * u + 1], v0[4 * u + 2], v0[4 * u + 3]);
+          *reinterpret_cast<uint4*>(myrow + 128 + u * 16) = make_uint4(v1[4 * u], v1[4 * u + 1], v1[4 * u + 2], v1[4 * u + 3]);
+        }
+        fence_async_smem();
+        if (th >= 0 && alive) bulk_reduce_add_f32(a.dq_acc + (long long)th * D, myrow, (uint32_t)D * 4u);
+        bulk_commit_group();
+        continue;
+      }
+      // Deterministic mode: 32 columns at a time through a 4 KB transposition buffer, eight lanes per row, integer
+      // reductions into the fixed-point accumulator.
       const int c4 = lane & 7;
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
@@ -196,6 +218,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         __syncwarp();
       }
     }
+    bulk_wait_group();   // the engine has finished with this CTA's shared memory and its reductions are performed
   } else if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 9) {
@@ -438,7 +461,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
 }
 
 cudaError_t launch_bwd_ws(const BwdArgs& a, cudaStream_t st) {
-  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (2 + 2 * kWsRing) + (size_t)kTile * kTile * 2 + 4 * 4096;
+  const size_t smem = 8192 + (size_t)kTile * 64 * 2 * (1 + 2 * kWsRing) + (size_t)kTile * kStageRow + (size_t)kTile * kTile * 2;
   const auto kernel = a.pv.fp16 ? attn_bwd_ws_kernel<true> : attn_bwd_ws_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
