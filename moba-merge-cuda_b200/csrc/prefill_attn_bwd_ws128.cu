@@ -5,12 +5,12 @@
 // formed transposed,
 //     S^T[128 keys, 64 q] = K Q^T,  dP^T = V dO^T,  dV[128, D] += P^T dO,  dK[128, D] += dS^T Q,
 //     dQ^T[D, 64 q] = K^T dS^T,
-// with the head dimension on the tensor-memory lanes; the drain warps turn it 16 query rows at a time
-// through a 2 KB buffer so that vector reductions cover whole 128-byte lines of the FP32 accumulator.
+// with the head dimension on the tensor-memory lanes; the drain warps write it to shared memory as query rows
+// and the copy engine adds every row to the FP32 accumulator with one bulk reduction.
 // Tensor memory: S^T 0-63 and dP^T 64-127 (P^T and dS^T as packed 16-bit values over the first columns of each
 // thread's own range), dV 128-255, dK 256-383, dQ^T 384-447, K 448-511 as a stationary A operand.
-// Shared memory: K and V images (32 KB each), a 4-slot ring of (Q, dO) half tiles (64 rows x 128 columns
-// each, 16 KB), the dS^T tile (128 key rows x 64 query columns, 16 KB).
+// Shared memory: K and V images (32 KB each), a 3-slot ring of (Q, dO) half tiles (64 rows x 128 columns
+// each, 16 KB), the dS^T tile (128 key rows x 64 query columns, 16 KB), the dQ rows of a step (32 KB).
 #include "prefill_bwd.cuh"
 
 namespace moba {
@@ -18,7 +18,7 @@ namespace moba {
 namespace {
 
 constexpr int kThreads = 512;  // 8 compute warps, MMA warp, producer warp (+2 idle), 4 dQ drain warps
-constexpr int kRing = 4;
+constexpr int kRing = 3;       // (Q, dO) half tiles in flight; the dQ staging takes the room of a fourth
 constexpr int kQRows = 64;     // query rows per step
 
 struct Smem128 {
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
   uint8_t* sQ = sV + KV_BYTES;
   uint8_t* sdO = sQ + HALF_BYTES;
   uint8_t* sdS = sQ + kRing * SLOT_BYTES;  // dS^T: 128 key rows x 64 query columns bf16 (one panel)
-  uint8_t* sStage = sdS + kTile * kQRows * 2;  // 4 x 2 KB: transposition buffers of the drain warps
+  uint8_t* sStage = sdS + kTile * kQRows * 2;  // dQ of a step as 64 query rows x 128 floats (32 KB); 4 x 2 KB of it in deterministic mode
 
   const PrefillView& pv = a.pv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -99,8 +99,11 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
     // 64 query rows of its dimension.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
     const int quad = warp & 3;
-    float* stage = reinterpret_cast<float*>(sStage + quad * 2048);
+    float* stage = reinterpret_cast<float*>(sStage + quad * 2048);   // deterministic mode
+    float* rows = reinterpret_cast<float*>(sStage);                  // ordinary mode: [64 queries][128 dimensions]
+    const bool fixed = a.dq_fixed != nullptr;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
+    auto drain_sync = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
     for (int it = 0; it < n_iter; ++it) {
       const int slot = it % kRing;
       alive = warp_wait(&cb.qdo_full[slot], (it / kRing) & 1, a.status, alive);
@@ -114,9 +117,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
       tmem_ld_wait();
       tc_fence_before_sync();
       warp_arrive(&cb.dq_free);
-      // 16 query rows at a time through a 2 KB buffer: written one dimension per lane, read back four
-      // dimensions per lane, so that one vector reduction covers four whole 128-byte lines (scalar
-      // reductions run at a quarter of the rate)
+      if (!fixed) {
+        // Ordinary mode: the step's dQ goes to shared memory as 64 query rows (a thread writes its dimension of every
+        // row, lanes on consecutive floats), and the copy engine adds each row to its place in the FP32 accumulator:
+        // one 512-byte reduction per row issued by warps 12 and 13, carried by the engine's own path to the L2 cache
+        // instead of the load/store pipe.  The four warps meet twice per step: before writing (the engine has read
+        // the previous step's rows) and before the rows are handed over.
+        if (quad < 2) bulk_wait_group_read();
+        drain_sync();
+        const int dcol = quad * 32 + lane;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          rows[i * 128 + dcol] = __uint_as_float(v0[i]);
+          rows[(32 + i) * 128 + dcol] = __uint_as_float(v1[i]);
+        }
+        fence_async_smem();
+        drain_sync();
+        if (quad < 2) {
+          const int th = quad == 0 ? th0 : th1;
+          if (th >= 0 && alive) bulk_reduce_add_f32(a.dq_acc + (long long)th * D, rows + (quad * 32 + lane) * 128, (uint32_t)D * 4u);
+          bulk_commit_group();
+        }
+        continue;
+      }
+      // Deterministic mode: 16 query rows at a time through a 2 KB buffer, written one dimension per lane, read back
+      // four dimensions per lane, integer reductions into the fixed-point accumulator.
 #pragma unroll
       for (int piece = 0; piece < 4; ++piece) {
 #pragma unroll
@@ -135,6 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
         __syncwarp();
       }
     }
+    bulk_wait_group();   // the engine has finished with this CTA's shared memory and its reductions are performed
   } else if (warp >= 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 9) {
@@ -377,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
 }
 
 cudaError_t launch_bwd_ws128(const BwdArgs& a, cudaStream_t st) {
-  const size_t smem = 4096 + 2 * (size_t)kTile * 128 * 2 + (size_t)kRing * 2 * kQRows * 128 * 2 + (size_t)kTile * kQRows * 2 + 4 * 2048;
+  const size_t smem = 4096 + 2 * (size_t)kTile * 128 * 2 + (size_t)kRing * 2 * kQRows * 128 * 2 + (size_t)kTile * kQRows * 2 + (size_t)kQRows * 128 * 4;
   const auto kernel = a.pv.fp16 ? attn_bwd_ws128_kernel<true> : attn_bwd_ws128_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
