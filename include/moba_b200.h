@@ -28,6 +28,11 @@ enum {
 /* Human-readable text for a status code (static storage). */
 const char* moba_status_string(int status);
 
+/* sizeof the descriptor structs below as the library was compiled (which = 0: moba_prefill_desc, 1: moba_cache_desc;
+ * 0 otherwise), so that a binding in another language can check its mirror of them when it loads the library. No
+ * counterpart in the reference, whose operators take tensors. */
+size_t moba_abi_sizeof(int which);
+
 /* ---------------------------------------------------------------------------------------------
  * Prefill: MoBA attention over a packed (varlen) batch, forward and backward.
  *

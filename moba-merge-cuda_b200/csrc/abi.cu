@@ -12,6 +12,12 @@ extern "C" const char* moba_status_string(int status) {
   }
 }
 
+// Size of a descriptor struct as this library was compiled: a binding compares it with its own mirror when it loads the
+// library (which = 0: moba_prefill_desc, 1: moba_cache_desc; 0 for anything else).
+extern "C" size_t moba_abi_sizeof(int which) {
+  return which == 0 ? sizeof(moba_prefill_desc) : which == 1 ? sizeof(moba_cache_desc) : 0;
+}
+
 // Profiling aid: events a caller registers are recorded on the launch stream immediately before and
 // after the named kernel, so its duration can be read with cudaEventElapsedTime without a profiler.
 // Process-wide and not thread-safe; pass null events to switch it off.

@@ -29,6 +29,9 @@ def lib():
         P = ctypes.POINTER(PrefillDesc)
         L.moba_status_string.restype = ctypes.c_char_p
         L.moba_status_string.argtypes = [ctypes.c_int]
+        L.moba_abi_sizeof.restype, L.moba_abi_sizeof.argtypes = c_sz, [ctypes.c_int]
+        if L.moba_abi_sizeof(0) != ctypes.sizeof(PrefillDesc):
+            raise ImportError(f"{_LIB_PATH} was built from another revision of include/moba_b200.h (moba_prefill_desc)")
         L.moba_selftest_umma.argtypes = [ctypes.c_int, c_vp, c_vp, c_vp, ctypes.c_int, ctypes.c_int, c_vp, c_vp]
         L.moba_selftest_wait.argtypes = [ctypes.c_longlong, c_vp, c_vp, c_vp]
         for name in ("moba_prefill_route_state_bytes", "moba_prefill_route_scratch_bytes",

@@ -65,6 +65,8 @@ def decode_library():
     """libmoba_b200.so with the decode entry points typed (once per process)."""
     lib = _ext.lib()
     if not getattr(lib, "_decode_abi_bound", False):
+        if lib.moba_abi_sizeof(1) != ctypes.sizeof(CacheDesc):
+            raise ImportError("libmoba_b200.so was built from another revision of include/moba_b200.h (moba_cache_desc)")
         for name, (restype, argtypes) in _DECODE_ABI.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = restype, argtypes

@@ -86,3 +86,21 @@ def test_library_exports_every_declared_symbol():
     assert not missing, missing
     lib.moba_status_string.restype = ctypes.c_char_p
     assert lib.moba_status_string(0) == b"ok"
+
+
+def test_descriptor_mirrors_have_the_library_sizes():
+    """The ctypes mirrors of the two descriptor structs are as large as the structs the library was compiled with (the
+    loaders refuse a library for which this does not hold); no GPU needed."""
+    import ctypes
+    from moba_opt import _ext
+    from moba_opt.kv_cache import CacheDesc, decode_library
+    lib = decode_library()
+    assert lib.moba_abi_sizeof(0) == ctypes.sizeof(_ext.PrefillDesc) == 176
+    assert lib.moba_abi_sizeof(1) == ctypes.sizeof(CacheDesc) == 80
+    assert lib.moba_abi_sizeof(2) == 0
+
+
+def test_both_16_bit_formats_pass_the_input_check():
+    import torch
+    from moba_opt import baseline_adapter as ba
+    assert ba.SUPPORTED_DTYPES == (torch.bfloat16, torch.float16)      # as src/moba_opt/baseline_adapter.py:13
