@@ -117,7 +117,8 @@ int moba_prefill_fwd(const moba_prefill_desc* d, const void* q, const void* k, c
 /* Backward (mixed_attention.py:141-225): gradients of out w.r.t. q, k, v with the route held fixed.
  * dq [T,Hq,D], dk/dv [T,Hkv,D] in the input format, contiguous.  dK, dV are bit-repeatable; dQ is summed over key blocks with FP32
  * reductions in arrival order unless d->flags has MOBA_BWD_DETERMINISTIC (the reference's deterministic=True,
- * mixed_attention.py:185,220), which costs scalar 64-bit reductions and a scratch twice the size. */
+ * mixed_attention.py:185,220), which sums 64-bit fixed-point values instead: about twice the backward kernel's time and a
+ * scratch twice the size. */
 size_t moba_prefill_bwd_scratch_bytes(const moba_prefill_desc* d);
 int moba_prefill_bwd(const moba_prefill_desc* d, const void* q, const void* k, const void* v, const void* out,
                      const float* lse, const void* dout, const void* route_state, void* scratch, size_t scratch_bytes,

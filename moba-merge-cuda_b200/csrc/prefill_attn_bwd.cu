@@ -4,10 +4,10 @@
 //
 // Launch sequence: dq_acc = 0, delta = rowsum(dO * O), pack dO / LSE / delta per query tile, the KV-stationary main
 // kernel (prefill_attn_bwd_ws.cu for head_dim <= 64, prefill_attn_bwd_ws128.cu above that: dK and dV of a key block
-// accumulate in tensor memory and are written once, dQ of every tile is reduced into the FP32 buffer with vector
-// atomics), dq = dq_acc rounded to the input format.  With MOBA_BWD_DETERMINISTIC the accumulator is 64-bit fixed point and the reductions
-// are integer, which makes dQ bit-repeatable like everything else (the reference asks FlashAttention for the same:
-// deterministic=True in both backward calls, mixed_attention.py:185,220).
+// accumulate in tensor memory and are written once, dQ of every tile is added into the FP32 buffer row by row with bulk
+// reductions of the copy engine), dq = dq_acc rounded to the input format.  With MOBA_BWD_DETERMINISTIC the accumulator
+// is 64-bit fixed point and the reductions are integer, which makes dQ bit-repeatable like everything else (the
+// reference asks FlashAttention for the same: deterministic=True in both backward calls, mixed_attention.py:185,220).
 #include "prefill_bwd.cuh"
 
 namespace moba {

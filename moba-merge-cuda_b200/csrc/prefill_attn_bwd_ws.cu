@@ -101,8 +101,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
   uint8_t* sK = smem + 8192;
   uint8_t* sV = sK + TILE_BYTES;
   // dQ staging of the drain warps.  It starts on the V image, which is dead once V sits in tensor memory (long before
-  // the first dQ exists): 128 rows of kStageRow bytes for the copy-engine reductions, or 4 x 4 KB transposition buffers
-  // in deterministic mode.
+  // the first dQ exists): 128 rows of kStageRow bytes for the copy-engine reductions.
   uint8_t* sStage = sV;
   constexpr int SLOT_BYTES = 2 * TILE_BYTES;  // ring slot: Q tile followed by dO tile
   uint8_t* sQ = sStage + kTile * kStageRow;
@@ -161,8 +160,7 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
     const int quad = warp & 3;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
     const bool fixed = a.dq_fixed != nullptr;
-    uint8_t* stage = sStage + quad * 4096;                          // deterministic mode
-    uint8_t* myrow = sStage + (quad * 32 + lane) * kStageRow;       // ordinary mode: this thread's row
+    uint8_t* myrow = sStage + (quad * 32 + lane) * kStageRow;       // this thread's row
     for (int it = 0; it < n_iter; ++it) {
       const int slot = it % kWsRing;
       alive = warp_wait(&cb.qdo_full[slot], (it / kWsRing) & 1, a.status, alive);
@@ -193,29 +191,21 @@ __global__ void __launch_bounds__(kWsThreads, 1) attn_bwd_ws_kernel(BwdArgs a) {
         bulk_commit_group();
         continue;
       }
-      // Deterministic mode: 32 columns at a time through a 4 KB transposition buffer, eight lanes per row, integer
-      // reductions into the fixed-point accumulator.
-      const int c4 = lane & 7;
+      // Deterministic mode: the same hand-over with 64-bit fixed-point values (32 fractional bits), whose integer sums
+      // do not depend on the order in which the key blocks' contributions arrive; a row of 64 such values is twice the
+      // size of the staging row, so it goes in two rounds of 32 dimensions.
 #pragma unroll
       for (int p = 0; p < 2; ++p) {
+        bulk_wait_group_read();
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const uint4 val = p == 0 ? make_uint4(v0[4 * u], v0[4 * u + 1], v0[4 * u + 2], v0[4 * u + 3])
-                                   : make_uint4(v1[4 * u], v1[4 * u + 1], v1[4 * u + 2], v1[4 * u + 3]);
-          *reinterpret_cast<uint4*>(stage + lane * 128 + ((u ^ (lane & 7)) << 4)) = val;
+        for (int u = 0; u < 16; ++u) {
+          const float x0 = __uint_as_float(p == 0 ? v0[2 * u] : v1[2 * u]), x1 = __uint_as_float(p == 0 ? v0[2 * u + 1] : v1[2 * u + 1]);
+          *reinterpret_cast<longlong2*>(myrow + u * 16) = make_longlong2(__float2ll_rn(x0 * 4294967296.f), __float2ll_rn(x1 * 4294967296.f));
         }
-        __syncwarp();
-        const int col = p * 32 + c4 * 4;
-#pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          const int rl = (lane >> 3) + 4 * x;
-          const int rth = __shfl_sync(0xFFFFFFFFu, th, rl);
-          const uint4 w = *reinterpret_cast<const uint4*>(stage + rl * 128 + ((c4 ^ (rl & 7)) << 4));
-          if (rth >= 0 && alive && col < D)
-            dq_accumulate(a.dq_acc, a.dq_fixed, (long long)rth * D + col, __uint_as_float(w.x), __uint_as_float(w.y),
-                          __uint_as_float(w.z), __uint_as_float(w.w));
-        }
-        __syncwarp();
+        fence_async_smem();
+        if (th >= 0 && alive && p * 32 < D)
+          bulk_reduce_add_u64(a.dq_fixed + (long long)th * D + p * 32, myrow, (uint32_t)min(32, D - p * 32) * 8u);
+        bulk_commit_group();
       }
     }
     bulk_wait_group();   // the engine has finished with this CTA's shared memory and its reductions are performed

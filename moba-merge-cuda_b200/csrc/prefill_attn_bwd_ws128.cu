@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
   uint8_t* sQ = sV + KV_BYTES;
   uint8_t* sdO = sQ + HALF_BYTES;
   uint8_t* sdS = sQ + kRing * SLOT_BYTES;  // dS^T: 128 key rows x 64 query columns bf16 (one panel)
-  uint8_t* sStage = sdS + kTile * kQRows * 2;  // dQ of a step as 64 query rows x 128 floats (32 KB); 4 x 2 KB of it in deterministic mode
+  uint8_t* sStage = sdS + kTile * kQRows * 2;  // dQ of a step as 64 query rows x 128 floats (32 KB)
 
   const PrefillView& pv = a.pv;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -99,8 +99,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
     // 64 query rows of its dimension.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
     const int quad = warp & 3;
-    float* stage = reinterpret_cast<float*>(sStage + quad * 2048);   // deterministic mode
-    float* rows = reinterpret_cast<float*>(sStage);                  // ordinary mode: [64 queries][128 dimensions]
+    float* rows = reinterpret_cast<float*>(sStage);                  // [64 queries][128 dimensions]
     const bool fixed = a.dq_fixed != nullptr;
     const uint32_t tlane = tmem + (uint32_t(quad * 32) << 16);
     auto drain_sync = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
@@ -140,24 +139,31 @@ __global__ void __launch_bounds__(kThreads, 1) attn_bwd_ws128_kernel(BwdArgs a) 
         }
         continue;
       }
-      // Deterministic mode: 16 query rows at a time through a 2 KB buffer, written one dimension per lane, read back
-      // four dimensions per lane, integer reductions into the fixed-point accumulator.
+      // Deterministic mode: the same hand-over with 64-bit fixed-point values (32 fractional bits), whose integer sums
+      // do not depend on the order in which the key blocks' contributions arrive.  A query row of 128 such values is
+      // twice the size of a staged row, so it goes in two rounds of 64 dimensions: warps 12, 13 hold the first 64,
+      // warps 14, 15 the second.
+      unsigned long long* rows64 = reinterpret_cast<unsigned long long*>(sStage);   // [64 queries][64 dimensions]
 #pragma unroll
-      for (int piece = 0; piece < 4; ++piece) {
+      for (int r = 0; r < 2; ++r) {
+        if (quad < 2) bulk_wait_group_read();
+        drain_sync();
+        if ((quad >> 1) == r) {
+          const int dl = (quad & 1) * 32 + lane;   // dimension inside the round
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          stage[i * 32 + lane] = piece < 2 ? __uint_as_float(v0[(piece & 1) * 16 + i]) : __uint_as_float(v1[(piece & 1) * 16 + i]);
-        __syncwarp();
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int ql = (lane >> 3) + 4 * x;                 // query row inside the piece
-          const int qi = (piece & 1) * 16 + ql;               // inside its group of 32
-          const int rth = __shfl_sync(0xFFFFFFFFu, piece < 2 ? th0 : th1, qi);
-          const float4 w = *reinterpret_cast<const float4*>(stage + ql * 32 + (lane & 7) * 4);
-          const int col = quad * 32 + (lane & 7) * 4;
-          if (rth >= 0 && alive && col < D) dq_accumulate(a.dq_acc, a.dq_fixed, (long long)rth * D + col, w.x, w.y, w.z, w.w);
+          for (int i = 0; i < 32; ++i) {
+            rows64[i * 64 + dl] = (unsigned long long)__float2ll_rn(__uint_as_float(v0[i]) * 4294967296.f);
+            rows64[(32 + i) * 64 + dl] = (unsigned long long)__float2ll_rn(__uint_as_float(v1[i]) * 4294967296.f);
+          }
+          fence_async_smem();
         }
-        __syncwarp();
+        drain_sync();
+        if (quad < 2) {
+          const int th = quad == 0 ? th0 : th1;
+          if (th >= 0 && alive && r * 64 < D)
+            bulk_reduce_add_u64(a.dq_fixed + (long long)th * D + r * 64, rows64 + (quad * 32 + lane) * 64, (uint32_t)min(64, D - r * 64) * 8u);
+          bulk_commit_group();
+        }
       }
     }
     bulk_wait_group();   // the engine has finished with this CTA's shared memory and its reductions are performed

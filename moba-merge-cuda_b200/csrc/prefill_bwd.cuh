@@ -15,27 +15,6 @@ __device__ __forceinline__ uint32_t bwd_pack_bf16(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
-__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-
-// dQ contribution into the accumulator.  Ordinary mode: one FP32 vector reduction (the order in which the key blocks'
-// contributions arrive is not fixed, so the last bit of a sum may differ between runs).  Deterministic mode: the
-// accumulator holds 64-bit fixed-point numbers (32 fractional bits) and integer addition does not care about order,
-// so dQ is bit-repeatable; the reductions are scalar and cost more.
-__device__ __forceinline__ void dq_accumulate(float* acc, unsigned long long* acc_fixed, long long index, float a, float b, float c,
-                                              float d) {
-  if (acc_fixed) {
-    unsigned long long* p = acc_fixed + index;
-    atomicAdd(p, (unsigned long long)__float2ll_rn(a * 4294967296.f));
-    atomicAdd(p + 1, (unsigned long long)__float2ll_rn(b * 4294967296.f));
-    atomicAdd(p + 2, (unsigned long long)__float2ll_rn(c * 4294967296.f));
-    atomicAdd(p + 3, (unsigned long long)__float2ll_rn(d * 4294967296.f));
-  } else {
-    red_add_v4(acc + index, a, b, c, d);
-  }
-}
-
 struct BwdArgs {
   PrefillView pv;
   const __nv_bfloat16* q;

@@ -254,6 +254,12 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float* gmem_dst, const void*
                "r"(bytes)
                : "memory");
 }
+// The same for 64-bit integers (two's complement: order of the additions does not matter).
+__device__ __forceinline__ void bulk_reduce_add_u64(unsigned long long* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.u64 [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the calling thread's bulk groups have read their shared-memory sources / have completed.
 __device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
