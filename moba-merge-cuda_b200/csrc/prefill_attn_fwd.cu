@@ -518,37 +518,58 @@ __global__ void __launch_bounds__(kFwdThreads, 1) attn_fwd_kernel(FwdArgs a) {
         }
         a.part_lse[row_id] = m_used + log2f(l_run);
       } else {
-        // global-softmax merge of the self branch with the row's remote partials (fixed slot order)
+        // global-softmax merge of the self branch with the row's remote partials (fixed slot order).  The loads are
+        // issued in batches that do not depend on each other - the selection and the partial LSEs of four slots, then
+        // the partial output rows of two slots - so that a row costs a few trips to memory, not three per slot.
         const int R = pv.R;
         const float l2_self = m_used + log2f(l_run);
         float big = l2_self;
         const int* mysel = a.sel + (long long)row_id * R;
-        int nsel = 0;
-        for (int s = 0; s < R; ++s) {
-          if (mysel[s] < 0) break;
-          big = fmaxf(big, a.part_lse[(long long)row_id * R + s]);
-          ++nsel;
+        const float* mylse = a.part_lse + (long long)row_id * R;
+        int nsel = 0;  // sel is ascending with -1 padding at the end: the chosen slots are the first nsel
+        for (int s0 = 0; s0 < R; s0 += 4) {
+          int c[4];
+          float e[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            c[i] = s0 + i < R ? mysel[s0 + i] : -1;
+            e[i] = s0 + i < R ? mylse[s0 + i] : 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (c[i] >= 0) { big = fmaxf(big, e[i]); ++nsel; }
+          }
         }
         const float w_self = fast_exp2(l2_self - big);
         float z = w_self;
         const float f_self = w_self / l_run;
 #pragma unroll
         for (int d = 0; d < DPAD; ++d) o_acc[d] *= f_self;
-        for (int s = 0; s < nsel; ++s) {
-          const long long slot = (long long)row_id * R + s;
-          const float w = fast_exp2(a.part_lse[slot] - big);
-          z += w;
-          const __nv_bfloat16* src = a.part_o + slot * D;
+        for (int s0 = 0; s0 < nsel; s0 += 2) {
+          uint4 raw[2][UPR];
+          float w[2];
 #pragma unroll
-          for (int u = 0; u < UPR; ++u) {
-            if (u * 8 < D) {
-              const uint4 raw = *reinterpret_cast<const uint4*>(src + u * 8);
-              const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+          for (int i = 0; i < 2; ++i) {
+            const bool on = s0 + i < nsel;
+            const long long slot = (long long)row_id * R + (on ? s0 + i : s0);
+            w[i] = on ? mylse[on ? s0 + i : s0] : -INFINITY;
+            const __nv_bfloat16* src = a.part_o + slot * D;
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 pv2 = unpack16<F16>(wv[i]);
-                o_acc[u * 8 + 2 * i] = fmaf(w, pv2.x, o_acc[u * 8 + 2 * i]);
-                o_acc[u * 8 + 2 * i + 1] = fmaf(w, pv2.y, o_acc[u * 8 + 2 * i + 1]);
+            for (int u = 0; u < UPR; ++u)
+              raw[i][u] = (on && u * 8 < D) ? *reinterpret_cast<const uint4*>(src + u * 8) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const float wi = fast_exp2(w[i] - big);   // 0 for the slot that is not there
+            z += wi;
+#pragma unroll
+            for (int u = 0; u < UPR; ++u) {
+              const uint32_t wv[4] = {raw[i][u].x, raw[i][u].y, raw[i][u].z, raw[i][u].w};
+#pragma unroll
+              for (int x = 0; x < 4; ++x) {
+                const float2 pv2 = unpack16<F16>(wv[x]);
+                o_acc[u * 8 + 2 * x] = fmaf(wi, pv2.x, o_acc[u * 8 + 2 * x]);
+                o_acc[u * 8 + 2 * x + 1] = fmaf(wi, pv2.y, o_acc[u * 8 + 2 * x + 1]);
               }
             }
           }
