@@ -64,6 +64,34 @@ def lib():
     return _lib
 
 
+class _NoRange:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_RANGE = _NoRange()
+
+
+def nvtx(name):
+    """An NVTX range around a stage of the host wrapper (routing, forward, backward, a cache call, a decode step) when
+    MOBA_NVTX=1 is set in the environment - the counterpart of the reference's record_function stage marks
+    (src/moba_opt/diagnostic.py:105-305) for timeline tools; a no-op object otherwise, so the default path pays nothing."""
+    global _nvtx_on
+    if _nvtx_on is None:
+        import os
+        _nvtx_on = os.environ.get("MOBA_NVTX", "0") not in ("", "0")
+    if not _nvtx_on:
+        return _NO_RANGE
+    import torch
+    return torch.cuda.nvtx.range(name)
+
+
+_nvtx_on = None
+
+
 def check(status, what):
     if status != 0:
         raise RuntimeError(f"{what} failed: {lib().moba_status_string(status).decode()} (status {status})")

@@ -152,8 +152,9 @@ def route(q, k, plan, remote_k, flags=0):
     state = torch.empty(lib.moba_prefill_route_state_bytes(ctypes.byref(d)), dtype=torch.uint8, device=q.device)
     nbytes = lib.moba_prefill_route_scratch_bytes(ctypes.byref(d))
     scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-    _ext.check(lib.moba_prefill_route(ctypes.byref(d), q.data_ptr(), k.data_ptr(), state.data_ptr(),
-                                      scratch.data_ptr(), nbytes, _stream(q.device)), "moba_prefill_route")
+    with _ext.nvtx("moba.route"):
+        _ext.check(lib.moba_prefill_route(ctypes.byref(d), q.data_ptr(), k.data_ptr(), state.data_ptr(),
+                                          scratch.data_ptr(), nbytes, _stream(q.device)), "moba_prefill_route")
     return state
 
 
@@ -179,10 +180,11 @@ class _MobaPrefill(torch.autograd.Function):
             scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
             out = torch.empty((q.shape[0], q.shape[1], q.shape[2]), dtype=q.dtype, device=q.device)
             lse = torch.empty((q.shape[0], q.shape[1]), dtype=torch.float32, device=q.device)
-            _ext.check(lib.moba_prefill_fwd(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                            state.data_ptr(), scratch.data_ptr(), nbytes,
-                                            out.data_ptr(), lse.data_ptr(), _status_word(q.device).data_ptr(),
-                                            _stream(q.device)), "moba_prefill_fwd")
+            with _ext.nvtx("moba.forward"):
+                _ext.check(lib.moba_prefill_fwd(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                state.data_ptr(), scratch.data_ptr(), nbytes,
+                                                out.data_ptr(), lse.data_ptr(), _status_word(q.device).data_ptr(),
+                                                _stream(q.device)), "moba_prefill_fwd")
         ctx.save_for_backward(q, k, v, out, lse, state)
         ctx.plan, ctx.remote_k, ctx.bwd_flags = plan, remote_k, bwd_flags
         ctx.mark_non_differentiable(lse)
@@ -201,10 +203,11 @@ class _MobaPrefill(torch.autograd.Function):
             dq = torch.empty(q.shape, dtype=q.dtype, device=q.device)
             dk = torch.empty(k.shape, dtype=k.dtype, device=q.device)
             dv = torch.empty(v.shape, dtype=v.dtype, device=q.device)
-            _ext.check(lib.moba_prefill_bwd(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                            lse.data_ptr(), d_out.data_ptr(), state.data_ptr(),
-                                            scratch.data_ptr(), nbytes, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                            _status_word(q.device).data_ptr(), _stream(q.device)), "moba_prefill_bwd")
+            with _ext.nvtx("moba.backward"):
+                _ext.check(lib.moba_prefill_bwd(ctypes.byref(d), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                                lse.data_ptr(), d_out.data_ptr(), state.data_ptr(),
+                                                scratch.data_ptr(), nbytes, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                                _status_word(q.device).data_ptr(), _stream(q.device)), "moba_prefill_bwd")
         return dq, dk, dv, None, None, None, None
 
 

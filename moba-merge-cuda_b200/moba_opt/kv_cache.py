@@ -277,7 +277,8 @@ class PagedKVCache:
 
     def _launch(self, name, *args):
         """One C-ABI call on the cache's stream; a refused launch leaves the cache contents undefined."""
-        status = getattr(self._lib, name)(*args, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        with _ext.nvtx(name):
+            status = getattr(self._lib, name)(*args, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
         if status != 0:
             self._life = CacheLife.BROKEN
         _ext.check(status, name)

@@ -260,7 +260,8 @@ class PreparedDecode:
 
     def _execute(self, kind, use_graph):
         try:
-            self.replay(kind) if use_graph else self.launch(kind)
+            with _ext.nvtx("moba.decode." + kind):
+                self.replay(kind) if use_graph else self.launch(kind)
         except Exception:
             self.mark_failed()
             raise
