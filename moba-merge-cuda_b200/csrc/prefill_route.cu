@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(256) chunk_mean_kernel(PrefillView pv, const _
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float2 f = unpack16(w[i], f16);
+        const float2 f = f16 ? unpack16<true>(w[i]) : unpack16<false>(w[i]);
         acc[2 * i] += f.x;
         acc[2 * i + 1] += f.y;
       }
@@ -174,10 +174,12 @@ __global__ void __launch_bounds__(32 * LPR) gate_topk_kernel(PrefillView pv, con
           uint4 raw = make_uint4(0u, 0u, 0u, 0u);
           if (row0 + j < nrows) raw = *reinterpret_cast<const uint4*>(qrow + u * 16);
           const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+          if (pv.fp16) {   // one uniform branch per 16 bytes, not a select per value
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = unpack16(w[i], pv.fp16 != 0);
-            qp[j][u * 4 + i] = pack2(f.x, f.y);
+            for (int i = 0; i < 4; ++i) { const float2 f = unpack16<true>(w[i]); qp[j][u * 4 + i] = pack2(f.x, f.y); }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = unpack16<false>(w[i]); qp[j][u * 4 + i] = pack2(f.x, f.y); }
           }
         }
       }
